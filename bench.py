@@ -1,0 +1,375 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 quantized matrix-product path.
+
+    python bench.py --gpus N --steps K --warmup W [--workload NAME] [--impl reference]
+
+A step is one pass of the decode (or prefill) layer set: every projection of
+every layer of the named model shape against synthetic Q8_0 activations.  The
+metric is the reference benchmark's own (hearth-llm/examples/benchk.rs:162,
+:198): packed weight bytes streamed per second.  With N > 1 every weight is
+row-sharded over the ranks (rank r holds rows [r*ceil(n/N), ...)) and each step
+ends with an NCCL all-gather of the output slices, so the total work is fixed
+("strong" scaling).  Prints one JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from hearth_b200 import synth  # noqa: E402
+
+DEFAULT_WORKLOAD = "c4_pq2_27b_decode"
+METRIC = "quant GEMV weight-stream bandwidth"
+UNIT = "GB/s"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def shard_rows(n_rows: int, rank: int, world: int) -> tuple[int, int]:
+    """The reference's static row split (hearth-llm/src/pool.rs:321-323) over ranks instead of threads."""
+    chunk = -(-n_rows // world)
+    lo = min(rank * chunk, n_rows)
+    return lo, min(lo + chunk, n_rows)
+
+
+def algorithmic_bytes(cfg: dict) -> dict:
+    """Per step: packed weights + Q8_0 activations + f32 outputs (whole job, all ranks together)."""
+    m = cfg["seq_len"]
+    w = a = o = 0
+    for _, n_rows, n_cols in cfg["shapes"]:
+        w += n_rows * synth.row_bytes(cfg["dtype"], n_cols)
+        a += m * (n_cols // 32) * 34
+        o += m * n_rows * 4
+    L = cfg["layers"]
+    return {"weights": w * L, "activations": a * L, "outputs": o * L}
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+
+class CpuArm:
+    """The restated reference CPU path (SIMD arms + row-splitting pool) on a bounded sample of the workload."""
+
+    def __init__(self, cfg: dict, threads: int, sample_layers: int):
+        from oracle import oracle as O
+        O.build()
+        self.O, self.cfg = O, cfg
+        self.S = O.simd()
+        self.threads = self.S.hs_pool_start(threads)  # <= 0: physical cores, the reference's dense rule (pool.rs:150-152)
+        self.mats = []
+        for li in range(sample_layers):
+            for ti, (_, n_rows, n_cols) in enumerate(cfg["shapes"]):
+                w = synth.weights(cfg["dtype"], n_rows, n_cols, seed=4000 + 10 * li + ti)
+                a = O.quantize_q8_0(synth.activations(cfg["seq_len"], n_cols, seed=5000 + 10 * li + ti))
+                self.mats.append((w, a, n_rows, n_cols, np.zeros((cfg["seq_len"], n_rows), dtype=np.float32)))
+        self.nbytes = sum(w.size for w, *_ in self.mats)
+        self.kernel = self.S.hs_selected_kernel(cfg["dtype"]).decode()
+        self.desc = (f"{sample_layers} layer(s) x {len(cfg['shapes'])} projections of the workload, M={cfg['seq_len']}, "
+                     f"{self.nbytes / 1e6:.1f} MB of weights per pass; arm={self.kernel}; {self.threads} threads of "
+                     f"{self.S.hs_logical_cores()} logical CPUs; C restatement of the reference's SIMD kernels and pool")
+        t_end = time.perf_counter() + 0.3  # time-based warm-up, as benchk does (benchk.rs:172-182)
+        self.one_pass()
+        while time.perf_counter() < t_end:
+            self.one_pass()
+
+    def one_pass(self) -> float:
+        t0 = time.perf_counter()
+        for w, a, n_rows, n_cols, out in self.mats:
+            self.O.simd_dot_rows_batched(self.cfg["dtype"], w, a, n_rows, n_cols, out)
+        return time.perf_counter() - t0
+
+    def gbs(self, passes: int = 2) -> float:
+        return self.nbytes / min(self.one_pass() for _ in range(passes)) / 1e9
+
+    def close(self):
+        self.S.hs_pool_stop()
+
+
+def run_reference(args, cfg, rank):
+    """The reference arm: the reference's CPU implementation of the path (here its C restatement, because the
+    Rust original cannot be built) on all physical cores; a step is one pass over a one-layer sample."""
+    if rank != 0:
+        return
+    arm = CpuArm(cfg, 0, 1)
+    t0 = time.perf_counter()
+    times = []
+    for i in range(args.warmup + args.steps):
+        t = arm.one_pass()
+        if i >= args.warmup:
+            times.append(t)
+        if time.perf_counter() - t0 > 150:
+            break
+    arm.close()
+    sec = statistics.median(times)
+    value = arm.nbytes / sec / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8 x {1,2}-bit -> int32, fp32 scales", "data": "synthetic",
+        "config": {"workload": args.workload, "tokens": cfg["seq_len"], "sample": arm.desc},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": arm.threads, "kind": "port", "sample": arm.desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+
+def run_ours(args, cfg, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from hearth_b200 import api as hb
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    hb.init(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    M = cfg["seq_len"]
+    dtype = cfg["dtype"]
+    stream = torch.cuda.Stream(device=dev)
+
+    # ---- resident data: this rank's row shard of every weight, one activation per distinct input width
+    weights, acts, outs = [], {}, []
+    slice_rows = 0
+    for li in range(cfg["layers"]):
+        for ti, (_, n_rows, n_cols) in enumerate(cfg["shapes"]):
+            lo, hi = shard_rows(n_rows, rank, world)
+            packed = synth.weights_torch(dtype, hi - lo, n_cols, seed=1000 * (li + 1) + 10 * ti + rank, device=dev)
+            weights.append((hb.Weight.upload_dev(dtype, hi - lo, n_cols, packed), -(-n_rows // world)))
+            del packed
+            slice_rows += -(-n_rows // world)
+    torch.cuda.synchronize()
+    widths = sorted({k for _, _, k in cfg["shapes"]})
+    x_host = {}
+    for k in widths:
+        acts[k] = hb.Act(M, k)
+        xh = torch.from_numpy(synth.activations(M, k, seed=77 + k)).pin_memory()
+        x_host[k] = xh
+        xd = xh.to(dev)
+        acts[k].quantize(M, x_dev=xd)
+    torch.cuda.synchronize()
+
+    # outputs: one packed buffer per rank [M, slice_rows]; gathered into [world, M, slice_rows]
+    out_local = torch.zeros((M, slice_rows), dtype=torch.float32, device=dev)
+    out_all = torch.zeros((world, M, slice_rows), dtype=torch.float32, device=dev) if world > 1 else None
+    batch = hb.Batch()
+    off = 0
+    i = 0
+    for li in range(cfg["layers"]):
+        for ti, (_, n_rows, n_cols) in enumerate(cfg["shapes"]):
+            W, pad_rows = weights[i]
+            i += 1
+            if W.n_rows > 0:
+                batch.add(W, acts[n_cols], M, out_local[:, off:], ld_out=slice_rows)
+            off += pad_rows
+    batch.seal()
+    launches_per_step = batch.launch_count
+
+    def step():
+        batch.launch(stream)
+        if world > 1:
+            with torch.cuda.stream(stream):
+                dist.all_gather_into_tensor(out_all, out_local)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        t_end = time.perf_counter() + 0.7
+    # An untimed burst of the same steps first, so that the clock sampler (100 ms period) has samples
+    # under load on both sides of the timed region; rank 0 decides when it ends.
+    burst = 0
+    while burst < 4000:
+        step()
+        burst += 1
+        if burst % 50 == 0:
+            stream.synchronize()
+            flag = torch.tensor([1.0 if (rank == 0 and time.perf_counter() >= t_end) else 0.0], device=dev)
+            if world > 1:
+                dist.broadcast(flag, 0)
+            if flag.item() > 0:
+                break
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    for _ in range(50):
+        step()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    ms_per_step = ms / args.steps
+
+    # ---- end to end through the host-buffer entry point (rank-local inputs and outputs, pinned memory)
+    e2e_ms, h2d, d2h = None, 0, 0
+    if M <= 4:
+        hosts_out = [torch.zeros((M, W.n_rows), dtype=torch.float32).pin_memory() for W, _ in weights]
+        xs = [x_host[k].numpy() for _, _, k in cfg["shapes"]] * cfg["layers"]
+        outs_np = [o.numpy() for o in hosts_out]
+        import ctypes as C
+        from hearth_b200 import lib as L
+        lib = L.load()
+
+        def e2e_step():
+            for (W, _), x, o in zip(weights, xs, outs_np):
+                if W.n_rows:
+                    rc = lib.hb200_matmul_f32(W._h, C.c_void_p(x.ctypes.data), M, C.c_void_p(o.ctypes.data))
+                    if rc:
+                        hb.check(rc)
+        e2e_steps = max(1, min(args.steps, 5))
+        e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        tt = torch.tensor([dt], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_ms = float(tt.item()) / e2e_steps * 1e3
+        h2d = sum(x.nbytes for (W, _), x in zip(weights, xs) if W.n_rows)
+        d2h = sum(o.nbytes for o in outs_np)
+
+    if rank == 0:
+        ab = algorithmic_bytes(cfg)
+        total_alg = ab["weights"] + ab["activations"] + ab["outputs"]
+        value = ab["weights"] / (ms_per_step * 1e-3) / 1e9
+        peak, peak_src = measured_peaks()
+        per_rank_alg = total_alg / world
+        achieved = per_rank_alg / (ms_per_step * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8 x {1,2}-bit -> int32, fp32 scales", "data": "synthetic",
+            "config": {"workload": args.workload, "format": {41: "Q1_0", 42: "Q2_0", 142: "PQ2_0", 8: "Q8_0"}.get(dtype, str(dtype)),
+                       "tokens": M, "layers": cfg["layers"], "matrices_per_step": cfg["layers"] * len(cfg["shapes"]),
+                       "weight_bytes": ab["weights"], "parallelism": f"rows/{world}" + (" + NCCL all-gather of output slices" if world > 1 else ""),
+                       "l2": "per-GPU inputs exceed the 126 MB L2" if ab["weights"] / world > 126e6 else "inputs fit in L2",
+                       "launch": "one recorded batch (work list) per step"},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "kernel": hb.selected_kernel(dtype, M), "peak_source": peak_src,
+                         "algorithmic_bytes_per_launch": per_rank_alg},
+            "e2e": ({"value": ab["weights"] / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                     "ms_per_step": e2e_ms, "call": "hb200_matmul_f32 per matrix, pinned host buffers"} if e2e_ms else None),
+        }
+        if world == 1 and not args.no_cpu:
+            arm = CpuArm(cfg, 0, 1)
+            t0 = time.perf_counter()
+            best = arm.gbs(2)
+            while time.perf_counter() - t0 < 8.0:  # bounded: about ten seconds of CPU work
+                best = max(best, arm.gbs(2))
+            arm.close()
+            line["cpu_baseline"] = {"value": best, "unit": UNIT, "cores": arm.threads, "kind": "port", "sample": arm.desc}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(synth.CONFIGS))
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    cfg = synth.CONFIGS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, cfg, rank)
+        return
+    if world != args.gpus:
+        if args.gpus > 1 and world == 1:
+            raise SystemExit("bench.py: launch with torch.distributed.run for --gpus > 1")
+    run_ours(args, cfg, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

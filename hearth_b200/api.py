@@ -1,0 +1,254 @@
+"""Python face of the C ABI, named after the reference interfaces it stands in for.
+
+Host-buffer calls take and return numpy arrays and follow the reference's call
+shapes (hearth-llm/src/pool.rs, hearth-llm/src/model/matmul.rs,
+hearth-quant/src/lib.rs).  Device-buffer calls take torch CUDA tensors; torch is
+used for device memory and streams only.  Everything computes in the CUDA
+library; a missing library or device raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import lib as _l
+from .lib import PQ2_0, Q1_0, Q1_0_G128, Q2_0, Q4_K, Q6_K, Q8_0, Hb200Error, check  # noqa: F401
+
+_initialized_device = None
+
+
+def init(device: int = 0) -> None:
+    """GpuCompute::new (hearth-compute/src/lib.rs:127): bind this process to one B200."""
+    global _initialized_device
+    check(_l.load().hb200_init(device))
+    _initialized_device = device
+
+
+def shutdown() -> None:
+    global _initialized_device
+    check(_l.load().hb200_shutdown())
+    _initialized_device = None
+
+
+def sm_count() -> int:
+    return int(_l.load().hb200_sm_count())
+
+
+def block_size(dtype: int) -> int:
+    return int(_l.load().hb200_block_size(dtype))
+
+
+def block_bytes(dtype: int) -> int:
+    return int(_l.load().hb200_block_bytes(dtype))
+
+
+def byte_size(dtype: int, n_cols: int) -> int:
+    """GgmlDType::byte_size (hearth-gguf/src/ggml.rs:173-176)."""
+    return int(_l.load().hb200_byte_size(dtype, n_cols))
+
+
+def selected_kernel(dtype: int, seq_len: int = 1) -> str:
+    """hearth_quant::selected_kernel (hearth-quant/src/lib.rs:411-418)."""
+    return _l.load().hb200_selected_kernel(dtype, seq_len).decode()
+
+
+def _np_ptr(a: np.ndarray) -> C.c_void_p:
+    assert a.flags["C_CONTIGUOUS"]
+    return C.c_void_p(a.ctypes.data)
+
+
+def _stream_ptr(stream) -> C.c_void_p:
+    if stream is None:
+        import torch
+        stream = torch.cuda.current_stream()
+    return C.c_void_p(int(stream.cuda_stream))
+
+
+class Weight:
+    """A weight tensor resident on the device (GpuCompute::upload_bytes residency)."""
+
+    def __init__(self, handle, dtype, n_rows, n_cols):
+        self._h = handle
+        self.dtype, self.n_rows, self.n_cols = dtype, n_rows, n_cols
+
+    @classmethod
+    def upload(cls, dtype: int, n_rows: int, n_cols: int, packed: np.ndarray, rows: tuple[int, int] | None = None):
+        packed = np.ascontiguousarray(packed, dtype=np.uint8).reshape(-1)
+        h = C.c_void_p()
+        L = _l.load()
+        if rows is None:
+            check(L.hb200_weight_upload(dtype, n_rows, n_cols, _np_ptr(packed), packed.size, C.byref(h)))
+            return cls(h, dtype, n_rows, n_cols)
+        check(L.hb200_weight_upload_rows(dtype, n_rows, n_cols, _np_ptr(packed), packed.size, rows[0], rows[1], C.byref(h)))
+        return cls(h, dtype, rows[1] - rows[0], n_cols)
+
+    @classmethod
+    def upload_dev(cls, dtype: int, n_rows: int, n_cols: int, packed_dev, stream=None):
+        """packed_dev: torch.uint8 CUDA tensor holding the reference's packed bytes."""
+        assert packed_dev.is_cuda and packed_dev.is_contiguous()
+        h = C.c_void_p()
+        check(_l.load().hb200_weight_upload_dev(dtype, n_rows, n_cols, C.c_void_p(packed_dev.data_ptr()),
+                                                packed_dev.numel(), _stream_ptr(stream), C.byref(h)))
+        return cls(h, dtype, n_rows, n_cols)
+
+    @property
+    def resident_bytes(self) -> int:
+        d, r, c, b = C.c_int(), C.c_size_t(), C.c_size_t(), C.c_size_t()
+        check(_l.load().hb200_weight_info(self._h, C.byref(d), C.byref(r), C.byref(c), C.byref(b)))
+        return int(b.value)
+
+    @property
+    def packed_bytes(self) -> int:
+        return self.n_rows * byte_size(self.dtype, self.n_cols)
+
+    def free(self) -> None:
+        if self._h:
+            check(_l.load().hb200_weight_free(self._h))
+            self._h = None
+
+
+class Act:
+    """A resident activation: an f32 staging area plus its Q8_0 planes."""
+
+    def __init__(self, max_seq_len: int, n_cols: int):
+        self._h = C.c_void_p()
+        check(_l.load().hb200_act_create(max_seq_len, n_cols, C.byref(self._h)))
+        self.max_seq_len, self.n_cols = max_seq_len, n_cols
+
+    def f32_ptr(self) -> int:
+        p = C.c_void_p()
+        check(_l.load().hb200_act_f32_ptr(self._h, C.byref(p)))
+        return int(p.value)
+
+    def set_f32(self, x, stream=None) -> None:
+        """Copy a torch CUDA f32 tensor [seq, n_cols] into the staging area (device to device)."""
+        import torch
+        assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()
+        n = x.numel()
+        dst = _as_torch_f32(self.f32_ptr(), n, x.device)
+        dst.copy_(x.reshape(-1))
+
+    def quantize(self, seq_len: int, x_dev=None, stream=None) -> None:
+        """par_quantize (hearth-llm/src/pool.rs:467) on the device."""
+        xp = C.c_void_p(x_dev.data_ptr()) if x_dev is not None else C.c_void_p(0)
+        check(_l.load().hb200_act_quantize_dev(self._h, xp, seq_len, _stream_ptr(stream)))
+
+    def load_q8_0(self, q8_dev, seq_len: int, q8_stride: int, stream=None) -> None:
+        check(_l.load().hb200_act_load_q8_0_dev(self._h, C.c_void_p(q8_dev.data_ptr()), seq_len, q8_stride, _stream_ptr(stream)))
+
+    def store_q8_0(self, q8_dev, seq_len: int, q8_stride: int, stream=None) -> None:
+        check(_l.load().hb200_act_store_q8_0_dev(self._h, C.c_void_p(q8_dev.data_ptr()), seq_len, q8_stride, _stream_ptr(stream)))
+
+    def free(self) -> None:
+        if self._h:
+            check(_l.load().hb200_act_free(self._h))
+            self._h = None
+
+
+def _as_torch_f32(ptr: int, n: int, device):
+    """View n floats of library-owned device memory as a torch tensor (no copy)."""
+    import torch
+
+    class _Holder:
+        pass
+
+    h = _Holder()
+    h.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 3}
+    return torch.as_tensor(h, device=device)
+
+
+# ---- host-buffer calls --------------------------------------------------------------------------
+
+def quantize_q8_0(x: np.ndarray) -> np.ndarray:
+    """quantize_q8_0_into / par_quantize: f32 [seq, dim] (or [dim]) -> uint8 [seq, ceil(dim/32)*34]."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    x2 = x.reshape(1, -1) if x.ndim == 1 else x
+    seq_len, dim = x2.shape
+    out = np.zeros((seq_len, byte_size(Q8_0, dim)), dtype=np.uint8)
+    check(_l.load().hb200_quantize_q8_0(_np_ptr(x2), seq_len, dim, _np_ptr(out)))
+    return out[0] if x.ndim == 1 else out
+
+
+def par_dot_rows(w: Weight, a_q8: np.ndarray) -> np.ndarray:
+    """ThreadPool::par_dot_rows: one Q8_0 activation -> f32 [n_rows]."""
+    a_q8 = np.ascontiguousarray(a_q8, dtype=np.uint8)
+    out = np.zeros(w.n_rows, dtype=np.float32)
+    check(_l.load().hb200_dot_rows(w._h, _np_ptr(a_q8), _np_ptr(out)))
+    return out
+
+
+def par_dot_rows_batched(w: Weight, a_q8: np.ndarray, seq_len: int | None = None, q8_stride: int | None = None) -> np.ndarray:
+    """ThreadPool::par_dot_rows_batched: uint8 [seq, stride] -> token-major f32 [seq, n_rows]."""
+    a_q8 = np.ascontiguousarray(a_q8, dtype=np.uint8)
+    if seq_len is None:
+        seq_len = a_q8.shape[0]
+    if q8_stride is None:
+        q8_stride = a_q8.shape[-1] if a_q8.ndim == 2 else byte_size(Q8_0, w.n_cols)
+    out = np.zeros((seq_len, w.n_rows), dtype=np.float32)
+    check(_l.load().hb200_dot_rows_batched(w._h, _np_ptr(a_q8), seq_len, q8_stride, _np_ptr(out)))
+    return out
+
+
+def matmul(w: Weight, x: np.ndarray) -> np.ndarray:
+    """LlamaModel::matmul / matmul_batch with x_q8=None: f32 [seq, n_cols] (or [n_cols]) -> f32 [seq, n_rows]."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    x2 = x.reshape(1, -1) if x.ndim == 1 else x
+    if x2.shape[1] != w.n_cols:
+        raise Hb200Error(-4, f"Matmul dim mismatch: cols={w.n_cols} x.len={x2.shape[1]}")
+    out = np.zeros((x2.shape[0], w.n_rows), dtype=np.float32)
+    check(_l.load().hb200_matmul_f32(w._h, _np_ptr(x2), x2.shape[0], _np_ptr(out)))
+    return out[0] if x.ndim == 1 else out
+
+
+def block_dots_i32(w: Weight, a_q8: np.ndarray) -> np.ndarray:
+    """Exact int32 dots per (token, row, 32-column block): int32 [seq, n_rows, n_cols // 32]."""
+    a_q8 = np.ascontiguousarray(a_q8, dtype=np.uint8)
+    a2 = a_q8.reshape(1, -1) if a_q8.ndim == 1 else a_q8
+    seq_len, stride = a2.shape
+    n_sub = (w.n_cols // 32) if w.dtype == Q8_0 else (w.n_cols // 128) * 4
+    out = np.zeros((seq_len, w.n_rows, n_sub), dtype=np.int32)
+    check(_l.load().hb200_block_dots_i32(w._h, _np_ptr(a2), seq_len, stride, _np_ptr(out)))
+    return out
+
+
+# ---- device-buffer calls ------------------------------------------------------------------------
+
+def dot_rows_dev(w: Weight, a: Act, seq_len: int, out_dev, ld_out: int | None = None, stream=None) -> None:
+    check(_l.load().hb200_dot_rows_dev(w._h, a._h, seq_len, C.c_void_p(out_dev.data_ptr()),
+                                       ld_out if ld_out is not None else w.n_rows, _stream_ptr(stream)))
+
+
+def matmul_f32_dev(w: Weight, a: Act, seq_len: int, out_dev, ld_out: int | None = None, stream=None) -> None:
+    check(_l.load().hb200_matmul_f32_dev(w._h, a._h, seq_len, C.c_void_p(out_dev.data_ptr()),
+                                         ld_out if ld_out is not None else w.n_rows, _stream_ptr(stream)))
+
+
+class Batch:
+    """begin_batch / end_batch (hearth-compute/src/lib.rs:206-224): record ops, launch them together."""
+
+    def __init__(self):
+        self._h = C.c_void_p()
+        check(_l.load().hb200_batch_create(C.byref(self._h)))
+        self._keep = []
+
+    def add(self, w: Weight, a: Act, seq_len: int, out_dev, ld_out: int | None = None) -> None:
+        self._keep.append((w, a, out_dev))
+        check(_l.load().hb200_batch_add(self._h, w._h, a._h, seq_len, C.c_void_p(out_dev.data_ptr()),
+                                        ld_out if ld_out is not None else w.n_rows))
+
+    def seal(self) -> None:
+        check(_l.load().hb200_batch_seal(self._h))
+
+    def launch(self, stream=None) -> None:
+        check(_l.load().hb200_batch_launch(self._h, _stream_ptr(stream)))
+
+    @property
+    def launch_count(self) -> int:
+        return int(_l.load().hb200_batch_launch_count(self._h))
+
+    def free(self) -> None:
+        if self._h:
+            check(_l.load().hb200_batch_free(self._h))
+            self._h = None
+            self._keep = []

@@ -1,0 +1,735 @@
+// Host layer behind include/hb200.h: context, resident weights and
+// activations, the dtype -> kernel table, the recorded batch, and the
+// host-buffer entry points that mirror the reference's call shapes.
+//
+// Mirrors, at whole-matrix granularity:
+//   ThreadPool::par_dot_rows / par_dot_rows_batched / par_quantize  hearth-llm/src/pool.rs:467-618
+//   LlamaModel::matmul / matmul_batch dtype table                  hearth-llm/src/model/matmul.rs:152-343, :606-672
+//   GpuCompute residency and begin_batch/end_batch                 hearth-compute/src/lib.rs:104, :206-251
+// Errors never cross the boundary as exceptions: every entry point is
+// wrapped in a catch-all and returns a status code.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../include/hb200.h"
+#include "common.cuh"
+
+using namespace hb200;
+
+// ------------------------------------------------------------------ errors --
+
+namespace hb200 {
+static thread_local std::string g_last_error;
+void set_error(const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+}
+}  // namespace hb200
+
+#define HB_GUARD_BEGIN try {
+#define HB_GUARD_END                                          \
+    }                                                         \
+    catch (const std::bad_alloc&) {                           \
+        set_error("host allocation failed");                  \
+        return HB200_ERR_TOO_LARGE;                           \
+    }                                                         \
+    catch (...) {                                             \
+        set_error("unexpected C++ exception");                \
+        return HB200_ERR_CUDA;                                \
+    }
+
+// ----------------------------------------------------------------- objects --
+
+struct hb200_weight {
+    int dtype = 0, kind = KIND_NONE;
+    size_t n_rows = 0, n_cols = 0;
+    size_t row_bytes = 0;  // of the reference layout
+    int nb = 0, n_panels = 0, n_sub = 0;
+    uint4* bits = nullptr;   // panel layout (Q1_0 / Q2_0 / Q8_0)
+    void* scales = nullptr;
+    uint8_t* raw = nullptr;  // reference layout (Q4_K / Q6_K)
+    size_t resident_bytes = 0;
+};
+
+struct hb200_act {
+    size_t max_seq = 0, n_cols = 0;
+    int ld_q = 0, ld_b = 0;
+    float* x = nullptr;
+    int8_t* q = nullptr;
+    float* d = nullptr;
+    float* sums = nullptr;
+};
+
+struct BatchEntry {
+    hb200_weight_t w;
+    hb200_act_t a;
+    size_t seq_len;
+    float* out;
+    size_t ld_out;
+};
+struct BatchGroup {  // one launch
+    int kind, m;
+    DotOp* ops_dev = nullptr;
+    DotItem* items_dev = nullptr;
+    int n_items = 0;
+};
+struct hb200_batch {
+    std::vector<BatchEntry> entries;
+    std::vector<BatchGroup> groups;
+    std::vector<BatchEntry> kquant;  // K-quant ops launch on their own
+    bool sealed = false;
+};
+
+namespace {
+
+struct Context {
+    bool ready = false;
+    int device = -1;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;  // used by the host-buffer calls
+    // scratch for the host-buffer calls, grown on demand
+    uint8_t* d_in = nullptr;
+    size_t d_in_bytes = 0;
+    uint8_t* d_out = nullptr;
+    size_t d_out_bytes = 0;
+    hb200_act_t act = nullptr;
+};
+Context g_ctx;
+
+int kind_of(int dtype) {
+    switch (dtype) {
+        case HB200_Q1_0: case HB200_Q1_0_G128: case HB200_Q1_0_G128_LEGACY: return KIND_Q1;
+        case HB200_Q2_0: case HB200_PQ2_0: return KIND_Q2;
+        case HB200_Q8_0: return KIND_Q8;
+        case HB200_Q4_K: return KIND_Q4K;
+        case HB200_Q6_K: return KIND_Q6K;
+        default: return KIND_NONE;
+    }
+}
+
+int need_ctx() {
+    if (!g_ctx.ready) {
+        set_error("hb200_init has not succeeded in this process");
+        return HB200_ERR_NOT_INITIALIZED;
+    }
+    return 0;
+}
+
+int grow(uint8_t** p, size_t* have, size_t want) {
+    if (*have >= want) return 0;
+    if (*p) HB_CUDA(cudaFree(*p));
+    *p = nullptr;
+    *have = 0;
+    size_t sz = want + want / 4 + 4096;
+    HB_CUDA(cudaMalloc(p, sz));
+    *have = sz;
+    return 0;
+}
+
+void fill_op(DotOp& op, const hb200_weight* w, const hb200_act* a, size_t tok0, float* out, size_t ld_out, int32_t* iout) {
+    op.bits = w->bits;
+    op.scales = w->scales;
+    op.aq = a->q + tok0 * (size_t)a->ld_q;
+    op.ad = a->d + tok0 * (size_t)a->ld_b;
+    op.asum = a->sums + tok0 * (size_t)a->ld_b;
+    op.out = out ? out + tok0 * ld_out : nullptr;
+    op.iout = iout;
+    op.n_rows = (int)w->n_rows;
+    op.nb = w->nb;
+    op.n_sub = w->n_sub;
+    op.ld_out = (int)ld_out;
+    op.ld_q = a->ld_q;
+    op.ld_b = a->ld_b;
+}
+
+int check_pair(const hb200_weight* w, const hb200_act* a, size_t seq_len, size_t ld_out) {
+    if (!w || !a) { set_error("null weight or activation handle"); return HB200_ERR_NULL; }
+    if (a->n_cols != w->n_cols) {
+        set_error("dim mismatch: weight has %zu columns, activation %zu", w->n_cols, a->n_cols);
+        return HB200_ERR_BAD_SHAPE;
+    }
+    if (seq_len > a->max_seq) { set_error("seq_len %zu exceeds the activation's capacity %zu", seq_len, a->max_seq); return HB200_ERR_BAD_SHAPE; }
+    if (ld_out < w->n_rows) { set_error("ld_out %zu is smaller than n_rows %zu", ld_out, w->n_rows); return HB200_ERR_BAD_SHAPE; }
+    return 0;
+}
+
+}  // namespace
+
+namespace {
+
+int dot_rows_launch(const hb200_weight* w, const hb200_act* a, size_t seq_len, float* out, size_t ld_out, cudaStream_t st) {
+    if (w->kind == KIND_Q4K || w->kind == KIND_Q6K) {
+        set_error("K-quant weights take f32 activations; use hb200_matmul_f32[_dev]");
+        return HB200_ERR_UNSUPPORTED;
+    }
+    for (size_t tok0 = 0; tok0 < seq_len; tok0 += GEMV_MAX_M) {
+        const int m = (int)((seq_len - tok0) < (size_t)GEMV_MAX_M ? (seq_len - tok0) : GEMV_MAX_M);
+        DotOp op;
+        fill_op(op, w, a, tok0, out, ld_out, nullptr);
+        const int rc = launch_gemv_dp4a(w->kind, m, false, nullptr, nullptr, w->n_panels, &op, g_ctx.sm_count, st);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+int ensure_ctx_act(size_t seq_len, size_t n_cols) {
+    if (g_ctx.act && g_ctx.act->n_cols == n_cols && g_ctx.act->max_seq >= seq_len) return 0;
+    if (g_ctx.act) { hb200_act_free(g_ctx.act); g_ctx.act = nullptr; }
+    return hb200_act_create(seq_len, n_cols, &g_ctx.act);
+}
+
+}  // namespace
+
+// --------------------------------------------------------------- lifecycle --
+
+extern "C" int hb200_init(int device) {
+    HB_GUARD_BEGIN
+    if (g_ctx.ready) {
+        if (g_ctx.device == device) return HB200_OK;
+        set_error("already bound to device %d", g_ctx.device);
+        return HB200_ERR_BAD_SHAPE;
+    }
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0) {
+        set_error("no CUDA device: %s", e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+        return HB200_ERR_NO_DEVICE;
+    }
+    if (device < 0 || device >= n) { set_error("device %d out of range (0..%d)", device, n - 1); return HB200_ERR_NO_DEVICE; }
+    cudaDeviceProp prop;
+    HB_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        set_error("device %d is sm_%d%d; this library contains sm_100a code only", device, prop.major, prop.minor);
+        return HB200_ERR_NO_DEVICE;
+    }
+    HB_CUDA(cudaSetDevice(device));
+    HB_CUDA(cudaStreamCreateWithFlags(&g_ctx.stream, cudaStreamNonBlocking));
+    g_ctx.device = device;
+    g_ctx.sm_count = prop.multiProcessorCount;
+    int rc;
+    if ((rc = gemv_dp4a_prepare())) return rc;
+    if ((rc = kquant_prepare())) return rc;
+    g_ctx.ready = true;
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_shutdown(void) {
+    HB_GUARD_BEGIN
+    if (!g_ctx.ready) return HB200_OK;
+    cudaSetDevice(g_ctx.device);
+    cudaDeviceSynchronize();
+    if (g_ctx.act) { hb200_act_free(g_ctx.act); g_ctx.act = nullptr; }
+    if (g_ctx.d_in) cudaFree(g_ctx.d_in);
+    if (g_ctx.d_out) cudaFree(g_ctx.d_out);
+    if (g_ctx.stream) cudaStreamDestroy(g_ctx.stream);
+    g_ctx = Context();
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" const char* hb200_last_error(void) { return g_last_error.c_str(); }
+extern "C" int hb200_sm_count(void) { return g_ctx.ready ? g_ctx.sm_count : 0; }
+
+// ---------------------------------------------------------------- geometry --
+
+extern "C" size_t hb200_block_size(int dtype) {
+    switch (kind_of(dtype)) {
+        case KIND_Q1: case KIND_Q2: return 128;
+        case KIND_Q8: return 32;
+        case KIND_Q4K: case KIND_Q6K: return 256;
+        default: return 0;
+    }
+}
+extern "C" size_t hb200_block_bytes(int dtype) {
+    switch (kind_of(dtype)) {
+        case KIND_Q1: return 18;
+        case KIND_Q2: case KIND_Q8: return 34;
+        case KIND_Q4K: return 144;
+        case KIND_Q6K: return 210;
+        default: return 0;
+    }
+}
+extern "C" size_t hb200_byte_size(int dtype, size_t n_cols) {
+    const size_t bs = hb200_block_size(dtype);
+    if (!bs) return 0;
+    return ((n_cols + bs - 1) / bs) * hb200_block_bytes(dtype);
+}
+
+extern "C" const char* hb200_selected_kernel(int dtype, size_t seq_len) {
+    const int kind = kind_of(dtype);
+    if (seq_len == 0) return "none";
+    switch (kind) {
+        case KIND_Q1: return "gemv_dp4a_q1_0";
+        case KIND_Q2: return "gemv_dp4a_q2_0";
+        case KIND_Q8: return "gemv_dp4a_q8_0";
+        case KIND_Q4K: return "kquant_gemv_q4_k_f32";
+        case KIND_Q6K: return "kquant_gemv_q6_k_f32";
+        default: return "none";
+    }
+}
+
+// ----------------------------------------------------------------- weights --
+
+static int weight_build(int dtype, size_t n_rows, size_t n_cols, const uint8_t* src, bool src_on_device, cudaStream_t st,
+                        hb200_weight_t* out) {
+    const int kind = kind_of(dtype);
+    hb200_weight* w = new hb200_weight();
+    w->dtype = dtype;
+    w->kind = kind;
+    w->n_rows = n_rows;
+    w->n_cols = n_cols;
+    w->row_bytes = hb200_byte_size(dtype, n_cols);
+    const size_t bytes = n_rows * w->row_bytes;
+    int rc = 0;
+    uint8_t* d_raw = nullptr;
+    bool own_raw = false;
+    auto fail = [&](int code) {
+        if (own_raw && d_raw) cudaFree(d_raw);
+        if (w->bits) cudaFree(w->bits);
+        if (w->scales) cudaFree(w->scales);
+        if (w->raw) cudaFree(w->raw);
+        delete w;
+        return code;
+    };
+    if (bytes > 0) {
+        if (src_on_device && kind != KIND_Q4K && kind != KIND_Q6K) {
+            d_raw = const_cast<uint8_t*>(src);
+        } else {
+            cudaError_t e = cudaMalloc(&d_raw, bytes);
+            if (e != cudaSuccess) { set_error("cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e)); return fail(HB200_ERR_CUDA); }
+            own_raw = true;
+            e = cudaMemcpyAsync(d_raw, src, bytes, src_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, st);
+            if (e != cudaSuccess) { set_error("weight copy failed: %s", cudaGetErrorString(e)); return fail(HB200_ERR_CUDA); }
+        }
+    }
+    if (kind == KIND_Q4K || kind == KIND_Q6K) {
+        w->raw = d_raw;
+        own_raw = false;
+        w->resident_bytes = bytes;
+        cudaError_t e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) { set_error("weight upload failed: %s", cudaGetErrorString(e)); return fail(HB200_ERR_CUDA); }
+    } else {
+        const int rpg = rows_per_group(kind);
+        const size_t rp = 32 * (size_t)rpg;
+        w->n_panels = (int)((n_rows + rp - 1) / rp);
+        if (kind == KIND_Q8) {
+            w->nb = (int)((n_cols + 127) / 128);
+            w->n_sub = (int)(n_cols / 32);
+        } else {
+            w->nb = (int)(n_cols / 128);  // a tail shorter than a block is dropped, as in the reference
+            w->n_sub = w->nb * 4;
+        }
+        const size_t tiles = (size_t)w->n_panels * w->nb * 32;
+        const size_t bits_bytes = tiles * 128;
+        const size_t scale_bytes = tiles * (size_t)scales_per_tile(kind) * 2;
+        if (tiles > 0) {
+            cudaError_t e = cudaMalloc(&w->bits, bits_bytes);
+            if (e == cudaSuccess) e = cudaMalloc(&w->scales, scale_bytes);
+            if (e != cudaSuccess) { set_error("cudaMalloc for %zu weight bytes failed: %s", bits_bytes + scale_bytes, cudaGetErrorString(e)); return fail(HB200_ERR_CUDA); }
+            const int eff_cols = (kind == KIND_Q8) ? (int)n_cols : w->nb * 128;
+            rc = launch_repack(kind, d_raw, w->row_bytes, (int)n_rows, eff_cols, w->nb, w->n_panels, w->bits, w->scales, st);
+            if (rc) return fail(rc);
+        }
+        cudaError_t e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) { set_error("weight re-tiling failed: %s", cudaGetErrorString(e)); return fail(HB200_ERR_CUDA); }
+        if (own_raw) { cudaFree(d_raw); own_raw = false; }
+        w->resident_bytes = bits_bytes + scale_bytes;
+    }
+    *out = w;
+    return HB200_OK;
+}
+
+static int weight_check(int dtype, size_t n_rows, size_t n_cols, const void* packed, size_t bytes, hb200_weight_t* out) {
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!out) { set_error("null output handle"); return HB200_ERR_NULL; }
+    if (kind_of(dtype) == KIND_NONE) { set_error("GGML type id %d is not on this path", dtype); return HB200_ERR_BAD_DTYPE; }
+    if (n_cols == 0) { set_error("Matmul dim mismatch: weight has 0 columns"); return HB200_ERR_BAD_SHAPE; }
+    const size_t want = n_rows * hb200_byte_size(dtype, n_cols);
+    if (bytes != want) { set_error("weight byte count %zu != n_rows * byte_size = %zu", bytes, want); return HB200_ERR_BAD_SHAPE; }
+    if (!packed && bytes) { set_error("null weight bytes"); return HB200_ERR_NULL; }
+    if (n_rows > (1u << 30) || n_cols > (1u << 24)) { set_error("weight shape %zu x %zu too large", n_rows, n_cols); return HB200_ERR_TOO_LARGE; }
+    return 0;
+}
+
+extern "C" int hb200_weight_upload(int dtype, size_t n_rows, size_t n_cols, const uint8_t* packed, size_t bytes,
+                                   hb200_weight_t* out) {
+    HB_GUARD_BEGIN
+    int rc = weight_check(dtype, n_rows, n_cols, packed, bytes, out);
+    if (rc) return rc;
+    return weight_build(dtype, n_rows, n_cols, packed, false, g_ctx.stream, out);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_weight_upload_dev(int dtype, size_t n_rows, size_t n_cols, const uint8_t* packed_dev, size_t bytes,
+                                       void* stream, hb200_weight_t* out) {
+    HB_GUARD_BEGIN
+    int rc = weight_check(dtype, n_rows, n_cols, packed_dev, bytes, out);
+    if (rc) return rc;
+    return weight_build(dtype, n_rows, n_cols, packed_dev, true, (cudaStream_t)stream, out);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_weight_upload_rows(int dtype, size_t n_rows, size_t n_cols, const uint8_t* packed, size_t bytes,
+                                        size_t row_begin, size_t row_end, hb200_weight_t* out) {
+    HB_GUARD_BEGIN
+    int rc = weight_check(dtype, n_rows, n_cols, packed, bytes, out);
+    if (rc) return rc;
+    if (row_begin > row_end || row_end > n_rows) { set_error("row range [%zu, %zu) outside 0..%zu", row_begin, row_end, n_rows); return HB200_ERR_BAD_SHAPE; }
+    const size_t rb = hb200_byte_size(dtype, n_cols);
+    return weight_build(dtype, row_end - row_begin, n_cols, packed + row_begin * rb, false, g_ctx.stream, out);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_weight_free(hb200_weight_t w) {
+    HB_GUARD_BEGIN
+    if (!w) return HB200_OK;
+    if (w->bits) cudaFree(w->bits);
+    if (w->scales) cudaFree(w->scales);
+    if (w->raw) cudaFree(w->raw);
+    delete w;
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_weight_info(hb200_weight_t w, int* dtype, size_t* n_rows, size_t* n_cols, size_t* resident_bytes) {
+    if (!w) { set_error("null weight handle"); return HB200_ERR_NULL; }
+    if (dtype) *dtype = w->dtype;
+    if (n_rows) *n_rows = w->n_rows;
+    if (n_cols) *n_cols = w->n_cols;
+    if (resident_bytes) *resident_bytes = w->resident_bytes;
+    return HB200_OK;
+}
+
+// ------------------------------------------------------------- activations --
+
+extern "C" int hb200_act_create(size_t max_seq_len, size_t n_cols, hb200_act_t* out) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!out) { set_error("null output handle"); return HB200_ERR_NULL; }
+    if (n_cols == 0 || max_seq_len == 0) { set_error("activation of %zu x %zu", max_seq_len, n_cols); return HB200_ERR_BAD_SHAPE; }
+    if (n_cols > (1u << 24) || max_seq_len > (1u << 20)) { set_error("activation %zu x %zu too large", max_seq_len, n_cols); return HB200_ERR_TOO_LARGE; }
+    hb200_act* a = new hb200_act();
+    a->max_seq = max_seq_len;
+    a->n_cols = n_cols;
+    a->ld_q = (int)((n_cols + ACT_PAD - 1) / ACT_PAD * ACT_PAD);
+    a->ld_b = a->ld_q / 32;
+    cudaError_t e = cudaMalloc(&a->x, max_seq_len * n_cols * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&a->q, max_seq_len * (size_t)a->ld_q);
+    if (e == cudaSuccess) e = cudaMalloc(&a->d, max_seq_len * (size_t)a->ld_b * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&a->sums, max_seq_len * (size_t)a->ld_b * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemset(a->q, 0, max_seq_len * (size_t)a->ld_q);
+    if (e == cudaSuccess) e = cudaMemset(a->d, 0, max_seq_len * (size_t)a->ld_b * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemset(a->sums, 0, max_seq_len * (size_t)a->ld_b * sizeof(float));
+    if (e != cudaSuccess) {
+        set_error("activation allocation failed: %s", cudaGetErrorString(e));
+        hb200_act_free(a);
+        return HB200_ERR_CUDA;
+    }
+    *out = a;
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_act_free(hb200_act_t a) {
+    HB_GUARD_BEGIN
+    if (!a) return HB200_OK;
+    if (a->x) cudaFree(a->x);
+    if (a->q) cudaFree(a->q);
+    if (a->d) cudaFree(a->d);
+    if (a->sums) cudaFree(a->sums);
+    delete a;
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_act_f32_ptr(hb200_act_t a, float** dev_ptr) {
+    if (!a || !dev_ptr) { set_error("null handle"); return HB200_ERR_NULL; }
+    *dev_ptr = a->x;
+    return HB200_OK;
+}
+
+extern "C" int hb200_act_q8_planes(hb200_act_t a, int8_t** q, float** d, float** sums, size_t* ld_q, size_t* ld_b) {
+    if (!a) { set_error("null handle"); return HB200_ERR_NULL; }
+    if (q) *q = a->q;
+    if (d) *d = a->d;
+    if (sums) *sums = a->sums;
+    if (ld_q) *ld_q = (size_t)a->ld_q;
+    if (ld_b) *ld_b = (size_t)a->ld_b;
+    return HB200_OK;
+}
+
+extern "C" int hb200_act_quantize_dev(hb200_act_t a, const float* x_dev, size_t seq_len, void* stream) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!a) { set_error("null activation handle"); return HB200_ERR_NULL; }
+    if (seq_len > a->max_seq) { set_error("seq_len %zu exceeds capacity %zu", seq_len, a->max_seq); return HB200_ERR_BAD_SHAPE; }
+    return launch_quantize_q8_0(x_dev ? x_dev : a->x, (int)seq_len, (int)a->n_cols, a->q, a->d, a->sums, a->ld_q, a->ld_b,
+                                nullptr, 0, (cudaStream_t)stream);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_act_load_q8_0_dev(hb200_act_t a, const uint8_t* q8_dev, size_t seq_len, size_t q8_stride, void* stream) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!a || !q8_dev) { set_error("null handle or pointer"); return HB200_ERR_NULL; }
+    if (seq_len > a->max_seq) { set_error("seq_len %zu exceeds capacity %zu", seq_len, a->max_seq); return HB200_ERR_BAD_SHAPE; }
+    if (q8_stride < hb200_byte_size(HB200_Q8_0, a->n_cols)) { set_error("q8_stride %zu shorter than a Q8_0 row", q8_stride); return HB200_ERR_BAD_SHAPE; }
+    return launch_load_q8_0(q8_dev, q8_stride, (int)seq_len, (int)a->n_cols, a->q, a->d, a->sums, a->ld_q, a->ld_b,
+                            (cudaStream_t)stream);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_act_store_q8_0_dev(hb200_act_t a, uint8_t* q8_dev, size_t seq_len, size_t q8_stride, void* stream) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!a || !q8_dev) { set_error("null handle or pointer"); return HB200_ERR_NULL; }
+    if (seq_len > a->max_seq) { set_error("seq_len %zu exceeds capacity %zu", seq_len, a->max_seq); return HB200_ERR_BAD_SHAPE; }
+    if (q8_stride < hb200_byte_size(HB200_Q8_0, a->n_cols)) { set_error("q8_stride %zu shorter than a Q8_0 row", q8_stride); return HB200_ERR_BAD_SHAPE; }
+    return launch_store_q8_0(a->q, a->d, a->ld_q, a->ld_b, (int)seq_len, (int)a->n_cols, q8_dev, q8_stride, (cudaStream_t)stream);
+    HB_GUARD_END
+}
+
+// ------------------------------------------------------- device-buffer calls --
+
+extern "C" int hb200_dot_rows_dev(hb200_weight_t w, hb200_act_t a, size_t seq_len, float* out_dev, size_t ld_out, void* stream) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if ((rc = check_pair(w, a, seq_len, ld_out))) return rc;
+    if (!out_dev) { set_error("null output"); return HB200_ERR_NULL; }
+    if (seq_len == 0 || w->n_rows == 0) return HB200_OK;  // par_dot_rows returns early on n == 0 (pool.rs:520)
+    return dot_rows_launch(w, a, seq_len, out_dev, ld_out, (cudaStream_t)stream);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_matmul_f32_dev(hb200_weight_t w, hb200_act_t a, size_t seq_len, float* out_dev, size_t ld_out, void* stream) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if ((rc = check_pair(w, a, seq_len, ld_out))) return rc;
+    if (!out_dev) { set_error("null output"); return HB200_ERR_NULL; }
+    if (seq_len == 0 || w->n_rows == 0) return HB200_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (w->kind == KIND_Q4K || w->kind == KIND_Q6K)
+        return launch_kquant_gemv(w->kind, w->raw, w->row_bytes, (int)w->n_rows, (int)w->n_cols, a->x, (int)seq_len, out_dev,
+                                  (int)ld_out, st);
+    rc = launch_quantize_q8_0(a->x, (int)seq_len, (int)a->n_cols, a->q, a->d, a->sums, a->ld_q, a->ld_b, nullptr, 0, st);
+    if (rc) return rc;
+    return dot_rows_launch(w, a, seq_len, out_dev, ld_out, st);
+    HB_GUARD_END
+}
+
+// --------------------------------------------------------- host-buffer calls --
+
+extern "C" int hb200_quantize_q8_0(const float* x, size_t seq_len, size_t dim, uint8_t* q8_out) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (seq_len == 0) return HB200_OK;  // par_quantize returns early (pool.rs:468)
+    if (!x || !q8_out) { set_error("null buffer"); return HB200_ERR_NULL; }
+    if (dim == 0) return HB200_OK;
+    if ((rc = ensure_ctx_act(seq_len, dim))) return rc;
+    const size_t q8_size = hb200_byte_size(HB200_Q8_0, dim);
+    if ((rc = grow(&g_ctx.d_out, &g_ctx.d_out_bytes, seq_len * q8_size))) return rc;
+    hb200_act* a = g_ctx.act;
+    cudaStream_t st = g_ctx.stream;
+    HB_CUDA(cudaMemcpyAsync(a->x, x, seq_len * dim * sizeof(float), cudaMemcpyHostToDevice, st));
+    if ((rc = launch_quantize_q8_0(a->x, (int)seq_len, (int)dim, a->q, a->d, a->sums, a->ld_q, a->ld_b, g_ctx.d_out, q8_size, st))) return rc;
+    HB_CUDA(cudaMemcpyAsync(q8_out, g_ctx.d_out, seq_len * q8_size, cudaMemcpyDeviceToHost, st));
+    HB_CUDA(cudaStreamSynchronize(st));
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+static int host_q8_to_act(hb200_weight_t w, const uint8_t* a_q8, size_t seq_len, size_t q8_stride) {
+    int rc;
+    const size_t q8_size = hb200_byte_size(HB200_Q8_0, w->n_cols);
+    if (q8_stride < q8_size) { set_error("q8_stride %zu shorter than a Q8_0 row of %zu bytes", q8_stride, q8_size); return HB200_ERR_BAD_SHAPE; }
+    if ((rc = ensure_ctx_act(seq_len, w->n_cols))) return rc;
+    const size_t span = (seq_len - 1) * q8_stride + q8_size;
+    if ((rc = grow(&g_ctx.d_in, &g_ctx.d_in_bytes, span))) return rc;
+    HB_CUDA(cudaMemcpyAsync(g_ctx.d_in, a_q8, span, cudaMemcpyHostToDevice, g_ctx.stream));
+    hb200_act* a = g_ctx.act;
+    return launch_load_q8_0(g_ctx.d_in, q8_stride, (int)seq_len, (int)w->n_cols, a->q, a->d, a->sums, a->ld_q, a->ld_b, g_ctx.stream);
+}
+
+extern "C" int hb200_dot_rows_batched(hb200_weight_t w, const uint8_t* a_q8, size_t seq_len, size_t q8_stride, float* out) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!w) { set_error("null weight handle"); return HB200_ERR_NULL; }
+    if (w->n_rows == 0 || seq_len == 0) return HB200_OK;  // pool.rs:581
+    if (!a_q8 || !out) { set_error("null buffer"); return HB200_ERR_NULL; }
+    if (w->kind == KIND_Q4K || w->kind == KIND_Q6K) { set_error("K-quant weights have no Q8_0 dot in the reference; use hb200_matmul_f32"); return HB200_ERR_UNSUPPORTED; }
+    if ((rc = host_q8_to_act(w, a_q8, seq_len, q8_stride))) return rc;
+    const size_t out_bytes = seq_len * w->n_rows * sizeof(float);
+    if ((rc = grow(&g_ctx.d_out, &g_ctx.d_out_bytes, out_bytes))) return rc;
+    if ((rc = dot_rows_launch(w, g_ctx.act, seq_len, (float*)g_ctx.d_out, w->n_rows, g_ctx.stream))) return rc;
+    HB_CUDA(cudaMemcpyAsync(out, g_ctx.d_out, out_bytes, cudaMemcpyDeviceToHost, g_ctx.stream));
+    HB_CUDA(cudaStreamSynchronize(g_ctx.stream));
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_dot_rows(hb200_weight_t w, const uint8_t* a_q8, float* out) {
+    if (!w) { set_error("null weight handle"); return HB200_ERR_NULL; }
+    return hb200_dot_rows_batched(w, a_q8, 1, hb200_byte_size(HB200_Q8_0, w->n_cols), out);
+}
+
+extern "C" int hb200_matmul_f32(hb200_weight_t w, const float* x, size_t seq_len, float* out) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!w) { set_error("null weight handle"); return HB200_ERR_NULL; }
+    if (w->n_rows == 0 || seq_len == 0) return HB200_OK;
+    if (!x || !out) { set_error("null buffer"); return HB200_ERR_NULL; }
+    if ((rc = ensure_ctx_act(seq_len, w->n_cols))) return rc;
+    const size_t out_bytes = seq_len * w->n_rows * sizeof(float);
+    if ((rc = grow(&g_ctx.d_out, &g_ctx.d_out_bytes, out_bytes))) return rc;
+    HB_CUDA(cudaMemcpyAsync(g_ctx.act->x, x, seq_len * w->n_cols * sizeof(float), cudaMemcpyHostToDevice, g_ctx.stream));
+    if ((rc = hb200_matmul_f32_dev(w, g_ctx.act, seq_len, (float*)g_ctx.d_out, w->n_rows, g_ctx.stream))) return rc;
+    HB_CUDA(cudaMemcpyAsync(out, g_ctx.d_out, out_bytes, cudaMemcpyDeviceToHost, g_ctx.stream));
+    HB_CUDA(cudaStreamSynchronize(g_ctx.stream));
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_block_dots_i32(hb200_weight_t w, const uint8_t* a_q8, size_t seq_len, size_t q8_stride, int32_t* out) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!w) { set_error("null weight handle"); return HB200_ERR_NULL; }
+    if (w->kind == KIND_Q4K || w->kind == KIND_Q6K) { set_error("K-quant dots have no integer form in the reference"); return HB200_ERR_UNSUPPORTED; }
+    if (w->n_rows == 0 || seq_len == 0 || w->n_sub == 0) return HB200_OK;
+    if (!a_q8 || !out) { set_error("null buffer"); return HB200_ERR_NULL; }
+    if ((rc = host_q8_to_act(w, a_q8, seq_len, q8_stride))) return rc;
+    const size_t per_tok = w->n_rows * (size_t)w->n_sub;
+    const size_t out_bytes = seq_len * per_tok * sizeof(int32_t);
+    if ((rc = grow(&g_ctx.d_out, &g_ctx.d_out_bytes, out_bytes))) return rc;
+    for (size_t s = 0; s < seq_len; s++) {
+        DotOp op;
+        fill_op(op, w, g_ctx.act, s, nullptr, w->n_rows, (int32_t*)g_ctx.d_out + s * per_tok);
+        if ((rc = launch_gemv_dp4a(w->kind, 1, true, nullptr, nullptr, w->n_panels, &op, g_ctx.sm_count, g_ctx.stream))) return rc;
+    }
+    HB_CUDA(cudaMemcpyAsync(out, g_ctx.d_out, out_bytes, cudaMemcpyDeviceToHost, g_ctx.stream));
+    HB_CUDA(cudaStreamSynchronize(g_ctx.stream));
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+// ------------------------------------------------------------------ batches --
+
+extern "C" int hb200_batch_create(hb200_batch_t* out) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!out) { set_error("null output handle"); return HB200_ERR_NULL; }
+    *out = new hb200_batch();
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_batch_add(hb200_batch_t b, hb200_weight_t w, hb200_act_t a, size_t seq_len, float* out_dev, size_t ld_out) {
+    HB_GUARD_BEGIN
+    if (!b) { set_error("null batch"); return HB200_ERR_NULL; }
+    if (b->sealed) { set_error("batch is sealed"); return HB200_ERR_BAD_SHAPE; }
+    int rc = check_pair(w, a, seq_len, ld_out);
+    if (rc) return rc;
+    if (!out_dev) { set_error("null output"); return HB200_ERR_NULL; }
+    if (seq_len == 0 || w->n_rows == 0) return HB200_OK;
+    BatchEntry e{w, a, seq_len, out_dev, ld_out};
+    if (w->kind == KIND_Q4K || w->kind == KIND_Q6K) b->kquant.push_back(e);
+    else b->entries.push_back(e);
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_batch_seal(hb200_batch_t b) {
+    HB_GUARD_BEGIN
+    if (!b) { set_error("null batch"); return HB200_ERR_NULL; }
+    if (b->sealed) return HB200_OK;
+    // One launch per (kind, tokens-per-op) combination.
+    std::map<std::pair<int, int>, std::pair<std::vector<DotOp>, std::vector<DotItem>>> acc;
+    for (const BatchEntry& e : b->entries) {
+        for (size_t tok0 = 0; tok0 < e.seq_len; tok0 += GEMV_MAX_M) {
+            const int m = (int)((e.seq_len - tok0) < (size_t)GEMV_MAX_M ? (e.seq_len - tok0) : GEMV_MAX_M);
+            auto& slot = acc[{e.w->kind, m}];
+            DotOp op;
+            fill_op(op, e.w, e.a, tok0, e.out, e.ld_out, nullptr);
+            const int idx = (int)slot.first.size();
+            slot.first.push_back(op);
+            for (int p = 0; p < e.w->n_panels; p++) slot.second.push_back(make_int2(idx, p));
+        }
+    }
+    for (auto& kv : acc) {
+        BatchGroup g;
+        g.kind = kv.first.first;
+        g.m = kv.first.second;
+        g.n_items = (int)kv.second.second.size();
+        if (g.n_items == 0) continue;
+        HB_CUDA(cudaMalloc(&g.ops_dev, kv.second.first.size() * sizeof(DotOp)));
+        HB_CUDA(cudaMalloc(&g.items_dev, kv.second.second.size() * sizeof(DotItem)));
+        HB_CUDA(cudaMemcpy(g.ops_dev, kv.second.first.data(), kv.second.first.size() * sizeof(DotOp), cudaMemcpyHostToDevice));
+        HB_CUDA(cudaMemcpy(g.items_dev, kv.second.second.data(), kv.second.second.size() * sizeof(DotItem), cudaMemcpyHostToDevice));
+        b->groups.push_back(g);
+    }
+    b->sealed = true;
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!b) { set_error("null batch"); return HB200_ERR_NULL; }
+    if (!b->sealed) { set_error("batch is not sealed"); return HB200_ERR_BAD_SHAPE; }
+    cudaStream_t st = (cudaStream_t)stream;
+    for (const BatchGroup& g : b->groups)
+        if ((rc = launch_gemv_dp4a(g.kind, g.m, false, g.ops_dev, g.items_dev, g.n_items, nullptr, g_ctx.sm_count, st))) return rc;
+    for (const BatchEntry& e : b->kquant)
+        if ((rc = launch_kquant_gemv(e.w->kind, e.w->raw, e.w->row_bytes, (int)e.w->n_rows, (int)e.w->n_cols, e.a->x, (int)e.seq_len,
+                                     e.out, (int)e.ld_out, st)))
+            return rc;
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_batch_launch_count(hb200_batch_t b) {
+    if (!b || !b->sealed) return 0;
+    return (int)(b->groups.size() + b->kquant.size());
+}
+
+extern "C" int hb200_batch_free(hb200_batch_t b) {
+    HB_GUARD_BEGIN
+    if (!b) return HB200_OK;
+    for (BatchGroup& g : b->groups) {
+        if (g.ops_dev) cudaFree(g.ops_dev);
+        if (g.items_dev) cudaFree(g.items_dev);
+    }
+    delete b;
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_stream_synchronize(void* stream) {
+    HB_GUARD_BEGIN
+    HB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return HB200_OK;
+    HB_GUARD_END
+}

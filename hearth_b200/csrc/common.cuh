@@ -1,0 +1,99 @@
+// Shared definitions for the sm_100a kernels and the C-ABI host layer.
+//
+// Device data layouts (all chosen once at upload; the resident byte count
+// equals the reference's packed byte count up to row / column padding):
+//
+//  Weights, Q1_0 / Q2_0 / Q8_0 ("panel" layout).
+//    A row group (rg) is RPG consecutive rows whose codes share one byte per
+//    column: Q1_0 RPG=8 (bit r of the byte = sign bit of row 8*rg+r),
+//    Q2_0 RPG=4 (bits 2r..2r+1 = code of row 4*rg+r), Q8_0 RPG=1 (the int8).
+//    A tile is one row group x one 128-column block = 128 bytes = 32 words.
+//    Word position q = t*8 + s*2 + e (t 0..3, s 0..3, e 0..1) holds columns
+//    s*32 + (2t+e)*4 .. +3 of the block, one column per byte.  This order
+//    puts, for every 32-column sub-block s, words {2t, 2t+1} in the 16-byte
+//    pieces 2t and 2t+1, which is what one thread of an m16n8k32 MMA quad
+//    needs, and is as good as any other order for the dp4a kernel.
+//    A panel is 32 row groups.  Address of 16-byte piece p (0..7) of tile
+//    (panel, blk) for lane l:  bits[((panel*nb + blk)*8 + p)*32 + l]  (uint4),
+//    so a warp reads 512 contiguous bytes per piece and a panel is contiguous.
+//    Scales are f16, per tile: Q1_0 8 (one per row) as uint4, Q2_0 4 as uint2,
+//    Q8_0 4 (one per 32-column sub-block) as uint2, at [(panel*nb + blk)*32 + l].
+//
+//  Activations, Q8_0 ("planes").  Per token: int8 values q[ld_q] (ld_q = n_cols
+//    rounded up to 1024, padding zero), block scales d[ld_b] (ld_b = ld_q/32; the
+//    stored f16 widened to f32) and block sums sum[ld_b] (sum of the 32 int8 as f32).
+//
+//  Weights, Q4_K / Q6_K: the reference's bytes unchanged (rows contiguous).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hb200 {
+
+enum Kind : int { KIND_Q1 = 0, KIND_Q2 = 1, KIND_Q8 = 2, KIND_Q4K = 3, KIND_Q6K = 4, KIND_NONE = -1 };
+
+__host__ __device__ constexpr int rows_per_group(int kind) { return kind == KIND_Q1 ? 8 : (kind == KIND_Q2 ? 4 : 1); }
+__host__ __device__ constexpr int scales_per_tile(int kind) { return kind == KIND_Q1 ? 8 : 4; }
+
+constexpr int ACT_PAD = 1024;  // activation planes are padded to this many columns
+
+// One dot-rows operation: every row of one weight against M consecutive tokens.
+struct DotOp {
+    const uint4* bits;     // panel layout
+    const void* scales;    // uint4 (Q1_0) or uint2 (Q2_0, Q8_0) per (tile, lane)
+    const int8_t* aq;      // first token's int8 plane
+    const float* ad;       // first token's scale plane
+    const float* asum;     // first token's sum plane
+    float* out;            // out[m*ld_out + row], m relative to the first token
+    int32_t* iout;         // optional: iout[(m*n_rows + row)*n_sub + sub]
+    int n_rows;
+    int nb;                // 128-column blocks per row used by the dot
+    int n_sub;             // 32-column sub-blocks that carry data (Q8_0: n_cols/32)
+    int ld_out;
+    int ld_q;              // bytes between tokens in aq
+    int ld_b;              // floats between tokens in ad / asum
+};
+
+// One work item of a batched launch: panel `y` of op `x`.
+typedef int2 DotItem;
+
+// Error plumbing shared by the .cu files.
+void set_error(const char* fmt, ...);
+#define HB_CUDA(expr)                                                                        \
+    do {                                                                                     \
+        cudaError_t _e = (expr);                                                             \
+        if (_e != cudaSuccess) {                                                             \
+            hb200::set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+            return -6; /* HB200_ERR_CUDA */                                                  \
+        }                                                                                    \
+    } while (0)
+
+// ---- launchers implemented in the kernel translation units ----------------
+
+// quantize.cu
+int launch_quantize_q8_0(const float* x, int seq_len, int n_cols, int8_t* q, float* d, float* sums, int ld_q, int ld_b,
+                         uint8_t* raw_out, size_t raw_stride, cudaStream_t st);
+int launch_load_q8_0(const uint8_t* raw, size_t raw_stride, int seq_len, int n_cols, int8_t* q, float* d, float* sums,
+                     int ld_q, int ld_b, cudaStream_t st);
+int launch_store_q8_0(const int8_t* q, const float* d, int ld_q, int ld_b, int seq_len, int n_cols, uint8_t* raw,
+                      size_t raw_stride, cudaStream_t st);
+
+// repack.cu
+int launch_repack(int kind, const uint8_t* raw, size_t row_bytes, int n_rows, int n_cols, int nb, int n_panels,
+                  uint4* bits, void* scales, cudaStream_t st);
+
+// gemv_dp4a.cu
+constexpr int GEMV_MAX_M = 4;  // tokens one dp4a launch handles per op
+// Either an op list in device memory (ops_dev / items_dev / n_items), or, with ops_dev == nullptr, the
+// one op `single` (host memory, passed by value to the grid) whose n_items panels are walked in order.
+int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const DotItem* items_dev, int n_items,
+                     const DotOp* single, int sm_count, cudaStream_t st);
+int gemv_dp4a_prepare();  // sets the dynamic shared-memory attributes once
+
+// kquant.cu
+int launch_kquant_gemv(int kind, const uint8_t* w, size_t row_bytes, int n_rows, int n_cols, const float* x, int seq_len, float* out,
+                       int ld_out, cudaStream_t st);
+int kquant_prepare();
+
+}  // namespace hb200

@@ -1,0 +1,337 @@
+// Decode matvec: every row of a Q1_0 / Q2_0 / Q8_0 weight against M <= 4 Q8_0
+// activations, for a whole list of independent (weight, activation, output)
+// operations in one launch.
+//
+// Replaces the per-row DotFn loop that ThreadPool::par_dot_rows{,_batched}
+// (hearth-llm/src/pool.rs:40-80, :510-618) runs over
+//   dot_q1_0g128_q8_0_ptr  hearth-quant/src/q1_0g128.rs:1000-1053
+//   dot_q2_0_q8_0_ptr      hearth-quant/src/q2_0.rs:537-574, :628-676
+//   dot_q8_0_q8_0_ptr      hearth-quant/src/q8_0.rs:154-171
+// and reproduces their scalar arithmetic bit for bit:
+//   * the int32 dot of every 32-column sub-block is exact;
+//   * block_acc = (((0 + I0*a0) + I1*a1) + I2*a2) + I3*a3, sum += block_acc * w_scale,
+//     blocks in order, every step separately rounded.  I*a is exact in fp32
+//     (|I| <= 2^13, an f16 scale has 11 significant bits), so fmaf(I, a, acc)
+//     rounds exactly as the reference's separate multiply and add do; the
+//     `* w_scale` and the running sum use __fmul_rn / __fadd_rn.
+//
+// Work decomposition (HBM-bound streaming; grid = resident CTAs x SM count).
+//   item  = one panel (32 row groups) of one op; CTAs walk the item list.
+//   lane  = one row group of the panel; all lanes of a warp read the same
+//           128-column block, so activation reads from shared memory are broadcasts.
+//   warp  = one block per round; 8 warps cover 8 consecutive blocks (1024
+//           columns) per round.  Weight pieces for the next round are loaded
+//           into registers (8 x 128-bit, 512 contiguous bytes per warp per
+//           piece) before the current round is computed.
+//   unpack: the byte of a tile word holds RPG rows of one column, so
+//           `word & (mask << r)` isolates row r's code for four columns and a
+//           u8 x s8 dp4a accumulates (code << shift) * a: one LOP3 per dp4a, no
+//           shifts.  The 2^shift factor and the "-sum(a)" term that turn codes
+//           into {-1,+1} / {-1,0,+1,+2} weights are removed exactly when the
+//           sub-block sum is widened to fp32.
+//   order: per-block terms go to shared memory; one thread per (token, row)
+//          adds them in block order, one round behind the producers.
+#include "common.cuh"
+
+namespace hb200 {
+
+namespace {
+
+constexpr int THREADS = 256;
+constexpr int WARPS = 8;
+
+__device__ __forceinline__ int dp4a_u8s8(uint32_t a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp4a_s8s8(uint32_t a, int b, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_wait_all() {
+    asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t comp(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
+__device__ __forceinline__ int compi(const int4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
+
+template <int KIND, int M>
+struct Smem {
+    static constexpr int RPG = rows_per_group(KIND);
+    static constexpr int RP = 32 * RPG;                               // rows per panel
+    static constexpr int TPB = (KIND == KIND_Q8) ? 4 * 32 : RP;      // per-block terms per token
+    // one round: 8 blocks
+    alignas(16) int8_t aq[2][M][1024];
+    alignas(16) float ad[2][M][32];
+    alignas(16) float asum[2][M][32];
+    alignas(16) float term[2][WARPS][M][TPB];
+};
+
+template <int KIND, int M, bool INT_OUT>
+__global__ void __launch_bounds__(THREADS, (M <= 2 ? 2 : 1))
+gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ items, int n_items,
+                 const __grid_constant__ DotOp single) {
+    using S = Smem<KIND, M>;
+    constexpr int RPG = S::RPG;
+    constexpr int RP = S::RP;
+    constexpr int NRUN = (M * RP + THREADS - 1) / THREADS;  // running sums per thread
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    S& sm = *reinterpret_cast<S*>(smem_raw);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    for (int it = blockIdx.x; it < n_items; it += gridDim.x) {
+        // A list launch reads (op, panel) pairs; a single-op launch walks the panels of `single`.
+        const DotOp op = ops ? ops[items[it].x] : single;
+        const int panel = ops ? items[it].y : it;
+        const int nb = op.nb;
+        const int rounds = (nb + WARPS - 1) / WARPS;
+
+        // Stage the activation columns of round r into buffer r&1 (cp.async, 16 B each).
+        auto stage = [&](int r) {
+            const int buf = r & 1;
+            for (int idx = tid; idx < 80 * M; idx += THREADS) {
+                const int m = idx / 80, p = idx % 80;
+                if (p < 64)
+                    cp_async16(&sm.aq[buf][m][p * 16], op.aq + (size_t)m * op.ld_q + (size_t)r * 1024 + p * 16);
+                else if (p < 72)
+                    cp_async16(&sm.ad[buf][m][(p - 64) * 4], op.ad + (size_t)m * op.ld_b + r * 32 + (p - 64) * 4);
+                else
+                    cp_async16(&sm.asum[buf][m][(p - 72) * 4], op.asum + (size_t)m * op.ld_b + r * 32 + (p - 72) * 4);
+            }
+        };
+
+        uint4 wn[8];   // weight pieces of the next round
+        uint4 wsn;     // its scales (Q1_0: 8 f16; Q2_0 / Q8_0: 4 f16 in .x .y)
+        auto load_w = [&](int r) {
+            const int blk = r * WARPS + warp;
+            if (blk < nb) {
+                const size_t tile = (size_t)panel * nb + blk;
+                const uint4* p = op.bits + tile * 256 + lane;
+#pragma unroll
+                for (int i = 0; i < 8; i++) wn[i] = __ldg(p + i * 32);
+                if (KIND == KIND_Q1) {
+                    wsn = __ldg(reinterpret_cast<const uint4*>(op.scales) + tile * 32 + lane);
+                } else {
+                    const uint2 s2 = __ldg(reinterpret_cast<const uint2*>(op.scales) + tile * 32 + lane);
+                    wsn = make_uint4(s2.x, s2.y, 0u, 0u);
+                }
+            }
+        };
+
+        float run[NRUN];
+#pragma unroll
+        for (int k = 0; k < NRUN; k++) run[k] = 0.0f;
+
+        // Adds the terms of round r (buffer r&1) to the running sums, in block order.
+        auto replay = [&](int r) {
+            const int buf = r & 1;
+            const int nvalid = min(WARPS, nb - r * WARPS);
+#pragma unroll
+            for (int k = 0; k < NRUN; k++) {
+                const int idx = tid + k * THREADS;
+                if (idx < M * RP) {
+                    const int m = idx / RP, row = idx % RP;
+                    float acc = run[k];
+                    if (KIND == KIND_Q8) {
+                        const int nsub = min(4 * nvalid, op.n_sub - r * WARPS * 4);
+                        for (int sb = 0; sb < nsub; sb++)
+                            acc = __fadd_rn(acc, sm.term[buf][sb >> 2][m][(sb & 3) * 32 + row]);
+                    } else {
+                        for (int b = 0; b < nvalid; b++) acc = __fadd_rn(acc, sm.term[buf][b][m][row]);
+                    }
+                    run[k] = acc;
+                }
+            }
+        };
+
+        __syncthreads();  // previous item's shared memory is no longer read
+        stage(0);
+        load_w(0);
+
+        for (int r = 0; r < rounds; r++) {
+            cp_async_commit_wait_all();
+            __syncthreads();  // activations of round r landed; terms of round r-1 visible
+            uint4 w[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) w[i] = wn[i];
+            const uint4 ws = wsn;
+            if (r + 1 < rounds) {
+                stage(r + 1);
+                load_w(r + 1);
+            }
+            if (!INT_OUT && r > 0) replay(r - 1);
+
+            const int buf = r & 1;
+            const int blk = r * WARPS + warp;
+            if (blk < nb) {
+                float bacc[M][RPG];
+#pragma unroll
+                for (int m = 0; m < M; m++)
+#pragma unroll
+                    for (int g = 0; g < RPG; g++) bacc[m][g] = 0.0f;
+
+#pragma unroll
+                for (int s = 0; s < 4; s++) {
+                    int acc[M][RPG];
+#pragma unroll
+                    for (int m = 0; m < M; m++)
+#pragma unroll
+                        for (int g = 0; g < RPG; g++) acc[m][g] = 0;
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        int4 a4[M];
+#pragma unroll
+                        for (int m = 0; m < M; m++)
+                            a4[m] = *reinterpret_cast<const int4*>(&sm.aq[buf][m][warp * 128 + s * 32 + h * 16]);
+#pragma unroll
+                        for (int jj = 0; jj < 4; jj++) {
+                            const int j = 4 * h + jj;                  // word of the sub-block: columns 4j..4j+3
+                            const int q = (j >> 1) * 8 + s * 2 + (j & 1);  // its position in the tile
+                            const uint32_t word = comp(w[q >> 2], q & 3);
+#pragma unroll
+                            for (int g = 0; g < RPG; g++) {
+                                uint32_t msk;
+                                if (KIND == KIND_Q1) msk = word & (0x01010101u << g);
+                                else if (KIND == KIND_Q2) msk = word & (0x03030303u << (2 * g));
+                                else msk = word;
+#pragma unroll
+                                for (int m = 0; m < M; m++) {
+                                    if (KIND == KIND_Q8) acc[m][g] = dp4a_s8s8(msk, compi(a4[m], jj), acc[m][g]);
+                                    else acc[m][g] = dp4a_u8s8(msk, compi(a4[m], jj), acc[m][g]);
+                                }
+                            }
+                        }
+                    }
+                    // Widen the sub-block sums.
+#pragma unroll
+                    for (int m = 0; m < M; m++) {
+                        const float a_d = sm.ad[buf][m][warp * 4 + s];
+                        const float a_sum = sm.asum[buf][m][warp * 4 + s];
+#pragma unroll
+                        for (int g = 0; g < RPG; g++) {
+                            if (INT_OUT) {
+                                int iv;
+                                if (KIND == KIND_Q1) iv = ((acc[m][g] << 1) >> g) - (int)a_sum;  // 2*S1 - sum(a)
+                                else if (KIND == KIND_Q2) iv = (acc[m][g] >> (2 * g)) - (int)a_sum;  // S_code - sum(a)
+                                else iv = acc[m][g];
+                                const int row = panel * RP + lane * RPG + g;
+                                if (row < op.n_rows && blk * 4 + s < op.n_sub)
+                                    op.iout[((size_t)m * op.n_rows + row) * op.n_sub + blk * 4 + s] = iv;
+                            } else if (KIND == KIND_Q8) {
+                                const float wd = __half2float(__ushort_as_half(
+                                    (unsigned short)((s < 2 ? ws.x : ws.y) >> (16 * (s & 1)))));
+                                // ((float)sumi * d_w) * d_a, each product rounded (q8_0.rs:169)
+                                sm.term[buf][warp][m][s * 32 + lane] =
+                                    __fmul_rn(__fmul_rn((float)acc[m][g], wd), a_d);
+                            } else {
+                                // exact integer I as fp32, then block_acc += I * a_scale (exact product, one rounding)
+                                const float c = (KIND == KIND_Q1) ? (2.0f / (float)(1 << g)) : (1.0f / (float)(1 << (2 * g)));
+                                const float i_f = fmaf((float)acc[m][g], c, -a_sum);
+                                bacc[m][g] = fmaf(i_f, a_d, bacc[m][g]);
+                            }
+                        }
+                    }
+                }
+                if (!INT_OUT && KIND != KIND_Q8) {
+#pragma unroll
+                    for (int g = 0; g < RPG; g++) {
+                        const uint32_t pair = (g < 2) ? ws.x : (g < 4 ? ws.y : (g < 6 ? ws.z : ws.w));
+                        const float wd = __half2float(__ushort_as_half((unsigned short)(pair >> (16 * (g & 1)))));
+#pragma unroll
+                        for (int m = 0; m < M; m++) sm.term[buf][warp][m][lane * RPG + g] = __fmul_rn(bacc[m][g], wd);
+                    }
+                }
+            }
+        }
+        if (!INT_OUT) {
+            __syncthreads();
+            if (rounds > 0) replay(rounds - 1);
+#pragma unroll
+            for (int k = 0; k < NRUN; k++) {
+                const int idx = tid + k * THREADS;
+                if (idx < M * RP) {
+                    const int m = idx / RP, row = panel * RP + idx % RP;
+                    if (row < op.n_rows) op.out[(size_t)m * op.ld_out + row] = run[k];
+                }
+            }
+        }
+    }
+}
+
+template <int KIND, int M, bool INT_OUT>
+int launch_one(const DotOp* ops, const DotItem* items, int n_items, const DotOp& single, int sm_count, cudaStream_t st) {
+    using S = Smem<KIND, M>;
+    const int per_sm = (M <= 2) ? 2 : 1;
+    int grid = sm_count * per_sm;
+    if (grid > n_items) grid = n_items;
+    if (grid <= 0) return 0;
+    gemv_dp4a_kernel<KIND, M, INT_OUT><<<grid, THREADS, sizeof(S), st>>>(ops, items, n_items, single);
+    HB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <int KIND, int M, bool INT_OUT>
+int prepare_one() {
+    using S = Smem<KIND, M>;
+    HB_CUDA(cudaFuncSetAttribute(gemv_dp4a_kernel<KIND, M, INT_OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)sizeof(S)));
+    return 0;
+}
+
+template <int KIND>
+int launch_kind(int m, bool int_out, const DotOp* ops, const DotItem* items, int n_items, const DotOp& single, int sm_count,
+                cudaStream_t st) {
+    if (int_out) {
+        if (m != 1) { set_error("integer block-dot output runs one token per launch"); return -4; }
+        return launch_one<KIND, 1, true>(ops, items, n_items, single, sm_count, st);
+    }
+    switch (m) {
+        case 1: return launch_one<KIND, 1, false>(ops, items, n_items, single, sm_count, st);
+        case 2: return launch_one<KIND, 2, false>(ops, items, n_items, single, sm_count, st);
+        case 3: return launch_one<KIND, 3, false>(ops, items, n_items, single, sm_count, st);
+        case 4: return launch_one<KIND, 4, false>(ops, items, n_items, single, sm_count, st);
+        default: set_error("gemv_dp4a: m=%d outside 1..%d", m, GEMV_MAX_M); return -4;
+    }
+}
+
+template <int KIND>
+int prepare_kind() {
+    int rc;
+    if ((rc = prepare_one<KIND, 1, true>())) return rc;
+    if ((rc = prepare_one<KIND, 1, false>())) return rc;
+    if ((rc = prepare_one<KIND, 2, false>())) return rc;
+    if ((rc = prepare_one<KIND, 3, false>())) return rc;
+    if ((rc = prepare_one<KIND, 4, false>())) return rc;
+    return 0;
+}
+
+}  // namespace
+
+int gemv_dp4a_prepare() {
+    int rc;
+    if ((rc = prepare_kind<KIND_Q1>())) return rc;
+    if ((rc = prepare_kind<KIND_Q2>())) return rc;
+    if ((rc = prepare_kind<KIND_Q8>())) return rc;
+    return 0;
+}
+
+int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const DotItem* items_dev, int n_items,
+                     const DotOp* single, int sm_count, cudaStream_t st) {
+    static const DotOp none = {};
+    const DotOp& one = single ? *single : none;
+    if (!ops_dev && !single) { set_error("gemv_dp4a: neither an op list nor a single op"); return -5; }
+    switch (kind) {
+        case KIND_Q1: return launch_kind<KIND_Q1>(m, int_out, ops_dev, items_dev, n_items, one, sm_count, st);
+        case KIND_Q2: return launch_kind<KIND_Q2>(m, int_out, ops_dev, items_dev, n_items, one, sm_count, st);
+        case KIND_Q8: return launch_kind<KIND_Q8>(m, int_out, ops_dev, items_dev, n_items, one, sm_count, st);
+        default: set_error("gemv_dp4a: kind %d has no Q8_0 dot", kind); return -7;
+    }
+}
+
+}  // namespace hb200

@@ -1,0 +1,99 @@
+"""ctypes loader for libhearth_b200.so (the C ABI declared in include/hb200.h).
+
+There is no fallback of any kind: if the shared object is missing or a symbol
+cannot be bound, import fails with an explicit message.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libhearth_b200.so")
+
+# GGML type ids on this path (hearth-gguf/src/ggml.rs:49-101 of the reference).
+Q8_0, Q4_K, Q6_K, Q1_0_G128_LEGACY, Q1_0, Q2_0, Q1_0_G128, PQ2_0 = 8, 12, 14, 39, 41, 42, 43, 142
+
+STATUS = {
+    0: "HB200_OK", -1: "HB200_ERR_NOT_INITIALIZED", -2: "HB200_ERR_NO_DEVICE", -3: "HB200_ERR_BAD_DTYPE",
+    -4: "HB200_ERR_BAD_SHAPE", -5: "HB200_ERR_NULL", -6: "HB200_ERR_CUDA", -7: "HB200_ERR_UNSUPPORTED",
+    -8: "HB200_ERR_TOO_LARGE", -9: "HB200_ERR_TIMEOUT",
+}
+
+_vp = C.c_void_p
+_sz = C.c_size_t
+_int = C.c_int
+
+# name -> (restype, argtypes); must list every symbol include/hb200.h declares.
+SIGNATURES = {
+    "hb200_init": (_int, [_int]),
+    "hb200_shutdown": (_int, []),
+    "hb200_last_error": (C.c_char_p, []),
+    "hb200_sm_count": (_int, []),
+    "hb200_block_size": (_sz, [_int]),
+    "hb200_block_bytes": (_sz, [_int]),
+    "hb200_byte_size": (_sz, [_int, _sz]),
+    "hb200_selected_kernel": (C.c_char_p, [_int, _sz]),
+    "hb200_weight_upload": (_int, [_int, _sz, _sz, _vp, _sz, C.POINTER(_vp)]),
+    "hb200_weight_upload_dev": (_int, [_int, _sz, _sz, _vp, _sz, _vp, C.POINTER(_vp)]),
+    "hb200_weight_upload_rows": (_int, [_int, _sz, _sz, _vp, _sz, _sz, _sz, C.POINTER(_vp)]),
+    "hb200_weight_free": (_int, [_vp]),
+    "hb200_weight_info": (_int, [_vp, C.POINTER(_int), C.POINTER(_sz), C.POINTER(_sz), C.POINTER(_sz)]),
+    "hb200_act_create": (_int, [_sz, _sz, C.POINTER(_vp)]),
+    "hb200_act_free": (_int, [_vp]),
+    "hb200_act_f32_ptr": (_int, [_vp, C.POINTER(_vp)]),
+    "hb200_act_q8_planes": (_int, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_sz), C.POINTER(_sz)]),
+    "hb200_act_quantize_dev": (_int, [_vp, _vp, _sz, _vp]),
+    "hb200_act_load_q8_0_dev": (_int, [_vp, _vp, _sz, _sz, _vp]),
+    "hb200_act_store_q8_0_dev": (_int, [_vp, _vp, _sz, _sz, _vp]),
+    "hb200_quantize_q8_0": (_int, [_vp, _sz, _sz, _vp]),
+    "hb200_dot_rows": (_int, [_vp, _vp, _vp]),
+    "hb200_dot_rows_batched": (_int, [_vp, _vp, _sz, _sz, _vp]),
+    "hb200_matmul_f32": (_int, [_vp, _vp, _sz, _vp]),
+    "hb200_block_dots_i32": (_int, [_vp, _vp, _sz, _sz, _vp]),
+    "hb200_dot_rows_dev": (_int, [_vp, _vp, _sz, _vp, _sz, _vp]),
+    "hb200_matmul_f32_dev": (_int, [_vp, _vp, _sz, _vp, _sz, _vp]),
+    "hb200_batch_create": (_int, [C.POINTER(_vp)]),
+    "hb200_batch_add": (_int, [_vp, _vp, _vp, _sz, _vp, _sz]),
+    "hb200_batch_seal": (_int, [_vp]),
+    "hb200_batch_launch": (_int, [_vp, _vp]),
+    "hb200_batch_free": (_int, [_vp]),
+    "hb200_batch_launch_count": (_int, [_vp]),
+    "hb200_stream_synchronize": (_int, [_vp]),
+}
+
+
+class Hb200Error(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"{STATUS.get(code, code)}: {message}")
+        self.code = code
+        self.message = message
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the library and bind every declared symbol; raises if anything is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m hearth_b200.build` (nvcc, sm_100a). "
+            "There is no CPU or PyTorch fallback for this path.")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as e:
+            raise ImportError(f"{LIB_PATH} does not export {name}") from e
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(code: int) -> None:
+    if code != 0:
+        raise Hb200Error(code, load().hb200_last_error().decode("utf-8", "replace"))

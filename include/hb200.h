@@ -1,0 +1,200 @@
+/*
+ * hb200.h -- C ABI of the B200 (sm_100a) quantized matrix-product path for Hearth.
+ *
+ * Drop-in boundary for one path of Eric-Lautanen/hearth v0.2.0: the Q8_0
+ * activation quantizer, the Q1_0 / Q2_0 / PQ2_0 / Q8_0 x Q8_0 block-dot
+ * matvec / matmul, the Q4_K / Q6_K x f32 matvec, and the row dispatch around
+ * them.  Every entry point names the reference interface it replaces
+ * (path:line inside the reference repository).
+ *
+ * Conventions
+ *   - Plain C types only.  Every function returns HB200_OK (0) or a negative
+ *     hb200_status; hb200_last_error() gives the message of the calling
+ *     thread's last failure.  Nothing throws or aborts across this boundary.
+ *   - Calls are synchronous unless the name ends in _dev / _launch (those
+ *     enqueue on the given CUDA stream and return).  Like the reference's
+ *     ThreadPool (one shared WorkParams slot, hearth-llm/src/pool.rs:230-231)
+ *     a context is not re-entrant: serialise calls per context.
+ *   - Weights are uploaded once and stay resident, the residency model of
+ *     hearth_compute::GpuCompute (hearth-compute/src/lib.rs:104, :239;
+ *     hearth-llm/src/model/gpu.rs:8-49).  The caller keeps ownership of every
+ *     host buffer; the library only reads / writes it during the call.
+ *   - There is no CPU fallback: without a usable sm_100 device hb200_init
+ *     fails and every other call returns HB200_ERR_NOT_INITIALIZED.
+ *   - Activation layout is the reference's: f32 row-major [seq_len][n_cols];
+ *     Q8_0 rows of ceil(n_cols/32) blocks [f16 d][32 x i8] at a byte stride
+ *     (q8_stride); outputs token-major out[s * n_rows + row]
+ *     (hearth-llm/src/pool.rs:36, :63-64, :73).
+ */
+#ifndef HB200_H
+#define HB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define HB200_API __attribute__((visibility("default")))
+#else
+#define HB200_API
+#endif
+
+typedef enum hb200_status {
+    HB200_OK = 0,
+    HB200_ERR_NOT_INITIALIZED = -1,
+    HB200_ERR_NO_DEVICE = -2,      /* no CUDA device, or not compute capability 10.x */
+    HB200_ERR_BAD_DTYPE = -3,      /* GGML type id outside this path */
+    HB200_ERR_BAD_SHAPE = -4,      /* size / stride / byte-count mismatch */
+    HB200_ERR_NULL = -5,           /* null pointer or handle */
+    HB200_ERR_CUDA = -6,           /* a CUDA runtime call failed; see hb200_last_error */
+    HB200_ERR_UNSUPPORTED = -7,    /* valid request this build has no kernel for */
+    HB200_ERR_TOO_LARGE = -8,      /* exceeds a stated fixed capacity */
+    HB200_ERR_TIMEOUT = -9         /* a bounded device-side wait ran out */
+} hb200_status;
+
+/* GGML type ids accepted, as the reference parses them
+ * (hearth-gguf/src/ggml.rs:49-101). */
+enum {
+    HB200_Q8_0 = 8,
+    HB200_Q4_K = 12,
+    HB200_Q6_K = 14,
+    HB200_Q1_0_G128_LEGACY = 39,
+    HB200_Q1_0 = 41,
+    HB200_Q2_0 = 42,
+    HB200_Q1_0_G128 = 43,
+    HB200_PQ2_0 = 142
+};
+
+typedef struct hb200_weight *hb200_weight_t; /* resident weight matrix */
+typedef struct hb200_act *hb200_act_t;       /* resident activation (f32 and Q8_0 forms) */
+typedef struct hb200_batch *hb200_batch_t;   /* recorded list of dot-row ops, one launch */
+
+/* ---- lifecycle ---------------------------------------------------------- */
+
+/* Replaces GpuCompute::new() (hearth-compute/src/lib.rs:127-184): binds the
+ * calling process to CUDA device `device`.  Idempotent for the same device. */
+HB200_API int hb200_init(int device);
+HB200_API int hb200_shutdown(void);
+HB200_API const char *hb200_last_error(void);
+/* Number of streaming multiprocessors of the bound device (sizing of grids). */
+HB200_API int hb200_sm_count(void);
+
+/* ---- block geometry ----------------------------------------------------- */
+
+/* GgmlDType::block_size / block_bytes / byte_size
+ * (hearth-gguf/src/ggml.rs:105-176).  0 for a dtype outside this path. */
+HB200_API size_t hb200_block_size(int dtype);
+HB200_API size_t hb200_block_bytes(int dtype);
+HB200_API size_t hb200_byte_size(int dtype, size_t n_cols);
+
+/* hearth_quant::selected_kernel (hearth-quant/src/lib.rs:411-418): name of the
+ * CUDA kernel variant that serves (dtype, seq_len); "none" if unsupported. */
+HB200_API const char *hb200_selected_kernel(int dtype, size_t seq_len);
+
+/* ---- weights ------------------------------------------------------------ */
+
+/* Replaces GpuCompute::upload_bytes (hearth-compute/src/lib.rs:239) for a
+ * weight tensor: `packed` is the reference's row-major block stream,
+ * n_rows * byte_size(dtype, n_cols) bytes (TensorEntry::data,
+ * hearth-llm/src/model/tensor.rs:11-55).  The bytes are re-tiled once on the
+ * device; the same number of bytes stays resident.  `packed` is host memory. */
+HB200_API int hb200_weight_upload(int dtype, size_t n_rows, size_t n_cols, const uint8_t *packed, size_t bytes,
+                                  hb200_weight_t *out);
+/* Same, with `packed_dev` already in device memory (read on `stream`). */
+HB200_API int hb200_weight_upload_dev(int dtype, size_t n_rows, size_t n_cols, const uint8_t *packed_dev, size_t bytes,
+                                      void *stream, hb200_weight_t *out);
+/* Rows [row_begin, row_end) only: the row split of pool.rs:321-323 applied
+ * across GPUs instead of worker threads.  `packed` is the whole tensor. */
+HB200_API int hb200_weight_upload_rows(int dtype, size_t n_rows, size_t n_cols, const uint8_t *packed, size_t bytes,
+                                       size_t row_begin, size_t row_end, hb200_weight_t *out);
+HB200_API int hb200_weight_free(hb200_weight_t w);
+HB200_API int hb200_weight_info(hb200_weight_t w, int *dtype, size_t *n_rows, size_t *n_cols, size_t *resident_bytes);
+
+/* ---- activations -------------------------------------------------------- */
+
+/* A resident activation: up to max_seq_len rows of n_cols values. */
+HB200_API int hb200_act_create(size_t max_seq_len, size_t n_cols, hb200_act_t *out);
+HB200_API int hb200_act_free(hb200_act_t a);
+/* Device address of the f32 [max_seq_len][n_cols] staging area of `a`. */
+HB200_API int hb200_act_f32_ptr(hb200_act_t a, float **dev_ptr);
+/* Device addresses of the Q8_0 planes of `a`: int8 values [seq][ld_q],
+ * f32 block scales [seq][ld_b] (each an f16 value widened), f32 block sums. */
+HB200_API int hb200_act_q8_planes(hb200_act_t a, int8_t **q, float **d, float **sums, size_t *ld_q, size_t *ld_b);
+
+/* ThreadPool::par_quantize (hearth-llm/src/pool.rs:467-508) /
+ * quantize_q8_0_into (hearth-quant/src/q8_0.rs:20-51) on the device: reads
+ * f32 [seq_len][n_cols] at x_dev (or the act's own f32 area if x_dev is null)
+ * and fills the Q8_0 planes of `a`. */
+HB200_API int hb200_act_quantize_dev(hb200_act_t a, const float *x_dev, size_t seq_len, void *stream);
+/* Loads caller-made Q8_0 rows (reference byte layout, device memory) into `a`. */
+HB200_API int hb200_act_load_q8_0_dev(hb200_act_t a, const uint8_t *q8_dev, size_t seq_len, size_t q8_stride,
+                                      void *stream);
+/* Writes the Q8_0 planes of `a` back out in the reference byte layout. */
+HB200_API int hb200_act_store_q8_0_dev(hb200_act_t a, uint8_t *q8_dev, size_t seq_len, size_t q8_stride, void *stream);
+
+/* ---- host-buffer calls (the reference's own call shapes) ---------------- */
+
+/* quantize_q8_0_into / par_quantize with host buffers
+ * (hearth-quant/src/lib.rs:381-387, hearth-llm/src/pool.rs:467).  q8_out gets
+ * seq_len rows of ceil(dim/32)*34 bytes. */
+HB200_API int hb200_quantize_q8_0(const float *x, size_t seq_len, size_t dim, uint8_t *q8_out);
+
+/* ThreadPool::par_dot_rows(DotRowsParams) (pool.rs:246-257, :510-566): every
+ * row of `w` against one Q8_0 activation; out[n_rows]. */
+HB200_API int hb200_dot_rows(hb200_weight_t w, const uint8_t *a_q8, float *out);
+
+/* ThreadPool::par_dot_rows_batched(BatchedDotRowsParams) (pool.rs:259-272,
+ * :568-618): seq_len activations at byte stride q8_stride; out token-major
+ * [seq_len][n_rows]. */
+HB200_API int hb200_dot_rows_batched(hb200_weight_t w, const uint8_t *a_q8, size_t seq_len, size_t q8_stride,
+                                     float *out);
+
+/* LlamaModel::matmul / matmul_batch with x_q8 = None
+ * (hearth-llm/src/model/matmul.rs:50-378, :580-674): quantizes x when the
+ * weight's kernel wants Q8_0 (quantize_act :569-573), uses f32 x for
+ * Q4_K / Q6_K (:270-280, :333-343).  x is [seq_len][n_cols]; out token-major. */
+HB200_API int hb200_matmul_f32(hb200_weight_t w, const float *x, size_t seq_len, float *out);
+
+/* Per-(row, token, 32-block) int32 dots, out[seq_len][n_rows][n_cols/32]:
+ * the `dot` / `sumi` integers of q1_0g128.rs:1033-1047, q2_0.rs:553-568,
+ * q8_0.rs:164-168, exposed so the integer path can be checked bit for bit. */
+HB200_API int hb200_block_dots_i32(hb200_weight_t w, const uint8_t *a_q8, size_t seq_len, size_t q8_stride,
+                                   int32_t *out);
+
+/* ---- device-buffer calls ------------------------------------------------ */
+
+/* par_dot_rows / par_dot_rows_batched with everything resident: `a` holds
+ * seq_len quantized rows, out_dev is f32 [seq_len][ld_out] with
+ * ld_out >= n_rows (ld_out > n_rows lets several matrices that share an input
+ * write one buffer, as matmul_fused_qkv / matmul_fused2 do,
+ * hearth-llm/src/model/matmul.rs:383-567). */
+HB200_API int hb200_dot_rows_dev(hb200_weight_t w, hb200_act_t a, size_t seq_len, float *out_dev, size_t ld_out,
+                                 void *stream);
+/* matmul / matmul_batch for f32 input resident in `a`'s f32 area. */
+HB200_API int hb200_matmul_f32_dev(hb200_weight_t w, hb200_act_t a, size_t seq_len, float *out_dev, size_t ld_out,
+                                   void *stream);
+
+/* ---- recorded batches --------------------------------------------------- */
+
+/* GpuCompute::begin_batch / end_batch (hearth-compute/src/lib.rs:206-224)
+ * record many ops and submit them together.  Here: add independent dot-row
+ * ops, seal once, then launch the whole list as one grid per launch call. */
+HB200_API int hb200_batch_create(hb200_batch_t *out);
+HB200_API int hb200_batch_add(hb200_batch_t b, hb200_weight_t w, hb200_act_t a, size_t seq_len, float *out_dev,
+                              size_t ld_out);
+HB200_API int hb200_batch_seal(hb200_batch_t b);
+HB200_API int hb200_batch_launch(hb200_batch_t b, void *stream);
+HB200_API int hb200_batch_free(hb200_batch_t b);
+/* Number of kernel launches one hb200_batch_launch performs. */
+HB200_API int hb200_batch_launch_count(hb200_batch_t b);
+
+/* ---- stream helper ------------------------------------------------------ */
+HB200_API int hb200_stream_synchronize(void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HB200_H */
