@@ -251,7 +251,7 @@ def run_ours(args, cfg, rank, world, local_rank):
     # An untimed burst of the same steps first, so that the clock sampler (100 ms period) has samples
     # under load on both sides of the timed region; rank 0 decides when it ends.
     burst = 0
-    while burst < 4000:
+    while burst < 4000 and not args.quick:
         step()
         burst += 1
         if burst % 50 == 0:
@@ -269,7 +269,7 @@ def run_ours(args, cfg, rank, world, local_rank):
     e1.record(stream)
     barrier()
     ms = e0.elapsed_time(e1)
-    for _ in range(50):
+    for _ in range(0 if args.quick else 50):
         step()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -282,7 +282,7 @@ def run_ours(args, cfg, rank, world, local_rank):
 
     # ---- end to end through the host-buffer entry point (rank-local inputs and outputs, pinned memory)
     e2e_ms, h2d, d2h = None, 0, 0
-    if M <= 4:
+    if M <= 4 and not args.quick:
         hosts_out = [torch.zeros((M, W.n_rows), dtype=torch.float32).pin_memory() for W, _ in weights]
         xs = [x_host[k].numpy() for _, _, k in cfg["shapes"]] * cfg["layers"]
         outs_np = [o.numpy() for o in hosts_out]
@@ -335,7 +335,7 @@ def run_ours(args, cfg, rank, world, local_rank):
             "e2e": ({"value": ab["weights"] / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                      "ms_per_step": e2e_ms, "call": "hb200_matmul_f32 per matrix, pinned host buffers"} if e2e_ms else None),
         }
-        if world == 1 and not args.no_cpu:
+        if world == 1 and not args.no_cpu and not args.quick:
             arm = CpuArm(cfg, 0, 1)
             t0 = time.perf_counter()
             best = arm.gbs(2)
@@ -357,6 +357,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(synth.CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--quick", action="store_true",
+                    help="kernel timing only: no clock-sampling burst, no end-to-end leg, no CPU leg (for profiler runs)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -126,14 +126,16 @@ __global__ void __launch_bounds__(256) store_q8_0_kernel(const int8_t* __restric
     if (blk * 32 >= n_cols) return;
     uint8_t* rb = raw + (size_t)m * raw_stride + (size_t)blk * 34;
     const uint32_t word = *reinterpret_cast<const uint32_t*>(q + (size_t)m * ld_q + c0);
-    const int i0 = (threadIdx.x & 7) * 4;
-#pragma unroll
-    for (int i = 0; i < 4; i++) rb[2 + i0 + i] = (uint8_t)(word >> (8 * i));
+    const uint32_t hbits = __half_as_ushort(__float2half_rn(d[(size_t)m * ld_b + blk]));
     if ((threadIdx.x & 7) == 0) {
-        const unsigned short hb = __half_as_ushort(__float2half_rn(d[(size_t)m * ld_b + blk]));
-        rb[0] = (uint8_t)(hb & 0xff);
-        rb[1] = (uint8_t)(hb >> 8);
+        rb[0] = (uint8_t)(hbits & 0xffu);
+        rb[1] = (uint8_t)((hbits >> 8) & 0xffu);
     }
+    uint8_t* vals = rb + 2 + (threadIdx.x & 7) * 4;
+    vals[0] = (uint8_t)(word & 0xffu);
+    vals[1] = (uint8_t)((word >> 8) & 0xffu);
+    vals[2] = (uint8_t)((word >> 16) & 0xffu);
+    vals[3] = (uint8_t)(word >> 24);
 }
 
 }  // namespace
