@@ -224,6 +224,14 @@ def matmul_f32_dev(w: Weight, a: Act, seq_len: int, out_dev, ld_out: int | None 
                                          ld_out if ld_out is not None else w.n_rows, _stream_ptr(stream)))
 
 
+def matmul_f32_noalloc(w: Weight, x_dev, out_dev, ld_out: int | None = None, stream=None) -> None:
+    """hb200_matmul_f32_noalloc: x_dev is a torch CUDA f32 tensor [seq_len, n_cols] owned by the caller; the
+    call allocates nothing on the device (at most 4 tokens of 32768 columns)."""
+    seq_len = 1 if x_dev.dim() == 1 else x_dev.shape[0]
+    check(_l.load().hb200_matmul_f32_noalloc(w._h, C.c_void_p(x_dev.data_ptr()), seq_len, C.c_void_p(out_dev.data_ptr()),
+                                             ld_out if ld_out is not None else w.n_rows, _stream_ptr(stream)))
+
+
 class Batch:
     """begin_batch / end_batch (hearth-compute/src/lib.rs:206-224): record ops, launch them together."""
 

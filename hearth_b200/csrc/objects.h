@@ -1,0 +1,27 @@
+// Definitions of the opaque handles of include/hb200.h, shared by the host-layer translation units.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+struct hb200_weight {
+    int dtype = 0, kind = hb200::KIND_NONE;
+    size_t n_rows = 0, n_cols = 0;
+    size_t row_bytes = 0;  // of the reference layout
+    int nb = 0, n_panels = 0, n_sub = 0;
+    uint4* bits = nullptr;   // panel layout (Q1_0 / Q2_0 / Q8_0)
+    void* scales = nullptr;
+    uint8_t* raw = nullptr;  // reference layout (Q4_K / Q6_K)
+    size_t resident_bytes = 0;
+};
+
+struct hb200_act {
+    size_t max_seq = 0, n_cols = 0;
+    int ld_q = 0, ld_b = 0;
+    float* x = nullptr;
+    int8_t* q = nullptr;
+    float* d = nullptr;
+    float* sums = nullptr;
+};
+

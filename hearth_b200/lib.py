@@ -53,6 +53,7 @@ SIGNATURES = {
     "hb200_block_dots_i32": (_int, [_vp, _vp, _sz, _sz, _vp]),
     "hb200_dot_rows_dev": (_int, [_vp, _vp, _sz, _vp, _sz, _vp]),
     "hb200_matmul_f32_dev": (_int, [_vp, _vp, _sz, _vp, _sz, _vp]),
+    "hb200_matmul_f32_noalloc": (_int, [_vp, _vp, _sz, _vp, _sz, _vp]),
     "hb200_batch_create": (_int, [C.POINTER(_vp)]),
     "hb200_batch_add": (_int, [_vp, _vp, _vp, _sz, _vp, _sz]),
     "hb200_batch_seal": (_int, [_vp]),

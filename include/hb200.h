@@ -177,6 +177,27 @@ HB200_API int hb200_dot_rows_dev(hb200_weight_t w, hb200_act_t a, size_t seq_len
 HB200_API int hb200_matmul_f32_dev(hb200_weight_t w, hb200_act_t a, size_t seq_len, float *out_dev, size_t ld_out,
                                    void *stream);
 
+/* matmul for callers that cannot allocate device memory.  No counterpart in the
+ * reference: it exists for hosts that have given all device memory to another
+ * owner (a pre-sized KV cache, a caching allocator holding the whole card) or
+ * that cannot take the device-wide synchronisation of cudaMalloc / cudaFree in
+ * the middle of a decode loop.  Same result as hb200_matmul_f32_dev, but x_dev
+ * is the caller's own f32 [seq_len][n_cols] device buffer and the quantized
+ * activation lives in a fixed array inside the library's device image
+ * (160 KiB, held by every GPU that loads the library until the process ends).
+ * Limits: seq_len <= HB200_NOALLOC_MAX_TOKENS and n_cols <=
+ * HB200_NOALLOC_MAX_COLS, otherwise HB200_ERR_TOO_LARGE.  The call itself
+ * allocates and frees nothing.  The first call on a device resolves the
+ * array's device address (cudaGetSymbolAddress); make that first call before
+ * starting any stream capture.  All calls share the one array and it keeps the
+ * previous call's contents: every call rewrites the part it reads, but two
+ * calls whose kernels overlap on the GPU (different streams, no ordering)
+ * race on it.  Serialise them. */
+#define HB200_NOALLOC_MAX_TOKENS 4
+#define HB200_NOALLOC_MAX_COLS 32768
+HB200_API int hb200_matmul_f32_noalloc(hb200_weight_t w, const float *x_dev, size_t seq_len, float *out_dev,
+                                       size_t ld_out, void *stream);
+
 /* ---- recorded batches --------------------------------------------------- */
 
 /* GpuCompute::begin_batch / end_batch (hearth-compute/src/lib.rs:206-224)
