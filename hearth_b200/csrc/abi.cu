@@ -8,6 +8,8 @@
 //   GpuCompute residency and begin_batch/end_batch                 hearth-compute/src/lib.rs:104, :206-251
 // Errors never cross the boundary as exceptions: every entry point is
 // wrapped in a catch-all and returns a status code.
+#include <cuda.h>
+
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -68,6 +70,7 @@ struct hb200_batch {
     std::vector<BatchEntry> entries;
     std::vector<BatchGroup> groups;
     std::vector<BatchEntry> kquant;  // K-quant ops launch on their own
+    std::vector<BatchEntry> tensor;  // ops with five or more tokens: tensor-core kernel, one launch each
     bool sealed = false;
 };
 
@@ -84,8 +87,30 @@ struct Context {
     uint8_t* d_out = nullptr;
     size_t d_out_bytes = 0;
     hb200_act_t act = nullptr;
+    int* d_status = nullptr;  // device word set by kernels whose bounded waits expire
 };
 Context g_ctx;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+
+// Tensor map over an activation's int8 plane: [max_seq rows][ld_q bytes], box 128 rows x 128 bytes, 128-byte swizzle.
+int encode_qmap(hb200_act* a) {
+    if (!g_encode_tiled) { a->has_qmap = false; return 0; }
+    static_assert(sizeof(CUtensorMap) <= sizeof(a->qmap), "tensor map storage");
+    const cuuint64_t dims[2] = {(cuuint64_t)a->ld_q, (cuuint64_t)a->max_seq};
+    const cuuint64_t strides[1] = {(cuuint64_t)a->ld_q};
+    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode_tiled(reinterpret_cast<CUtensorMap*>(a->qmap), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->q, dims, strides, box,
+                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return HB200_ERR_CUDA; }
+    a->has_qmap = true;
+    return 0;
+}
 
 int kind_of(int dtype) {
     switch (dtype) {
@@ -153,12 +178,28 @@ int dot_rows_launch(const hb200_weight* w, const hb200_act* a, size_t seq_len, f
         set_error("K-quant weights take f32 activations; use hb200_matmul_f32[_dev]");
         return HB200_ERR_UNSUPPORTED;
     }
+    // Five or more tokens of a 1-/2-bit weight go to the tensor cores; up to four stay on the streaming dp4a kernel.
+    if (seq_len >= (size_t)GEMM_TC_MIN_TOKENS && (w->kind == KIND_Q1 || w->kind == KIND_Q2) && a->has_qmap && w->nb > 0)
+        return launch_gemm_tc(w->kind, a->qmap, w->bits, w->scales, a->d, a->ld_b, (int)w->n_rows, w->nb, (int)seq_len, out,
+                              (int)ld_out, g_ctx.d_status, st);
     for (size_t tok0 = 0; tok0 < seq_len; tok0 += GEMV_MAX_M) {
         const int m = (int)((seq_len - tok0) < (size_t)GEMV_MAX_M ? (seq_len - tok0) : GEMV_MAX_M);
         DotOp op;
         fill_op(op, w, a, tok0, out, ld_out, nullptr);
         const int rc = launch_gemv_dp4a(w->kind, m, false, nullptr, nullptr, w->n_panels, &op, g_ctx.sm_count, st);
         if (rc) return rc;
+    }
+    return 0;
+}
+
+// After a synchronising call: turn a device-side wait expiry into an error code, and clear it.
+int check_device_status() {
+    int h = 0;
+    HB_CUDA(cudaMemcpy(&h, g_ctx.d_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (h != 0) {
+        cudaMemset(g_ctx.d_status, 0, sizeof(int));
+        set_error("a bounded wait inside a tensor-core kernel expired (code %d); results of that call are invalid", h);
+        return HB200_ERR_TIMEOUT;
     }
     return 0;
 }
@@ -200,6 +241,19 @@ extern "C" int hb200_init(int device) {
     int rc;
     if ((rc = gemv_dp4a_prepare())) return rc;
     if ((rc = kquant_prepare())) return rc;
+    if ((rc = gemm_tc_prepare())) return rc;
+    {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e2 = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e2 != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+            set_error("cuTensorMapEncodeTiled is not available from this driver");
+            return HB200_ERR_CUDA;
+        }
+        g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    HB_CUDA(cudaMalloc(&g_ctx.d_status, sizeof(int)));
+    HB_CUDA(cudaMemset(g_ctx.d_status, 0, sizeof(int)));
     g_ctx.ready = true;
     return HB200_OK;
     HB_GUARD_END
@@ -213,6 +267,7 @@ extern "C" int hb200_shutdown(void) {
     if (g_ctx.act) { hb200_act_free(g_ctx.act); g_ctx.act = nullptr; }
     if (g_ctx.d_in) cudaFree(g_ctx.d_in);
     if (g_ctx.d_out) cudaFree(g_ctx.d_out);
+    if (g_ctx.d_status) cudaFree(g_ctx.d_status);
     if (g_ctx.stream) cudaStreamDestroy(g_ctx.stream);
     g_ctx = Context();
     return HB200_OK;
@@ -251,8 +306,8 @@ extern "C" const char* hb200_selected_kernel(int dtype, size_t seq_len) {
     const int kind = kind_of(dtype);
     if (seq_len == 0) return "none";
     switch (kind) {
-        case KIND_Q1: return "gemv_dp4a_q1_0";
-        case KIND_Q2: return "gemv_dp4a_q2_0";
+        case KIND_Q1: return seq_len >= (size_t)GEMM_TC_MIN_TOKENS ? "gemm_tcgen05_i8_q1_0" : "gemv_dp4a_q1_0";
+        case KIND_Q2: return seq_len >= (size_t)GEMM_TC_MIN_TOKENS ? "gemm_tcgen05_i8_q2_0" : "gemv_dp4a_q2_0";
         case KIND_Q8: return "gemv_dp4a_q8_0";
         case KIND_Q4K: return "kquant_gemv_q4_k_f32";
         case KIND_Q6K: return "kquant_gemv_q6_k_f32";
@@ -419,6 +474,7 @@ extern "C" int hb200_act_create(size_t max_seq_len, size_t n_cols, hb200_act_t* 
         hb200_act_free(a);
         return HB200_ERR_CUDA;
     }
+    if ((rc = encode_qmap(a))) { hb200_act_free(a); return rc; }
     *out = a;
     return HB200_OK;
     HB_GUARD_END
@@ -564,6 +620,7 @@ extern "C" int hb200_dot_rows_batched(hb200_weight_t w, const uint8_t* a_q8, siz
     if ((rc = dot_rows_launch(w, g_ctx.act, seq_len, (float*)g_ctx.d_out, w->n_rows, g_ctx.stream))) return rc;
     HB_CUDA(cudaMemcpyAsync(out, g_ctx.d_out, out_bytes, cudaMemcpyDeviceToHost, g_ctx.stream));
     HB_CUDA(cudaStreamSynchronize(g_ctx.stream));
+    if (seq_len >= (size_t)GEMM_TC_MIN_TOKENS) return check_device_status();
     return HB200_OK;
     HB_GUARD_END
 }
@@ -587,6 +644,7 @@ extern "C" int hb200_matmul_f32(hb200_weight_t w, const float* x, size_t seq_len
     if ((rc = hb200_matmul_f32_dev(w, g_ctx.act, seq_len, (float*)g_ctx.d_out, w->n_rows, g_ctx.stream))) return rc;
     HB_CUDA(cudaMemcpyAsync(out, g_ctx.d_out, out_bytes, cudaMemcpyDeviceToHost, g_ctx.stream));
     HB_CUDA(cudaStreamSynchronize(g_ctx.stream));
+    if (seq_len >= (size_t)GEMM_TC_MIN_TOKENS) return check_device_status();
     return HB200_OK;
     HB_GUARD_END
 }
@@ -648,6 +706,10 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
     // One launch per (kind, tokens-per-op) combination.
     std::map<std::pair<int, int>, std::pair<std::vector<DotOp>, std::vector<DotItem>>> acc;
     for (const BatchEntry& e : b->entries) {
+        if (e.seq_len >= (size_t)GEMM_TC_MIN_TOKENS && (e.w->kind == KIND_Q1 || e.w->kind == KIND_Q2) && e.a->has_qmap && e.w->nb > 0) {
+            b->tensor.push_back(e);  // tensor-core kernel: one launch per op
+            continue;
+        }
         for (size_t tok0 = 0; tok0 < e.seq_len; tok0 += GEMV_MAX_M) {
             const int m = (int)((e.seq_len - tok0) < (size_t)GEMV_MAX_M ? (e.seq_len - tok0) : GEMV_MAX_M);
             auto& slot = acc[{e.w->kind, m}];
@@ -684,6 +746,10 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     for (const BatchGroup& g : b->groups)
         if ((rc = launch_gemv_dp4a(g.kind, g.m, false, g.ops_dev, g.items_dev, g.n_items, nullptr, g_ctx.sm_count, st))) return rc;
+    for (const BatchEntry& e : b->tensor)
+        if ((rc = launch_gemm_tc(e.w->kind, e.a->qmap, e.w->bits, e.w->scales, e.a->d, e.a->ld_b, (int)e.w->n_rows, e.w->nb,
+                                 (int)e.seq_len, e.out, (int)e.ld_out, g_ctx.d_status, st)))
+            return rc;
     for (const BatchEntry& e : b->kquant)
         if ((rc = launch_kquant_gemv(e.w->kind, e.w->raw, e.w->row_bytes, (int)e.w->n_rows, (int)e.w->n_cols, e.a->x, (int)e.seq_len,
                                      e.out, (int)e.ld_out, st)))
@@ -694,7 +760,7 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
 
 extern "C" int hb200_batch_launch_count(hb200_batch_t b) {
     if (!b || !b->sealed) return 0;
-    return (int)(b->groups.size() + b->kquant.size());
+    return (int)(b->groups.size() + b->kquant.size() + b->tensor.size());
 }
 
 extern "C" int hb200_batch_free(hb200_batch_t b) {

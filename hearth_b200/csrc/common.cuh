@@ -91,6 +91,14 @@ int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const 
                      const DotOp* single, int sm_count, cudaStream_t st);
 int gemv_dp4a_prepare();  // sets the dynamic shared-memory attributes once
 
+// gemm_tc.cu: tcgen05 kind::i8 path for 5 or more tokens (Q1_0 / Q2_0).  `amap` points at a CUtensorMap over the
+// activation's int8 plane ([max_seq][ld_q] bytes, box 128 x 128, SWIZZLE_128B).  `status` is a device word that
+// receives a non-zero code if a bounded wait inside the kernel expires.
+constexpr int GEMM_TC_MIN_TOKENS = 5;
+int launch_gemm_tc(int kind, const void* amap, const uint4* bits, const void* scales, const float* ad, int ld_b, int n_rows,
+                   int nb, int seq_len, float* out, int ld_out, int* status, cudaStream_t st);
+int gemm_tc_prepare();
+
 // kquant.cu
 int launch_kquant_gemv(int kind, const uint8_t* w, size_t row_bytes, int n_rows, int n_cols, const float* x, int seq_len, float* out,
                        int ld_out, cudaStream_t st);

@@ -23,5 +23,7 @@ struct hb200_act {
     int8_t* q = nullptr;
     float* d = nullptr;
     float* sums = nullptr;
+    alignas(64) unsigned char qmap[128] = {};  // CUtensorMap over the int8 plane (tcgen05 path)
+    bool has_qmap = false;
 };
 
