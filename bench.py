@@ -31,6 +31,26 @@ from hearth_b200 import synth  # noqa: E402
 DEFAULT_WORKLOAD = "c4_pq2_27b_decode"
 METRIC = "quant GEMV weight-stream bandwidth"
 UNIT = "GB/s"
+PREFILL_METRIC = "prefill GEMM throughput (2*M*N*K int8 ops)"
+PREFILL_UNIT = "TOPS"
+
+
+def is_prefill(cfg: dict) -> bool:
+    return cfg["seq_len"] >= 128
+
+
+def total_ops(cfg: dict) -> float:
+    return 2.0 * cfg["seq_len"] * cfg["layers"] * sum(r * k for _, r, k in cfg["shapes"])
+
+
+def tensor_peak():
+    """Dense int8 peak is not in MEASURED_PEAKS.json; the int8 tensor rate is twice the bf16 rate, so use
+    2 x the measured sustained bf16 figure (a long step runs under the power cap)."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return 2.0 * float(d["bf16_tflops_sustained"]), "2 x measured sustained bf16 (MEASURED_PEAKS.json bf16_tflops_sustained)"
+    return 2.0 * 1400.0, "2 x fallback sustained bf16 (1.4 PFLOP/s)"
 
 
 def measured_peaks():
@@ -86,11 +106,7 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def shard_rows(n_rows: int, rank: int, world: int) -> tuple[int, int]:
-    """The reference's static row split (hearth-llm/src/pool.rs:321-323) over ranks instead of threads."""
-    chunk = -(-n_rows // world)
-    lo = min(rank * chunk, n_rows)
-    return lo, min(lo + chunk, n_rows)
+from hearth_b200.sharding import ShardPlan, shard_rows  # noqa: E402
 
 
 def algorithmic_bytes(cfg: dict) -> dict:
@@ -123,6 +139,7 @@ class CpuArm:
                 a = O.quantize_q8_0(synth.activations(cfg["seq_len"], n_cols, seed=5000 + 10 * li + ti))
                 self.mats.append((w, a, n_rows, n_cols, np.zeros((cfg["seq_len"], n_rows), dtype=np.float32)))
         self.nbytes = sum(w.size for w, *_ in self.mats)
+        self.ops = 2.0 * cfg["seq_len"] * sum(n_rows * n_cols for _, _, n_rows, n_cols, _ in self.mats)
         self.kernel = self.S.hs_selected_kernel(cfg["dtype"]).decode()
         self.desc = (f"{sample_layers} layer(s) x {len(cfg['shapes'])} projections of the workload, M={cfg['seq_len']}, "
                      f"{self.nbytes / 1e6:.1f} MB of weights per pass; arm={self.kernel}; {self.threads} threads of "
@@ -162,13 +179,16 @@ def run_reference(args, cfg, rank):
     arm.close()
     sec = statistics.median(times)
     value = arm.nbytes / sec / 1e9
+    metric, unit = METRIC, UNIT
+    if is_prefill(cfg):
+        metric, unit, value = PREFILL_METRIC, PREFILL_UNIT, arm.ops / sec / 1e12
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": len(times),
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 x {1,2}-bit -> int32, fp32 scales", "data": "synthetic",
         "config": {"workload": args.workload, "tokens": cfg["seq_len"], "sample": arm.desc},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": arm.threads, "kind": "port", "sample": arm.desc},
-        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": arm.threads, "kind": "port", "sample": arm.desc},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
@@ -215,7 +235,7 @@ def run_ours(args, cfg, rank, world, local_rank):
 
     # outputs: one packed buffer per rank [M, slice_rows]; gathered into [world, M, slice_rows]
     out_local = torch.zeros((M, slice_rows), dtype=torch.float32, device=dev)
-    out_all = torch.zeros((world, M, slice_rows), dtype=torch.float32, device=dev) if world > 1 else None
+    out_all = torch.zeros((world * M, slice_rows), dtype=torch.float32, device=dev) if world > 1 else None  # [world][M][slice]
     batch = hb.Batch()
     off = 0
     i = 0
@@ -282,7 +302,7 @@ def run_ours(args, cfg, rank, world, local_rank):
 
     # ---- end to end through the host-buffer entry point (rank-local inputs and outputs, pinned memory)
     e2e_ms, h2d, d2h = None, 0, 0
-    if M <= 4 and not args.quick:
+    if not args.quick:
         hosts_out = [torch.zeros((M, W.n_rows), dtype=torch.float32).pin_memory() for W, _ in weights]
         xs = [x_host[k].numpy() for _, _, k in cfg["shapes"]] * cfg["layers"]
         outs_np = [o.numpy() for o in hosts_out]
@@ -296,7 +316,7 @@ def run_ours(args, cfg, rank, world, local_rank):
                     rc = lib.hb200_matmul_f32(W._h, C.c_void_p(x.ctypes.data), M, C.c_void_p(o.ctypes.data))
                     if rc:
                         hb.check(rc)
-        e2e_steps = max(1, min(args.steps, 5))
+        e2e_steps = max(1, min(args.steps, 5 if M <= 4 else 1))
         e2e_step()
         barrier()
         t0 = time.perf_counter()
@@ -318,8 +338,20 @@ def run_ours(args, cfg, rank, world, local_rank):
         peak, peak_src = measured_peaks()
         per_rank_alg = total_alg / world
         achieved = per_rank_alg / (ms_per_step * 1e-3) / 1e9
+        metric, unit = METRIC, UNIT
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": None, "kernel": hb.selected_kernel(dtype, M), "peak_source": peak_src,
+                "algorithmic_bytes_per_launch": per_rank_alg}
+        if is_prefill(cfg):
+            metric, unit = PREFILL_METRIC, PREFILL_UNIT
+            value = total_ops(cfg) / (ms_per_step * 1e-3) / 1e12
+            tpeak, tsrc = tensor_peak()
+            per_rank_tops = value / world
+            roof = {"bound": "tensor", "achieved": per_rank_tops, "peak": tpeak, "unit": "TOP/s", "frac": per_rank_tops / tpeak,
+                    "traffic": None, "kernel": hb.selected_kernel(dtype, M), "peak_source": tsrc,
+                    "ops_per_step": total_ops(cfg), "weight_stream_gbs": ab["weights"] / (ms_per_step * 1e-3) / 1e9}
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8 x {1,2}-bit -> int32, fp32 scales", "data": "synthetic",
             "config": {"workload": args.workload, "format": {41: "Q1_0", 42: "Q2_0", 142: "PQ2_0", 8: "Q8_0"}.get(dtype, str(dtype)),
@@ -329,10 +361,8 @@ def run_ours(args, cfg, rank, world, local_rank):
                        "launch": "one recorded batch (work list) per step"},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "kernel": hb.selected_kernel(dtype, M), "peak_source": peak_src,
-                         "algorithmic_bytes_per_launch": per_rank_alg},
-            "e2e": ({"value": ab["weights"] / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "roofline": roof,
+            "e2e": ({"value": (total_ops(cfg) / (e2e_ms * 1e-3) / 1e12) if is_prefill(cfg) else ab["weights"] / (e2e_ms * 1e-3) / 1e9, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                      "ms_per_step": e2e_ms, "call": "hb200_matmul_f32 per matrix, pinned host buffers"} if e2e_ms else None),
         }
         if world == 1 and not args.no_cpu and not args.quick:
@@ -342,7 +372,9 @@ def run_ours(args, cfg, rank, world, local_rank):
             while time.perf_counter() - t0 < 8.0:  # bounded: about ten seconds of CPU work
                 best = max(best, arm.gbs(2))
             arm.close()
-            line["cpu_baseline"] = {"value": best, "unit": UNIT, "cores": arm.threads, "kind": "port", "sample": arm.desc}
+            if is_prefill(cfg):  # same unit as the line: ops of the sample / time
+                best = best * 1e9 / arm.nbytes * arm.ops / 1e12
+            line["cpu_baseline"] = {"value": best, "unit": unit, "cores": arm.threads, "kind": "port", "sample": arm.desc}
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

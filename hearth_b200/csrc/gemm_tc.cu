@@ -114,7 +114,18 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr)
         : "memory");
 }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+#define HB_R32(v)                                                                                                    \
+    "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),  \
+        "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]),  \
+        "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]),  \
+        "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
+// Waits for every outstanding tcgen05.ld of this thread.  The loaded registers are listed as read-write operands so
+// that the compiler cannot schedule a use of them ahead of the wait.
+__device__ __forceinline__ void tc_wait_ld(uint32_t (&v)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : HB_R32(v)::"memory");
+}
+// Same ordering guarantee for a second register array covered by the same wait.
+__device__ __forceinline__ void tc_pin(uint32_t (&v)[32]) { asm volatile("" : HB_R32(v)::"memory"); }
 
 // K-major, SWIZZLE_128B shared-memory matrix descriptor: rows of 128 B, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
@@ -129,11 +140,13 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
 // kind::i8, D = S32, A and B signed int8, both K-major, M = 128, N = 64.
 constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(ROW_TILE >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
+constexpr int SCALE_SLOTS = 8;  // ring of per-block weight scales (f32); deeper than the tile ring, see the unpack loop
 struct Barriers {
     uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES];
     uint64_t tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
+    alignas(16) float wscale[SCALE_SLOTS][ROW_TILE];
 };
 
 template <int KIND>
@@ -219,9 +232,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
         }
     } else if (warp < 6) {
         // ---------------------------------------------------------------- unpack (128 threads)
+        // Each thread owns two units (row of the tile, sub-block); the packed words of the next block are
+        // fetched before the current block is expanded, so the global-load latency hides behind the ring.
         const int ut = threadIdx.x - 64;
+        const uint2* src[2][4];
+        int rsh[2], ris[2], ss[2];
+#pragma unroll
+        for (int uu = 0; uu < 2; uu++) {
+            const int u = ut + uu * 128;
+            const int ri = u >> 2, s = u & 3;
+            const int grow = row0 + ri;
+            const int rg = grow / RPG, r = grow % RPG;
+            ris[uu] = ri; ss[uu] = s;
+            rsh[uu] = (KIND == KIND_Q1) ? r : 2 * r;
+            const uint4* tp = args.bits + (size_t)(rg >> 5) * nb * 256 + (rg & 31);
+#pragma unroll
+            for (int jp = 0; jp < 4; jp++)  // words 2jp, 2jp+1 of sub-block s: piece 2jp + (s>>1), components (s&1)*2, +1
+                src[uu][jp] = reinterpret_cast<const uint2*>(tp + (2 * jp + (s >> 1)) * 32) + (s & 1);
+        }
+        // weight scale of row (ut & 63) of the tile, block 0 (only threads 0..63 stage scales)
+        const int srow = row0 + (ut & 63);
+        const int srg = srow / RPG, sr = srow % RPG;
+        const unsigned short* sc16 = reinterpret_cast<const unsigned short*>(args.scales) +
+                                     ((size_t)(srg >> 5) * nb * 32 + (srg & 31)) * scales_per_tile(KIND) + sr;
+        uint2 cur[2][4], nxt[2][4];
+        unsigned short sc_cur = 0, sc_nxt = 0;
+        auto fetch = [&](int blk, uint2 (&dst)[2][4], unsigned short& sc) {
+            const size_t off = (size_t)blk * 256 * 2;  // uint2 units per tile: 256 uint4
+#pragma unroll
+            for (int uu = 0; uu < 2; uu++)
+#pragma unroll
+                for (int jp = 0; jp < 4; jp++) dst[uu][jp] = __ldg(src[uu][jp] + off);
+            if (ut < 64) sc = __ldg(sc16 + (size_t)blk * 32 * scales_per_tile(KIND));
+        };
+        if (nb > 0) fetch(0, cur, sc_cur);
         for (int blk = 0; blk < nb; blk++) {
             const int st = blk % STAGES;
+            if (blk + 1 < nb) fetch(blk + 1, nxt, sc_nxt);
             bool ok = true;
             if (blk >= STAGES) {
                 if (lane == 0) ok = mbar_wait(smem_u32(&bars->empty[st]), ((blk / STAGES) - 1) & 1, abort_flag, args.status, 5);
@@ -231,39 +278,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
             unsigned char* bt = tiles + st * STAGE_BYTES + A_BYTES;
 #pragma unroll
             for (int uu = 0; uu < 2; uu++) {
-                const int u = ut + uu * 128;       // unit = (row of the tile, sub-block)
-                const int ri = u >> 2, s = u & 3;
-                const int grow = row0 + ri;
-                const int rg = grow / RPG, r = grow % RPG;
-                const size_t tile = (size_t)(rg >> 5) * nb + blk;
-                const uint4* tp = args.bits + tile * 256 + (rg & 31);
                 uint32_t vals[8];
 #pragma unroll
                 for (int jp = 0; jp < 4; jp++) {
-                    // words 2jp, 2jp+1 of sub-block s live in piece 2jp + (s>>1), components (s&1)*2, +1
-                    const uint2 w2 = __ldg(reinterpret_cast<const uint2*>(tp + (2 * jp + (s >> 1)) * 32) + (s & 1));
-                    const uint32_t ww[2] = {w2.x, w2.y};
+                    const uint32_t ww[2] = {cur[uu][jp].x, cur[uu][jp].y};
 #pragma unroll
                     for (int e = 0; e < 2; e++) {
                         uint32_t v;
                         if (KIND == KIND_Q1) {
-                            const uint32_t m = (ww[e] >> r) & 0x01010101u;  // bit -> 0/1
-                            v = (m * 0xFEu) ^ 0xFFFFFFFFu;                   // 1 -> 0x01 (+1), 0 -> 0xFF (-1)
+                            const uint32_t m = (ww[e] >> rsh[uu]) & 0x01010101u;  // bit -> 0/1
+                            v = (m * 0xFEu) ^ 0xFFFFFFFFu;                         // 1 -> 0x01 (+1), 0 -> 0xFF (-1)
                         } else {
-                            const uint32_t c = ((ww[e] >> (2 * r)) & 0x03030303u) | 0x80808080u;
-                            v = (c - 0x01010101u) ^ 0x80808080u;             // code - 1 per byte, no borrow across bytes
+                            const uint32_t c = ((ww[e] >> rsh[uu]) & 0x03030303u) | 0x80808080u;
+                            v = (c - 0x01010101u) ^ 0x80808080u;                   // code - 1 per byte, no borrow across bytes
                         }
                         vals[2 * jp + e] = v;
                     }
                 }
-                unsigned char* rowp = bt + ri * 128;
-                const int sw = ri & 7;
-                *reinterpret_cast<uint4*>(rowp + (((2 * s) ^ sw) << 4)) = make_uint4(vals[0], vals[1], vals[2], vals[3]);
-                *reinterpret_cast<uint4*>(rowp + (((2 * s + 1) ^ sw) << 4)) = make_uint4(vals[4], vals[5], vals[6], vals[7]);
+                unsigned char* rowp = bt + ris[uu] * 128;
+                const int sw = ris[uu] & 7;
+                *reinterpret_cast<uint4*>(rowp + (((2 * ss[uu]) ^ sw) << 4)) = make_uint4(vals[0], vals[1], vals[2], vals[3]);
+                *reinterpret_cast<uint4*>(rowp + (((2 * ss[uu] + 1) ^ sw) << 4)) = make_uint4(vals[4], vals[5], vals[6], vals[7]);
             }
+            // The scale ring is read by the promotion warps up to two blocks after the MMA released the tile
+            // stage; SCALE_SLOTS = 8 keeps a slot untouched for that long (the producers run at most
+            // STAGES + 2 blocks ahead of the slowest reader).
+            if (ut < 64) bars->wscale[blk % SCALE_SLOTS][ut] = __half2float(__ushort_as_half(sc_cur));
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // make the generic-proxy writes visible to the MMA
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->full_b[st]));
+#pragma unroll
+            for (int uu = 0; uu < 2; uu++)
+#pragma unroll
+                for (int jp = 0; jp < 4; jp++) cur[uu][jp] = nxt[uu][jp];
+            sc_cur = sc_nxt;
         }
     } else {
         // ---------------------------------------------------------------- promotion (8 warps; thread = token)
@@ -274,58 +322,60 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
         const bool tok_ok = tok < args.seq_len;
         const float* adp = args.ad + (size_t)(tok_ok ? tok : 0) * args.ld_b;
         const int rbase = row0 + half * 32;  // first weight row of this thread's columns
+        // A warp none of whose 32 tokens exist only keeps the barrier protocol going.
+        const bool warp_has_tokens = (tok0 + quarter * 32) < args.seq_len;
         float sum[32];
 #pragma unroll
         for (int c = 0; c < 32; c++) sum[c] = 0.0f;
+        float4 as_next = (nb > 0) ? *reinterpret_cast<const float4*>(adp) : make_float4(0.f, 0.f, 0.f, 0.f);
 
         for (int blk = 0; blk < nb; blk++) {
             const int buf = blk & 1;
+            const float4 as4 = as_next;
+            if (blk + 1 < nb) as_next = *reinterpret_cast<const float4*>(adp + 4 * (blk + 1));
             bool ok = true;
             if (lane == 0) ok = mbar_wait(smem_u32(&bars->tmem_full[buf]), (blk >> 1) & 1, abort_flag, args.status, 6);
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (!ok) break;
             tc_fence_after();
-            const float4 as4 = *reinterpret_cast<const float4*>(adp + 4 * blk);
-            const float asv[4] = {as4.x, as4.y, as4.z, as4.w};
-            float bacc[32];
+            if (warp_has_tokens) {
+                const float asv[4] = {as4.x, as4.y, as4.z, as4.w};
+                float bacc[32];
+                const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256 + half * 32;
+                uint32_t v0[32], v1[32];
+                tc_ld32(tbase, v0);
+                tc_ld32(tbase + ROW_TILE, v1);
+                tc_wait_ld(v0);
+                tc_pin(v1);
 #pragma unroll
-            for (int c = 0; c < 32; c++) bacc[c] = 0.0f;
+                for (int c = 0; c < 32; c++) bacc[c] = fmaf((float)(int)v0[c], asv[0], 0.0f);
+                tc_ld32(tbase + 2 * ROW_TILE, v0);
 #pragma unroll
-            for (int s = 0; s < 4; s++) {
-                uint32_t v[32];
-                tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256 + s * ROW_TILE + half * 32, v);
-                tc_wait_ld();
+                for (int c = 0; c < 32; c++) bacc[c] = fmaf((float)(int)v1[c], asv[1], bacc[c]);
+                tc_ld32(tbase + 3 * ROW_TILE, v1);
+                tc_wait_ld(v0);
+                tc_pin(v1);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[buf]));
 #pragma unroll
-                for (int c = 0; c < 32; c++) bacc[c] = fmaf((float)(int)v[c], asv[s], bacc[c]);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[buf]));
-            // sum += block_acc * w_scale, rounded separately (q2_0.rs:572, q1_0g128.rs:1050)
-            if (KIND == KIND_Q1) {
+                for (int c = 0; c < 32; c++) bacc[c] = fmaf((float)(int)v0[c], asv[2], bacc[c]);
 #pragma unroll
-                for (int g = 0; g < 4; g++) {  // four row groups of 8 rows
-                    const int rg = (rbase >> 3) + g;
-                    const uint4 sc = __ldg(reinterpret_cast<const uint4*>(args.scales) + ((size_t)(rg >> 5) * nb + blk) * 32 + (rg & 31));
-                    const uint32_t sw[4] = {sc.x, sc.y, sc.z, sc.w};
+                for (int c = 0; c < 32; c++) bacc[c] = fmaf((float)(int)v1[c], asv[3], bacc[c]);
+                // sum += block_acc * w_scale, rounded separately (q2_0.rs:572, q1_0g128.rs:1050)
+                const float4* wsp = reinterpret_cast<const float4*>(&bars->wscale[blk % SCALE_SLOTS][half * 32]);
 #pragma unroll
-                    for (int k = 0; k < 8; k++) {
-                        const float wd = __half2float(__ushort_as_half((unsigned short)(sw[k >> 1] >> (16 * (k & 1)))));
-                        sum[g * 8 + k] = __fadd_rn(sum[g * 8 + k], __fmul_rn(bacc[g * 8 + k], wd));
-                    }
+                for (int c4 = 0; c4 < 8; c4++) {
+                    const float4 wd = wsp[c4];
+                    sum[4 * c4 + 0] = __fadd_rn(sum[4 * c4 + 0], __fmul_rn(bacc[4 * c4 + 0], wd.x));
+                    sum[4 * c4 + 1] = __fadd_rn(sum[4 * c4 + 1], __fmul_rn(bacc[4 * c4 + 1], wd.y));
+                    sum[4 * c4 + 2] = __fadd_rn(sum[4 * c4 + 2], __fmul_rn(bacc[4 * c4 + 2], wd.z));
+                    sum[4 * c4 + 3] = __fadd_rn(sum[4 * c4 + 3], __fmul_rn(bacc[4 * c4 + 3], wd.w));
                 }
             } else {
-#pragma unroll
-                for (int g = 0; g < 8; g++) {  // eight row groups of 4 rows
-                    const int rg = (rbase >> 2) + g;
-                    const uint2 sc = __ldg(reinterpret_cast<const uint2*>(args.scales) + ((size_t)(rg >> 5) * nb + blk) * 32 + (rg & 31));
-                    const uint32_t sw[2] = {sc.x, sc.y};
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const float wd = __half2float(__ushort_as_half((unsigned short)(sw[k >> 1] >> (16 * (k & 1)))));
-                        sum[g * 4 + k] = __fadd_rn(sum[g * 4 + k], __fmul_rn(bacc[g * 4 + k], wd));
-                    }
-                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[buf]));
             }
         }
         if (tok_ok && !*abort_flag) {
