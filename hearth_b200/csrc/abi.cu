@@ -64,6 +64,8 @@ struct BatchGroup {  // one launch
     int kind, m;
     DotOp* ops_dev = nullptr;
     DotItem* items_dev = nullptr;
+    int* chunks_dev = nullptr;  // grid + 1 item boundaries, balanced by blocks per panel
+    int grid = 0;
     int n_items = 0;
 };
 struct hb200_batch {
@@ -186,7 +188,9 @@ int dot_rows_launch(const hb200_weight* w, const hb200_act* a, size_t seq_len, f
         const int m = (int)((seq_len - tok0) < (size_t)GEMV_MAX_M ? (seq_len - tok0) : GEMV_MAX_M);
         DotOp op;
         fill_op(op, w, a, tok0, out, ld_out, nullptr);
-        const int rc = launch_gemv_dp4a(w->kind, m, false, nullptr, nullptr, w->n_panels, &op, g_ctx.sm_count, st);
+        int grid = g_ctx.sm_count * gemv_dp4a_ctas_per_sm(m);
+        if (grid > w->n_panels) grid = w->n_panels;
+        const int rc = launch_gemv_dp4a(w->kind, m, false, nullptr, nullptr, nullptr, grid, w->n_panels, &op, st);
         if (rc) return rc;
     }
     return 0;
@@ -664,7 +668,9 @@ extern "C" int hb200_block_dots_i32(hb200_weight_t w, const uint8_t* a_q8, size_
     for (size_t s = 0; s < seq_len; s++) {
         DotOp op;
         fill_op(op, w, g_ctx.act, s, nullptr, w->n_rows, (int32_t*)g_ctx.d_out + s * per_tok);
-        if ((rc = launch_gemv_dp4a(w->kind, 1, true, nullptr, nullptr, w->n_panels, &op, g_ctx.sm_count, g_ctx.stream))) return rc;
+        int grid = g_ctx.sm_count * gemv_dp4a_ctas_per_sm(1);
+        if (grid > w->n_panels) grid = w->n_panels;
+        if ((rc = launch_gemv_dp4a(w->kind, 1, true, nullptr, nullptr, nullptr, grid, w->n_panels, &op, g_ctx.stream))) return rc;
     }
     HB_CUDA(cudaMemcpyAsync(out, g_ctx.d_out, out_bytes, cudaMemcpyDeviceToHost, g_ctx.stream));
     HB_CUDA(cudaStreamSynchronize(g_ctx.stream));
@@ -704,7 +710,8 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
     if (!b) { set_error("null batch"); return HB200_ERR_NULL; }
     if (b->sealed) return HB200_OK;
     // One launch per (kind, tokens-per-op) combination.
-    std::map<std::pair<int, int>, std::pair<std::vector<DotOp>, std::vector<DotItem>>> acc;
+    struct Acc { std::vector<DotOp> first; std::vector<DotItem> second; std::vector<int> cost; };
+    std::map<std::pair<int, int>, Acc> acc;
     for (const BatchEntry& e : b->entries) {
         if (e.seq_len >= (size_t)GEMM_TC_MIN_TOKENS && (e.w->kind == KIND_Q1 || e.w->kind == KIND_Q2) && e.a->has_qmap && e.w->nb > 0) {
             b->tensor.push_back(e);  // tensor-core kernel: one launch per op
@@ -717,7 +724,10 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
             fill_op(op, e.w, e.a, tok0, e.out, e.ld_out, nullptr);
             const int idx = (int)slot.first.size();
             slot.first.push_back(op);
-            for (int p = 0; p < e.w->n_panels; p++) slot.second.push_back(make_int2(idx, p));
+            for (int p = 0; p < e.w->n_panels; p++) {
+                slot.second.push_back(make_int2(idx, p));
+                slot.cost.push_back((e.w->nb + 7) / 8 + 1);  // rounds of the panel, plus a fixed per-panel share
+            }
         }
     }
     for (auto& kv : acc) {
@@ -730,6 +740,21 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
         HB_CUDA(cudaMalloc(&g.items_dev, kv.second.second.size() * sizeof(DotItem)));
         HB_CUDA(cudaMemcpy(g.ops_dev, kv.second.first.data(), kv.second.first.size() * sizeof(DotOp), cudaMemcpyHostToDevice));
         HB_CUDA(cudaMemcpy(g.items_dev, kv.second.second.data(), kv.second.second.size() * sizeof(DotItem), cudaMemcpyHostToDevice));
+        // Contiguous, cost-balanced runs of items per CTA: boundary c is the first item whose prefix cost reaches c/grid of the total.
+        g.grid = g_ctx.sm_count * gemv_dp4a_ctas_per_sm(g.m);
+        if (g.grid > g.n_items) g.grid = g.n_items;
+        long long total_cost = 0;
+        for (int c : kv.second.cost) total_cost += c;
+        std::vector<int> chunks(g.grid + 1, g.n_items);
+        chunks[0] = 0;
+        long long run = 0;
+        int next_c = 1;
+        for (int i = 0; i < g.n_items && next_c < g.grid; i++) {
+            run += kv.second.cost[i];
+            while (next_c < g.grid && run * g.grid >= total_cost * next_c) chunks[next_c++] = i + 1;
+        }
+        HB_CUDA(cudaMalloc(&g.chunks_dev, chunks.size() * sizeof(int)));
+        HB_CUDA(cudaMemcpy(g.chunks_dev, chunks.data(), chunks.size() * sizeof(int), cudaMemcpyHostToDevice));
         b->groups.push_back(g);
     }
     b->sealed = true;
@@ -745,7 +770,7 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
     if (!b->sealed) { set_error("batch is not sealed"); return HB200_ERR_BAD_SHAPE; }
     cudaStream_t st = (cudaStream_t)stream;
     for (const BatchGroup& g : b->groups)
-        if ((rc = launch_gemv_dp4a(g.kind, g.m, false, g.ops_dev, g.items_dev, g.n_items, nullptr, g_ctx.sm_count, st))) return rc;
+        if ((rc = launch_gemv_dp4a(g.kind, g.m, false, g.ops_dev, g.items_dev, g.chunks_dev, g.grid, g.n_items, nullptr, st))) return rc;
     for (const BatchEntry& e : b->tensor)
         if ((rc = launch_gemm_tc(e.w->kind, e.a->qmap, e.w->bits, e.w->scales, e.a->d, e.a->ld_b, (int)e.w->n_rows, e.w->nb,
                                  (int)e.seq_len, e.out, (int)e.ld_out, g_ctx.d_status, st)))
@@ -769,6 +794,7 @@ extern "C" int hb200_batch_free(hb200_batch_t b) {
     for (BatchGroup& g : b->groups) {
         if (g.ops_dev) cudaFree(g.ops_dev);
         if (g.items_dev) cudaFree(g.items_dev);
+        if (g.chunks_dev) cudaFree(g.chunks_dev);
     }
     delete b;
     return HB200_OK;

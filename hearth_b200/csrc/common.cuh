@@ -85,10 +85,12 @@ int launch_repack(int kind, const uint8_t* raw, size_t row_bytes, int n_rows, in
 
 // gemv_dp4a.cu
 constexpr int GEMV_MAX_M = 4;  // tokens one dp4a launch handles per op
-// Either an op list in device memory (ops_dev / items_dev / n_items), or, with ops_dev == nullptr, the
-// one op `single` (host memory, passed by value to the grid) whose n_items panels are walked in order.
-int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const DotItem* items_dev, int n_items,
-                     const DotOp* single, int sm_count, cudaStream_t st);
+// Either an op list in device memory (ops_dev / items_dev, with chunks_dev[grid + 1] giving each CTA its contiguous,
+// cost-balanced run of items; items of one op must be consecutive panels), or, with ops_dev == nullptr, the one op
+// `single` (host memory, passed by value to the grid) whose n_items panels are split evenly over `grid` CTAs.
+int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const DotItem* items_dev, const int* chunks_dev,
+                     int grid, int n_items, const DotOp* single, cudaStream_t st);
+int gemv_dp4a_ctas_per_sm(int m);  // resident CTAs per SM the kernel for m tokens is built for
 int gemv_dp4a_prepare();  // sets the dynamic shared-memory attributes once
 
 // gemm_tc.cu: tcgen05 kind::i8 path for 5 or more tokens (Q1_0 / Q2_0).  `amap` points at a CUtensorMap over the

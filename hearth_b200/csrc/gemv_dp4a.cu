@@ -72,10 +72,15 @@ struct Smem {
     alignas(16) float term[2][WARPS][M][TPB];
 };
 
+// as_float(MAGIC_I + x) == MAGIC_F + x exactly for |x| < 2^22: starting the dp4a accumulators at MAGIC_I turns the
+// int -> float conversion of a sub-block sum into one FADD, off the ALU pipe that the LOP3 unpack saturates.
+constexpr int MAGIC_I = 0x4B400000;
+constexpr float MAGIC_F = 12582912.0f;
+
 template <int KIND, int M, bool INT_OUT>
 __global__ void __launch_bounds__(THREADS, (M <= 2 ? 2 : 1))
-gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ items, int n_items,
-                 const __grid_constant__ DotOp single) {
+gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ items, const int* __restrict__ chunks,
+                 int n_items, const __grid_constant__ DotOp single) {
     using S = Smem<KIND, M>;
     constexpr int RPG = S::RPG;
     constexpr int RP = S::RP;
@@ -85,16 +90,25 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    for (int it = blockIdx.x; it < n_items; it += gridDim.x) {
-        // A list launch reads (op, panel) pairs; a single-op launch walks the panels of `single`.
-        const DotOp op = ops ? ops[items[it].x] : single;
-        const int panel = ops ? items[it].y : it;
-        const int nb = op.nb;
-        const int rounds = (nb + WARPS - 1) / WARPS;
+    // This CTA's contiguous run of work items.  A list launch reads cost-balanced boundaries; a single-op launch
+    // splits the panels of `single` evenly.
+    int it = ops ? chunks[blockIdx.x] : (int)(((long long)n_items * blockIdx.x) / gridDim.x);
+    const int it_end = ops ? chunks[blockIdx.x + 1] : (int)(((long long)n_items * (blockIdx.x + 1)) / gridDim.x);
 
-        // Stage the activation columns of round r into buffer r&1 (cp.async, 16 B each).
-        auto stage = [&](int r) {
-            const int buf = r & 1;
+    while (it < it_end) {
+        // One segment: consecutive panels [p0, p0 + cnt) of one op.  Rounds run back to back across the panels,
+        // so the weight prefetch never drains inside a segment.
+        const DotOp op = ops ? ops[items[it].x] : single;
+        const int p0 = ops ? items[it].y : it;
+        const int op_panels = (op.n_rows + RP - 1) / RP;
+        const int cnt = min(it_end - it, op_panels - p0);
+        it += cnt;
+        const int nb = op.nb;
+        const int rounds = max(1, (nb + WARPS - 1) / WARPS);
+        const int total = cnt * rounds;
+
+        // Stage the activation columns of round r into buffer `buf` (cp.async, 16 B each).
+        auto stage = [&](int r, int buf) {
             for (int idx = tid; idx < 80 * M; idx += THREADS) {
                 const int m = idx / 80, p = idx % 80;
                 if (p < 64)
@@ -108,7 +122,7 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
 
         uint4 wn[8];   // weight pieces of the next round
         uint4 wsn;     // its scales (Q1_0: 8 f16; Q2_0 / Q8_0: 4 f16 in .x .y)
-        auto load_w = [&](int r) {
+        auto load_w = [&](int panel, int r) {
             const int blk = r * WARPS + warp;
             if (blk < nb) {
                 const size_t tile = (size_t)panel * nb + blk;
@@ -128,10 +142,11 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
 #pragma unroll
         for (int k = 0; k < NRUN; k++) run[k] = 0.0f;
 
-        // Adds the terms of round r (buffer r&1) to the running sums, in block order.
-        auto replay = [&](int r) {
-            const int buf = r & 1;
+        // Adds the terms of round r of `panel` (buffer `buf`) to the running sums, in block order; after the last
+        // round of a panel the sums are the outputs of that panel.
+        auto replay = [&](int panel, int r, int buf) {
             const int nvalid = min(WARPS, nb - r * WARPS);
+            const bool last = (r == rounds - 1);
 #pragma unroll
             for (int k = 0; k < NRUN; k++) {
                 const int idx = tid + k * THREADS;
@@ -145,29 +160,38 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
                     } else {
                         for (int b = 0; b < nvalid; b++) acc = __fadd_rn(acc, sm.term[buf][b][m][row]);
                     }
+                    if (last) {
+                        const int grow = panel * RP + row;
+                        if (grow < op.n_rows) op.out[(size_t)m * op.ld_out + grow] = acc;
+                        acc = 0.0f;
+                    }
                     run[k] = acc;
                 }
             }
         };
 
-        __syncthreads();  // previous item's shared memory is no longer read
-        stage(0);
-        load_w(0);
+        __syncthreads();  // the previous segment's shared memory is no longer read
+        stage(0, 0);
+        load_w(p0, 0);
 
-        for (int r = 0; r < rounds; r++) {
+        int panel = p0, r = 0;            // position of round t
+        int ppanel = p0, pr = 0;          // position of round t - 1
+        for (int t = 0; t < total; t++) {
             cp_async_commit_wait_all();
-            __syncthreads();  // activations of round r landed; terms of round r-1 visible
+            __syncthreads();  // activations of round t landed; terms of round t-1 visible
             uint4 w[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) w[i] = wn[i];
             const uint4 ws = wsn;
-            if (r + 1 < rounds) {
-                stage(r + 1);
-                load_w(r + 1);
+            int npanel = panel, nr = r + 1;
+            if (nr == rounds) { nr = 0; npanel = panel + 1; }
+            if (t + 1 < total) {
+                stage(nr, (t + 1) & 1);
+                load_w(npanel, nr);
             }
-            if (!INT_OUT && r > 0) replay(r - 1);
+            if (!INT_OUT && t > 0) replay(ppanel, pr, (t - 1) & 1);
 
-            const int buf = r & 1;
+            const int buf = t & 1;
             const int blk = r * WARPS + warp;
             if (blk < nb) {
                 float bacc[M][RPG];
@@ -182,7 +206,7 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
 #pragma unroll
                     for (int m = 0; m < M; m++)
 #pragma unroll
-                        for (int g = 0; g < RPG; g++) acc[m][g] = 0;
+                        for (int g = 0; g < RPG; g++) acc[m][g] = INT_OUT ? 0 : MAGIC_I;
 #pragma unroll
                     for (int h = 0; h < 2; h++) {
                         int4 a4[M];
@@ -191,7 +215,7 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
                             a4[m] = *reinterpret_cast<const int4*>(&sm.aq[buf][m][warp * 128 + s * 32 + h * 16]);
 #pragma unroll
                         for (int jj = 0; jj < 4; jj++) {
-                            const int j = 4 * h + jj;                  // word of the sub-block: columns 4j..4j+3
+                            const int j = 4 * h + jj;                      // word of the sub-block: columns 4j..4j+3
                             const int q = (j >> 1) * 8 + s * 2 + (j & 1);  // its position in the tile
                             const uint32_t word = comp(w[q >> 2], q & 3);
 #pragma unroll
@@ -217,61 +241,62 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
                         for (int g = 0; g < RPG; g++) {
                             if (INT_OUT) {
                                 int iv;
-                                if (KIND == KIND_Q1) iv = ((acc[m][g] << 1) >> g) - (int)a_sum;  // 2*S1 - sum(a)
+                                if (KIND == KIND_Q1) iv = ((acc[m][g] << 1) >> g) - (int)a_sum;       // 2*S1 - sum(a)
                                 else if (KIND == KIND_Q2) iv = (acc[m][g] >> (2 * g)) - (int)a_sum;  // S_code - sum(a)
                                 else iv = acc[m][g];
                                 const int row = panel * RP + lane * RPG + g;
                                 if (row < op.n_rows && blk * 4 + s < op.n_sub)
                                     op.iout[((size_t)m * op.n_rows + row) * op.n_sub + blk * 4 + s] = iv;
-                            } else if (KIND == KIND_Q8) {
-                                const float wd = __half2float(__ushort_as_half(
-                                    (unsigned short)((s < 2 ? ws.x : ws.y) >> (16 * (s & 1)))));
-                                // ((float)sumi * d_w) * d_a, each product rounded (q8_0.rs:169)
-                                sm.term[buf][warp][m][s * 32 + lane] =
-                                    __fmul_rn(__fmul_rn((float)acc[m][g], wd), a_d);
                             } else {
-                                // exact integer I as fp32, then block_acc += I * a_scale (exact product, one rounding)
-                                const float c = (KIND == KIND_Q1) ? (2.0f / (float)(1 << g)) : (1.0f / (float)(1 << (2 * g)));
-                                const float i_f = fmaf((float)acc[m][g], c, -a_sum);
-                                bacc[m][g] = fmaf(i_f, a_d, bacc[m][g]);
+                                const float accf = __fadd_rn(__int_as_float(acc[m][g]), -MAGIC_F);  // exact (float)sum
+                                if (KIND == KIND_Q8) {
+                                    const float wd = __half2float(__ushort_as_half(
+                                        (unsigned short)((s < 2 ? ws.x : ws.y) >> (16 * (s & 1)))));
+                                    // ((float)sumi * d_w) * d_a, each product rounded (q8_0.rs:169)
+                                    sm.term[buf][warp][m][s * 32 + lane] = __fmul_rn(__fmul_rn(accf, wd), a_d);
+                                } else {
+                                    // exact integer I as fp32, then block_acc += I * a_scale (exact product, one rounding)
+                                    const float c = (KIND == KIND_Q1) ? (2.0f / (float)(1 << g)) : (1.0f / (float)(1 << (2 * g)));
+                                    const float i_f = fmaf(accf, c, -a_sum);
+                                    bacc[m][g] = fmaf(i_f, a_d, bacc[m][g]);
+                                }
                             }
                         }
                     }
                 }
                 if (!INT_OUT && KIND != KIND_Q8) {
+                    float wd[RPG];
 #pragma unroll
                     for (int g = 0; g < RPG; g++) {
                         const uint32_t pair = (g < 2) ? ws.x : (g < 4 ? ws.y : (g < 6 ? ws.z : ws.w));
-                        const float wd = __half2float(__ushort_as_half((unsigned short)(pair >> (16 * (g & 1)))));
+                        wd[g] = __half2float(__ushort_as_half((unsigned short)(pair >> (16 * (g & 1)))));
+                    }
 #pragma unroll
-                        for (int m = 0; m < M; m++) sm.term[buf][warp][m][lane * RPG + g] = __fmul_rn(bacc[m][g], wd);
+                    for (int m = 0; m < M; m++) {
+                        float4* tp = reinterpret_cast<float4*>(&sm.term[buf][warp][m][lane * RPG]);
+#pragma unroll
+                        for (int g4 = 0; g4 < RPG / 4; g4++)
+                            tp[g4] = make_float4(__fmul_rn(bacc[m][4 * g4], wd[4 * g4]), __fmul_rn(bacc[m][4 * g4 + 1], wd[4 * g4 + 1]),
+                                                 __fmul_rn(bacc[m][4 * g4 + 2], wd[4 * g4 + 2]), __fmul_rn(bacc[m][4 * g4 + 3], wd[4 * g4 + 3]));
                     }
                 }
             }
+            ppanel = panel; pr = r;
+            panel = npanel; r = nr;
         }
         if (!INT_OUT) {
             __syncthreads();
-            if (rounds > 0) replay(rounds - 1);
-#pragma unroll
-            for (int k = 0; k < NRUN; k++) {
-                const int idx = tid + k * THREADS;
-                if (idx < M * RP) {
-                    const int m = idx / RP, row = panel * RP + idx % RP;
-                    if (row < op.n_rows) op.out[(size_t)m * op.ld_out + row] = run[k];
-                }
-            }
+            replay(ppanel, pr, (total - 1) & 1);
         }
     }
 }
 
 template <int KIND, int M, bool INT_OUT>
-int launch_one(const DotOp* ops, const DotItem* items, int n_items, const DotOp& single, int sm_count, cudaStream_t st) {
+int launch_one(const DotOp* ops, const DotItem* items, const int* chunks, int grid, int n_items, const DotOp& single,
+               cudaStream_t st) {
     using S = Smem<KIND, M>;
-    const int per_sm = (M <= 2) ? 2 : 1;
-    int grid = sm_count * per_sm;
-    if (grid > n_items) grid = n_items;
-    if (grid <= 0) return 0;
-    gemv_dp4a_kernel<KIND, M, INT_OUT><<<grid, THREADS, sizeof(S), st>>>(ops, items, n_items, single);
+    if (grid <= 0 || n_items <= 0) return 0;
+    gemv_dp4a_kernel<KIND, M, INT_OUT><<<grid, THREADS, sizeof(S), st>>>(ops, items, chunks, n_items, single);
     HB_CUDA(cudaGetLastError());
     return 0;
 }
@@ -285,17 +310,17 @@ int prepare_one() {
 }
 
 template <int KIND>
-int launch_kind(int m, bool int_out, const DotOp* ops, const DotItem* items, int n_items, const DotOp& single, int sm_count,
-                cudaStream_t st) {
+int launch_kind(int m, bool int_out, const DotOp* ops, const DotItem* items, const int* chunks, int grid, int n_items,
+                const DotOp& single, cudaStream_t st) {
     if (int_out) {
         if (m != 1) { set_error("integer block-dot output runs one token per launch"); return -4; }
-        return launch_one<KIND, 1, true>(ops, items, n_items, single, sm_count, st);
+        return launch_one<KIND, 1, true>(ops, items, chunks, grid, n_items, single, st);
     }
     switch (m) {
-        case 1: return launch_one<KIND, 1, false>(ops, items, n_items, single, sm_count, st);
-        case 2: return launch_one<KIND, 2, false>(ops, items, n_items, single, sm_count, st);
-        case 3: return launch_one<KIND, 3, false>(ops, items, n_items, single, sm_count, st);
-        case 4: return launch_one<KIND, 4, false>(ops, items, n_items, single, sm_count, st);
+        case 1: return launch_one<KIND, 1, false>(ops, items, chunks, grid, n_items, single, st);
+        case 2: return launch_one<KIND, 2, false>(ops, items, chunks, grid, n_items, single, st);
+        case 3: return launch_one<KIND, 3, false>(ops, items, chunks, grid, n_items, single, st);
+        case 4: return launch_one<KIND, 4, false>(ops, items, chunks, grid, n_items, single, st);
         default: set_error("gemv_dp4a: m=%d outside 1..%d", m, GEMV_MAX_M); return -4;
     }
 }
@@ -321,15 +346,18 @@ int gemv_dp4a_prepare() {
     return 0;
 }
 
-int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const DotItem* items_dev, int n_items,
-                     const DotOp* single, int sm_count, cudaStream_t st) {
+int gemv_dp4a_ctas_per_sm(int m) { return m <= 2 ? 2 : 1; }
+
+int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const DotItem* items_dev, const int* chunks_dev,
+                     int grid, int n_items, const DotOp* single, cudaStream_t st) {
     static const DotOp none = {};
     const DotOp& one = single ? *single : none;
     if (!ops_dev && !single) { set_error("gemv_dp4a: neither an op list nor a single op"); return -5; }
+    if (ops_dev && !chunks_dev) { set_error("gemv_dp4a: a list launch needs chunk boundaries"); return -5; }
     switch (kind) {
-        case KIND_Q1: return launch_kind<KIND_Q1>(m, int_out, ops_dev, items_dev, n_items, one, sm_count, st);
-        case KIND_Q2: return launch_kind<KIND_Q2>(m, int_out, ops_dev, items_dev, n_items, one, sm_count, st);
-        case KIND_Q8: return launch_kind<KIND_Q8>(m, int_out, ops_dev, items_dev, n_items, one, sm_count, st);
+        case KIND_Q1: return launch_kind<KIND_Q1>(m, int_out, ops_dev, items_dev, chunks_dev, grid, n_items, one, st);
+        case KIND_Q2: return launch_kind<KIND_Q2>(m, int_out, ops_dev, items_dev, chunks_dev, grid, n_items, one, st);
+        case KIND_Q8: return launch_kind<KIND_Q8>(m, int_out, ops_dev, items_dev, chunks_dev, grid, n_items, one, st);
         default: set_error("gemv_dp4a: kind %d has no Q8_0 dot", kind); return -7;
     }
 }

@@ -130,6 +130,7 @@ CONFIGS = {
     "c1_q2_1p7b_decode": dict(dtype=Q2_0, shapes=layer_shapes(2048, 6144, 1024), layers=28, seq_len=1),
     "c1_q1_1p7b_decode": dict(dtype=Q1_0, shapes=layer_shapes(2048, 6144, 1024), layers=28, seq_len=1),
     "c2_q1_8b_prefill": dict(dtype=Q1_0, shapes=layer_shapes(4096, 12288, 1024), layers=36, seq_len=512),
+    "c2_q1_8b_prefill_1layer": dict(dtype=Q1_0, shapes=layer_shapes(4096, 12288, 1024), layers=1, seq_len=512),
     "c2_q1_8b_decode": dict(dtype=Q1_0, shapes=layer_shapes(4096, 12288, 1024), layers=36, seq_len=1),
     "c2_q2_8b_decode": dict(dtype=Q2_0, shapes=layer_shapes(4096, 12288, 1024), layers=36, seq_len=1),
     "c4_pq2_27b_decode": dict(dtype=PQ2_0, shapes=layer_shapes(5120, 17408, 1024), layers=64, seq_len=1),
