@@ -213,7 +213,7 @@ def run_ours(args, cfg, rank, world, local_rank):
     stream = torch.cuda.Stream(device=dev)
 
     # ---- resident data: this rank's row shard of every weight, one activation per distinct input width
-    weights, acts, outs = [], {}, []
+    weights, acts = [], {}
     slice_rows = 0
     for li in range(cfg["layers"]):
         for ti, (_, n_rows, n_cols) in enumerate(cfg["shapes"]):
@@ -223,15 +223,9 @@ def run_ours(args, cfg, rank, world, local_rank):
             del packed
             slice_rows += -(-n_rows // world)
     torch.cuda.synchronize()
-    widths = sorted({k for _, _, k in cfg["shapes"]})
-    x_host = {}
-    for k in widths:
-        acts[k] = hb.Act(M, k)
-        xh = torch.from_numpy(synth.activations(M, k, seed=77 + k)).pin_memory()
-        x_host[k] = xh
-        xd = xh.to(dev)
-        acts[k].quantize(M, x_dev=xd)
-    torch.cuda.synchronize()
+    # One activation per input-sharing group of each layer, as in the model: q|k|v read one vector, o another,
+    # gate|up a third, down a fourth (hearth-llm/src/model/mod.rs:527-775).
+    group_of = {"q": 0, "k": 0, "v": 0, "o": 1, "gate": 2, "up": 2, "down": 3}
 
     # outputs: one packed buffer per rank [M, slice_rows]; gathered into [world, M, slice_rows]
     out_local = torch.zeros((M, slice_rows), dtype=torch.float32, device=dev)
@@ -240,20 +234,58 @@ def run_ours(args, cfg, rank, world, local_rank):
     off = 0
     i = 0
     for li in range(cfg["layers"]):
-        for ti, (_, n_rows, n_cols) in enumerate(cfg["shapes"]):
+        for ti, (name, n_rows, n_cols) in enumerate(cfg["shapes"]):
             W, pad_rows = weights[i]
             i += 1
+            key = (li, group_of.get(name, ti))
+            if key not in acts:
+                acts[key] = hb.Act(M, n_cols)
             if W.n_rows > 0:
-                batch.add(W, acts[n_cols], M, out_local[:, off:], ld_out=slice_rows)
+                batch.add(W, acts[key], M, out_local[:, off:], ld_out=slice_rows)
             off += pad_rows
     batch.seal()
+    # all inputs of a step in one pinned host buffer, outputs in another (the end-to-end leg copies both every step)
+    rng = np.random.Generator(np.random.PCG64(4242))
+    x_pinned = torch.from_numpy(rng.standard_normal(batch.input_floats, dtype=np.float32)).pin_memory()
+    out_pinned = torch.zeros((M, slice_rows), dtype=torch.float32).pin_memory()
+    batch.run_host(x_pinned.numpy(), out_local, out_pinned.numpy())  # uploads and quantizes the activations once
     launches_per_step = batch.launch_count
 
-    def step():
+    # Fused gather (N > 1, up to four tokens): a second recording of the same ops whose outputs go straight into
+    # every rank's assembled [M, sum of n_rows] buffer.
+    fused = None
+    use_fused = world > 1 and args.gather == "fused" and M <= 4
+    if use_fused:
+        full_cols = sum(n for _, n, _ in cfg["shapes"]) * cfg["layers"]
+        mine = hb.PeerBuffer.alloc(M * full_cols)
+        handles = [None] * world
+        dist.all_gather_object(handles, mine.handle)
+        bufs = [mine if r == rank else hb.PeerBuffer.open(handles[r], M * full_cols) for r in range(world)]
+        full_local = mine.tensor(dev).view(M, full_cols)
+        fused = hb.Batch()
+        fused.set_peers(rank, bufs, wait=True)
+        coff, i = 0, 0
+        for li in range(cfg["layers"]):
+            for ti, (name, n_rows, n_cols) in enumerate(cfg["shapes"]):
+                W, _ = weights[i]
+                i += 1
+                lo, hi = shard_rows(n_rows, rank, world)
+                if hi > lo:
+                    fused.add(W, acts[(li, group_of.get(name, ti))], M, full_local[:, coff + lo:], ld_out=full_cols)
+                coff += n_rows
+        fused.seal()
+        launches_per_step = fused.launch_count
+
+    def step_nccl():
         batch.launch(stream)
         if world > 1:
             with torch.cuda.stream(stream):
                 dist.all_gather_into_tensor(out_all, out_local)
+
+    def step_fused():
+        fused.launch(stream)
+
+    step = step_fused if use_fused else step_nccl
 
     def barrier():
         torch.cuda.synchronize()
@@ -292,31 +324,46 @@ def run_ours(args, cfg, rank, world, local_rank):
     for _ in range(0 if args.quick else 50):
         step()
     barrier()
+    ms_nccl = None
+    if use_fused:  # the same steps with the collective instead, for comparison
+        hb.check_status()
+        for _ in range(5):
+            step_nccl()
+        barrier()
+        e0.record(stream)
+        for _ in range(args.steps):
+            step_nccl()
+        e1.record(stream)
+        barrier()
+        ms_nccl = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
 
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    t = torch.tensor([ms, ms_nccl or 0.0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    ms, ms_nccl = float(t[0].item()), (float(t[1].item()) if ms_nccl else None)
     ms_per_step = ms / args.steps
 
-    # ---- end to end through the host-buffer entry point (rank-local inputs and outputs, pinned memory)
+    # ---- end to end through the host-buffer entry point: every step copies all inputs from pinned host memory,
+    # quantizes, runs the recorded batch, (all-gathers) and copies the results back to pinned host memory.
     e2e_ms, h2d, d2h = None, 0, 0
     if not args.quick:
-        hosts_out = [torch.zeros((M, W.n_rows), dtype=torch.float32).pin_memory() for W, _ in weights]
-        xs = [x_host[k].numpy() for _, _, k in cfg["shapes"]] * cfg["layers"]
-        outs_np = [o.numpy() for o in hosts_out]
-        import ctypes as C
-        from hearth_b200 import lib as L
-        lib = L.load()
+        xh, oh = x_pinned.numpy(), out_pinned.numpy()
+        out_all_pinned = torch.zeros((world * M, slice_rows), dtype=torch.float32).pin_memory() if world > 1 else None
+        empty = np.zeros(0, dtype=np.float32)
+        full_pinned = torch.zeros((M, full_cols), dtype=torch.float32).pin_memory() if use_fused else None
 
         def e2e_step():
-            for (W, _), x, o in zip(weights, xs, outs_np):
-                if W.n_rows:
-                    rc = lib.hb200_matmul_f32(W._h, C.c_void_p(x.ctypes.data), M, C.c_void_p(o.ctypes.data))
-                    if rc:
-                        hb.check(rc)
-        e2e_steps = max(1, min(args.steps, 5 if M <= 4 else 1))
+            if world == 1:
+                batch.run_host(xh, out_local, oh)
+            elif use_fused:
+                fused.run_host(xh, full_local, full_pinned.numpy())  # the kernel itself assembles every rank's outputs
+            else:
+                batch.run_host(xh, out_local, empty)           # inputs in, compute; results stay on the device
+                dist.all_gather_into_tensor(out_all, out_local)
+                out_all_pinned.copy_(out_all, non_blocking=True)
+                torch.cuda.synchronize()
+        e2e_steps = max(1, min(args.steps, 20 if M <= 4 else 3))
         e2e_step()
         barrier()
         t0 = time.perf_counter()
@@ -328,8 +375,8 @@ def run_ours(args, cfg, rank, world, local_rank):
         if world > 1:
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e2e_ms = float(tt.item()) / e2e_steps * 1e3
-        h2d = sum(x.nbytes for (W, _), x in zip(weights, xs) if W.n_rows)
-        d2h = sum(o.nbytes for o in outs_np)
+        h2d = batch.input_floats * 4
+        d2h = (full_pinned.numel() if use_fused else (out_all_pinned.numel() if world > 1 else out_pinned.numel())) * 4
 
     if rank == 0:
         ab = algorithmic_bytes(cfg)
@@ -356,15 +403,19 @@ def run_ours(args, cfg, rank, world, local_rank):
             "dtype": "int8 x {1,2}-bit -> int32, fp32 scales", "data": "synthetic",
             "config": {"workload": args.workload, "format": {41: "Q1_0", 42: "Q2_0", 142: "PQ2_0", 8: "Q8_0"}.get(dtype, str(dtype)),
                        "tokens": M, "layers": cfg["layers"], "matrices_per_step": cfg["layers"] * len(cfg["shapes"]),
-                       "weight_bytes": ab["weights"], "parallelism": f"rows/{world}" + (" + NCCL all-gather of output slices" if world > 1 else ""),
+                       "weight_bytes": ab["weights"], "parallelism": f"rows/{world}" + ((" + outputs stored to all ranks from the kernel (peer stores, flag exchange)" if use_fused
+                                                                else " + NCCL all-gather of output slices") if world > 1 else ""),
                        "l2": "per-GPU inputs exceed the 126 MB L2" if ab["weights"] / world > 126e6 else "inputs fit in L2",
                        "launch": "one recorded batch (work list) per step"},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "roofline": roof,
             "e2e": ({"value": (total_ops(cfg) / (e2e_ms * 1e-3) / 1e12) if is_prefill(cfg) else ab["weights"] / (e2e_ms * 1e-3) / 1e9, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                     "ms_per_step": e2e_ms, "call": "hb200_matmul_f32 per matrix, pinned host buffers"} if e2e_ms else None),
+                     "ms_per_step": e2e_ms, "call": "hb200_batch_run_host: one H2D of the step's inputs, list quantize, recorded batch, one D2H; pinned host buffers"} if e2e_ms else None),
         }
+        if ms_nccl:
+            line["nccl_allgather_variant"] = {"ms_per_step": ms_nccl / args.steps,
+                                              "value": ab["weights"] / (ms_nccl / args.steps * 1e-3) / 1e9, "unit": UNIT}
         if world == 1 and not args.no_cpu and not args.quick:
             arm = CpuArm(cfg, 0, 1)
             t0 = time.perf_counter()
@@ -389,6 +440,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(synth.CONFIGS))
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: 'fused' stores every output into all ranks' buffers from the kernel (peer stores + flag "
+                         "exchange); 'nccl' runs an all-gather of the output slices after the kernel")
     ap.add_argument("--quick", action="store_true",
                     help="kernel timing only: no clock-sampling burst, no end-to-end leg, no CPU leg (for profiler runs)")
     args = ap.parse_args()

@@ -245,11 +245,27 @@ class Batch:
         check(_l.load().hb200_batch_add(self._h, w._h, a._h, seq_len, C.c_void_p(out_dev.data_ptr()),
                                         ld_out if ld_out is not None else w.n_rows))
 
+    def set_peers(self, my_rank: int, buffers: list, wait: bool = True) -> None:
+        """Row-sharded run: buffers[r] is rank r's PeerBuffer (local or opened); outputs are stored into all of them."""
+        arr = (C.c_void_p * len(buffers))(*[C.c_void_p(b.ptr) for b in buffers])
+        check(_l.load().hb200_batch_set_peers(self._h, len(buffers), my_rank, arr, 1 if wait else 0))
+        self._keep.append(buffers)
+
     def seal(self) -> None:
         check(_l.load().hb200_batch_seal(self._h))
 
     def launch(self, stream=None) -> None:
         check(_l.load().hb200_batch_launch(self._h, _stream_ptr(stream)))
+
+    @property
+    def input_floats(self) -> int:
+        return int(_l.load().hb200_batch_input_floats(self._h))
+
+    def run_host(self, x_host: np.ndarray, out_dev, out_host: np.ndarray) -> None:
+        """One recorded step from host memory: x_host (float32, input_floats long) holds every distinct activation's
+        rows in order of first use; out_dev is the device tensor the ops write into, copied whole into out_host."""
+        assert x_host.dtype == np.float32 and x_host.size >= self.input_floats and out_host.dtype == np.float32
+        check(_l.load().hb200_batch_run_host(self._h, _np_ptr(x_host), C.c_void_p(out_dev.data_ptr()), out_host.size, _np_ptr(out_host)))
 
     @property
     def launch_count(self) -> int:
@@ -260,3 +276,38 @@ class Batch:
             check(_l.load().hb200_batch_free(self._h))
             self._h = None
             self._keep = []
+
+
+class PeerBuffer:
+    """An output buffer other ranks can store into (hb200_peer_alloc / hb200_peer_open)."""
+
+    def __init__(self, ptr: int, n_floats: int, handle: bytes | None, owned: bool):
+        self.ptr, self.n_floats, self.handle, self.owned = ptr, n_floats, handle, owned
+
+    @classmethod
+    def alloc(cls, n_floats: int) -> "PeerBuffer":
+        p = C.c_void_p()
+        h = (C.c_uint8 * 64)()
+        check(_l.load().hb200_peer_alloc(n_floats * 4, C.byref(p), h))
+        return cls(int(p.value), n_floats, bytes(h), True)
+
+    @classmethod
+    def open(cls, handle: bytes, n_floats: int) -> "PeerBuffer":
+        p = C.c_void_p()
+        h = (C.c_uint8 * 64).from_buffer_copy(handle)
+        check(_l.load().hb200_peer_open(h, C.byref(p)))
+        return cls(int(p.value), n_floats, None, False)
+
+    def tensor(self, device):
+        """The output area as a torch float32 tensor (no copy)."""
+        return _as_torch_f32(self.ptr, self.n_floats, device)
+
+    def close(self) -> None:
+        if self.ptr:
+            L = _l.load()
+            check(L.hb200_peer_free(C.c_void_p(self.ptr)) if self.owned else L.hb200_peer_close(C.c_void_p(self.ptr)))
+            self.ptr = 0
+
+
+def check_status() -> None:
+    check(_l.load().hb200_check_status())

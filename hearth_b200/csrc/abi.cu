@@ -73,6 +73,17 @@ struct hb200_batch {
     std::vector<BatchGroup> groups;
     std::vector<BatchEntry> kquant;  // K-quant ops launch on their own
     std::vector<BatchEntry> tensor;  // ops with five or more tokens: tensor-core kernel, one launch each
+    // host-input path: distinct activations in order of first use, a staging buffer for their f32 rows
+    std::vector<hb200_act_t> acts;
+    std::vector<size_t> act_seq;       // rows used of each
+    std::vector<size_t> act_offset;    // float offset of each inside x_stage
+    size_t input_floats = 0;
+    float* x_stage = nullptr;
+    QuantDesc* qdescs_dev = nullptr;
+    int q_max_chunks = 0, q_max_seq = 0, n_qacts = 0;
+    bool has_kquant_inputs = false;
+    PeerTable peers = {};   // n > 1: outputs go to every rank's buffer
+    int epoch = 0;
     bool sealed = false;
 };
 
@@ -701,6 +712,11 @@ extern "C" int hb200_batch_add(hb200_batch_t b, hb200_weight_t w, hb200_act_t a,
     BatchEntry e{w, a, seq_len, out_dev, ld_out};
     if (w->kind == KIND_Q4K || w->kind == KIND_Q6K) b->kquant.push_back(e);
     else b->entries.push_back(e);
+    size_t ai = 0;
+    for (; ai < b->acts.size(); ai++)
+        if (b->acts[ai] == a) break;
+    if (ai == b->acts.size()) { b->acts.push_back(a); b->act_seq.push_back(seq_len); }
+    else if (seq_len > b->act_seq[ai]) b->act_seq[ai] = seq_len;
     return HB200_OK;
     HB_GUARD_END
 }
@@ -709,6 +725,14 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
     HB_GUARD_BEGIN
     if (!b) { set_error("null batch"); return HB200_ERR_NULL; }
     if (b->sealed) return HB200_OK;
+    if (b->peers.n > 1) {
+        if (!b->kquant.empty()) { set_error("peer-store batches carry Q8_0-activation ops only"); return HB200_ERR_UNSUPPORTED; }
+        for (const BatchEntry& e : b->entries)
+            if (e.seq_len >= (size_t)GEMM_TC_MIN_TOKENS && (e.w->kind == KIND_Q1 || e.w->kind == KIND_Q2)) {
+                set_error("peer-store batches take at most %d tokens per op", GEMM_TC_MIN_TOKENS - 1);
+                return HB200_ERR_UNSUPPORTED;
+            }
+    }
     // One launch per (kind, tokens-per-op) combination.
     struct Acc { std::vector<DotOp> first; std::vector<DotItem> second; std::vector<int> cost; };
     std::map<std::pair<int, int>, Acc> acc;
@@ -757,6 +781,40 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
         HB_CUDA(cudaMemcpy(g.chunks_dev, chunks.data(), chunks.size() * sizeof(int), cudaMemcpyHostToDevice));
         b->groups.push_back(g);
     }
+    // Host-input path: one staging buffer for every distinct activation's f32 rows and one descriptor list for the
+    // list quantizer.  K-quant ops read f32 from the activation's own area, so those rows are also copied there.
+    {
+        std::vector<QuantDesc> qd;
+        size_t off = 0;
+        for (size_t i = 0; i < b->acts.size(); i++) {
+            hb200_act* a = b->acts[i];
+            b->act_offset.push_back(off);
+            off += b->act_seq[i] * a->n_cols;
+            off = (off + 3) & ~(size_t)3;  // keep every activation 16-byte aligned in the staging buffer
+        }
+        b->input_floats = off;
+        if (off) HB_CUDA(cudaMalloc(&b->x_stage, off * sizeof(float)));
+        for (size_t i = 0; i < b->acts.size(); i++) {
+            hb200_act* a = b->acts[i];
+            bool q8_user = false;
+            for (const BatchEntry& e : b->entries) q8_user = q8_user || e.a == a;
+            for (const BatchEntry& e : b->tensor) q8_user = q8_user || e.a == a;
+            for (const BatchEntry& e : b->kquant) b->has_kquant_inputs = b->has_kquant_inputs || e.a == a;
+            if (!q8_user) continue;
+            QuantDesc d;
+            d.x = b->x_stage + b->act_offset[i];
+            d.q = a->q; d.d = a->d; d.sums = a->sums;
+            d.n_cols = (int)a->n_cols; d.seq_len = (int)b->act_seq[i]; d.ld_q = a->ld_q; d.ld_b = a->ld_b;
+            qd.push_back(d);
+            if (a->ld_q / 1024 > b->q_max_chunks) b->q_max_chunks = a->ld_q / 1024;
+            if ((int)b->act_seq[i] > b->q_max_seq) b->q_max_seq = (int)b->act_seq[i];
+        }
+        b->n_qacts = (int)qd.size();
+        if (!qd.empty()) {
+            HB_CUDA(cudaMalloc(&b->qdescs_dev, qd.size() * sizeof(QuantDesc)));
+            HB_CUDA(cudaMemcpy(b->qdescs_dev, qd.data(), qd.size() * sizeof(QuantDesc), cudaMemcpyHostToDevice));
+        }
+    }
     b->sealed = true;
     return HB200_OK;
     HB_GUARD_END
@@ -770,7 +828,16 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
     if (!b->sealed) { set_error("batch is not sealed"); return HB200_ERR_BAD_SHAPE; }
     cudaStream_t st = (cudaStream_t)stream;
     for (const BatchGroup& g : b->groups)
-        if ((rc = launch_gemv_dp4a(g.kind, g.m, false, g.ops_dev, g.items_dev, g.chunks_dev, g.grid, g.n_items, nullptr, st))) return rc;
+    {
+        PeerTable pt = b->peers;
+        if (pt.n > 1) {
+            pt.epoch = ++b->epoch;
+            pt.status = g_ctx.d_status;
+        }
+        if ((rc = launch_gemv_dp4a(g.kind, g.m, false, g.ops_dev, g.items_dev, g.chunks_dev, g.grid, g.n_items, nullptr, st,
+                                   pt.n > 1 ? &pt : nullptr)))
+            return rc;
+    }
     for (const BatchEntry& e : b->tensor)
         if ((rc = launch_gemm_tc(e.w->kind, e.a->qmap, e.w->bits, e.w->scales, e.a->d, e.a->ld_b, (int)e.w->n_rows, e.w->nb,
                                  (int)e.seq_len, e.out, (int)e.ld_out, g_ctx.d_status, st)))
@@ -779,6 +846,31 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
         if ((rc = launch_kquant_gemv(e.w->kind, e.w->raw, e.w->row_bytes, (int)e.w->n_rows, (int)e.w->n_cols, e.a->x, (int)e.seq_len,
                                      e.out, (int)e.ld_out, st)))
             return rc;
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" size_t hb200_batch_input_floats(hb200_batch_t b) { return (b && b->sealed) ? b->input_floats : 0; }
+
+extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const float* out_dev_base, size_t out_floats,
+                                    float* out_host) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!b) { set_error("null batch"); return HB200_ERR_NULL; }
+    if (!b->sealed) { set_error("batch is not sealed"); return HB200_ERR_BAD_SHAPE; }
+    if ((b->input_floats && !x_host) || (out_floats && (!out_dev_base || !out_host))) { set_error("null buffer"); return HB200_ERR_NULL; }
+    cudaStream_t st = g_ctx.stream;
+    if (b->input_floats) HB_CUDA(cudaMemcpyAsync(b->x_stage, x_host, b->input_floats * sizeof(float), cudaMemcpyHostToDevice, st));
+    if (b->has_kquant_inputs)
+        for (size_t i = 0; i < b->acts.size(); i++)
+            HB_CUDA(cudaMemcpyAsync(b->acts[i]->x, b->x_stage + b->act_offset[i], b->act_seq[i] * b->acts[i]->n_cols * sizeof(float),
+                                    cudaMemcpyDeviceToDevice, st));
+    if ((rc = launch_quantize_q8_0_list(b->qdescs_dev, b->n_qacts, b->q_max_chunks, b->q_max_seq, st))) return rc;
+    if ((rc = hb200_batch_launch(b, st))) return rc;
+    if (out_floats) HB_CUDA(cudaMemcpyAsync(out_host, out_dev_base, out_floats * sizeof(float), cudaMemcpyDeviceToHost, st));
+    HB_CUDA(cudaStreamSynchronize(st));
+    if (!b->tensor.empty()) return check_device_status();
     return HB200_OK;
     HB_GUARD_END
 }
@@ -796,8 +888,88 @@ extern "C" int hb200_batch_free(hb200_batch_t b) {
         if (g.items_dev) cudaFree(g.items_dev);
         if (g.chunks_dev) cudaFree(g.chunks_dev);
     }
+    if (b->x_stage) cudaFree(b->x_stage);
+    if (b->qdescs_dev) cudaFree(b->qdescs_dev);
     delete b;
     return HB200_OK;
+    HB_GUARD_END
+}
+
+// ------------------------------------------------------------ peer buffers --
+
+extern "C" int hb200_peer_alloc(size_t bytes, void** data_dev, uint8_t handle[HB200_PEER_HANDLE_BYTES]) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!data_dev || !handle) { set_error("null output"); return HB200_ERR_NULL; }
+    static_assert(sizeof(cudaIpcMemHandle_t) == HB200_PEER_HANDLE_BYTES, "IPC handle size");
+    char* base = nullptr;
+    HB_CUDA(cudaMalloc(&base, bytes + PEER_CTRL_BYTES));
+    HB_CUDA(cudaMemset(base, 0, bytes + PEER_CTRL_BYTES));
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, base);
+    if (e != cudaSuccess) { cudaFree(base); set_error("cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e)); return HB200_ERR_CUDA; }
+    memcpy(handle, &h, sizeof(h));
+    *data_dev = base + PEER_CTRL_BYTES;
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_peer_free(void* data_dev) {
+    HB_GUARD_BEGIN
+    if (!data_dev) return HB200_OK;
+    HB_CUDA(cudaFree(static_cast<char*>(data_dev) - PEER_CTRL_BYTES));
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_peer_open(const uint8_t handle[HB200_PEER_HANDLE_BYTES], void** data_dev) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!data_dev || !handle) { set_error("null argument"); return HB200_ERR_NULL; }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* base = nullptr;
+    HB_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+    *data_dev = static_cast<char*>(base) + PEER_CTRL_BYTES;
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_peer_close(void* data_dev) {
+    HB_GUARD_BEGIN
+    if (!data_dev) return HB200_OK;
+    HB_CUDA(cudaIpcCloseMemHandle(static_cast<char*>(data_dev) - PEER_CTRL_BYTES));
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_batch_set_peers(hb200_batch_t b, int n_ranks, int my_rank, void* const* data, int wait) {
+    HB_GUARD_BEGIN
+    if (!b || !data) { set_error("null argument"); return HB200_ERR_NULL; }
+    if (b->sealed) { set_error("set the peers before sealing the batch"); return HB200_ERR_BAD_SHAPE; }
+    if (n_ranks < 1 || n_ranks > MAX_PEERS || my_rank < 0 || my_rank >= n_ranks) {
+        set_error("rank %d of %d: at most %d ranks", my_rank, n_ranks, MAX_PEERS);
+        return HB200_ERR_BAD_SHAPE;
+    }
+    PeerTable pt = {};
+    for (int r = 0; r < n_ranks; r++) {
+        if (!data[r]) { set_error("null buffer for rank %d", r); return HB200_ERR_NULL; }
+        pt.data[r] = static_cast<float*>(data[r]);
+    }
+    pt.n = n_ranks; pt.me = my_rank; pt.wait = wait ? 1 : 0;
+    b->peers = pt;
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_check_status(void) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    HB_CUDA(cudaDeviceSynchronize());
+    return check_device_status();
     HB_GUARD_END
 }
 

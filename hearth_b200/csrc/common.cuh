@@ -55,6 +55,22 @@ struct DotOp {
     int ld_b;              // floats between tokens in ad / asum
 };
 
+// Peer buffers of a row-sharded launch.  Every rank owns one buffer of identical layout: a 512-byte control block
+// (int flags[8] at byte 0: flags[r] = last epoch rank r finished writing here; int counter at byte 256) followed by the
+// output area.  A kernel stores each output value at the same offset in every rank's output area (plain peer stores),
+// then the last CTA publishes `epoch` in every rank's flags[me] and, if `wait` is set, waits with a bound until all
+// ranks have published theirs here.
+constexpr int MAX_PEERS = 8;
+constexpr int PEER_CTRL_BYTES = 512;
+struct PeerTable {
+    float* data[MAX_PEERS];  // output areas; data[me] is local
+    int n;                   // ranks (0 or 1: not sharded, plain local stores)
+    int me;
+    int epoch;
+    int wait;
+    int* status;             // device word for an expired wait
+};
+
 // One work item of a batched launch: panel `y` of op `x`.
 typedef int2 DotItem;
 
@@ -71,7 +87,17 @@ void set_error(const char* fmt, ...);
 
 // ---- launchers implemented in the kernel translation units ----------------
 
+// One activation of a list quantization: f32 rows at x -> the Q8_0 planes q / d / sums.
+struct QuantDesc {
+    const float* x;
+    int8_t* q;
+    float* d;
+    float* sums;
+    int n_cols, seq_len, ld_q, ld_b;
+};
+
 // quantize.cu
+int launch_quantize_q8_0_list(const QuantDesc* descs_dev, int n_acts, int max_chunks, int max_seq, cudaStream_t st);
 int launch_quantize_q8_0(const float* x, int seq_len, int n_cols, int8_t* q, float* d, float* sums, int ld_q, int ld_b,
                          uint8_t* raw_out, size_t raw_stride, cudaStream_t st);
 int launch_load_q8_0(const uint8_t* raw, size_t raw_stride, int seq_len, int n_cols, int8_t* q, float* d, float* sums,
@@ -88,8 +114,9 @@ constexpr int GEMV_MAX_M = 4;  // tokens one dp4a launch handles per op
 // Either an op list in device memory (ops_dev / items_dev, with chunks_dev[grid + 1] giving each CTA its contiguous,
 // cost-balanced run of items; items of one op must be consecutive panels), or, with ops_dev == nullptr, the one op
 // `single` (host memory, passed by value to the grid) whose n_items panels are split evenly over `grid` CTAs.
+// `peers` (may be null) turns the output stores into stores to every rank's buffer plus the closing flag exchange.
 int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const DotItem* items_dev, const int* chunks_dev,
-                     int grid, int n_items, const DotOp* single, cudaStream_t st);
+                     int grid, int n_items, const DotOp* single, cudaStream_t st, const PeerTable* peers = nullptr);
 int gemv_dp4a_ctas_per_sm(int m);  // resident CTAs per SM the kernel for m tokens is built for
 int gemv_dp4a_prepare();  // sets the dynamic shared-memory attributes once
 

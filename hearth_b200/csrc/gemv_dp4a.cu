@@ -80,7 +80,7 @@ constexpr float MAGIC_F = 12582912.0f;
 template <int KIND, int M, bool INT_OUT>
 __global__ void __launch_bounds__(THREADS, (M <= 2 ? 2 : 1))
 gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ items, const int* __restrict__ chunks,
-                 int n_items, const __grid_constant__ DotOp single) {
+                 int n_items, const __grid_constant__ DotOp single, const __grid_constant__ PeerTable peers) {
     using S = Smem<KIND, M>;
     constexpr int RPG = S::RPG;
     constexpr int RP = S::RP;
@@ -162,7 +162,18 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
                     }
                     if (last) {
                         const int grow = panel * RP + row;
-                        if (grow < op.n_rows) op.out[(size_t)m * op.ld_out + grow] = acc;
+                        if (grow < op.n_rows) {
+                            float* dst = op.out + (size_t)m * op.ld_out + grow;
+                            if (peers.n > 1) {
+                                // the same offset inside every rank's output area: one local and n-1 peer stores
+                                const ptrdiff_t off = dst - peers.data[peers.me];
+#pragma unroll
+                                for (int p = 0; p < MAX_PEERS; p++)
+                                    if (p < peers.n) peers.data[p][off] = acc;
+                            } else {
+                                *dst = acc;
+                            }
+                        }
                         acc = 0.0f;
                     }
                     run[k] = acc;
@@ -289,14 +300,48 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
             replay(ppanel, pr, (total - 1) & 1);
         }
     }
+
+    if (!INT_OUT && peers.n > 1) {
+        // Publish: every CTA makes its peer stores visible system-wide, the last one to finish raises this rank's flag
+        // in every rank's control block, then (optionally) waits, with a bound, for the other ranks' flags here.
+        __threadfence_system();
+        __syncthreads();
+        if (tid == 0) {
+            int* ctrl_me = reinterpret_cast<int*>(reinterpret_cast<char*>(peers.data[peers.me]) - PEER_CTRL_BYTES);
+            int* counter = ctrl_me + 64;
+            const int prev = atomicAdd(counter, 1);
+            if (prev == (int)gridDim.x - 1) {
+                *counter = 0;
+                __threadfence_system();
+                for (int p = 0; p < peers.n; p++) {
+                    volatile int* f = reinterpret_cast<volatile int*>(reinterpret_cast<char*>(peers.data[p]) - PEER_CTRL_BYTES);
+                    f[peers.me] = peers.epoch;
+                }
+                if (peers.wait) {
+                    volatile int* mine = reinterpret_cast<volatile int*>(ctrl_me);
+                    for (int r = 0; r < peers.n; r++) {
+                        unsigned spins = 0;
+                        while (mine[r] - peers.epoch < 0) {  // epochs only grow; the difference also survives wrap-around
+                            if (++spins > (1u << 24)) {
+                                atomicCAS(peers.status, 0, 100 + r);
+                                break;
+                            }
+                            __nanosleep(64);
+                        }
+                    }
+                    __threadfence_system();
+                }
+            }
+        }
+    }
 }
 
 template <int KIND, int M, bool INT_OUT>
 int launch_one(const DotOp* ops, const DotItem* items, const int* chunks, int grid, int n_items, const DotOp& single,
-               cudaStream_t st) {
+               const PeerTable& peers, cudaStream_t st) {
     using S = Smem<KIND, M>;
     if (grid <= 0 || n_items <= 0) return 0;
-    gemv_dp4a_kernel<KIND, M, INT_OUT><<<grid, THREADS, sizeof(S), st>>>(ops, items, chunks, n_items, single);
+    gemv_dp4a_kernel<KIND, M, INT_OUT><<<grid, THREADS, sizeof(S), st>>>(ops, items, chunks, n_items, single, peers);
     HB_CUDA(cudaGetLastError());
     return 0;
 }
@@ -311,16 +356,16 @@ int prepare_one() {
 
 template <int KIND>
 int launch_kind(int m, bool int_out, const DotOp* ops, const DotItem* items, const int* chunks, int grid, int n_items,
-                const DotOp& single, cudaStream_t st) {
+                const DotOp& single, const PeerTable& peers, cudaStream_t st) {
     if (int_out) {
         if (m != 1) { set_error("integer block-dot output runs one token per launch"); return -4; }
-        return launch_one<KIND, 1, true>(ops, items, chunks, grid, n_items, single, st);
+        return launch_one<KIND, 1, true>(ops, items, chunks, grid, n_items, single, peers, st);
     }
     switch (m) {
-        case 1: return launch_one<KIND, 1, false>(ops, items, chunks, grid, n_items, single, st);
-        case 2: return launch_one<KIND, 2, false>(ops, items, chunks, grid, n_items, single, st);
-        case 3: return launch_one<KIND, 3, false>(ops, items, chunks, grid, n_items, single, st);
-        case 4: return launch_one<KIND, 4, false>(ops, items, chunks, grid, n_items, single, st);
+        case 1: return launch_one<KIND, 1, false>(ops, items, chunks, grid, n_items, single, peers, st);
+        case 2: return launch_one<KIND, 2, false>(ops, items, chunks, grid, n_items, single, peers, st);
+        case 3: return launch_one<KIND, 3, false>(ops, items, chunks, grid, n_items, single, peers, st);
+        case 4: return launch_one<KIND, 4, false>(ops, items, chunks, grid, n_items, single, peers, st);
         default: set_error("gemv_dp4a: m=%d outside 1..%d", m, GEMV_MAX_M); return -4;
     }
 }
@@ -349,15 +394,17 @@ int gemv_dp4a_prepare() {
 int gemv_dp4a_ctas_per_sm(int m) { return m <= 2 ? 2 : 1; }
 
 int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const DotItem* items_dev, const int* chunks_dev,
-                     int grid, int n_items, const DotOp* single, cudaStream_t st) {
+                     int grid, int n_items, const DotOp* single, cudaStream_t st, const PeerTable* peers) {
     static const DotOp none = {};
+    static const PeerTable no_peers = {};
     const DotOp& one = single ? *single : none;
+    const PeerTable& pt = peers ? *peers : no_peers;
     if (!ops_dev && !single) { set_error("gemv_dp4a: neither an op list nor a single op"); return -5; }
     if (ops_dev && !chunks_dev) { set_error("gemv_dp4a: a list launch needs chunk boundaries"); return -5; }
     switch (kind) {
-        case KIND_Q1: return launch_kind<KIND_Q1>(m, int_out, ops_dev, items_dev, chunks_dev, grid, n_items, one, st);
-        case KIND_Q2: return launch_kind<KIND_Q2>(m, int_out, ops_dev, items_dev, chunks_dev, grid, n_items, one, st);
-        case KIND_Q8: return launch_kind<KIND_Q8>(m, int_out, ops_dev, items_dev, chunks_dev, grid, n_items, one, st);
+        case KIND_Q1: return launch_kind<KIND_Q1>(m, int_out, ops_dev, items_dev, chunks_dev, grid, n_items, one, pt, st);
+        case KIND_Q2: return launch_kind<KIND_Q2>(m, int_out, ops_dev, items_dev, chunks_dev, grid, n_items, one, pt, st);
+        case KIND_Q8: return launch_kind<KIND_Q8>(m, int_out, ops_dev, items_dev, chunks_dev, grid, n_items, one, pt, st);
         default: set_error("gemv_dp4a: kind %d has no Q8_0 dot", kind); return -7;
     }
 }

@@ -23,15 +23,12 @@ __device__ __forceinline__ int quant_one(float x, float scale) {
     return (int)r;
 }
 
-// grid (ld_q/1024, seq_len), block 256.  Thread t handles columns c0..c0+3;
-// eight consecutive threads share one 32-column block.
+// One thread's share of the quantizer: columns c0..c0+3 of token m; eight consecutive threads share one
+// 32-column block (all 32 lanes of the warp must call this together: it shuffles).
 template <bool RAW_OUT>
-__global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float* __restrict__ x, int n_cols,
-                                                            int8_t* __restrict__ q, float* __restrict__ d,
-                                                            float* __restrict__ sums, int ld_q, int ld_b,
-                                                            uint8_t* __restrict__ raw, size_t raw_stride) {
-    const int m = blockIdx.y;
-    const int c0 = blockIdx.x * 1024 + threadIdx.x * 4;
+__device__ __forceinline__ void quantize_thread(const float* __restrict__ x, int n_cols, int m, int c0, int8_t* __restrict__ q,
+                                                float* __restrict__ d, float* __restrict__ sums, int ld_q, int ld_b,
+                                                uint8_t* __restrict__ raw, size_t raw_stride) {
     const float* xr = x + (size_t)m * n_cols;
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     const bool vec_ok = ((n_cols & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
@@ -83,6 +80,23 @@ __global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float* __restr
 #pragma unroll
         for (int i = 0; i < 4; i++) rb[2 + i0 + i] = (uint8_t)(qi[i] & 0xff);
     }
+}
+
+// grid (ld_q/1024, seq_len), block 256.
+template <bool RAW_OUT>
+__global__ void __launch_bounds__(256) quantize_q8_0_kernel(const float* __restrict__ x, int n_cols,
+                                                            int8_t* __restrict__ q, float* __restrict__ d,
+                                                            float* __restrict__ sums, int ld_q, int ld_b,
+                                                            uint8_t* __restrict__ raw, size_t raw_stride) {
+    quantize_thread<RAW_OUT>(x, n_cols, blockIdx.y, blockIdx.x * 1024 + threadIdx.x * 4, q, d, sums, ld_q, ld_b, raw, raw_stride);
+}
+
+// Many activations in one launch: grid (max chunks, max seq_len, n_acts); CTAs outside an activation's extent exit.
+__global__ void __launch_bounds__(256) quantize_q8_0_list_kernel(const QuantDesc* __restrict__ descs) {
+    const QuantDesc qd = descs[blockIdx.z];
+    if ((int)blockIdx.y >= qd.seq_len || (int)blockIdx.x * 1024 >= qd.ld_q) return;
+    quantize_thread<false>(qd.x, qd.n_cols, blockIdx.y, blockIdx.x * 1024 + threadIdx.x * 4, qd.q, qd.d, qd.sums, qd.ld_q, qd.ld_b,
+                           nullptr, 0);
 }
 
 // Reference byte layout -> planes.  Same grid shape as the quantizer.
@@ -148,6 +162,14 @@ int launch_quantize_q8_0(const float* x, int seq_len, int n_cols, int8_t* q, flo
         quantize_q8_0_kernel<true><<<grid, 256, 0, st>>>(x, n_cols, q, d, sums, ld_q, ld_b, raw_out, raw_stride);
     else
         quantize_q8_0_kernel<false><<<grid, 256, 0, st>>>(x, n_cols, q, d, sums, ld_q, ld_b, nullptr, 0);
+    HB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_quantize_q8_0_list(const QuantDesc* descs_dev, int n_acts, int max_chunks, int max_seq, cudaStream_t st) {
+    if (n_acts <= 0 || max_chunks <= 0 || max_seq <= 0) return 0;
+    dim3 grid(max_chunks, max_seq, n_acts);
+    quantize_q8_0_list_kernel<<<grid, 256, 0, st>>>(descs_dev);
     HB_CUDA(cudaGetLastError());
     return 0;
 }

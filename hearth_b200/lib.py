@@ -60,6 +60,14 @@ SIGNATURES = {
     "hb200_batch_launch": (_int, [_vp, _vp]),
     "hb200_batch_free": (_int, [_vp]),
     "hb200_batch_launch_count": (_int, [_vp]),
+    "hb200_batch_run_host": (_int, [_vp, _vp, _vp, _sz, _vp]),
+    "hb200_batch_input_floats": (_sz, [_vp]),
+    "hb200_peer_alloc": (_int, [_sz, C.POINTER(_vp), _vp]),
+    "hb200_peer_free": (_int, [_vp]),
+    "hb200_peer_open": (_int, [_vp, C.POINTER(_vp)]),
+    "hb200_peer_close": (_int, [_vp]),
+    "hb200_batch_set_peers": (_int, [_vp, _int, _int, C.POINTER(_vp), _int]),
+    "hb200_check_status": (_int, []),
     "hb200_stream_synchronize": (_int, [_vp]),
 }
 

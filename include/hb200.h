@@ -211,6 +211,48 @@ HB200_API int hb200_batch_launch(hb200_batch_t b, void *stream);
 HB200_API int hb200_batch_free(hb200_batch_t b);
 /* Number of kernel launches one hb200_batch_launch performs. */
 HB200_API int hb200_batch_launch_count(hb200_batch_t b);
+/* A whole recorded step from host memory, the shape of GpuCompute's
+ * upload_f32 -> begin_batch .. end_batch -> one readback_f32
+ * (hearth-compute/src/lib.rs:206-251): x_host holds, for every distinct
+ * activation of the batch in order of first use, its f32 rows
+ * [seq_len][n_cols] back to back (hb200_batch_input_floats() floats in all).
+ * They are copied to the device in one transfer, quantized in one launch, the
+ * batch runs, and out_floats floats starting at out_dev_base (the caller's
+ * device buffer that the batch's ops write into) are copied to out_host.
+ * Synchronous.  Ops on Q4_K / Q6_K weights read the f32 rows directly. */
+HB200_API int hb200_batch_run_host(hb200_batch_t b, const float *x_host, const float *out_dev_base, size_t out_floats,
+                                   float *out_host);
+HB200_API size_t hb200_batch_input_floats(hb200_batch_t b);
+
+/* ---- row-sharded multi-GPU outputs --------------------------------------- */
+
+/* The reference has no multi-device path; its row split over worker threads
+ * (hearth-llm/src/pool.rs:321-323) is applied here across GPUs, one process
+ * per GPU.  Instead of gathering output slices with a collective after the
+ * kernel, a sharded batch can store every output value straight into the
+ * same place of every rank's output buffer over NVLink (ordinary peer stores,
+ * no multicast) and close with a flag exchange.
+ *
+ * hb200_peer_alloc: device buffer of `bytes` for the assembled outputs plus a
+ *   small control block; `handle` (64 bytes) identifies it to other processes.
+ * hb200_peer_open / hb200_peer_close: map / unmap another rank's buffer.
+ * hb200_batch_set_peers: before hb200_batch_seal.  data[r] is rank r's
+ *   buffer as seen from this process (data[my_rank] the local one); every op
+ *   of the batch must write inside data[my_rank].  With wait != 0 each launch
+ *   returns only after all ranks' outputs have landed here (bounded wait,
+ *   HB200_ERR_TIMEOUT is reported by the next synchronising call); with
+ *   wait == 0 the kernel only publishes.  All ranks must launch the batch the
+ *   same number of times. */
+#define HB200_PEER_HANDLE_BYTES 64
+#define HB200_MAX_PEERS 8
+HB200_API int hb200_peer_alloc(size_t bytes, void **data_dev, uint8_t handle[HB200_PEER_HANDLE_BYTES]);
+HB200_API int hb200_peer_free(void *data_dev);
+HB200_API int hb200_peer_open(const uint8_t handle[HB200_PEER_HANDLE_BYTES], void **data_dev);
+HB200_API int hb200_peer_close(void *data_dev);
+HB200_API int hb200_batch_set_peers(hb200_batch_t b, int n_ranks, int my_rank, void *const *data, int wait);
+/* Reads and clears the device status word: HB200_OK, or HB200_ERR_TIMEOUT if a
+ * bounded device-side wait expired since the last check.  Synchronises. */
+HB200_API int hb200_check_status(void);
 
 /* ---- stream helper ------------------------------------------------------ */
 HB200_API int hb200_stream_synchronize(void *stream);

@@ -356,3 +356,44 @@ def test_full_size_linearity_of_integer_dots(hb, oracle):
             assert (da[r] == oracle.block_dots_i32(PQ2_0, w[r], raw(a), n_cols)).all()
     finally:
         W.free()
+
+
+def test_batch_run_from_host_buffers(hb, oracle):
+    """hb200_batch_run_host: all inputs in one host buffer, one readback; K-quant and Q8_0-activation ops together."""
+    import torch
+    dev = torch.device("cuda:0")
+    seq = 2
+    specs = [(Q2_0, 300, 2048, 0), (Q1_0, 64, 2048, 0), (Q2_0, 100, 1152, 1), (Q6_K, 24, 512, 2), (Q1_0, 40, 256, 3)]
+    widths = {0: 2048, 1: 1152, 2: 512, 3: 256}
+    xs = {g: synth.activations(seq, k, seed=300 + g) for g, k in widths.items()}
+    acts = {g: hb.Act(seq, k) for g, k in widths.items()}
+    ws = [synth.weights(dt, n, k, seed=400 + i) for i, (dt, n, k, _) in enumerate(specs)]
+    Ws = [hb.Weight.upload(dt, n, k, w) for (dt, n, k, _), w in zip(specs, ws)]
+    total = sum(n for _, n, _, _ in specs)
+    out_dev = torch.zeros((seq, total), dtype=torch.float32, device=dev)
+    batch = hb.Batch()
+    off = 0
+    for (dt, n, k, g), W in zip(specs, Ws):
+        batch.add(W, acts[g], seq, out_dev[:, off:], ld_out=total)
+        off += n
+    batch.seal()
+    assert batch.input_floats == sum(seq * k for k in widths.values())
+    x_host = np.concatenate([xs[g].reshape(-1) for g in sorted(widths)])  # order of first use: groups 0, 1, 2, 3
+    out_host = np.zeros((seq, total), dtype=np.float32)
+    try:
+        for _ in range(2):
+            batch.run_host(x_host, out_dev, out_host)
+            off = 0
+            for (dt, n, k, g), w in zip(specs, ws):
+                if dt == Q6_K:
+                    want = oracle.matmul_kquant_f32(dt, w, xs[g], n, k)
+                else:
+                    want = oracle.dot_rows_batched(dt, w, oracle.quantize_q8_0(xs[g]), n, k)
+                assert_bits_equal(out_host[:, off:off + n], want, f"run_host op dtype {dt}")
+                off += n
+    finally:
+        batch.free()
+        for a in acts.values():
+            a.free()
+        for W in Ws:
+            W.free()
