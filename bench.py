@@ -115,7 +115,7 @@ def algorithmic_bytes(cfg: dict) -> dict:
     w = a = o = 0
     for _, n_rows, n_cols in cfg["shapes"]:
         w += n_rows * synth.row_bytes(cfg["dtype"], n_cols)
-        a += m * (n_cols // 32) * 34
+        a += m * n_cols * 4 if cfg["dtype"] in (12, 14) else m * (n_cols // 32) * 34  # K-quants read f32 activations
         o += m * n_rows * 4
     L = cfg["layers"]
     return {"weights": w * L, "activations": a * L, "outputs": o * L}
@@ -401,7 +401,7 @@ def run_ours(args, cfg, rank, world, local_rank):
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8 x {1,2}-bit -> int32, fp32 scales", "data": "synthetic",
-            "config": {"workload": args.workload, "format": {41: "Q1_0", 42: "Q2_0", 142: "PQ2_0", 8: "Q8_0"}.get(dtype, str(dtype)),
+            "config": {"workload": args.workload, "format": {41: "Q1_0", 42: "Q2_0", 142: "PQ2_0", 8: "Q8_0", 12: "Q4_K", 14: "Q6_K"}.get(dtype, str(dtype)),
                        "tokens": M, "layers": cfg["layers"], "matrices_per_step": cfg["layers"] * len(cfg["shapes"]),
                        "weight_bytes": ab["weights"], "parallelism": f"rows/{world}" + ((" + outputs stored to all ranks from the kernel (peer stores, flag exchange)" if use_fused
                                                                 else " + NCCL all-gather of output slices") if world > 1 else ""),
@@ -416,7 +416,7 @@ def run_ours(args, cfg, rank, world, local_rank):
         if ms_nccl:
             line["nccl_allgather_variant"] = {"ms_per_step": ms_nccl / args.steps,
                                               "value": ab["weights"] / (ms_nccl / args.steps * 1e-3) / 1e9, "unit": UNIT}
-        if world == 1 and not args.no_cpu and not args.quick:
+        if world == 1 and not args.no_cpu and not args.quick and cfg["dtype"] not in (12, 14):
             arm = CpuArm(cfg, 0, 1)
             t0 = time.perf_counter()
             best = arm.gbs(2)

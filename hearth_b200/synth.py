@@ -133,6 +133,13 @@ CONFIGS = {
     "c2_q1_8b_prefill_1layer": dict(dtype=Q1_0, shapes=layer_shapes(4096, 12288, 1024), layers=1, seq_len=512),
     "c2_q1_8b_decode": dict(dtype=Q1_0, shapes=layer_shapes(4096, 12288, 1024), layers=36, seq_len=1),
     "c2_q2_8b_decode": dict(dtype=Q2_0, shapes=layer_shapes(4096, 12288, 1024), layers=36, seq_len=1),
+    # config 3: K-quant decode matvec, f32 activations; eight copies of the pair so a step streams 5x the L2
+    "c3_q4k_m1": dict(dtype=Q4_K, shapes=[("a", 14336, 4096), ("b", 4096, 14336)], layers=8, seq_len=1),
+    "c3_q4k_m8": dict(dtype=Q4_K, shapes=[("a", 14336, 4096), ("b", 4096, 14336)], layers=8, seq_len=8),
+    "c3_q4k_m32": dict(dtype=Q4_K, shapes=[("a", 14336, 4096), ("b", 4096, 14336)], layers=8, seq_len=32),
+    "c3_q6k_m1": dict(dtype=Q6_K, shapes=[("a", 14336, 4096), ("b", 4096, 14336)], layers=8, seq_len=1),
+    "c3_q6k_m8": dict(dtype=Q6_K, shapes=[("a", 14336, 4096), ("b", 4096, 14336)], layers=8, seq_len=8),
+    "c3_q6k_m32": dict(dtype=Q6_K, shapes=[("a", 14336, 4096), ("b", 4096, 14336)], layers=8, seq_len=32),
     "c4_pq2_27b_decode": dict(dtype=PQ2_0, shapes=layer_shapes(5120, 17408, 1024), layers=64, seq_len=1),
     "c4_pq2_27b_m32": dict(dtype=PQ2_0, shapes=layer_shapes(5120, 17408, 1024), layers=64, seq_len=32),
 }
