@@ -349,12 +349,13 @@ static int weight_build(int dtype, size_t n_rows, size_t n_cols, const uint8_t* 
         if (own_raw && d_raw) cudaFree(d_raw);
         if (w->bits) cudaFree(w->bits);
         if (w->scales) cudaFree(w->scales);
-        if (w->raw) cudaFree(w->raw);
+        if (w->kq) cudaFree(w->kq);
+        if (w->d16) cudaFree(w->d16);
         delete w;
         return code;
     };
     if (bytes > 0) {
-        if (src_on_device && kind != KIND_Q4K && kind != KIND_Q6K) {
+        if (src_on_device) {
             d_raw = const_cast<uint8_t*>(src);
         } else {
             cudaError_t e = cudaMalloc(&d_raw, bytes);
@@ -365,11 +366,21 @@ static int weight_build(int dtype, size_t n_rows, size_t n_cols, const uint8_t* 
         }
     }
     if (kind == KIND_Q4K || kind == KIND_Q6K) {
-        w->raw = d_raw;
-        own_raw = false;
-        w->resident_bytes = bytes;
+        w->nb = (int)(n_cols / 256);  // whole 256-column blocks only, as the reference's loops do
+        w->n_panels = (int)((n_rows + 31) / 32);
+        const size_t pieces = (size_t)w->n_panels * w->nb * kquant_pieces_per_block(kind) * 32;
+        const size_t d_count = (kind == KIND_Q6K) ? (size_t)w->n_panels * w->nb * 32 : 0;
+        if (pieces > 0) {
+            cudaError_t e = cudaMalloc(&w->kq, pieces * sizeof(uint4));
+            if (e == cudaSuccess && d_count) e = cudaMalloc(&w->d16, d_count * sizeof(unsigned short));
+            if (e != cudaSuccess) { set_error("cudaMalloc for %zu weight bytes failed: %s", pieces * 16 + d_count * 2, cudaGetErrorString(e)); return fail(HB200_ERR_CUDA); }
+            rc = launch_kquant_repack(kind, d_raw, w->row_bytes, (int)n_rows, w->nb, w->n_panels, w->kq, w->d16, st);
+            if (rc) return fail(rc);
+        }
         cudaError_t e = cudaStreamSynchronize(st);
-        if (e != cudaSuccess) { set_error("weight upload failed: %s", cudaGetErrorString(e)); return fail(HB200_ERR_CUDA); }
+        if (e != cudaSuccess) { set_error("weight re-tiling failed: %s", cudaGetErrorString(e)); return fail(HB200_ERR_CUDA); }
+        if (own_raw) { cudaFree(d_raw); own_raw = false; }
+        w->resident_bytes = pieces * 16 + d_count * 2;
     } else {
         const int rpg = rows_per_group(kind);
         const size_t rp = 32 * (size_t)rpg;
@@ -448,7 +459,8 @@ extern "C" int hb200_weight_free(hb200_weight_t w) {
     if (!w) return HB200_OK;
     if (w->bits) cudaFree(w->bits);
     if (w->scales) cudaFree(w->scales);
-    if (w->raw) cudaFree(w->raw);
+    if (w->kq) cudaFree(w->kq);
+    if (w->d16) cudaFree(w->d16);
     delete w;
     return HB200_OK;
     HB_GUARD_END
@@ -579,8 +591,8 @@ extern "C" int hb200_matmul_f32_dev(hb200_weight_t w, hb200_act_t a, size_t seq_
     if (seq_len == 0 || w->n_rows == 0) return HB200_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (w->kind == KIND_Q4K || w->kind == KIND_Q6K)
-        return launch_kquant_gemv(w->kind, w->raw, w->row_bytes, (int)w->n_rows, (int)w->n_cols, a->x, (int)seq_len, out_dev,
-                                  (int)ld_out, st);
+        return launch_kquant_gemv(w->kind, w->kq, w->d16, (int)w->n_rows, (int)w->n_cols, w->nb, w->n_panels, a->x, (int)seq_len,
+                                  out_dev, (int)ld_out, g_ctx.sm_count, st);
     rc = launch_quantize_q8_0(a->x, (int)seq_len, (int)a->n_cols, a->q, a->d, a->sums, a->ld_q, a->ld_b, nullptr, 0, st);
     if (rc) return rc;
     return dot_rows_launch(w, a, seq_len, out_dev, ld_out, st);
@@ -843,8 +855,8 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
                                  (int)e.seq_len, e.out, (int)e.ld_out, g_ctx.d_status, st)))
             return rc;
     for (const BatchEntry& e : b->kquant)
-        if ((rc = launch_kquant_gemv(e.w->kind, e.w->raw, e.w->row_bytes, (int)e.w->n_rows, (int)e.w->n_cols, e.a->x, (int)e.seq_len,
-                                     e.out, (int)e.ld_out, st)))
+        if ((rc = launch_kquant_gemv(e.w->kind, e.w->kq, e.w->d16, (int)e.w->n_rows, (int)e.w->n_cols, e.w->nb, e.w->n_panels, e.a->x,
+                                     (int)e.seq_len, e.out, (int)e.ld_out, g_ctx.sm_count, st)))
             return rc;
     return HB200_OK;
     HB_GUARD_END

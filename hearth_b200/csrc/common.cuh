@@ -128,9 +128,13 @@ int launch_gemm_tc(int kind, const void* amap, const uint4* bits, const void* sc
                    int nb, int seq_len, float* out, int ld_out, int* status, cudaStream_t st);
 int gemm_tc_prepare();
 
-// kquant.cu
-int launch_kquant_gemv(int kind, const uint8_t* w, size_t row_bytes, int n_rows, int n_cols, const float* x, int seq_len, float* out,
-                       int ld_out, cudaStream_t st);
+// kquant.cu: Q4_K / Q6_K weights are re-tiled at upload into 32-row panels of interleaved 16-byte pieces
+// (layout described in kquant.cu); d16 holds Q6_K's per-block f16 scale and is null for Q4_K.
+size_t kquant_pieces_per_block(int kind);
+int launch_kquant_repack(int kind, const uint8_t* raw, size_t row_bytes, int n_rows, int nblk, int n_panels, uint4* kq,
+                         unsigned short* d16, cudaStream_t st);
+int launch_kquant_gemv(int kind, const uint4* kq, const unsigned short* d16, int n_rows, int n_cols, int nblk, int n_panels,
+                       const float* x, int seq_len, float* out, int ld_out, int sm_count, cudaStream_t st);
 int kquant_prepare();
 
 }  // namespace hb200

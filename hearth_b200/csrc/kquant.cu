@@ -13,10 +13,17 @@
 // crate, whose source is not part of the reference tree; it is an assumption
 // shared with the CPU checker, so this path's parity is tolerance-level.
 //
-// Shape of the kernel: a CTA owns RT rows of one token; all threads produce
-// the per-unit terms into shared memory, then one thread per row adds them in
-// order.  Weights stream from HBM once per token (Q4_K 144 B, Q6_K 210 B per
-// 256 columns); x is read through L1/L2.
+// Device layout (built once at upload, same bytes as the reference's):
+//   panel = 32 consecutive rows; the 16-byte pieces of one 256-column block are interleaved over the rows,
+//   piece p of (panel, blk) for lane l at kq[((panel*nblk + blk)*NP + p)*32 + l], so a warp reads 512
+//   contiguous bytes per piece.  Q4_K: NP = 9 (header with d, dmin and the 12 scale bytes; one piece of
+//   nibbles per 32-element sub-block).  Q6_K: NP = 13 (8 of ql, 4 of qh, 1 of int8 scales) and the f16 d of
+//   every block in a separate array d16[(panel*nblk + blk)*32 + l].
+//
+// Kernel: lane = row, so all lanes of a warp use the same columns and x comes from shared memory as
+// broadcasts; a warp takes one block (Q4_K) or a quarter block (Q6_K) per round, eight warps make 64 ordered
+// terms per row and round; next round's pieces are prefetched into registers; one thread per (token, row)
+// adds the terms in order, one round behind.  Up to four tokens share one pass over the weights.
 #include "common.cuh"
 
 namespace hb200 {
@@ -24,128 +31,323 @@ namespace hb200 {
 namespace {
 
 constexpr int KQ_THREADS = 256;
+constexpr int KQ_WARPS = 8;
+constexpr int TERMS = 64;  // ordered terms per row and round
 
-__device__ __forceinline__ float h2f_bytes(const uint8_t* p) {
-    return __half2float(__ushort_as_half((unsigned short)(p[0] | (p[1] << 8))));
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit_wait_all() {
+    asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ float h2f_bits(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
 __device__ __forceinline__ float reduce8(const float* l) {
     const float q0 = __fadd_rn(l[0], l[4]), q1 = __fadd_rn(l[1], l[5]);
     const float q2 = __fadd_rn(l[2], l[6]), q3 = __fadd_rn(l[3], l[7]);
     return __fadd_rn(__fadd_rn(q0, q2), __fadd_rn(q1, q3));
 }
 
-// One 32-element sub-block of Q4_K: [f16 d][f16 dmin][12 B scales][128 B nibbles].
-__device__ __forceinline__ float term_q4k(const uint8_t* __restrict__ row, const float* __restrict__ x, int unit) {
-    const int b = unit >> 3, sb = unit & 7;
-    const uint8_t* bp = row + (size_t)b * 144;
-    const float d = h2f_bytes(bp), dmin = h2f_bytes(bp + 2);
-    const int i = sb >> 1;
-    const uint32_t s0 = bp[4 + 3 * i], s1 = bp[5 + 3 * i], s2 = bp[6 + 3 * i];
-    uint32_t sc, mn;
-    if ((sb & 1) == 0) {
-        sc = s0 & 0x3F;
-        mn = (s0 >> 6) | ((s1 & 0x0F) << 2);
-    } else {
-        sc = (s1 >> 4) | ((s2 & 0x03) << 4);
-        mn = (s2 >> 2) & 0x3F;
-    }
-    const float scf = __fmul_rn((float)sc, d), mnf = __fmul_rn((float)mn, dmin);
-    const uint4 qv = *reinterpret_cast<const uint4*>(bp + 16 + sb * 16);  // 144-byte blocks keep this 16-byte aligned
-    const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
-    const float* xv = x + (size_t)b * 256 + sb * 32;
-    float lanes[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+template <int KIND>
+struct KqGeom {
+    static constexpr int NP = (KIND == KIND_Q4K) ? 9 : 13;           // pieces per block
+    static constexpr int BLK_PER_ROUND = (KIND == KIND_Q4K) ? 8 : 2;  // blocks the eight warps cover per round
+    static constexpr int CH = BLK_PER_ROUND * 256;                    // columns of x per round
+    static constexpr int NW = (KIND == KIND_Q4K) ? 9 : 4;             // pieces a thread holds per round
+    static constexpr int TERMS_PER_BLK = (KIND == KIND_Q4K) ? 8 : 32;
+};
+
+template <int KIND, int MT>
+struct KqSmem {
+    alignas(16) float x[2][MT][KqGeom<KIND>::CH];
+    alignas(16) float term[2][TERMS][MT][32];
+};
+
+struct KqArgs {
+    const uint4* kq;
+    const unsigned short* d16;  // Q6_K only
+    const float* x;             // [seq_len][n_cols]
+    float* out;
+    int n_rows, n_cols, nblk, n_panels, seq_len, ld_out;
+};
+
+// ---- one-time re-tiling -------------------------------------------------------------------------------------------
+
+template <int KIND>
+__global__ void kq_repack_kernel(const uint8_t* __restrict__ raw, size_t row_bytes, int n_rows, int nblk, long long n_pieces,
+                                 uint4* __restrict__ kq, unsigned short* __restrict__ d16) {
+    constexpr int NP = KqGeom<KIND>::NP;
+    constexpr int BB = (KIND == KIND_Q4K) ? 144 : 210;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_pieces) return;
+    const int lane = (int)(i & 31);
+    const long long t = i >> 5;
+    const int p = (int)(t % NP);
+    const long long pb = t / NP;
+    const int blk = (int)(pb % nblk);
+    const int panel = (int)(pb / nblk);
+    const int row = panel * 32 + lane;
+    uint32_t w[4] = {0, 0, 0, 0};
+    if (row < n_rows) {
+        const uint8_t* src = raw + (size_t)row * row_bytes + (size_t)blk * BB + p * 16;  // 2-byte aligned at least
 #pragma unroll
-    for (int t = 0; t < 4; t++) {  // elements 8t..8t+7 live in word t: byte k holds elements 2k (low) and 2k+1 (high)
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-            const uint32_t nib = (qw[t] >> (4 * j)) & 0xF;
-            const float v = __fsub_rn(__fmul_rn((float)nib, scf), mnf);
-            lanes[j] = fmaf(v, xv[8 * t + j], lanes[j]);
+        for (int k = 0; k < 4; k++) {
+            const unsigned short lo = *reinterpret_cast<const unsigned short*>(src + 4 * k);
+            const unsigned short hi = *reinterpret_cast<const unsigned short*>(src + 4 * k + 2);
+            w[k] = (uint32_t)lo | ((uint32_t)hi << 16);
         }
+        if (KIND == KIND_Q6K && p == 0)
+            d16[pb * 32 + lane] = *reinterpret_cast<const unsigned short*>(raw + (size_t)row * row_bytes + (size_t)blk * BB + 208);
+    } else if (KIND == KIND_Q6K && p == 0) {
+        d16[pb * 32 + lane] = 0;
     }
-    return reduce8(lanes);
+    kq[i] = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// Eight elements of Q6_K: [ql 128][qh 64][i8 scales 16][f16 d]; blocks are 210 B, so byte loads.
-__device__ __forceinline__ float term_q6k(const uint8_t* __restrict__ row, const float* __restrict__ x, int unit) {
-    const int b = unit >> 5, e0 = (unit & 31) * 8;
-    const uint8_t* bp = row + (size_t)b * 210;
-    const float d = h2f_bytes(bp + 208);
-    const float sd = __fmul_rn((float)(int8_t)bp[192 + (e0 >> 4)], d);
-    const float* xv = x + (size_t)b * 256 + e0;
-    float lanes[8];
-    const uint32_t qh2 = bp[128 + (e0 >> 2)] | ((uint32_t)bp[129 + (e0 >> 2)] << 8);  // 8 x 2 bits
-#pragma unroll
-    for (int j = 0; j < 8; j++) {
-        const uint32_t ql = bp[(e0 + j) >> 1];
-        const uint32_t low4 = (j & 1) ? (ql >> 4) : (ql & 0x0F);
-        const uint32_t high2 = (qh2 >> (2 * j)) & 3;
-        const int quant = (int)(low4 | (high2 << 4)) - 32;
-        const float q = __fmul_rn((float)quant, sd);
-        lanes[j] = fmaf(q, xv[j], 0.0f);
-    }
-    return reduce8(lanes);
-}
+// ---- the matvec ------------------------------------------------------------------------------------------------
 
-template <int KIND, int RT>
-__global__ void __launch_bounds__(KQ_THREADS) kquant_gemv_kernel(const uint8_t* __restrict__ w, size_t row_bytes,
-                                                                 int n_rows, int n_cols, const float* __restrict__ x,
-                                                                 float* __restrict__ out, int ld_out) {
-    extern __shared__ float terms[];  // RT rows x (units + 1)
-    const int units = (n_cols / 256) * (KIND == KIND_Q4K ? 8 : 32);
-    const int stride = units + 1;
-    const int r0 = blockIdx.x * RT, m = blockIdx.y;
-    const float* xr = x + (size_t)m * n_cols;
-    for (int u = threadIdx.x; u < RT * units; u += KQ_THREADS) {
-        const int row = u / units, unit = u - row * units;
-        const int grow = r0 + row;
-        if (grow < n_rows) {
-            const uint8_t* rp = w + (size_t)grow * row_bytes;
-            terms[row * stride + unit] = (KIND == KIND_Q4K) ? term_q4k(rp, xr, unit) : term_q6k(rp, xr, unit);
+template <int KIND, int MT>
+__global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_constant__ KqArgs a, int n_items) {
+    using G = KqGeom<KIND>;
+    using S = KqSmem<KIND, MT>;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    S& sm = *reinterpret_cast<S*>(smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nblk = a.nblk;
+    const int rounds = max(1, (nblk + G::BLK_PER_ROUND - 1) / G::BLK_PER_ROUND);
+
+    // This CTA's contiguous run of items; item = token_tile * n_panels + panel.
+    const int it0 = (int)(((long long)n_items * blockIdx.x) / gridDim.x);
+    const int it1 = (int)(((long long)n_items * (blockIdx.x + 1)) / gridDim.x);
+    if (it0 >= it1) return;
+    const int total = (it1 - it0) * rounds;
+
+    auto stage = [&](int item, int r, int buf) {
+        const int tok0 = (item / a.n_panels) * MT;
+        constexpr int PIECES = G::CH / 4;
+        for (int idx = tid; idx < MT * PIECES; idx += KQ_THREADS) {
+            const int m = idx / PIECES, p = idx % PIECES;
+            const int col = r * G::CH + p * 4;
+            float* dst = &sm.x[buf][m][p * 4];
+            if (tok0 + m < a.seq_len && col + 3 < a.n_cols && ((a.n_cols & 3) == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0)) {
+                cp_async16(dst, a.x + (size_t)(tok0 + m) * a.n_cols + col);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; k++)
+                    dst[k] = (tok0 + m < a.seq_len && col + k < a.n_cols) ? a.x[(size_t)(tok0 + m) * a.n_cols + col + k] : 0.0f;
+            }
         }
+    };
+
+    uint4 wn[G::NW];
+    uint32_t dn = 0;
+    auto load_w = [&](int item, int r) {
+        const int panel = item % a.n_panels;
+        const int blk = (KIND == KIND_Q4K) ? (r * 8 + warp) : (r * 2 + (warp >> 2));
+        if (blk < nblk) {
+            const size_t base = ((size_t)panel * nblk + blk);
+            const uint4* p = a.kq + base * G::NP * 32 + lane;
+            if (KIND == KIND_Q4K) {
+#pragma unroll
+                for (int i = 0; i < 9; i++) wn[i] = __ldg(p + i * 32);
+            } else {
+                const int q = warp & 3;
+                wn[0] = __ldg(p + (2 * q) * 32);
+                wn[1] = __ldg(p + (2 * q + 1) * 32);
+                wn[2] = __ldg(p + (8 + q) * 32);
+                wn[3] = __ldg(p + 12 * 32);
+                dn = __ldg(a.d16 + base * 32 + lane);
+            }
+        }
+    };
+
+    float run = 0.0f;  // thread tid < MT*32 owns the chain of (token tid/32, row tid%32)
+    auto replay = [&](int item, int r, int buf) {
+        if (tid < MT * 32) {
+            const int m = tid >> 5, row = tid & 31;
+            const int nvalid = min(TERMS, G::TERMS_PER_BLK * (nblk - r * G::BLK_PER_ROUND));
+            float acc = run;
+            for (int k = 0; k < nvalid; k++) acc = __fadd_rn(acc, sm.term[buf][k][m][row]);
+            if (r == rounds - 1) {
+                const int grow = (item % a.n_panels) * 32 + row;
+                const int tok = (item / a.n_panels) * MT + m;
+                if (grow < a.n_rows && tok < a.seq_len) a.out[(size_t)tok * a.ld_out + grow] = acc;
+                acc = 0.0f;
+            }
+            run = acc;
+        }
+    };
+
+    stage(it0, 0, 0);
+    load_w(it0, 0);
+    int item = it0, r = 0, pitem = it0, pr = 0;
+    for (int t = 0; t < total; t++) {
+        cp_async_commit_wait_all();
+        __syncthreads();
+        uint4 w[G::NW];
+#pragma unroll
+        for (int i = 0; i < G::NW; i++) w[i] = wn[i];
+        const uint32_t dcur = dn;
+        int nitem = item, nr = r + 1;
+        if (nr == rounds) { nr = 0; nitem = item + 1; }
+        if (t + 1 < total) {
+            stage(nitem, nr, (t + 1) & 1);
+            load_w(nitem, nr);
+        }
+        if (t > 0) replay(pitem, pr, (t - 1) & 1);
+
+        const int buf = t & 1;
+        if (KIND == KIND_Q4K) {
+            const int blk = r * 8 + warp;
+            if (blk < nblk) {
+                const float d = h2f_bits(w[0].x & 0xffffu), dmin = h2f_bits(w[0].x >> 16);
+                const uint32_t sw[3] = {w[0].y, w[0].z, w[0].w};  // the 12 scale bytes
+#pragma unroll
+                for (int sb = 0; sb < 8; sb++) {
+                    const int i3 = (sb >> 1) * 3;
+                    const uint32_t s0 = (sw[i3 >> 2] >> (8 * (i3 & 3))) & 0xff;
+                    const uint32_t s1 = (sw[(i3 + 1) >> 2] >> (8 * ((i3 + 1) & 3))) & 0xff;
+                    const uint32_t s2 = (sw[(i3 + 2) >> 2] >> (8 * ((i3 + 2) & 3))) & 0xff;
+                    uint32_t sc, mn;
+                    if ((sb & 1) == 0) { sc = s0 & 0x3F; mn = (s0 >> 6) | ((s1 & 0x0F) << 2); }
+                    else { sc = (s1 >> 4) | ((s2 & 0x03) << 4); mn = (s2 >> 2) & 0x3F; }
+                    const float scf = __fmul_rn((float)sc, d), mnf = __fmul_rn((float)mn, dmin);
+                    const uint4 qv = w[1 + sb];
+                    const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+                    float lanes[MT][8];
+#pragma unroll
+                    for (int m = 0; m < MT; m++)
+#pragma unroll
+                        for (int j = 0; j < 8; j++) lanes[m][j] = 0.0f;
+#pragma unroll
+                    for (int tt = 0; tt < 4; tt++) {  // elements 8tt..8tt+7 of the sub-block live in word tt
+                        float v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; j++) v[j] = __fsub_rn(__fmul_rn((float)((qw[tt] >> (4 * j)) & 0xF), scf), mnf);
+#pragma unroll
+                        for (int m = 0; m < MT; m++) {
+                            const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][warp * 256 + sb * 32 + tt * 8]);
+                            const float4 x0 = xp[0], x1 = xp[1];
+                            lanes[m][0] = fmaf(v[0], x0.x, lanes[m][0]); lanes[m][1] = fmaf(v[1], x0.y, lanes[m][1]);
+                            lanes[m][2] = fmaf(v[2], x0.z, lanes[m][2]); lanes[m][3] = fmaf(v[3], x0.w, lanes[m][3]);
+                            lanes[m][4] = fmaf(v[4], x1.x, lanes[m][4]); lanes[m][5] = fmaf(v[5], x1.y, lanes[m][5]);
+                            lanes[m][6] = fmaf(v[6], x1.z, lanes[m][6]); lanes[m][7] = fmaf(v[7], x1.w, lanes[m][7]);
+                        }
+                    }
+#pragma unroll
+                    for (int m = 0; m < MT; m++) sm.term[buf][warp * 8 + sb][m][lane] = reduce8(lanes[m]);
+                }
+            }
+        } else {
+            const int blk = r * 2 + (warp >> 2), q = warp & 3;
+            if (blk < nblk) {
+                const float d = h2f_bits(dcur);
+                const uint32_t qlw[8] = {w[0].x, w[0].y, w[0].z, w[0].w, w[1].x, w[1].y, w[1].z, w[1].w};
+                const uint32_t qhw[4] = {w[2].x, w[2].y, w[2].z, w[2].w};
+                const uint32_t scw = (q == 0) ? w[3].x : (q == 1 ? w[3].y : (q == 2 ? w[3].z : w[3].w));
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int sci = (int)(int8_t)((scw >> (8 * (u >> 1))) & 0xff);
+                    const float sd = __fmul_rn((float)sci, d);
+                    const uint32_t qh16 = (qhw[u >> 1] >> (16 * (u & 1))) & 0xffffu;
+                    float qf[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const int quant = (int)(((qlw[u] >> (4 * j)) & 0xF) | (((qh16 >> (2 * j)) & 3) << 4)) - 32;
+                        qf[j] = __fmul_rn((float)quant, sd);
+                    }
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][(warp >> 2) * 256 + q * 64 + u * 8]);
+                        const float4 x0 = xp[0], x1 = xp[1];
+                        float lanes[8];
+                        lanes[0] = fmaf(qf[0], x0.x, 0.0f); lanes[1] = fmaf(qf[1], x0.y, 0.0f);
+                        lanes[2] = fmaf(qf[2], x0.z, 0.0f); lanes[3] = fmaf(qf[3], x0.w, 0.0f);
+                        lanes[4] = fmaf(qf[4], x1.x, 0.0f); lanes[5] = fmaf(qf[5], x1.y, 0.0f);
+                        lanes[6] = fmaf(qf[6], x1.z, 0.0f); lanes[7] = fmaf(qf[7], x1.w, 0.0f);
+                        sm.term[buf][warp * 8 + u][m][lane] = reduce8(lanes);
+                    }
+                }
+            }
+        }
+        pitem = item; pr = r;
+        item = nitem; r = nr;
     }
     __syncthreads();
-    if (threadIdx.x < RT && r0 + threadIdx.x < n_rows) {
-        const float* t = terms + threadIdx.x * stride;
-        float sum = 0.0f;
-        for (int i = 0; i < units; i++) sum = __fadd_rn(sum, t[i]);
-        out[(size_t)m * ld_out + r0 + threadIdx.x] = sum;
-    }
+    replay(pitem, pr, (total - 1) & 1);
 }
 
-constexpr int RT_Q4K = 8, RT_Q6K = 4;
-constexpr int KQ_MAX_SMEM = 200 * 1024;
+// Resident CTAs per SM of each instantiation, measured by the occupancy API at prepare time: the grid of the
+// persistent kernel is sized to exactly one wave.
+int g_kq_ctas[2][5] = {};
+
+template <int KIND, int MT>
+int launch_mt(const KqArgs& a, int sm_count, cudaStream_t st) {
+    const int tiles = (a.seq_len + MT - 1) / MT;
+    const int n_items = tiles * a.n_panels;
+    if (n_items <= 0) return 0;
+    const size_t smem = sizeof(KqSmem<KIND, MT>);
+    const int per_sm = g_kq_ctas[KIND == KIND_Q4K ? 0 : 1][MT] > 0 ? g_kq_ctas[KIND == KIND_Q4K ? 0 : 1][MT] : 1;
+    int grid = sm_count * per_sm;
+    if (grid > n_items) grid = n_items;
+    kq_gemv_kernel<KIND, MT><<<grid, KQ_THREADS, smem, st>>>(a, n_items);
+    HB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <int KIND>
+int launch_kind(const KqArgs& a, int sm_count, cudaStream_t st) {
+    if (a.seq_len == 1) return launch_mt<KIND, 1>(a, sm_count, st);
+    if (a.seq_len == 2) return launch_mt<KIND, 2>(a, sm_count, st);
+    return launch_mt<KIND, 4>(a, sm_count, st);
+}
+
+template <int KIND, int MT>
+int prepare_one() {
+    HB_CUDA(cudaFuncSetAttribute(kq_gemv_kernel<KIND, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(KqSmem<KIND, MT>)));
+    int n = 0;
+    HB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kq_gemv_kernel<KIND, MT>, KQ_THREADS, sizeof(KqSmem<KIND, MT>)));
+    g_kq_ctas[KIND == KIND_Q4K ? 0 : 1][MT] = n > 0 ? n : 1;
+    return 0;
+}
 
 }  // namespace
 
 int kquant_prepare() {
-    HB_CUDA(cudaFuncSetAttribute(kquant_gemv_kernel<KIND_Q4K, RT_Q4K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 KQ_MAX_SMEM));
-    HB_CUDA(cudaFuncSetAttribute(kquant_gemv_kernel<KIND_Q6K, RT_Q6K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 KQ_MAX_SMEM));
+    int rc;
+    if ((rc = prepare_one<KIND_Q4K, 1>())) return rc;
+    if ((rc = prepare_one<KIND_Q4K, 2>())) return rc;
+    if ((rc = prepare_one<KIND_Q4K, 4>())) return rc;
+    if ((rc = prepare_one<KIND_Q6K, 1>())) return rc;
+    if ((rc = prepare_one<KIND_Q6K, 2>())) return rc;
+    if ((rc = prepare_one<KIND_Q6K, 4>())) return rc;
     return 0;
 }
 
-int launch_kquant_gemv(int kind, const uint8_t* w, size_t row_bytes, int n_rows, int n_cols, const float* x, int seq_len, float* out,
-                       int ld_out, cudaStream_t st) {
-    if (n_rows <= 0 || seq_len <= 0) return 0;
-    const int blocks = n_cols / 256;
-    if (kind == KIND_Q4K) {
-        const size_t smem = (size_t)RT_Q4K * (blocks * 8 + 1) * sizeof(float);
-        if (smem > (size_t)KQ_MAX_SMEM) { set_error("Q4_K row of %d columns exceeds the shared-memory tile", n_cols); return -8; }
-        dim3 grid((n_rows + RT_Q4K - 1) / RT_Q4K, seq_len);
-        kquant_gemv_kernel<KIND_Q4K, RT_Q4K><<<grid, KQ_THREADS, smem, st>>>(w, row_bytes, n_rows, n_cols, x, out, ld_out);
-    } else if (kind == KIND_Q6K) {
-        const size_t smem = (size_t)RT_Q6K * (blocks * 32 + 1) * sizeof(float);
-        if (smem > (size_t)KQ_MAX_SMEM) { set_error("Q6_K row of %d columns exceeds the shared-memory tile", n_cols); return -8; }
-        dim3 grid((n_rows + RT_Q6K - 1) / RT_Q6K, seq_len);
-        kquant_gemv_kernel<KIND_Q6K, RT_Q6K><<<grid, KQ_THREADS, smem, st>>>(w, row_bytes, n_rows, n_cols, x, out, ld_out);
-    } else {
-        set_error("kquant_gemv: kind %d", kind);
-        return -7;
-    }
+size_t kquant_pieces_per_block(int kind) { return kind == KIND_Q4K ? 9 : 13; }
+
+int launch_kquant_repack(int kind, const uint8_t* raw, size_t row_bytes, int n_rows, int nblk, int n_panels, uint4* kq,
+                         unsigned short* d16, cudaStream_t st) {
+    const long long n_pieces = (long long)n_panels * nblk * (long long)kquant_pieces_per_block(kind) * 32;
+    if (n_pieces <= 0) return 0;
+    const unsigned grid = (unsigned)((n_pieces + 255) / 256);
+    if (kind == KIND_Q4K) kq_repack_kernel<KIND_Q4K><<<grid, 256, 0, st>>>(raw, row_bytes, n_rows, nblk, n_pieces, kq, d16);
+    else if (kind == KIND_Q6K) kq_repack_kernel<KIND_Q6K><<<grid, 256, 0, st>>>(raw, row_bytes, n_rows, nblk, n_pieces, kq, d16);
+    else { set_error("kquant repack: kind %d", kind); return -7; }
     HB_CUDA(cudaGetLastError());
     return 0;
+}
+
+int launch_kquant_gemv(int kind, const uint4* kq, const unsigned short* d16, int n_rows, int n_cols, int nblk, int n_panels,
+                       const float* x, int seq_len, float* out, int ld_out, int sm_count, cudaStream_t st) {
+    if (n_rows <= 0 || seq_len <= 0) return 0;
+    KqArgs a;
+    a.kq = kq; a.d16 = d16; a.x = x; a.out = out;
+    a.n_rows = n_rows; a.n_cols = n_cols; a.nblk = nblk; a.n_panels = n_panels; a.seq_len = seq_len; a.ld_out = ld_out;
+    if (kind == KIND_Q4K) return launch_kind<KIND_Q4K>(a, sm_count, st);
+    if (kind == KIND_Q6K) return launch_kind<KIND_Q6K>(a, sm_count, st);
+    set_error("kquant_gemv: kind %d", kind);
+    return -7;
 }
 
 }  // namespace hb200

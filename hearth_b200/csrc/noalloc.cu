@@ -74,8 +74,8 @@ extern "C" int hb200_matmul_f32_noalloc(hb200_weight_t w, const float* x_dev, si
         }
         cudaStream_t st = (cudaStream_t)stream;
         if (w->kind == KIND_Q4K || w->kind == KIND_Q6K)  // f32-activation formats need no scratch at all
-            return launch_kquant_gemv(w->kind, w->raw, w->row_bytes, (int)w->n_rows, (int)w->n_cols, x_dev, (int)seq_len,
-                                      out_dev, (int)ld_out, st);
+            return launch_kquant_gemv(w->kind, w->kq, w->d16, (int)w->n_rows, (int)w->n_cols, w->nb, w->n_panels, x_dev, (int)seq_len,
+                                      out_dev, (int)ld_out, sms, st);
 
         unsigned char* base = nullptr;
         int rc = scratch_for_current_device(&base);

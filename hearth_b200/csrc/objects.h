@@ -12,7 +12,8 @@ struct hb200_weight {
     int nb = 0, n_panels = 0, n_sub = 0;
     uint4* bits = nullptr;   // panel layout (Q1_0 / Q2_0 / Q8_0)
     void* scales = nullptr;
-    uint8_t* raw = nullptr;  // reference layout (Q4_K / Q6_K)
+    uint4* kq = nullptr;             // Q4_K / Q6_K: 32-row panels of interleaved 16-byte pieces
+    unsigned short* d16 = nullptr;   // Q6_K: per-block f16 scale
     size_t resident_bytes = 0;
 };
 
