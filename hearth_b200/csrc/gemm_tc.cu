@@ -12,10 +12,11 @@
 //
 // Tile: 128 tokens (TMEM lanes) x 64 weight rows (TMEM columns) per CTA, K walked in 128-column blocks.
 //   warp 0      TMA producer: int8 activation tile 128 tokens x 128 B per block (SWIZZLE_128B, K-major)
-//   warp 1      TMEM allocation + single-thread MMA issue: 4 MMAs (128x64x32) per block into 4 x 64 columns
-//   warps 2-5   unpack: 64 rows x 128 columns of 1-/2-bit codes -> int8 {-1,+1} / {-1,0,+1,+2} in the same
-//               swizzled K-major layout, written with 128-bit shared stores
-//   warps 6-13  promotion: tcgen05.ld 32 columns at a time, thread = token, 32 running sums per thread
+//   warps 1-2   TMEM allocation (warp 1) + MMA issue, one thread each: warp 1 the even blocks, warp 2 the odd ones;
+//               4 MMAs (128x64x32) per block into 4 x 64 columns of that issuer's accumulator set
+//   warps 3-6   unpack, each warp every fourth block: packed codes arrive through a cp.async ring; 64 rows x 128 columns
+//               of 1-/2-bit codes -> int8 {-1,+1} / {-1,0,+1,+2} in the same swizzled K-major layout, 128-bit stores
+//   warps 7-22  promotion: tcgen05.ld 16 columns x 4 sub-blocks at a time, thread = token, 16 running sums per thread
 // Two accumulator sets (2 x 256 TMEM columns) let the MMAs of block b+1 run under the promotion of block b;
 // a 4-stage shared-memory ring decouples TMA / unpack from the MMA issue.
 // Every wait on an mbarrier is bounded; on expiry the CTA records a status code, stops issuing, drains its
@@ -28,7 +29,9 @@ namespace hb200 {
 
 namespace {
 
-constexpr int TC_THREADS = 448;
+constexpr int UNPACK_WARPS = 4;   // each warp expands every fourth block on its own (eight units per thread)
+constexpr int EPI_WARPS = 16;     // four per TMEM lane quarter, 16 accumulator columns per thread
+constexpr int TC_THREADS = 32 * (3 + UNPACK_WARPS + EPI_WARPS);  // 736: TMA, two MMA issuers, unpack, promotion
 constexpr int TOK_TILE = 128;
 constexpr int ROW_TILE = 64;
 constexpr int STAGES = 4;
@@ -75,7 +78,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
     for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
         if (mbar_try(bar, parity)) return true;
-        if ((i & 63) == 63 && *abort_flag) return false;
+        if ((i & 7) == 7 && *abort_flag) return false;
     }
     *abort_flag = 1;
     atomicCAS(status, 0, code);
@@ -114,6 +117,32 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+#define HB_R8(v) "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7])
+__device__ __forceinline__ void tc_wait_ld8(uint32_t (&v)[8]) { asm volatile("tcgen05.wait::ld.sync.aligned;" : HB_R8(v)::"memory"); }
+__device__ __forceinline__ void tc_pin8(uint32_t (&v)[8]) { asm volatile("" : HB_R8(v)::"memory"); }
+
+#define HB_R16(v)                                                                                                   \
+    "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), \
+        "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+// Waits for every outstanding tcgen05.ld of this thread; the registers are read-write operands so that no use of them
+// can be scheduled ahead of the wait.  tc_pin16 gives the same guarantee to further arrays covered by that wait.
+__device__ __forceinline__ void tc_wait_ld16(uint32_t (&v)[16]) { asm volatile("tcgen05.wait::ld.sync.aligned;" : HB_R16(v)::"memory"); }
+__device__ __forceinline__ void tc_pin16(uint32_t (&v)[16]) { asm volatile("" : HB_R16(v)::"memory"); }
+
 #define HB_R32(v)                                                                                                    \
     "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),  \
         "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]),  \
@@ -126,6 +155,12 @@ __device__ __forceinline__ void tc_wait_ld(uint32_t (&v)[32]) {
 }
 // Same ordering guarantee for a second register array covered by the same wait.
 __device__ __forceinline__ void tc_pin(uint32_t (&v)[32]) { asm volatile("" : HB_R32(v)::"memory"); }
+
+// Pairs of fp32 lanes.  Written as two scalar IEEE operations each: the packed sm_100 forms (fma/mul/add .f32x2) did not
+// reproduce the scalar results bit for bit in the sum across blocks, so they are not used.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) { return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y)); }
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }
 
 // K-major, SWIZZLE_128B shared-memory matrix descriptor: rows of 128 B, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
@@ -141,18 +176,28 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
 constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(ROW_TILE >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
 constexpr int SCALE_SLOTS = 8;  // ring of per-block weight scales (f32); deeper than the tile ring, see the unpack loop
+constexpr int PSLOTS = 8;       // ring of packed weight bytes (cp.async): two slots per unpack warp
 struct Barriers {
-    uint64_t full_a[STAGES], full_b[STAGES], empty[STAGES];
+    uint64_t full[STAGES], empty[STAGES];
     uint64_t tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
     alignas(16) float wscale[SCALE_SLOTS][ROW_TILE];
+    alignas(16) unsigned char packed[PSLOTS][2048];  // 64 rows x 128 columns of codes: 1 KiB (Q1_0) or 2 KiB (Q2_0)
+    alignas(16) unsigned char pscale[PSLOTS][128];   // their f16 scales
 };
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
 
 template <int KIND>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
     constexpr int RPG = rows_per_group(KIND);
+    constexpr int SPT = scales_per_tile(KIND);
+    constexpr int RGS = ROW_TILE / RPG;  // row groups per tile: 8 (Q1_0) or 16 (Q2_0)
     extern __shared__ unsigned char smem_dyn[];
     // 1024-byte alignment for the swizzled tiles
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
@@ -160,19 +205,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
     volatile int* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * ROW_TILE;
-    const int tok0 = blockIdx.y * TOK_TILE;
+    // Token tiles vary fastest across the grid: CTAs that run at the same time then read different activation tiles.
+    const int tok0 = blockIdx.x * TOK_TILE;
+    const int row0 = blockIdx.y * ROW_TILE;
     const int nb = args.nb;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; i++) {
-            mbar_init(smem_u32(&bars->full_a[i]), 1);
-            mbar_init(smem_u32(&bars->full_b[i]), 4);
+            mbar_init(smem_u32(&bars->full[i]), 2);  // the TMA's expect_tx arrival + the unpack warp that filled the stage
             mbar_init(smem_u32(&bars->empty[i]), 1);
         }
         for (int i = 0; i < 2; i++) {
             mbar_init(smem_u32(&bars->tmem_full[i]), 1);
-            mbar_init(smem_u32(&bars->tmem_empty[i]), 8);
+            mbar_init(smem_u32(&bars->tmem_empty[i]), EPI_WARPS);
         }
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -196,29 +241,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
                 if (blk >= STAGES &&
                     !mbar_wait(smem_u32(&bars->empty[st]), ((blk / STAGES) - 1) & 1, abort_flag, args.status, 1))
                     break;
-                const uint32_t bar = smem_u32(&bars->full_a[st]);
+                const uint32_t bar = smem_u32(&bars->full[st]);
                 mbar_expect_tx(bar, A_BYTES);
                 tma_load_2d(smem_u32(tiles + st * STAGE_BYTES), &amap, blk * 128, tok0, bar);
                 issued = blk + 1;
             }
             if (*abort_flag) {
-                // Do not leave the CTA with bulk copies in flight: wait (bounded) for the ones already issued.
+                // Do not leave the CTA with bulk copies in flight: wait (bounded) for the ones already issued.  If the
+                // unpack warps have stopped arriving the phase cannot complete, so this loop simply runs out.
                 const int first = issued > STAGES ? issued - STAGES : 0;
                 for (int blk = first; blk < issued; blk++) {
-                    const uint32_t bar = smem_u32(&bars->full_a[blk % STAGES]);
-                    for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try(bar, (blk / STAGES) & 1); i++) {
+                    const uint32_t bar = smem_u32(&bars->full[blk % STAGES]);
+                    for (uint32_t i = 0; i < (SPIN_LIMIT >> 8) && !mbar_try(bar, (blk / STAGES) & 1); i++) {
                     }
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issue (one lane)
+    } else if (warp <= 2) {
+        // ---------------------------------------------------------------- MMA issue: warp 1 even blocks, warp 2 odd blocks
+        // Two issuing threads halve the serial cost of the waits and commits per block; each owns one accumulator set.
         if (lane == 0) {
-            for (int blk = 0; blk < nb; blk++) {
-                const int st = blk % STAGES, buf = blk & 1;
-                const uint32_t ph = (blk / STAGES) & 1;
-                if (!mbar_wait(smem_u32(&bars->full_a[st]), ph, abort_flag, args.status, 2)) break;
-                if (!mbar_wait(smem_u32(&bars->full_b[st]), ph, abort_flag, args.status, 3)) break;
+            const int par = warp - 1;
+            for (int blk = par; blk < nb; blk += 2) {
+                const int st = blk % STAGES, buf = par;
+                if (!mbar_wait(smem_u32(&bars->full[st]), (blk / STAGES) & 1, abort_flag, args.status, 2)) break;
                 if (blk >= 2 && !mbar_wait(smem_u32(&bars->tmem_empty[buf]), ((blk >> 1) - 1) & 1, abort_flag, args.status, 4)) break;
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(tiles + st * STAGE_BYTES);
@@ -230,45 +276,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
                 tc_commit(smem_u32(&bars->tmem_full[buf]));  // the accumulators are complete
             }
         }
-    } else if (warp < 6) {
-        // ---------------------------------------------------------------- unpack (128 threads)
-        // Each thread owns two units (row of the tile, sub-block); the packed words of the next block are
-        // fetched before the current block is expanded, so the global-load latency hides behind the ring.
-        const int ut = threadIdx.x - 64;
-        const uint2* src[2][4];
-        int rsh[2], ris[2], ss[2];
+    } else if (warp < 3 + UNPACK_WARPS) {
+        // ---------------------------------------------------------------- unpack (4 warps, one block each in turn)
+        // The expansion of one block is a long serial chain (ring wait, stage wait, expand, proxy fence, arrive), so
+        // four warps run four such chains side by side: warp w owns blocks w, w+4, ...  Packed codes and scales of a
+        // warp's next block stream into its two ring slots with cp.async while it expands the current one.
+        const int uw = warp - 3;
+        const int rg0 = row0 / RPG;  // first row group of the tile; a tile never straddles a 32-row-group panel
+        const size_t tile0 = (size_t)(rg0 >> 5) * nb;
+        const int lane0 = rg0 & 31;
+        auto issue = [&](int blk) {
+            if (blk < nb) {
+                const int slot = blk % PSLOTS;
+                const uint4* tp = args.bits + (tile0 + blk) * 256;
 #pragma unroll
-        for (int uu = 0; uu < 2; uu++) {
-            const int u = ut + uu * 128;
-            const int ri = u >> 2, s = u & 3;
-            const int grow = row0 + ri;
-            const int rg = grow / RPG, r = grow % RPG;
-            ris[uu] = ri; ss[uu] = s;
-            rsh[uu] = (KIND == KIND_Q1) ? r : 2 * r;
-            const uint4* tp = args.bits + (size_t)(rg >> 5) * nb * 256 + (rg & 31);
-#pragma unroll
-            for (int jp = 0; jp < 4; jp++)  // words 2jp, 2jp+1 of sub-block s: piece 2jp + (s>>1), components (s&1)*2, +1
-                src[uu][jp] = reinterpret_cast<const uint2*>(tp + (2 * jp + (s >> 1)) * 32) + (s & 1);
-        }
-        // weight scale of row (ut & 63) of the tile, block 0 (only threads 0..63 stage scales)
-        const int srow = row0 + (ut & 63);
-        const int srg = srow / RPG, sr = srow % RPG;
-        const unsigned short* sc16 = reinterpret_cast<const unsigned short*>(args.scales) +
-                                     ((size_t)(srg >> 5) * nb * 32 + (srg & 31)) * scales_per_tile(KIND) + sr;
-        uint2 cur[2][4], nxt[2][4];
-        unsigned short sc_cur = 0, sc_nxt = 0;
-        auto fetch = [&](int blk, uint2 (&dst)[2][4], unsigned short& sc) {
-            const size_t off = (size_t)blk * 256 * 2;  // uint2 units per tile: 256 uint4
-#pragma unroll
-            for (int uu = 0; uu < 2; uu++)
-#pragma unroll
-                for (int jp = 0; jp < 4; jp++) dst[uu][jp] = __ldg(src[uu][jp] + off);
-            if (ut < 64) sc = __ldg(sc16 + (size_t)blk * 32 * scales_per_tile(KIND));
+                for (int k = 0; k < RGS * 8 / 32; k++) {
+                    const int pi = lane + k * 32;  // piece: row group pi >> 3, piece pi & 7 of its tile
+                    cp_async16(&bars->packed[slot][pi * 16], tp + (pi & 7) * 32 + lane0 + (pi >> 3));
+                }
+                if (lane < 8)  // RGS * SPT f16 = 128 bytes
+                    cp_async16(&bars->pscale[slot][lane * 16],
+                               reinterpret_cast<const unsigned char*>(args.scales) + ((tile0 + blk) * 32 + lane0) * SPT * 2 + lane * 16);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        if (nb > 0) fetch(0, cur, sc_cur);
-        for (int blk = 0; blk < nb; blk++) {
-            const int st = blk % STAGES;
-            if (blk + 1 < nb) fetch(blk + 1, nxt, sc_nxt);
+        issue(uw);
+        issue(uw + UNPACK_WARPS);
+        for (int blk = uw; blk < nb; blk += UNPACK_WARPS) {
+            const int st = blk % STAGES, slot = blk % PSLOTS;
+            asm volatile("cp.async.wait_group 1;" ::: "memory");  // this block's group has landed (the next one may be in flight)
+            __syncwarp();
             bool ok = true;
             if (blk >= STAGES) {
                 if (lane == 0) ok = mbar_wait(smem_u32(&bars->empty[st]), ((blk / STAGES) - 1) & 1, abort_flag, args.status, 5);
@@ -277,56 +314,65 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
             if (!ok) break;
             unsigned char* bt = tiles + st * STAGE_BYTES + A_BYTES;
 #pragma unroll
-            for (int uu = 0; uu < 2; uu++) {
+            for (int uu = 0; uu < 8; uu++) {
+                const int u = lane + uu * 32;  // unit = (row of the tile, sub-block)
+                const int ri = u >> 2, s = u & 3;
+                const int rgl = ri / RPG, r = ri % RPG;
+                const int sh = (KIND == KIND_Q1) ? r : 2 * r;
+                const unsigned char* tsrc = &bars->packed[slot][rgl * 128];
                 uint32_t vals[8];
 #pragma unroll
                 for (int jp = 0; jp < 4; jp++) {
-                    const uint32_t ww[2] = {cur[uu][jp].x, cur[uu][jp].y};
+                    // words 2jp, 2jp+1 of sub-block s live in piece 2jp + (s>>1), components (s&1)*2, +1
+                    const uint2 w2 = *reinterpret_cast<const uint2*>(tsrc + (2 * jp + (s >> 1)) * 16 + (s & 1) * 8);
+                    const uint32_t ww[2] = {w2.x, w2.y};
 #pragma unroll
                     for (int e = 0; e < 2; e++) {
                         uint32_t v;
                         if (KIND == KIND_Q1) {
-                            const uint32_t m = (ww[e] >> rsh[uu]) & 0x01010101u;  // bit -> 0/1
-                            v = (m * 0xFEu) ^ 0xFFFFFFFFu;                         // 1 -> 0x01 (+1), 0 -> 0xFF (-1)
+                            const uint32_t m = (ww[e] >> sh) & 0x01010101u;  // bit -> 0/1
+                            v = (m * 0xFEu) ^ 0xFFFFFFFFu;                    // 1 -> 0x01 (+1), 0 -> 0xFF (-1)
                         } else {
-                            const uint32_t c = ((ww[e] >> rsh[uu]) & 0x03030303u) | 0x80808080u;
-                            v = (c - 0x01010101u) ^ 0x80808080u;                   // code - 1 per byte, no borrow across bytes
+                            const uint32_t c = ((ww[e] >> sh) & 0x03030303u) | 0x80808080u;
+                            v = (c - 0x01010101u) ^ 0x80808080u;              // code - 1 per byte, no borrow across bytes
                         }
                         vals[2 * jp + e] = v;
                     }
                 }
-                unsigned char* rowp = bt + ris[uu] * 128;
-                const int sw = ris[uu] & 7;
-                *reinterpret_cast<uint4*>(rowp + (((2 * ss[uu]) ^ sw) << 4)) = make_uint4(vals[0], vals[1], vals[2], vals[3]);
-                *reinterpret_cast<uint4*>(rowp + (((2 * ss[uu] + 1) ^ sw) << 4)) = make_uint4(vals[4], vals[5], vals[6], vals[7]);
+                unsigned char* rowp = bt + ri * 128;
+                const int sw = ri & 7;
+                *reinterpret_cast<uint4*>(rowp + (((2 * s) ^ sw) << 4)) = make_uint4(vals[0], vals[1], vals[2], vals[3]);
+                *reinterpret_cast<uint4*>(rowp + (((2 * s + 1) ^ sw) << 4)) = make_uint4(vals[4], vals[5], vals[6], vals[7]);
             }
-            // The scale ring is read by the promotion warps up to two blocks after the MMA released the tile
-            // stage; SCALE_SLOTS = 8 keeps a slot untouched for that long (the producers run at most
-            // STAGES + 2 blocks ahead of the slowest reader).
-            if (ut < 64) bars->wscale[blk % SCALE_SLOTS][ut] = __half2float(__ushort_as_half(sc_cur));
+            // The scale ring is read by the promotion warps up to two blocks after the MMA released the tile stage;
+            // SCALE_SLOTS = 8 keeps a slot untouched for that long (producers run at most STAGES + 2 blocks ahead).
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                const int row = lane + 32 * k;
+                const int rgl = row / RPG, r = row % RPG;
+                const unsigned short h = *reinterpret_cast<const unsigned short*>(&bars->pscale[slot][(rgl * SPT + r) * 2]);
+                bars->wscale[blk % SCALE_SLOTS][row] = __half2float(__ushort_as_half(h));
+            }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // make the generic-proxy writes visible to the MMA
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars->full_b[st]));
-#pragma unroll
-            for (int uu = 0; uu < 2; uu++)
-#pragma unroll
-                for (int jp = 0; jp < 4; jp++) cur[uu][jp] = nxt[uu][jp];
-            sc_cur = sc_nxt;
+            if (lane == 0) mbar_arrive(smem_u32(&bars->full[st]));
+            issue(blk + 2 * UNPACK_WARPS);  // refills the slot just consumed (same slot index modulo PSLOTS = 8)
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else {
-        // ---------------------------------------------------------------- promotion (8 warps; thread = token)
-        const int e = warp - 6;
+        // ---------------------------------------------------------------- promotion (16 warps; thread = token)
+        const int e = warp - (3 + UNPACK_WARPS);
         const int quarter = warp & 3;   // TMEM lanes this warp may read: 32*(warp % 4) ..
-        const int half = e >> 2;        // which 32 of the 64 columns (weight rows)
+        const int cg = e >> 2;          // which 16 of the 64 columns (weight rows); the four warps of a quarter differ in cg
         const int tok = tok0 + quarter * 32 + lane;
         const bool tok_ok = tok < args.seq_len;
         const float* adp = args.ad + (size_t)(tok_ok ? tok : 0) * args.ld_b;
-        const int rbase = row0 + half * 32;  // first weight row of this thread's columns
+        const int rbase = row0 + cg * 16;  // first weight row of this thread's columns
         // A warp none of whose 32 tokens exist only keeps the barrier protocol going.
         const bool warp_has_tokens = (tok0 + quarter * 32) < args.seq_len;
-        float sum[32];
+        float2 sum[8];
 #pragma unroll
-        for (int c = 0; c < 32; c++) sum[c] = 0.0f;
+        for (int c = 0; c < 8; c++) sum[c] = make_float2(0.0f, 0.0f);
         float4 as_next = (nb > 0) ? *reinterpret_cast<const float4*>(adp) : make_float4(0.f, 0.f, 0.f, 0.f);
 
         for (int blk = 0; blk < nb; blk++) {
@@ -340,37 +386,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
             tc_fence_after();
             if (warp_has_tokens) {
                 const float asv[4] = {as4.x, as4.y, as4.z, as4.w};
-                float bacc[32];
-                const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256 + half * 32;
-                uint32_t v0[32], v1[32];
-                tc_ld32(tbase, v0);
-                tc_ld32(tbase + ROW_TILE, v1);
-                tc_wait_ld(v0);
-                tc_pin(v1);
+                const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256 + cg * 16;
+                const float4* wsp = reinterpret_cast<const float4*>(&bars->wscale[blk % SCALE_SLOTS][cg * 16]);
+                // Two halves of eight columns: the four sub-block sums of a half are fetched together, the accumulator
+                // set is handed back to the MMA issuer as soon as the second half sits in registers.
 #pragma unroll
-                for (int c = 0; c < 32; c++) bacc[c] = fmaf((float)(int)v0[c], asv[0], 0.0f);
-                tc_ld32(tbase + 2 * ROW_TILE, v0);
+                for (int hf = 0; hf < 2; hf++) {
+                    uint32_t v[4][8];
 #pragma unroll
-                for (int c = 0; c < 32; c++) bacc[c] = fmaf((float)(int)v1[c], asv[1], bacc[c]);
-                tc_ld32(tbase + 3 * ROW_TILE, v1);
-                tc_wait_ld(v0);
-                tc_pin(v1);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[buf]));
+                    for (int s4 = 0; s4 < 4; s4++) tc_ld8(tbase + s4 * ROW_TILE + hf * 8, v[s4]);
+                    tc_wait_ld8(v[0]);
+                    tc_pin8(v[1]);
+                    tc_pin8(v[2]);
+                    tc_pin8(v[3]);
+                    if (hf == 1) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[buf]));
+                    }
+                    // block_acc = fma(I0,a0,0), fma(I1,a1,.), fma(I2,a2,.), fma(I3,a3,.); then sum += block_acc * w_scale,
+                    // rounded separately (q2_0.rs:545-573, q1_0g128.rs:1026-1051)
 #pragma unroll
-                for (int c = 0; c < 32; c++) bacc[c] = fmaf((float)(int)v0[c], asv[2], bacc[c]);
+                    for (int c4 = 0; c4 < 2; c4++) {
+                        const float4 wd = wsp[hf * 2 + c4];
 #pragma unroll
-                for (int c = 0; c < 32; c++) bacc[c] = fmaf((float)(int)v1[c], asv[3], bacc[c]);
-                // sum += block_acc * w_scale, rounded separately (q2_0.rs:572, q1_0g128.rs:1050)
-                const float4* wsp = reinterpret_cast<const float4*>(&bars->wscale[blk % SCALE_SLOTS][half * 32]);
+                        for (int hh = 0; hh < 2; hh++) {
+                            const int c = 4 * c4 + 2 * hh;
+                            float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
-                for (int c4 = 0; c4 < 8; c4++) {
-                    const float4 wd = wsp[c4];
-                    sum[4 * c4 + 0] = __fadd_rn(sum[4 * c4 + 0], __fmul_rn(bacc[4 * c4 + 0], wd.x));
-                    sum[4 * c4 + 1] = __fadd_rn(sum[4 * c4 + 1], __fmul_rn(bacc[4 * c4 + 1], wd.y));
-                    sum[4 * c4 + 2] = __fadd_rn(sum[4 * c4 + 2], __fmul_rn(bacc[4 * c4 + 2], wd.z));
-                    sum[4 * c4 + 3] = __fadd_rn(sum[4 * c4 + 3], __fmul_rn(bacc[4 * c4 + 3], wd.w));
+                            for (int s4 = 0; s4 < 4; s4++)
+                                acc = ffma2(make_float2((float)(int)v[s4][c], (float)(int)v[s4][c + 1]), make_float2(asv[s4], asv[s4]), acc);
+                            const float2 w2 = hh ? make_float2(wd.z, wd.w) : make_float2(wd.x, wd.y);
+                            sum[hf * 4 + (c >> 1)] = fadd2(sum[hf * 4 + (c >> 1)], fmul2(acc, w2));
+                        }
+                    }
                 }
             } else {
                 tc_fence_before();
@@ -381,8 +430,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
         if (tok_ok && !*abort_flag) {
             float* op = args.out + (size_t)tok * args.ld_out + rbase;
 #pragma unroll
-            for (int c = 0; c < 32; c++)
-                if (rbase + c < args.n_rows) op[c] = sum[c];
+            for (int c = 0; c < 8; c++) {
+                if (rbase + 2 * c < args.n_rows) op[2 * c] = sum[c].x;
+                if (rbase + 2 * c + 1 < args.n_rows) op[2 * c + 1] = sum[c].y;
+            }
         }
     }
 
@@ -410,7 +461,7 @@ int launch_gemm_tc(int kind, const void* amap, const uint4* bits, const void* sc
     TcArgs a;
     a.bits = bits; a.scales = scales; a.ad = ad; a.out = out; a.status = status;
     a.n_rows = n_rows; a.nb = nb; a.seq_len = seq_len; a.ld_out = ld_out; a.ld_b = ld_b;
-    dim3 grid((n_rows + ROW_TILE - 1) / ROW_TILE, (seq_len + TOK_TILE - 1) / TOK_TILE);
+    dim3 grid((seq_len + TOK_TILE - 1) / TOK_TILE, (n_rows + ROW_TILE - 1) / ROW_TILE);
     const CUtensorMap& map = *static_cast<const CUtensorMap*>(amap);
     if (kind == KIND_Q1) gemm_tc_kernel<KIND_Q1><<<grid, TC_THREADS, TC_SMEM, st>>>(map, a);
     else if (kind == KIND_Q2) gemm_tc_kernel<KIND_Q2><<<grid, TC_THREADS, TC_SMEM, st>>>(map, a);
