@@ -105,6 +105,18 @@ int launch_load_q8_0(const uint8_t* raw, size_t raw_stride, int seq_len, int n_c
 int launch_store_q8_0(const int8_t* q, const float* d, int ld_q, int ld_b, int seq_len, int n_cols, uint8_t* raw,
                       size_t raw_stride, cudaStream_t st);
 
+// producers.cu: f32 rows -> Q8_0 planes with the producing arithmetic fused in (norm, gated activation, rotation).
+constexpr int RMS_NORM_MAX_COLS = 32768;  // one row is staged in shared memory
+int producers_prepare();
+int launch_rms_norm_q8(const float* x, const float* weight, float eps, int seq_len, int n_cols, int8_t* q, float* d, float* sums,
+                       int ld_q, int ld_b, uint8_t* raw_out, size_t raw_stride, cudaStream_t st);
+int launch_silu_mul_q8(const float* gate, const float* up, int seq_len, int ld_x, int n_cols, int8_t* q, float* d, float* sums,
+                       int ld_q, int ld_b, uint8_t* raw_out, size_t raw_stride, cudaStream_t st);
+// block_size: a power of two up to 1024.  `rotated` (may be null) also receives the rotated f32 rows.
+int launch_hadamard_quantize(const float* x, const float* signs, int block_size, int seq_len, int n_cols, float* rotated,
+                             int8_t* q, float* d, float* sums, int ld_q, int ld_b, uint8_t* raw_out, size_t raw_stride,
+                             cudaStream_t st);
+
 // repack.cu
 int launch_repack(int kind, const uint8_t* raw, size_t row_bytes, int n_rows, int n_cols, int nb, int n_panels,
                   uint4* bits, void* scales, cudaStream_t st);
@@ -123,7 +135,9 @@ int gemv_dp4a_prepare();  // sets the dynamic shared-memory attributes once
 // gemm_tc.cu: tcgen05 kind::i8 path for 5 or more tokens (Q1_0 / Q2_0).  `amap` points at a CUtensorMap over the
 // activation's int8 plane ([max_seq][ld_q] bytes, box 128 x 128, SWIZZLE_128B).  `status` is a device word that
 // receives a non-zero code if a bounded wait inside the kernel expires.
-constexpr int GEMM_TC_MIN_TOKENS = 5;
+// Below this many tokens, passes of the streaming dp4a kernel (four tokens each) are faster than one 128-token
+// tensor-core tile that is mostly empty (measured crossover on B200: about 44 tokens for Q2_0, later for Q1_0).
+constexpr int GEMM_TC_MIN_TOKENS = 48;
 int launch_gemm_tc(int kind, const void* amap, const uint4* bits, const void* scales, const float* ad, int ld_b, int n_rows,
                    int nb, int seq_len, float* out, int ld_out, int* status, cudaStream_t st);
 int gemm_tc_prepare();

@@ -1,5 +1,5 @@
 // Prefill / multi-token matmul on the 5th-generation tensor cores: tcgen05.mma kind::i8 with TMEM
-// accumulators, for Q1_0 and Q2_0 / PQ2_0 weights against 5 or more Q8_0 activations.
+// accumulators, for Q1_0 and Q2_0 / PQ2_0 weights against 48 or more Q8_0 activations (prefill).
 //
 // Replaces ThreadPool::par_dot_rows_batched over the paired-token kernels
 // (hearth-llm/src/pool.rs:40-80, :568-618; hearth-quant/src/q1_0g128.rs:396-502, q2_0.rs:408-492) and keeps

@@ -141,6 +141,7 @@ CONFIGS = {
     "c3_q6k_m8": dict(dtype=Q6_K, shapes=[("a", 14336, 4096), ("b", 4096, 14336)], layers=8, seq_len=8),
     "c3_q6k_m32": dict(dtype=Q6_K, shapes=[("a", 14336, 4096), ("b", 4096, 14336)], layers=8, seq_len=32),
     "c4_pq2_27b_decode": dict(dtype=PQ2_0, shapes=layer_shapes(5120, 17408, 1024), layers=64, seq_len=1),
+    "c4_pq2_27b_m4": dict(dtype=PQ2_0, shapes=layer_shapes(5120, 17408, 1024), layers=64, seq_len=4),
     "c4_pq2_27b_m32": dict(dtype=PQ2_0, shapes=layer_shapes(5120, 17408, 1024), layers=64, seq_len=32),
 }
 
