@@ -134,6 +134,22 @@ class Act:
         xp = C.c_void_p(x_dev.data_ptr()) if x_dev is not None else C.c_void_p(0)
         check(_l.load().hb200_act_quantize_dev(self._h, xp, seq_len, _stream_ptr(stream)))
 
+    def rms_norm_q8(self, x_dev, weight_dev, eps: float, seq_len: int, stream=None) -> None:
+        """ops::rms_norm_q8_batch (hearth-llm/src/ops.rs:489) on the device, into this activation's planes."""
+        check(_l.load().hb200_act_rms_norm_q8_dev(self._h, C.c_void_p(x_dev.data_ptr()), C.c_void_p(weight_dev.data_ptr()),
+                                                  eps, seq_len, _stream_ptr(stream)))
+
+    def silu_mul_q8(self, gate_dev, up_dev, seq_len: int, stream=None) -> None:
+        """ops::silu_mul_q8 (hearth-llm/src/ops.rs:273) per token on the device."""
+        check(_l.load().hb200_act_silu_mul_q8_dev(self._h, C.c_void_p(gate_dev.data_ptr()), C.c_void_p(up_dev.data_ptr()),
+                                                  seq_len, _stream_ptr(stream)))
+
+    def hadamard_quantize(self, seq_len: int, block_size: int, x_dev=None, signs_dev=None, rotated_dev=None, stream=None) -> None:
+        """hadamard_rotate + quantize_q8_0 (hearth-llm/src/model/qwen35.rs:924-943) on the device."""
+        p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+        check(_l.load().hb200_act_hadamard_quantize_dev(self._h, p(x_dev), p(signs_dev), block_size, seq_len, p(rotated_dev),
+                                                        _stream_ptr(stream)))
+
     def load_q8_0(self, q8_dev, seq_len: int, q8_stride: int, stream=None) -> None:
         check(_l.load().hb200_act_load_q8_0_dev(self._h, C.c_void_p(q8_dev.data_ptr()), seq_len, q8_stride, _stream_ptr(stream)))
 
@@ -168,6 +184,48 @@ def quantize_q8_0(x: np.ndarray) -> np.ndarray:
     out = np.zeros((seq_len, byte_size(Q8_0, dim)), dtype=np.uint8)
     check(_l.load().hb200_quantize_q8_0(_np_ptr(x2), seq_len, dim, _np_ptr(out)))
     return out[0] if x.ndim == 1 else out
+
+
+def _rows(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    return x.reshape(1, -1) if x.ndim == 1 else x
+
+
+def rms_norm_q8(x: np.ndarray, weight: np.ndarray, eps: float) -> np.ndarray:
+    """ops::rms_norm_q8 / rms_norm_q8_batch: f32 [seq, dim] (or [dim]) -> uint8 [seq, ceil(dim/32)*34]."""
+    x2 = _rows(x)
+    w = np.ascontiguousarray(weight, dtype=np.float32)
+    seq_len, dim = x2.shape
+    assert w.size == dim
+    out = np.zeros((seq_len, byte_size(Q8_0, dim)), dtype=np.uint8)
+    check(_l.load().hb200_rms_norm_q8(_np_ptr(x2), _np_ptr(w), eps, _np_ptr(out), seq_len, dim))
+    return out[0] if np.ndim(x) == 1 else out
+
+
+def silu_mul_q8(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    """ops::silu_mul_q8 per token: f32 [seq, dim] x2 -> uint8 [seq, (dim/32)*34]."""
+    g2, u2 = _rows(gate), _rows(up)
+    assert g2.shape == u2.shape
+    seq_len, dim = g2.shape
+    out = np.zeros((seq_len, dim // 32 * 34), dtype=np.uint8)
+    check(_l.load().hb200_silu_mul_q8(_np_ptr(g2), _np_ptr(u2), _np_ptr(out), seq_len, dim))
+    return out[0] if np.ndim(gate) == 1 else out
+
+
+def hadamard_quantize_q8_0(x: np.ndarray, signs: np.ndarray | None, block_size: int, return_rotated: bool = False):
+    """hadamard_rotate then quantize_q8_0 (hearth-llm/src/model/qwen35.rs:924-943) per token."""
+    x2 = _rows(x)
+    seq_len, dim = x2.shape
+    sg = np.ascontiguousarray(signs, dtype=np.float32) if signs is not None else None
+    assert sg is None or sg.size == dim
+    out = np.zeros((seq_len, byte_size(Q8_0, dim)), dtype=np.uint8)
+    rot = np.zeros_like(x2) if return_rotated else None
+    check(_l.load().hb200_hadamard_quantize_q8_0(_np_ptr(x2), _np_ptr(sg) if sg is not None else None, block_size, _np_ptr(out),
+                                                 _np_ptr(rot) if rot is not None else None, seq_len, dim))
+    if np.ndim(x) == 1:
+        out = out[0]
+        rot = rot[0] if rot is not None else None
+    return (out, rot) if return_rotated else out
 
 
 def par_dot_rows(w: Weight, a_q8: np.ndarray) -> np.ndarray:

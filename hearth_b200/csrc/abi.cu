@@ -257,6 +257,7 @@ extern "C" int hb200_init(int device) {
     if ((rc = gemv_dp4a_prepare())) return rc;
     if ((rc = kquant_prepare())) return rc;
     if ((rc = gemm_tc_prepare())) return rc;
+    if ((rc = producers_prepare())) return rc;
     {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
@@ -569,6 +570,60 @@ extern "C" int hb200_act_store_q8_0_dev(hb200_act_t a, uint8_t* q8_dev, size_t s
     HB_GUARD_END
 }
 
+static int producer_check(hb200_act_t a, size_t seq_len) {
+    if (!a) { set_error("null activation handle"); return HB200_ERR_NULL; }
+    if (seq_len > a->max_seq) { set_error("seq_len %zu exceeds capacity %zu", seq_len, a->max_seq); return HB200_ERR_BAD_SHAPE; }
+    return 0;
+}
+
+static int hadamard_check(size_t block_size) {
+    if (block_size > 1024 || (block_size & (block_size - 1)) != 0) {
+        set_error("rotation block of %zu columns: must be a power of two up to 1024", block_size);
+        return HB200_ERR_BAD_SHAPE;
+    }
+    return 0;
+}
+
+extern "C" int hb200_act_rms_norm_q8_dev(hb200_act_t a, const float* x_dev, const float* weight_dev, float eps, size_t seq_len,
+                                         void* stream) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if ((rc = producer_check(a, seq_len))) return rc;
+    if (!x_dev || !weight_dev) { set_error("null pointer"); return HB200_ERR_NULL; }
+    if (a->n_cols > (size_t)RMS_NORM_MAX_COLS) { set_error("rms_norm_q8 of %zu columns (limit %d)", a->n_cols, RMS_NORM_MAX_COLS); return HB200_ERR_TOO_LARGE; }
+    return launch_rms_norm_q8(x_dev, weight_dev, eps, (int)seq_len, (int)a->n_cols, a->q, a->d, a->sums, a->ld_q, a->ld_b, nullptr, 0,
+                              (cudaStream_t)stream);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_act_silu_mul_q8_dev(hb200_act_t a, const float* gate_dev, const float* up_dev, size_t seq_len, void* stream) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if ((rc = producer_check(a, seq_len))) return rc;
+    if (!gate_dev || !up_dev) { set_error("null pointer"); return HB200_ERR_NULL; }
+    return launch_silu_mul_q8(gate_dev, up_dev, (int)seq_len, (int)a->n_cols, (int)(a->n_cols / 32 * 32), a->q, a->d, a->sums,
+                              a->ld_q, a->ld_b, nullptr, 0, (cudaStream_t)stream);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_act_hadamard_quantize_dev(hb200_act_t a, const float* x_dev, const float* signs_dev, size_t block_size,
+                                               size_t seq_len, float* rotated_dev, void* stream) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if ((rc = producer_check(a, seq_len))) return rc;
+    if ((rc = hadamard_check(block_size))) return rc;
+    const float* x = x_dev ? x_dev : a->x;
+    if (block_size == 0 && !signs_dev && !rotated_dev)
+        return launch_quantize_q8_0(x, (int)seq_len, (int)a->n_cols, a->q, a->d, a->sums, a->ld_q, a->ld_b, nullptr, 0,
+                                    (cudaStream_t)stream);
+    return launch_hadamard_quantize(x, signs_dev, block_size ? (int)block_size : 1, (int)seq_len, (int)a->n_cols, rotated_dev, a->q,
+                                    a->d, a->sums, a->ld_q, a->ld_b, nullptr, 0, (cudaStream_t)stream);
+    HB_GUARD_END
+}
+
 // ------------------------------------------------------- device-buffer calls --
 
 extern "C" int hb200_dot_rows_dev(hb200_weight_t w, hb200_act_t a, size_t seq_len, float* out_dev, size_t ld_out, void* stream) {
@@ -616,6 +671,80 @@ extern "C" int hb200_quantize_q8_0(const float* x, size_t seq_len, size_t dim, u
     HB_CUDA(cudaMemcpyAsync(a->x, x, seq_len * dim * sizeof(float), cudaMemcpyHostToDevice, st));
     if ((rc = launch_quantize_q8_0(a->x, (int)seq_len, (int)dim, a->q, a->d, a->sums, a->ld_q, a->ld_b, g_ctx.d_out, q8_size, st))) return rc;
     HB_CUDA(cudaMemcpyAsync(q8_out, g_ctx.d_out, seq_len * q8_size, cudaMemcpyDeviceToHost, st));
+    HB_CUDA(cudaStreamSynchronize(st));
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+// Host-buffer forms of the fused producers: inputs up, one kernel, Q8_0 rows (reference byte layout) back.
+extern "C" int hb200_rms_norm_q8(const float* x, const float* weight, float eps, uint8_t* q8_out, size_t seq_len, size_t dim) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (seq_len == 0 || dim == 0) return HB200_OK;
+    if (!x || !weight || !q8_out) { set_error("null buffer"); return HB200_ERR_NULL; }
+    if (dim > (size_t)RMS_NORM_MAX_COLS) { set_error("rms_norm_q8 of %zu columns (limit %d)", dim, RMS_NORM_MAX_COLS); return HB200_ERR_TOO_LARGE; }
+    if ((rc = ensure_ctx_act(seq_len, dim))) return rc;
+    const size_t q8_size = hb200_byte_size(HB200_Q8_0, dim);
+    if ((rc = grow(&g_ctx.d_out, &g_ctx.d_out_bytes, seq_len * q8_size))) return rc;
+    if ((rc = grow(&g_ctx.d_in, &g_ctx.d_in_bytes, dim * sizeof(float)))) return rc;
+    hb200_act* a = g_ctx.act;
+    cudaStream_t st = g_ctx.stream;
+    HB_CUDA(cudaMemcpyAsync(a->x, x, seq_len * dim * sizeof(float), cudaMemcpyHostToDevice, st));
+    HB_CUDA(cudaMemcpyAsync(g_ctx.d_in, weight, dim * sizeof(float), cudaMemcpyHostToDevice, st));
+    if ((rc = launch_rms_norm_q8(a->x, (const float*)g_ctx.d_in, eps, (int)seq_len, (int)dim, a->q, a->d, a->sums, a->ld_q, a->ld_b,
+                                 g_ctx.d_out, q8_size, st))) return rc;
+    HB_CUDA(cudaMemcpyAsync(q8_out, g_ctx.d_out, seq_len * q8_size, cudaMemcpyDeviceToHost, st));
+    HB_CUDA(cudaStreamSynchronize(st));
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_silu_mul_q8(const float* gate, const float* up, uint8_t* q8_out, size_t seq_len, size_t dim) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    const size_t blocks = dim / 32;
+    if (seq_len == 0 || blocks == 0) return HB200_OK;
+    if (!gate || !up || !q8_out) { set_error("null buffer"); return HB200_ERR_NULL; }
+    if ((rc = ensure_ctx_act(seq_len, dim))) return rc;
+    const size_t q8_size = blocks * 34;
+    const size_t in_bytes = seq_len * dim * sizeof(float);
+    if ((rc = grow(&g_ctx.d_out, &g_ctx.d_out_bytes, seq_len * q8_size))) return rc;
+    if ((rc = grow(&g_ctx.d_in, &g_ctx.d_in_bytes, in_bytes))) return rc;
+    hb200_act* a = g_ctx.act;
+    cudaStream_t st = g_ctx.stream;
+    HB_CUDA(cudaMemcpyAsync(a->x, gate, in_bytes, cudaMemcpyHostToDevice, st));
+    HB_CUDA(cudaMemcpyAsync(g_ctx.d_in, up, in_bytes, cudaMemcpyHostToDevice, st));
+    if ((rc = launch_silu_mul_q8(a->x, (const float*)g_ctx.d_in, (int)seq_len, (int)dim, (int)(blocks * 32), a->q, a->d, a->sums,
+                                 a->ld_q, a->ld_b, g_ctx.d_out, q8_size, st))) return rc;
+    HB_CUDA(cudaMemcpyAsync(q8_out, g_ctx.d_out, seq_len * q8_size, cudaMemcpyDeviceToHost, st));
+    HB_CUDA(cudaStreamSynchronize(st));
+    return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_hadamard_quantize_q8_0(const float* x, const float* signs, size_t block_size, uint8_t* q8_out,
+                                            float* rotated_out, size_t seq_len, size_t dim) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (seq_len == 0 || dim == 0) return HB200_OK;
+    if (!x || !q8_out) { set_error("null buffer"); return HB200_ERR_NULL; }
+    if ((rc = hadamard_check(block_size))) return rc;
+    if ((rc = ensure_ctx_act(seq_len, dim))) return rc;
+    const size_t q8_size = hb200_byte_size(HB200_Q8_0, dim);
+    if ((rc = grow(&g_ctx.d_out, &g_ctx.d_out_bytes, seq_len * q8_size))) return rc;
+    if (signs && (rc = grow(&g_ctx.d_in, &g_ctx.d_in_bytes, dim * sizeof(float)))) return rc;
+    hb200_act* a = g_ctx.act;
+    cudaStream_t st = g_ctx.stream;
+    HB_CUDA(cudaMemcpyAsync(a->x, x, seq_len * dim * sizeof(float), cudaMemcpyHostToDevice, st));
+    if (signs) HB_CUDA(cudaMemcpyAsync(g_ctx.d_in, signs, dim * sizeof(float), cudaMemcpyHostToDevice, st));
+    if ((rc = launch_hadamard_quantize(a->x, signs ? (const float*)g_ctx.d_in : nullptr, block_size ? (int)block_size : 1,
+                                       (int)seq_len, (int)dim, rotated_out ? a->x : nullptr, a->q, a->d, a->sums, a->ld_q, a->ld_b,
+                                       g_ctx.d_out, q8_size, st))) return rc;
+    HB_CUDA(cudaMemcpyAsync(q8_out, g_ctx.d_out, seq_len * q8_size, cudaMemcpyDeviceToHost, st));
+    if (rotated_out) HB_CUDA(cudaMemcpyAsync(rotated_out, a->x, seq_len * dim * sizeof(float), cudaMemcpyDeviceToHost, st));
     HB_CUDA(cudaStreamSynchronize(st));
     return HB200_OK;
     HB_GUARD_END

@@ -11,76 +11,11 @@
 // HBM-bound: reads 4 B and writes ~1.06 B (+1.06 B for the byte-layout copy)
 // per element; one CTA handles 1024 columns of one token, four per thread.
 #include "common.cuh"
+#include "quantize_core.cuh"
 
 namespace hb200 {
 
 namespace {
-
-__device__ __forceinline__ int quant_one(float x, float scale) {
-    float r = roundf(__fdiv_rn(x, scale));
-    if (r != r) return 0;
-    r = fminf(fmaxf(r, -128.0f), 127.0f);
-    return (int)r;
-}
-
-// One thread's share of the quantizer: columns c0..c0+3 of token m; eight consecutive threads share one
-// 32-column block (all 32 lanes of the warp must call this together: it shuffles).
-template <bool RAW_OUT>
-__device__ __forceinline__ void quantize_thread(const float* __restrict__ x, int n_cols, int m, int c0, int8_t* __restrict__ q,
-                                                float* __restrict__ d, float* __restrict__ sums, int ld_q, int ld_b,
-                                                uint8_t* __restrict__ raw, size_t raw_stride) {
-    const float* xr = x + (size_t)m * n_cols;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    const bool vec_ok = ((n_cols & 3) == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
-    if (vec_ok && c0 + 3 < n_cols) {
-        float4 f = *reinterpret_cast<const float4*>(xr + c0);
-        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
-    } else {
-#pragma unroll
-        for (int i = 0; i < 4; i++)
-            if (c0 + i < n_cols) v[i] = xr[c0 + i];
-    }
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        float a = fabsf(v[i]);
-        if (a > amax) amax = a;  // NaN compares false, as in the reference
-    }
-#pragma unroll
-    for (int off = 1; off < 8; off <<= 1) {
-        float o = __shfl_xor_sync(0xffffffffu, amax, off);
-        if (o > amax) amax = o;
-    }
-    const float scale = (amax == 0.0f) ? 1.0f : __fdiv_rn(amax, 127.0f);
-    const __half h = __float2half_rn(scale);
-    int qi[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) qi[i] = (c0 + i < n_cols) ? quant_one(v[i], scale) : 0;
-    const uint32_t word = (uint32_t)(qi[0] & 0xff) | ((uint32_t)(qi[1] & 0xff) << 8) | ((uint32_t)(qi[2] & 0xff) << 16) |
-                          ((uint32_t)(qi[3] & 0xff) << 24);
-    int s = qi[0] + qi[1] + qi[2] + qi[3];
-#pragma unroll
-    for (int off = 1; off < 8; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-
-    const int blk = c0 >> 5;
-    const bool live = (blk * 32) < n_cols;  // block holds at least one real column
-    *reinterpret_cast<uint32_t*>(q + (size_t)m * ld_q + c0) = live ? word : 0u;
-    if ((threadIdx.x & 7) == 0) {
-        d[(size_t)m * ld_b + blk] = live ? __half2float(h) : 0.0f;
-        sums[(size_t)m * ld_b + blk] = live ? (float)s : 0.0f;
-    }
-    if (RAW_OUT && live) {
-        uint8_t* rb = raw + (size_t)m * raw_stride + (size_t)blk * 34;
-        if ((threadIdx.x & 7) == 0) {
-            const unsigned short hb = __half_as_ushort(h);
-            rb[0] = (uint8_t)(hb & 0xff);
-            rb[1] = (uint8_t)(hb >> 8);
-        }
-        const int i0 = (threadIdx.x & 7) * 4;
-#pragma unroll
-        for (int i = 0; i < 4; i++) rb[2 + i0 + i] = (uint8_t)(qi[i] & 0xff);
-    }
-}
 
 // grid (ld_q/1024, seq_len), block 256.
 template <bool RAW_OUT>

@@ -46,7 +46,13 @@ SIGNATURES = {
     "hb200_act_quantize_dev": (_int, [_vp, _vp, _sz, _vp]),
     "hb200_act_load_q8_0_dev": (_int, [_vp, _vp, _sz, _sz, _vp]),
     "hb200_act_store_q8_0_dev": (_int, [_vp, _vp, _sz, _sz, _vp]),
+    "hb200_act_rms_norm_q8_dev": (_int, [_vp, _vp, _vp, C.c_float, _sz, _vp]),
+    "hb200_act_silu_mul_q8_dev": (_int, [_vp, _vp, _vp, _sz, _vp]),
+    "hb200_act_hadamard_quantize_dev": (_int, [_vp, _vp, _vp, _sz, _sz, _vp, _vp]),
     "hb200_quantize_q8_0": (_int, [_vp, _sz, _sz, _vp]),
+    "hb200_rms_norm_q8": (_int, [_vp, _vp, C.c_float, _vp, _sz, _sz]),
+    "hb200_silu_mul_q8": (_int, [_vp, _vp, _vp, _sz, _sz]),
+    "hb200_hadamard_quantize_q8_0": (_int, [_vp, _vp, _sz, _vp, _vp, _sz, _sz]),
     "hb200_dot_rows": (_int, [_vp, _vp, _vp]),
     "hb200_dot_rows_batched": (_int, [_vp, _vp, _sz, _sz, _vp]),
     "hb200_matmul_f32": (_int, [_vp, _vp, _sz, _vp]),

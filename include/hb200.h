@@ -135,12 +135,48 @@ HB200_API int hb200_act_load_q8_0_dev(hb200_act_t a, const uint8_t *q8_dev, size
 /* Writes the Q8_0 planes of `a` back out in the reference byte layout. */
 HB200_API int hb200_act_store_q8_0_dev(hb200_act_t a, uint8_t *q8_dev, size_t seq_len, size_t q8_stride, void *stream);
 
+/* Fused producers: the f32 row is computed and quantized in one kernel, as the
+ * reference does on the CPU, and lands in the Q8_0 planes of `a`.
+ *
+ * ops::rms_norm_q8_batch (hearth-llm/src/ops.rs:442-504): x_dev is
+ * f32 [seq_len][n_cols], weight_dev f32 [n_cols]; n_cols <= 32768.  Bit-exact
+ * with the reference given the eight-lane reduction order stated in DESIGN. */
+HB200_API int hb200_act_rms_norm_q8_dev(hb200_act_t a, const float *x_dev, const float *weight_dev, float eps,
+                                        size_t seq_len, void *stream);
+/* ops::silu_mul_q8 (hearth-llm/src/ops.rs:273-306) per token: gate_dev and
+ * up_dev are f32 [seq_len][n_cols]; only the n_cols / 32 whole blocks are
+ * produced, as in the reference.  exp is CUDA's expf, not `wide`'s polynomial:
+ * equal to the reference within one quantization step, not bit for bit. */
+HB200_API int hb200_act_silu_mul_q8_dev(hb200_act_t a, const float *gate_dev, const float *up_dev, size_t seq_len,
+                                        void *stream);
+/* hadamard_rotate then quantize_q8_0, the step in front of every folded
+ * matmul (hearth-llm/src/model/qwen35.rs:49-87, :924-943): multiplies by
+ * signs_dev[n_cols] (may be null), applies the normalized Walsh-Hadamard
+ * transform to every whole block of block_size columns (a power of two, at
+ * most 1024; 0 = no rotation) and quantizes.  x_dev null = the act's own f32
+ * area.  rotated_dev (may be null) also receives the rotated f32 rows, which
+ * may alias x_dev.  Bit-exact with the reference. */
+HB200_API int hb200_act_hadamard_quantize_dev(hb200_act_t a, const float *x_dev, const float *signs_dev,
+                                              size_t block_size, size_t seq_len, float *rotated_dev, void *stream);
+
 /* ---- host-buffer calls (the reference's own call shapes) ---------------- */
 
 /* quantize_q8_0_into / par_quantize with host buffers
  * (hearth-quant/src/lib.rs:381-387, hearth-llm/src/pool.rs:467).  q8_out gets
  * seq_len rows of ceil(dim/32)*34 bytes. */
 HB200_API int hb200_quantize_q8_0(const float *x, size_t seq_len, size_t dim, uint8_t *q8_out);
+
+/* ops::rms_norm_q8_batch with host buffers (hearth-llm/src/ops.rs:489-504):
+ * q8_out gets seq_len rows of ceil(dim/32)*34 bytes. */
+HB200_API int hb200_rms_norm_q8(const float *x, const float *weight, float eps, uint8_t *q8_out, size_t seq_len,
+                                size_t dim);
+/* ops::silu_mul_q8 per token with host buffers (hearth-llm/src/ops.rs:273):
+ * rows of gate / up are dim floats apart, q8_out rows (dim/32)*34 bytes. */
+HB200_API int hb200_silu_mul_q8(const float *gate, const float *up, uint8_t *q8_out, size_t seq_len, size_t dim);
+/* hadamard_rotate + quantize_q8_0 with host buffers (qwen35.rs:924-943);
+ * signs may be null; rotated_out (may be null) receives the rotated rows. */
+HB200_API int hb200_hadamard_quantize_q8_0(const float *x, const float *signs, size_t block_size, uint8_t *q8_out,
+                                           float *rotated_out, size_t seq_len, size_t dim);
 
 /* ThreadPool::par_dot_rows(DotRowsParams) (pool.rs:246-257, :510-566): every
  * row of `w` against one Q8_0 activation; out[n_rows]. */

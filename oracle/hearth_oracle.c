@@ -501,3 +501,118 @@ HO_API int ho_matmul_kquant_f32(int dtype, size_t n, size_t seq_len, const uint8
         }
     return 0;
 }
+
+/* ------------------------------------------- fused producers of Q8_0 rows -- */
+
+/* hadamard_rotate + walsh_hadamard_in_place (hearth-llm/src/model/qwen35.rs:49-87):
+ * optional sign vector, then per block_size chunk the in-place butterfly
+ * (stages h = 1, 2, 4, ...; x[i] = a + b, x[i|h] = a - b) and a final multiply
+ * by s = 1 / sqrt(n) computed in f32.  A tail shorter than block_size is left
+ * untouched (chunks_exact_mut).  Every operation is a plain f32 add / multiply. */
+HO_API void ho_hadamard_rotate(float *x, size_t n, const float *signs, size_t block_size) {
+    if (signs)
+        for (size_t i = 0; i < n; i++) x[i] *= signs[i];
+    if (block_size == 0) return;
+    for (size_t c = 0; c + block_size <= n; c += block_size) {
+        float *v = x + c;
+        float s = 1.0f / sqrtf((float)block_size);
+        for (size_t h = 1; h < block_size; h <<= 1)
+            for (size_t i = 0; i < block_size; i++)
+                if ((i & h) == 0) {
+                    float a = v[i], b = v[i | h];
+                    v[i] = a + b;
+                    v[i | h] = a - b;
+                }
+        for (size_t i = 0; i < block_size; i++) v[i] *= s;
+    }
+}
+
+/* The step in front of every PQ2_0 / PTQ1_0 matmul of the hybrid models:
+ * rotate a copy of x, then quantize_q8_0 (qwen35.rs:924-943). */
+HO_API void ho_hadamard_quantize_q8_0(const float *x, size_t n, const float *signs, size_t block_size, float *tmp,
+                                      uint8_t *q8_out) {
+    memcpy(tmp, x, n * sizeof(float));
+    ho_hadamard_rotate(tmp, n, signs, block_size);
+    ho_quantize_q8_0_into(tmp, n, q8_out);
+}
+
+/* ops::rms_norm_q8 (hearth-llm/src/ops.rs:442-487): sum of squares in eight
+ * fused-multiply-add lanes (lane j takes elements 8i+j), lanes reduced (order
+ * assumed, see reduce8), scalar remainder, rms = sqrt(sum/n + eps),
+ * inv = 1/rms, normed = (weight * x) * inv, then the Q8_0 block arithmetic. */
+HO_API void ho_rms_norm_q8(const float *x, const float *weight, float eps, uint8_t *q8_out, size_t dim) {
+    size_t n = dim, chunks = n / 8, rem = n % 8;
+    float lanes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (size_t i = 0; i < chunks; i++)
+        for (int j = 0; j < 8; j++) lanes[j] = fmaf(x[i * 8 + j], x[i * 8 + j], lanes[j]);
+    float sum_sq = 0.0f;
+    sum_sq += reduce8(lanes);
+    for (size_t i = n - rem; i < n; i++) sum_sq += x[i] * x[i];
+    float rms = sqrtf(sum_sq / (float)n + eps);
+    float inv_rms = 1.0f / rms;
+    size_t blocks = (n + 31) / 32;
+    for (size_t b = 0; b < blocks; b++) {
+        size_t start = b * 32, cnt = (n - start < 32) ? n - start : 32;
+        float max_abs = 0.0f;
+        for (size_t i = 0; i < cnt; i++) {
+            float normed = weight[start + i] * x[start + i] * inv_rms;
+            float a = fabsf(normed);
+            if (a > max_abs) max_abs = a;
+        }
+        float scale = (max_abs == 0.0f) ? 1.0f : max_abs / 127.0f;
+        uint16_t h = ho_f2h(scale);
+        size_t off = b * 34;
+        q8_out[off] = (uint8_t)(h & 0xFF);
+        q8_out[off + 1] = (uint8_t)(h >> 8);
+        for (size_t i = 0; i < 32; i++) {
+            int8_t q = 0;
+            if (i < cnt) {
+                float normed = weight[start + i] * x[start + i] * inv_rms;
+                float r = roundf(normed / scale);
+                if (r != r) q = 0;
+                else {
+                    if (r < -128.0f) r = -128.0f;
+                    if (r > 127.0f) r = 127.0f;
+                    q = (int8_t)r;
+                }
+            }
+            q8_out[off + 2 + i] = (uint8_t)q;
+        }
+    }
+}
+
+/* ops::silu_mul_q8 (hearth-llm/src/ops.rs:273-306): v = (g / (1 + exp(-g))) * u
+ * per element, then the Q8_0 block arithmetic; dim / 32 whole blocks.  The
+ * reference's exp is `wide`'s f32x8 polynomial, which is not available here;
+ * expf from libm stands in, so this function is a tolerance-level restatement
+ * (quantized values may differ by one step at a rounding boundary). */
+HO_API void ho_silu_mul_q8(const float *gate, const float *up, uint8_t *q8_out, size_t dim) {
+    size_t blocks = dim / 32;
+    for (size_t b = 0; b < blocks; b++) {
+        float tmp[32], max_abs = 0.0f;
+        for (int i = 0; i < 32; i++) {
+            float g = gate[b * 32 + i];
+            float s = g / (1.0f + expf(-g));
+            float v = s * up[b * 32 + i];
+            tmp[i] = v;
+            float a = fabsf(v);
+            if (a > max_abs) max_abs = a;
+        }
+        float scale = (max_abs == 0.0f) ? 1.0f : max_abs / 127.0f;
+        uint16_t h = ho_f2h(scale);
+        size_t off = b * 34;
+        q8_out[off] = (uint8_t)(h & 0xFF);
+        q8_out[off + 1] = (uint8_t)(h >> 8);
+        for (int i = 0; i < 32; i++) {
+            float r = roundf(tmp[i] / scale);
+            int8_t q;
+            if (r != r) q = 0;
+            else {
+                if (r < -128.0f) r = -128.0f;
+                if (r > 127.0f) r = 127.0f;
+                q = (int8_t)r;
+            }
+            q8_out[off + 2 + i] = (uint8_t)q;
+        }
+    }
+}

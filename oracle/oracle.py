@@ -72,6 +72,14 @@ def lib() -> C.CDLL:
                                               C.c_size_t, C.c_size_t]
         L.ho_matmul_kquant_f32.restype = C.c_int
         L.ho_matmul_kquant_f32.argtypes = [C.c_int, C.c_size_t, C.c_size_t, _u8p, _f32p, _f32p, C.c_size_t]
+        L.ho_hadamard_rotate.restype = None
+        L.ho_hadamard_rotate.argtypes = [_f32p, C.c_size_t, _f32p, C.c_size_t]
+        L.ho_hadamard_quantize_q8_0.restype = None
+        L.ho_hadamard_quantize_q8_0.argtypes = [_f32p, C.c_size_t, _f32p, C.c_size_t, _f32p, _u8p]
+        L.ho_rms_norm_q8.restype = None
+        L.ho_rms_norm_q8.argtypes = [_f32p, _f32p, C.c_float, _u8p, C.c_size_t]
+        L.ho_silu_mul_q8.restype = None
+        L.ho_silu_mul_q8.argtypes = [_f32p, _f32p, _u8p, C.c_size_t]
         _lib = L
     return _lib
 
@@ -176,3 +184,36 @@ def simd_dot_rows_batched(dtype: int, w: np.ndarray, a_q8: np.ndarray, n_rows: i
     rc = simd().hs_par_dot_rows_batched(dtype, n_rows, seq_len, stride, _u8(w), _u8(a2), _f32(out), rb, n_cols)
     assert rc == 0, rc
     return out
+
+
+def hadamard_rotate(x: np.ndarray, signs: np.ndarray | None, block_size: int) -> np.ndarray:
+    """qwen35.rs:49-87 on every row of x (f32 [seq, n] or [n]); returns the rotated copy."""
+    x2 = np.array(x, dtype=np.float32, copy=True)
+    rows = x2.reshape(1, -1) if x2.ndim == 1 else x2
+    sp = _f32(np.ascontiguousarray(signs, dtype=np.float32)) if signs is not None else None
+    for r in rows:
+        lib().ho_hadamard_rotate(_f32(r), r.size, sp, block_size)
+    return x2
+
+
+def hadamard_quantize_q8_0(x: np.ndarray, signs: np.ndarray | None, block_size: int) -> np.ndarray:
+    return quantize_q8_0(hadamard_rotate(x, signs, block_size))
+
+
+def rms_norm_q8(x: np.ndarray, weight: np.ndarray, eps: float) -> np.ndarray:
+    """ops::rms_norm_q8_batch: f32 [seq, dim] -> uint8 [seq, ceil(dim/32)*34]."""
+    x2 = np.ascontiguousarray(x.reshape(1, -1) if x.ndim == 1 else x, dtype=np.float32)
+    w = np.ascontiguousarray(weight, dtype=np.float32)
+    out = np.zeros((x2.shape[0], (x2.shape[1] + 31) // 32 * 34), dtype=np.uint8)
+    for s in range(x2.shape[0]):
+        lib().ho_rms_norm_q8(_f32(x2[s]), _f32(w), eps, _u8(out[s]), x2.shape[1])
+    return out[0] if x.ndim == 1 else out
+
+
+def silu_mul_q8(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
+    g2 = np.ascontiguousarray(gate.reshape(1, -1) if gate.ndim == 1 else gate, dtype=np.float32)
+    u2 = np.ascontiguousarray(up.reshape(1, -1) if up.ndim == 1 else up, dtype=np.float32)
+    out = np.zeros((g2.shape[0], g2.shape[1] // 32 * 34), dtype=np.uint8)
+    for s in range(g2.shape[0]):
+        lib().ho_silu_mul_q8(_f32(g2[s]), _f32(u2[s]), _u8(out[s]), g2.shape[1])
+    return out[0] if gate.ndim == 1 else out

@@ -75,3 +75,36 @@ def dot_q8x(kind: str, w: np.ndarray, a: np.ndarray, n: int):
             acc = f32(acc + f32(f32(d) * h2f(ab)))
         total = f32(total + f32(acc * ws))
     return total, np.array(ints, dtype=np.int32)
+
+
+def hadamard_rotate(x: np.ndarray, signs, block_size: int) -> np.ndarray:
+    """Independent float32 restatement of qwen35.rs:49-87 for one row (vectorised butterflies)."""
+    v = np.array(x, dtype=np.float32, copy=True)
+    if signs is not None:
+        v = (v * np.asarray(signs, dtype=np.float32)).astype(np.float32)
+    n_whole = (v.size // block_size) * block_size if block_size else 0
+    if n_whole:
+        blk = v[:n_whole].reshape(-1, block_size)
+        h = 1
+        while h < block_size:
+            t = blk.reshape(blk.shape[0], block_size // (2 * h), 2, h)
+            a, b = t[:, :, 0, :].copy(), t[:, :, 1, :].copy()
+            t[:, :, 0, :] = a + b
+            t[:, :, 1, :] = a - b
+            h *= 2
+        s = np.float32(1.0) / np.sqrt(np.float32(block_size))
+        v[:n_whole] = (blk * np.float32(s)).reshape(-1)
+    return v
+
+
+def rms_norm_values(x: np.ndarray, weight: np.ndarray, eps: float) -> np.ndarray:
+    """f64 normed values of ops::rms_norm_q8 (for tolerance checks, not bit parity)."""
+    x64 = x.astype(np.float64)
+    inv = 1.0 / np.sqrt((x64 * x64).mean() + eps)
+    return weight.astype(np.float64) * x64 * inv
+
+
+def dequantize_q8_0(q8: np.ndarray, n: int) -> np.ndarray:
+    blocks = q8.reshape(-1, 34)
+    d = blocks[:, :2].copy().view(np.float16).astype(np.float32)
+    return (d * blocks[:, 2:].view(np.int8).astype(np.float32)).reshape(-1)[:n]
