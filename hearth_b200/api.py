@@ -13,7 +13,7 @@ import ctypes as C
 import numpy as np
 
 from . import lib as _l
-from .lib import PQ2_0, Q1_0, Q1_0_G128, Q2_0, Q4_K, Q6_K, Q8_0, Hb200Error, check  # noqa: F401
+from .lib import PQ2_0, PTQ1_0, Q1_0, Q1_0_G128, Q2_0, Q4_K, Q6_K, Q8_0, Hb200Error, check  # noqa: F401
 
 _initialized_device = None
 

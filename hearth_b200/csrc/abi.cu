@@ -129,6 +129,7 @@ int kind_of(int dtype) {
     switch (dtype) {
         case HB200_Q1_0: case HB200_Q1_0_G128: case HB200_Q1_0_G128_LEGACY: return KIND_Q1;
         case HB200_Q2_0: case HB200_PQ2_0: return KIND_Q2;
+        case HB200_PTQ1_0: return KIND_Q2;  // re-coded to 2-bit codes at upload
         case HB200_Q8_0: return KIND_Q8;
         case HB200_Q4_K: return KIND_Q4K;
         case HB200_Q6_K: return KIND_Q6K;
@@ -304,6 +305,7 @@ extern "C" size_t hb200_block_size(int dtype) {
     }
 }
 extern "C" size_t hb200_block_bytes(int dtype) {
+    if (dtype == HB200_PTQ1_0) return 28;
     switch (kind_of(dtype)) {
         case KIND_Q1: return 18;
         case KIND_Q2: case KIND_Q8: return 34;
@@ -345,9 +347,11 @@ static int weight_build(int dtype, size_t n_rows, size_t n_cols, const uint8_t* 
     const size_t bytes = n_rows * w->row_bytes;
     int rc = 0;
     uint8_t* d_raw = nullptr;
+    uint8_t* d_recode = nullptr;
     bool own_raw = false;
     auto fail = [&](int code) {
         if (own_raw && d_raw) cudaFree(d_raw);
+        if (d_recode) cudaFree(d_recode);
         if (w->bits) cudaFree(w->bits);
         if (w->scales) cudaFree(w->scales);
         if (w->kq) cudaFree(w->kq);
@@ -401,12 +405,23 @@ static int weight_build(int dtype, size_t n_rows, size_t n_cols, const uint8_t* 
             if (e == cudaSuccess) e = cudaMalloc(&w->scales, scale_bytes);
             if (e != cudaSuccess) { set_error("cudaMalloc for %zu weight bytes failed: %s", bits_bytes + scale_bytes, cudaGetErrorString(e)); return fail(HB200_ERR_CUDA); }
             const int eff_cols = (kind == KIND_Q8) ? (int)n_cols : w->nb * 128;
-            rc = launch_repack(kind, d_raw, w->row_bytes, (int)n_rows, eff_cols, w->nb, w->n_panels, w->bits, w->scales, st);
+            const uint8_t* rows = d_raw;
+            size_t rows_stride = w->row_bytes;
+            if (dtype == HB200_PTQ1_0) {  // base-3 digits -> 2-bit codes, then the Q2_0 panels
+                rows_stride = (size_t)w->nb * 34;
+                e = cudaMalloc(&d_recode, n_rows * rows_stride);
+                if (e != cudaSuccess) { set_error("cudaMalloc(%zu) failed: %s", n_rows * rows_stride, cudaGetErrorString(e)); return fail(HB200_ERR_CUDA); }
+                rc = launch_ptq1_to_q2(d_raw, w->row_bytes, (int)n_rows, w->nb, d_recode, rows_stride, st);
+                if (rc) return fail(rc);
+                rows = d_recode;
+            }
+            rc = launch_repack(kind, rows, rows_stride, (int)n_rows, eff_cols, w->nb, w->n_panels, w->bits, w->scales, st);
             if (rc) return fail(rc);
         }
         cudaError_t e = cudaStreamSynchronize(st);
         if (e != cudaSuccess) { set_error("weight re-tiling failed: %s", cudaGetErrorString(e)); return fail(HB200_ERR_CUDA); }
         if (own_raw) { cudaFree(d_raw); own_raw = false; }
+        if (d_recode) { cudaFree(d_recode); d_recode = nullptr; }
         w->resident_bytes = bits_bytes + scale_bytes;
     }
     *out = w;

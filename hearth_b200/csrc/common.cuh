@@ -121,6 +121,10 @@ int launch_hadamard_quantize(const float* x, const float* signs, int block_size,
 int launch_repack(int kind, const uint8_t* raw, size_t row_bytes, int n_rows, int n_cols, int nb, int n_panels,
                   uint4* bits, void* scales, cudaStream_t st);
 
+// PTQ1_0 rows (28 B per 128 columns) -> Q2_0 rows (34 B per 128), the same weights in 2-bit codes.
+int launch_ptq1_to_q2(const uint8_t* raw, size_t row_bytes_in, int n_rows, int nb, uint8_t* out, size_t row_bytes_out,
+                      cudaStream_t st);
+
 // gemv_dp4a.cu
 constexpr int GEMV_MAX_M = 4;  // tokens one dp4a launch handles per op
 // Either an op list in device memory (ops_dev / items_dev, with chunks_dev[grid + 1] giving each CTA its contiguous,

@@ -108,7 +108,51 @@ int run(const uint8_t* raw, size_t row_bytes, int n_rows, int n_cols, int nb, in
     return 0;
 }
 
+// PTQ1_0 (28 B per 128: qs[24] five base-3 digits per byte, qh[2] four, f16 d at byte 26;
+// hearth-quant/src/ptq1_0.rs:1-57) -> the Q2_0 byte layout, digit + 1 being exactly Q2_0's code for the same
+// weight (-1 -> 0, 0 -> 1, +1 -> 2).  Element e of a block (ptq1_0.rs:563-585): e < 80 is digit e / 16 of
+// qs[e % 16], e < 120 digit (e - 80) / 8 of qs[16 + (e - 80) % 8], else digit (e - 120) / 2 of qh[(e - 120) % 2].
+// One thread per output byte (four elements); thread 0 of a block also moves the scale.
+__device__ __forceinline__ uint32_t ptq_digit(uint32_t byte, int n) {
+    const uint32_t pow3 = (n == 0) ? 1u : (n == 1) ? 3u : (n == 2) ? 9u : (n == 3) ? 27u : 81u;
+    return (((byte * pow3) & 255u) * 3u) >> 8;  // 0..2
+}
+
+__global__ void __launch_bounds__(256) ptq1_to_q2_kernel(const uint8_t* __restrict__ raw, size_t row_bytes_in, int n_rows, int nb,
+                                                         uint8_t* __restrict__ out, size_t row_bytes_out) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)n_rows * nb * 32;
+    if (idx >= total) return;
+    const int j = (int)(idx & 31);
+    const size_t blk = idx >> 5;
+    const size_t row = blk / nb;
+    const int b = (int)(blk % nb);
+    const uint8_t* src = raw + row * row_bytes_in + (size_t)b * 28;
+    uint8_t* dst = out + row * row_bytes_out + (size_t)b * 34;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int e = j * 4 + i;
+        uint32_t digit;
+        if (e < 80) digit = ptq_digit(src[e & 15], e >> 4);
+        else if (e < 120) digit = ptq_digit(src[16 + ((e - 80) & 7)], (e - 80) >> 3);
+        else digit = ptq_digit(src[24 + ((e - 120) & 1)], (e - 120) >> 1);
+        packed |= digit << (2 * i);
+    }
+    dst[2 + j] = (uint8_t)packed;
+    if (j == 0) { dst[0] = src[26]; dst[1] = src[27]; }
+}
+
 }  // namespace
+
+int launch_ptq1_to_q2(const uint8_t* raw, size_t row_bytes_in, int n_rows, int nb, uint8_t* out, size_t row_bytes_out,
+                      cudaStream_t st) {
+    const size_t total = (size_t)n_rows * nb * 32;
+    if (total == 0) return 0;
+    ptq1_to_q2_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(raw, row_bytes_in, n_rows, nb, out, row_bytes_out);
+    HB_CUDA(cudaGetLastError());
+    return 0;
+}
 
 int launch_repack(int kind, const uint8_t* raw, size_t row_bytes, int n_rows, int n_cols, int nb, int n_panels,
                   uint4* bits, void* scales, cudaStream_t st) {

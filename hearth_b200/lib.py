@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libhearth_b200.so")
 
 # GGML type ids on this path (hearth-gguf/src/ggml.rs:49-101 of the reference).
-Q8_0, Q4_K, Q6_K, Q1_0_G128_LEGACY, Q1_0, Q2_0, Q1_0_G128, PQ2_0 = 8, 12, 14, 39, 41, 42, 43, 142
+Q8_0, Q4_K, Q6_K, Q1_0_G128_LEGACY, Q1_0, Q2_0, Q1_0_G128, PQ2_0, PTQ1_0 = 8, 12, 14, 39, 41, 42, 43, 142, 143
 
 STATUS = {
     0: "HB200_OK", -1: "HB200_ERR_NOT_INITIALIZED", -2: "HB200_ERR_NO_DEVICE", -3: "HB200_ERR_BAD_DTYPE",

@@ -16,9 +16,9 @@ from __future__ import annotations
 
 import numpy as np
 
-from .lib import PQ2_0, Q1_0, Q1_0_G128, Q2_0, Q4_K, Q6_K, Q8_0
+from .lib import PQ2_0, PTQ1_0, Q1_0, Q1_0_G128, Q2_0, Q4_K, Q6_K, Q8_0
 
-_BLOCK = {Q1_0: (128, 18), Q1_0_G128: (128, 18), 39: (128, 18), Q2_0: (128, 34), PQ2_0: (128, 34), Q8_0: (32, 34),
+_BLOCK = {Q1_0: (128, 18), Q1_0_G128: (128, 18), 39: (128, 18), Q2_0: (128, 34), PQ2_0: (128, 34), Q8_0: (32, 34), PTQ1_0: (128, 28),
           Q4_K: (256, 144), Q6_K: (256, 210)}
 
 
@@ -52,6 +52,17 @@ def weights(dtype: int, n_rows: int, n_cols: int, seed: int, *, allow_code3: boo
         t0, t1, t2 = (72, 174, 246) if allow_code3 else (77, 179, 256)
         codes = (u >= t0).astype(np.uint8) + (u >= t1).astype(np.uint8) + (u.astype(np.uint16) >= t2).astype(np.uint8)
         out[:, :, 2:] = codes[..., 0] | (codes[..., 1] << 2) | (codes[..., 2] << 4) | (codes[..., 3] << 6)
+    elif dtype == PTQ1_0:
+        # digits 0/1/2 (weights -1/0/+1) with P = 0.30/0.40/0.30, packed as the reference's own packer does
+        # (hearth-quant/src/ptq1_0.rs:604-646): Q = sum of digit * 3^k, most significant first, byte = ceil(256 Q / 243).
+        out[:, :, 26:28] = _f16_bytes(np.abs(g.normal(0.0, 0.02, (n_rows, nb))))
+        u = g.integers(0, 256, (n_rows, nb, 26, 5), dtype=np.uint8)
+        dig = (u >= 77).astype(np.uint16) + (u >= 179).astype(np.uint16)
+        qv = np.zeros((n_rows, nb, 26), dtype=np.uint16)
+        for k in range(5):
+            use = dig[..., k] if k < 4 else np.concatenate([dig[..., :24, 4], np.zeros((n_rows, nb, 2), np.uint16)], axis=2)
+            qv = qv * 3 + use  # the two qh bytes carry four digits and a trailing zero
+        out[:, :, 0:26] = ((qv * 256 + 242) // 243).astype(np.uint8)
     elif dtype == Q8_0:
         out[:, :, 0:2] = _f16_bytes(np.abs(g.normal(0.0, 0.02, (n_rows, nb))) / 127.0 + 1e-6)
         out[:, :, 2:] = g.integers(-127, 128, (n_rows, nb, 32)).astype(np.int8).view(np.uint8)
@@ -100,6 +111,10 @@ def weights_torch(dtype: int, n_rows: int, n_cols: int, seed: int, device):
             packed |= code << (2 * j)
             del u, code
         out[:, :, 2:] = packed
+    elif dtype == PTQ1_0:
+        # every byte value decodes to valid base-3 digits (ptq1_0.rs:22-57), so uniform bytes are legal blocks
+        out[:, :, 0:26] = torch.randint(0, 256, (n_rows, nb, 26), dtype=torch.uint8, device=device, generator=g)
+        out[:, :, 26:28] = f16_bytes(0.02)
     elif dtype == Q8_0:
         v = torch.empty((n_rows, nb), dtype=torch.float32, device=device).normal_(0.0, 0.02, generator=g).abs_() / 127.0 + 1e-6
         out[:, :, 0:2] = v.to(torch.float16).view(torch.uint8).reshape(n_rows, nb, 2)
@@ -141,6 +156,7 @@ CONFIGS = {
     "c3_q6k_m8": dict(dtype=Q6_K, shapes=[("a", 14336, 4096), ("b", 4096, 14336)], layers=8, seq_len=8),
     "c3_q6k_m32": dict(dtype=Q6_K, shapes=[("a", 14336, 4096), ("b", 4096, 14336)], layers=8, seq_len=32),
     "c4_pq2_27b_decode": dict(dtype=PQ2_0, shapes=layer_shapes(5120, 17408, 1024), layers=64, seq_len=1),
+    "c4_ptq1_27b_decode": dict(dtype=PTQ1_0, shapes=layer_shapes(5120, 17408, 1024), layers=64, seq_len=1),
     "c4_pq2_27b_m4": dict(dtype=PQ2_0, shapes=layer_shapes(5120, 17408, 1024), layers=64, seq_len=4),
     "c4_pq2_27b_m32": dict(dtype=PQ2_0, shapes=layer_shapes(5120, 17408, 1024), layers=64, seq_len=32),
 }

@@ -65,7 +65,8 @@ enum {
     HB200_Q1_0 = 41,
     HB200_Q2_0 = 42,
     HB200_Q1_0_G128 = 43,
-    HB200_PQ2_0 = 142
+    HB200_PQ2_0 = 142,
+    HB200_PTQ1_0 = 143 /* dense base-3 ternary, 28 B per 128 (hearth-quant/src/ptq1_0.rs) */
 };
 
 typedef struct hb200_weight *hb200_weight_t; /* resident weight matrix */

@@ -103,6 +103,7 @@ enum {
     HO_Q2_0 = 42,
     HO_Q1_0_G128 = 43,
     HO_PQ2_0 = 142,
+    HO_PTQ1_0 = 143,
 };
 
 /* GgmlDType::block_size (hearth-gguf/src/ggml.rs:105-129); 0 = not on this path. */
@@ -112,6 +113,7 @@ HO_API size_t ho_block_size(int dtype) {
         case HO_Q4_K: case HO_Q6_K: return 256;
         case HO_Q1_0: case HO_Q1_0_G128: case HO_Q1_0_G128_LEGACY: return 128;
         case HO_Q2_0: case HO_PQ2_0: return 128;
+        case HO_PTQ1_0: return 128;
         default: return 0;
     }
 }
@@ -124,6 +126,7 @@ HO_API size_t ho_block_bytes(int dtype) {
         case HO_Q6_K: return 210;
         case HO_Q1_0: case HO_Q1_0_G128: case HO_Q1_0_G128_LEGACY: return 18;
         case HO_Q2_0: case HO_PQ2_0: return 34;
+        case HO_PTQ1_0: return 28;
         default: return 0;
     }
 }
@@ -228,6 +231,123 @@ HO_API void ho_dequantize_q2_0(const uint8_t *data, size_t bytes, float *out, si
     }
 }
 
+/* ------------------------------------------------ PTQ1_0 (dense trits) ---- */
+
+/* Block of 128 weights in 28 bytes: qs[24] with five base-3 digits per byte,
+ * qh[2] with four, f16 d at byte 26 (hearth-quant/src/ptq1_0.rs:1-13).
+ * Digit n of byte b, already in weight space {-1, 0, +1}: the TRIT_N / QH_TRIT
+ * tables (ptq1_0.rs:22-57) are this expression evaluated for every byte. */
+static inline int ptq_trit(uint8_t b, int n) {
+    static const uint16_t pow3[5] = {1, 3, 9, 27, 81};
+    uint8_t prod = (uint8_t)(((uint16_t)b * pow3[n]) & 0xFF);
+    return (int)(((uint16_t)prod * 3) >> 8) - 1;
+}
+
+/* The 128 weights of one block in element order (the wvals fill of
+ * dot_ptq1_0_q8_0_ptr_scalar, ptq1_0.rs:563-585): a 16-byte stage emits
+ * elements n*16 + m, an 8-byte stage 80 + n*8 + m, then qh 120 + n*2 + h. */
+static void ptq_decode_block(const uint8_t *blk, int8_t wvals[128]) {
+    static const size_t stages[3] = {32, 16, 8};
+    size_t out_off = 0, j = 0;
+    for (int si = 0; si < 3; si++) {
+        size_t c = stages[si];
+        while (j + c <= 24) {
+            for (size_t m = 0; m < c; m++)
+                for (int n = 0; n < 5; n++) wvals[out_off + (size_t)n * c + m] = (int8_t)ptq_trit(blk[j + m], n);
+            out_off += 5 * c;
+            j += c;
+        }
+    }
+    for (int n = 0; n < 4; n++)
+        for (int h = 0; h < 2; h++) wvals[out_off + (size_t)n * 2 + (size_t)h] = (int8_t)ptq_trit(blk[24 + h], n);
+}
+
+/* ptq1_0::dequantize (ptq1_0.rs:59-105). */
+HO_API void ho_dequantize_ptq1_0(const uint8_t *data, size_t bytes, float *out, size_t n_out) {
+    size_t blocks = bytes / 28;
+    int8_t wv[128];
+    for (size_t b = 0; b < blocks; b++) {
+        float scale = rd_h(data + b * 28 + 26);
+        ptq_decode_block(data + b * 28, wv);
+        for (size_t e = 0; e < 128; e++) {
+            size_t idx = b * 128 + e;
+            if (idx < n_out) out[idx] = (float)wv[e] * scale;
+        }
+    }
+}
+
+/* ptq1_0::quantize (ptq1_0.rs:604-646), the reference's own packer; its
+ * tests build their fixtures with it.  n / 128 whole blocks. */
+HO_API void ho_quantize_ptq1_0(const float *src, size_t n, uint8_t *dst) {
+    static const size_t stages[3] = {32, 16, 8};
+    size_t blocks = n / 128;
+    for (size_t b = 0; b < blocks; b++) {
+        const float *x = src + b * 128;
+        uint8_t *block = dst + b * 28;
+        float amax = 0.0f;
+        for (int i = 0; i < 128; i++) {
+            float a = fabsf(x[i]);
+            if (a > amax) amax = a; /* f32::max skips NaN */
+        }
+        float d = amax, id = (d != 0.0f) ? 1.0f / d : 0.0f;
+        uint16_t h = ho_f2h(d);
+        memset(block, 0, 28);
+        block[26] = (uint8_t)(h & 0xFF);
+        block[27] = (uint8_t)(h >> 8);
+        size_t x_off = 0, j = 0;
+        for (int si = 0; si < 3; si++) {
+            size_t c = stages[si];
+            while (j + c <= 24) {
+                for (size_t m = 0; m < c; m++) {
+                    uint8_t q = 0;
+                    for (size_t k = 0; k < 5; k++) {
+                        int xi = (int)roundf(x[x_off + m + k * c] * id) + 1;
+                        q = (uint8_t)(q * 3 + (uint8_t)xi);
+                    }
+                    block[j + m] = (uint8_t)(((uint16_t)q * 256 + 242) / 243);
+                }
+                x_off += 5 * c;
+                j += c;
+            }
+        }
+        for (size_t hh = 0; hh < 2; hh++) {
+            uint8_t q = 0;
+            for (size_t m = 0; m < 4; m++) {
+                int xi = (int)roundf(x[x_off + hh + m * 2] * id) + 1;
+                q = (uint8_t)(q * 3 + (uint8_t)xi);
+            }
+            q = (uint8_t)(q * 3);
+            block[24 + hh] = (uint8_t)(((uint16_t)q * 256 + 242) / 243);
+        }
+    }
+}
+
+/* dot_ptq1_0_f32 (ptq1_0.rs:107-142): slot-major accumulation order. */
+HO_API float ho_dot_ptq1_0_f32(const uint8_t *w, const float *x, size_t n) {
+    static const size_t stages[3] = {32, 16, 8};
+    size_t blocks = n / 128;
+    float sum = 0.0f;
+    for (size_t b = 0; b < blocks; b++) {
+        const uint8_t *blk = w + b * 28;
+        float scale = rd_h(blk + 26);
+        size_t base = b * 128, out_off = 0, j = 0;
+        float acc = 0.0f;
+        for (int si = 0; si < 3; si++) {
+            size_t c = stages[si];
+            while (j + c <= 24) {
+                for (int k = 0; k < 5; k++)
+                    for (size_t m = 0; m < c; m++) acc += (float)ptq_trit(blk[j + m], k) * x[base + out_off + (size_t)k * c + m];
+                out_off += 5 * c;
+                j += c;
+            }
+        }
+        for (int k = 0; k < 4; k++)
+            for (size_t hh = 0; hh < 2; hh++) acc += (float)ptq_trit(blk[24 + hh], k) * x[base + out_off + (size_t)k * 2 + hh];
+        sum += acc * scale;
+    }
+    return sum;
+}
+
 /* ---------------------------------------------- integer sub-block dots --- */
 
 /* The exact int32 dot of one 32-element Q8_0 sub-block against the matching
@@ -264,6 +384,14 @@ HO_API int ho_block_dots_i32(int dtype, const uint8_t *w, const uint8_t *a, size
                 for (int s = 0; s < 4; s++)
                     out[b * 4 + s] = isub_q2(w + b * 34 + 2, s, (const int8_t *)(a + (b * 4 + s) * 34 + 2));
             return 0;
+        case HO_PTQ1_0: {
+            int8_t wv[128];
+            for (size_t b = 0; b < n / 128; b++) {
+                ptq_decode_block(w + b * 28, wv);
+                for (int s = 0; s < 4; s++) out[b * 4 + s] = isub_q8(wv + s * 32, (const int8_t *)(a + (b * 4 + s) * 34 + 2));
+            }
+            return 0;
+        }
         case HO_Q8_0:
             for (size_t b = 0; b < n / 32; b++)
                 out[b] = isub_q8((const int8_t *)(w + b * 34 + 2), (const int8_t *)(a + b * 34 + 2));
@@ -458,6 +586,27 @@ HO_API void ho_dequantize_q6_k(const uint8_t *data, size_t bytes, float *out, si
     }
 }
 
+/* dot_ptq1_0_q8_0_ptr_scalar (ptq1_0.rs:555-602): decode the block's 128
+ * trits, then the same nesting as the other block dots. */
+HO_API float ho_dot_ptq1_0_q8_0(const uint8_t *w, const uint8_t *a, size_t n) {
+    size_t blocks = n / 128;
+    int8_t wv[128];
+    float sum = 0.0f;
+    for (size_t b = 0; b < blocks; b++) {
+        float scale = rd_h(w + b * 28 + 26);
+        ptq_decode_block(w + b * 28, wv);
+        float block_acc = 0.0f;
+        for (int sub = 0; sub < 4; sub++) {
+            const uint8_t *ab = a + (b * 4 + (size_t)sub) * 34;
+            float a_scale = rd_h(ab);
+            int32_t dot = isub_q8(wv + sub * 32, (const int8_t *)(ab + 2));
+            block_acc += (float)dot * a_scale;
+        }
+        sum += block_acc * scale;
+    }
+    return sum;
+}
+
 /* ------------------------------------------------------- row dispatch ----- */
 
 /* The kernel the reference's table picks per dtype for Q8_0 activations
@@ -467,6 +616,7 @@ static ho_dot_fn dot_for(int dtype) {
     switch (dtype) {
         case HO_Q1_0: case HO_Q1_0_G128: case HO_Q1_0_G128_LEGACY: return ho_dot_q1_0g128_q8_0;
         case HO_Q2_0: case HO_PQ2_0: return ho_dot_q2_0_q8_0;
+        case HO_PTQ1_0: return ho_dot_ptq1_0_q8_0;
         case HO_Q8_0: return ho_dot_q8_0_q8_0;
         default: return 0;
     }

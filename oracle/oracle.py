@@ -13,7 +13,7 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 
-Q8_0, Q4_K, Q6_K, Q1_0, Q2_0, Q1_0_G128, PQ2_0 = 8, 12, 14, 41, 42, 43, 142
+Q8_0, Q4_K, Q6_K, Q1_0, Q2_0, Q1_0_G128, PQ2_0, PTQ1_0 = 8, 12, 14, 41, 42, 43, 142, 143
 
 _u8p = C.POINTER(C.c_uint8)
 _f32p = C.POINTER(C.c_float)
@@ -56,15 +56,15 @@ def lib() -> C.CDLL:
         L.ho_par_quantize.restype = None
         L.ho_par_quantize.argtypes = [C.c_size_t, C.c_size_t, _f32p, _u8p]
         for fn in ("ho_dequantize_q8_0", "ho_dequantize_q1_0g128", "ho_dequantize_q2_0", "ho_dequantize_q4_k",
-                   "ho_dequantize_q6_k"):
+                   "ho_dequantize_q6_k", "ho_dequantize_ptq1_0"):
             getattr(L, fn).restype = None
             getattr(L, fn).argtypes = [_u8p, C.c_size_t, _f32p, C.c_size_t]
         L.ho_block_dots_i32.restype = C.c_int
         L.ho_block_dots_i32.argtypes = [C.c_int, _u8p, _u8p, C.c_size_t, _i32p]
-        for fn in ("ho_dot_q1_0g128_q8_0", "ho_dot_q2_0_q8_0", "ho_dot_q8_0_q8_0"):
+        for fn in ("ho_dot_q1_0g128_q8_0", "ho_dot_q2_0_q8_0", "ho_dot_q8_0_q8_0", "ho_dot_ptq1_0_q8_0"):
             getattr(L, fn).restype = C.c_float
             getattr(L, fn).argtypes = [_u8p, _u8p, C.c_size_t]
-        for fn in ("ho_dot_q2_0_f32", "ho_dot_q4_k_f32", "ho_dot_q6_k_f32"):
+        for fn in ("ho_dot_q2_0_f32", "ho_dot_q4_k_f32", "ho_dot_q6_k_f32", "ho_dot_ptq1_0_f32"):
             getattr(L, fn).restype = C.c_float
             getattr(L, fn).argtypes = [_u8p, _f32p, C.c_size_t]
         L.ho_par_dot_rows_batched.restype = C.c_int
@@ -72,6 +72,8 @@ def lib() -> C.CDLL:
                                               C.c_size_t, C.c_size_t]
         L.ho_matmul_kquant_f32.restype = C.c_int
         L.ho_matmul_kquant_f32.argtypes = [C.c_int, C.c_size_t, C.c_size_t, _u8p, _f32p, _f32p, C.c_size_t]
+        L.ho_quantize_ptq1_0.restype = None
+        L.ho_quantize_ptq1_0.argtypes = [_f32p, C.c_size_t, _u8p]
         L.ho_hadamard_rotate.restype = None
         L.ho_hadamard_rotate.argtypes = [_f32p, C.c_size_t, _f32p, C.c_size_t]
         L.ho_hadamard_quantize_q8_0.restype = None
@@ -139,7 +141,7 @@ def quantize_q8_0(x: np.ndarray) -> np.ndarray:
 def dequantize(dtype: int, data: np.ndarray, n_out: int) -> np.ndarray:
     fn = {Q8_0: "ho_dequantize_q8_0", Q1_0: "ho_dequantize_q1_0g128", Q1_0_G128: "ho_dequantize_q1_0g128",
           Q2_0: "ho_dequantize_q2_0", PQ2_0: "ho_dequantize_q2_0", Q4_K: "ho_dequantize_q4_k",
-          Q6_K: "ho_dequantize_q6_k"}[dtype]
+          Q6_K: "ho_dequantize_q6_k", PTQ1_0: "ho_dequantize_ptq1_0"}[dtype]
     data = np.ascontiguousarray(data, dtype=np.uint8)
     out = np.zeros(n_out, dtype=np.float32)
     getattr(lib(), fn)(_u8(data), data.size, _f32(out), n_out)
@@ -217,3 +219,15 @@ def silu_mul_q8(gate: np.ndarray, up: np.ndarray) -> np.ndarray:
     for s in range(g2.shape[0]):
         lib().ho_silu_mul_q8(_f32(g2[s]), _f32(u2[s]), _u8(out[s]), g2.shape[1])
     return out[0] if gate.ndim == 1 else out
+
+
+def quantize_ptq1_0(x: np.ndarray) -> np.ndarray:
+    """ptq1_0::quantize: f32 [n] -> uint8 [(n/128)*28]."""
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+    out = np.zeros(x.size // 128 * 28, dtype=np.uint8)
+    lib().ho_quantize_ptq1_0(_f32(x), x.size, _u8(out))
+    return out
+
+
+def dot_ptq1_0_f32(w_row: np.ndarray, x: np.ndarray, n: int) -> float:
+    return float(lib().ho_dot_ptq1_0_f32(_u8(np.ascontiguousarray(w_row)), _f32(np.ascontiguousarray(x, dtype=np.float32)), n))

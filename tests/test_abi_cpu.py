@@ -34,13 +34,13 @@ def test_header_and_bindings_agree(lib):
 def test_geometry_matches_reference_table(lib):
     # hearth-gguf/src/ggml.rs:105-176
     geo = {8: (32, 34), 12: (256, 144), 14: (256, 210), 39: (128, 18), 41: (128, 18), 43: (128, 18), 42: (128, 34),
-           142: (128, 34)}
+           142: (128, 34), 143: (128, 28)}
     for dt, (bs, bb) in geo.items():
         assert lib.hb200_block_size(dt) == bs
         assert lib.hb200_block_bytes(dt) == bb
         assert lib.hb200_byte_size(dt, 6144) == 6144 // bs * bb
         assert lib.hb200_byte_size(dt, bs + 1) == 2 * bb
-    for dt in (0, 1, 2, 143, 9999):
+    for dt in (0, 1, 2, 13, 144, 9999):
         assert lib.hb200_block_size(dt) == 0 and lib.hb200_byte_size(dt, 128) == 0
 
 
@@ -48,7 +48,8 @@ def test_selected_kernel_names(lib):
     assert lib.hb200_selected_kernel(41, 1).decode().startswith("gemv_dp4a_q1_0")
     assert lib.hb200_selected_kernel(142, 1).decode().startswith("gemv_dp4a_q2_0")
     assert lib.hb200_selected_kernel(12, 1).decode() == "kquant_gemv_q4_k_f32"
-    assert lib.hb200_selected_kernel(143, 1).decode() == "none"
+    assert lib.hb200_selected_kernel(143, 1).decode().startswith("gemv_dp4a_q2_0")  # trits re-coded at upload
+    assert lib.hb200_selected_kernel(13, 1).decode() == "none"
 
 
 def test_no_device_means_error_not_fallback(lib):

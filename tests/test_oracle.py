@@ -34,13 +34,13 @@ def test_f2h_is_round_to_nearest_even(oracle):
 def test_block_geometry(oracle):
     # hearth-gguf/src/ggml.rs:105-176
     geo = {8: (32, 34), 12: (256, 144), 14: (256, 210), 39: (128, 18), 41: (128, 18), 43: (128, 18), 42: (128, 34),
-           142: (128, 34)}
+           142: (128, 34), 143: (128, 28)}
     L = oracle.lib()
     for dt, (bs, bb) in geo.items():
         assert L.ho_block_size(dt) == bs and L.ho_block_bytes(dt) == bb
         assert oracle.byte_size(dt, 2048) == 2048 // bs * bb
         assert oracle.byte_size(dt, bs + 1) == 2 * bb  # div_ceil
-    assert oracle.byte_size(143, 128) == 0  # PTQ1_0 is outside this path
+    assert oracle.byte_size(13, 128) == 0  # Q5_K is outside this path
 
 
 def test_q2_0_code_mapping_known_answer(oracle):
