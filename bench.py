@@ -136,7 +136,9 @@ class CpuArm:
         for li in range(sample_layers):
             for ti, (_, n_rows, n_cols) in enumerate(cfg["shapes"]):
                 w = synth.weights(cfg["dtype"], n_rows, n_cols, seed=4000 + 10 * li + ti)
-                a = O.quantize_q8_0(synth.activations(cfg["seq_len"], n_cols, seed=5000 + 10 * li + ti))
+                a = synth.activations(cfg["seq_len"], n_cols, seed=5000 + 10 * li + ti)
+                if cfg["dtype"] not in (12, 14):  # K-quants take the f32 rows as they are
+                    a = O.quantize_q8_0(a)
                 self.mats.append((w, a, n_rows, n_cols, np.zeros((cfg["seq_len"], n_rows), dtype=np.float32)))
         self.nbytes = sum(w.size for w, *_ in self.mats)
         self.ops = 2.0 * cfg["seq_len"] * sum(n_rows * n_cols for _, _, n_rows, n_cols, _ in self.mats)
@@ -151,8 +153,9 @@ class CpuArm:
 
     def one_pass(self) -> float:
         t0 = time.perf_counter()
+        run = self.O.simd_matmul_kquant_f32 if self.cfg["dtype"] in (12, 14) else self.O.simd_dot_rows_batched
         for w, a, n_rows, n_cols, out in self.mats:
-            self.O.simd_dot_rows_batched(self.cfg["dtype"], w, a, n_rows, n_cols, out)
+            run(self.cfg["dtype"], w, a, n_rows, n_cols, out)
         return time.perf_counter() - t0
 
     def gbs(self, passes: int = 2) -> float:
@@ -389,6 +392,12 @@ def run_ours(args, cfg, rank, world, local_rank):
         roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "traffic": None, "kernel": hb.selected_kernel(dtype, M), "peak_source": peak_src,
                 "algorithmic_bytes_per_launch": per_rank_alg}
+        if dtype in (42, 142) and M <= 4:
+            # dram__bytes_read + dram__bytes_write of gemv_dp4a_kernel<Q2_0> from the ncu capture summarised in
+            # profiles/gemv_dp4a_q2_0__c1_1p7b_decode.md (1.7B layer set, 1.008 x its algorithmic bytes), scaled to this
+            # launch by algorithmic bytes: every launch streams each weight byte exactly once.
+            roof["traffic"] = 1.008 * per_rank_alg
+            roof["traffic_source"] = "ncu capture of the same kernel on the 1.7B layer set, scaled by algorithmic bytes"
         if is_prefill(cfg):
             metric, unit = PREFILL_METRIC, PREFILL_UNIT
             value = total_ops(cfg) / (ms_per_step * 1e-3) / 1e12
@@ -401,7 +410,7 @@ def run_ours(args, cfg, rank, world, local_rank):
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8 x {1,2}-bit -> int32, fp32 scales", "data": "synthetic",
-            "config": {"workload": args.workload, "format": {41: "Q1_0", 42: "Q2_0", 142: "PQ2_0", 8: "Q8_0", 12: "Q4_K", 14: "Q6_K"}.get(dtype, str(dtype)),
+            "config": {"workload": args.workload, "format": {41: "Q1_0", 43: "Q1_0_G128", 42: "Q2_0", 142: "PQ2_0", 143: "PTQ1_0", 8: "Q8_0", 12: "Q4_K", 14: "Q6_K"}.get(dtype, str(dtype)),
                        "tokens": M, "layers": cfg["layers"], "matrices_per_step": cfg["layers"] * len(cfg["shapes"]),
                        "weight_bytes": ab["weights"], "parallelism": f"rows/{world}" + ((" + outputs stored to all ranks from the kernel (peer stores, flag exchange)" if use_fused
                                                                 else " + NCCL all-gather of output slices") if world > 1 else ""),
@@ -416,7 +425,7 @@ def run_ours(args, cfg, rank, world, local_rank):
         if ms_nccl:
             line["nccl_allgather_variant"] = {"ms_per_step": ms_nccl / args.steps,
                                               "value": ab["weights"] / (ms_nccl / args.steps * 1e-3) / 1e9, "unit": UNIT}
-        if world == 1 and not args.no_cpu and not args.quick and cfg["dtype"] not in (12, 14):
+        if world == 1 and not args.no_cpu and not args.quick:
             arm = CpuArm(cfg, 0, 1)
             t0 = time.perf_counter()
             best = arm.gbs(2)

@@ -17,6 +17,12 @@
  *                      paired-token AVX2 LUT   q2_0.rs:408-469
  *                      VNNI-256 arm            q2_0.rs:155-205
  *                      dispatch order          q2_0.rs:628-676
+ *   PTQ1_0 x Q8_0      AVX-512 arm             hearth-quant/src/ptq1_0.rs:241-308
+ *                      AVX2 arm                ptq1_0.rs:323-404
+ *                      dispatch order          ptq1_0.rs:157-167
+ *   Q4_K / Q6_K x f32  eight-lane FMA loops    hearth-quant/src/q4_k.rs:51-96, qk_quant.rs:141-176
+ *                      (the reference's `wide` f32x8 code; rows through rayon's par_iter,
+ *                      hearth-llm/src/model/matmul.rs:270-280, :333-343; here the same static pool)
  *   width policy       avx512_full_width       hearth-quant/src/lib.rs:27-43, :113-143
  *   pool               static ceil(n/T) split, 1 MiB row tiles, token pairs
  *                      inside the tile          hearth-llm/src/pool.rs:40-80, :321-323, :510-618
@@ -351,16 +357,207 @@ static float q8_scalar(const uint8_t *w, const uint8_t *a, size_t n) {
 
 /* ------------------------------------------------------------- dispatch -- */
 
+
+/* ------------------------------------------------------------- PTQ1_0 ---- */
+
+static int8_t g_qh_trit[256][4];
+static void build_ptq_tables(void) {
+    static const unsigned pow3[4] = {1, 3, 9, 27};
+    for (unsigned b = 0; b < 256; b++)
+        for (int n = 0; n < 4; n++) g_qh_trit[b][n] = (int8_t)(((((b * pow3[n]) & 255u) * 3u) >> 8) - 1);
+}
+static int g_ptq_ready;
+
+static inline void ptq_qh(const uint8_t *blk, int8_t *wv) {
+    const int8_t *t0 = g_qh_trit[blk[24]], *t1 = g_qh_trit[blk[25]];
+    for (int n = 0; n < 4; n++) {
+        wv[120 + 2 * n] = t0[n];
+        wv[121 + 2 * n] = t1[n];
+    }
+}
+
+/* AVX2 arm (ptq1_0.rs:323-404): digits by multiply / mask / shift on u16 lanes, trits widened to i16 and
+ * multiplied with vpmaddwd, eight fp32 lanes per block summed left to right. */
+T_AVX2 static float ptq_avx2(const uint8_t *w, const uint8_t *a, size_t n) {
+    static const int16_t pow3[5] = {1, 3, 9, 27, 81};
+    const __m128i ff = _mm_set1_epi16(0xFF), three = _mm_set1_epi16(3), one = _mm_set1_epi16(1), z = _mm_setzero_si128();
+    int8_t wv[128];
+    float sum = 0.0f;
+    for (size_t b = 0; b < n / 128; b++) {
+        const uint8_t *blk = w + b * 28;
+        float scale = h2f(blk + 26);
+        __m128i qs = _mm_loadu_si128((const __m128i *)blk), q8 = _mm_loadl_epi64((const __m128i *)(blk + 16));
+        __m128i alo = _mm_unpacklo_epi8(qs, z), ahi = _mm_unpackhi_epi8(qs, z);
+        __m128i blo = _mm_unpacklo_epi8(q8, z), bhi = _mm_unpackhi_epi8(q8, z);
+        for (int k = 0; k < 5; k++) {
+            __m128i p = _mm_set1_epi16(pow3[k]);
+#define HS_DIGIT(v) _mm_sub_epi16(_mm_srli_epi16(_mm_mullo_epi16(_mm_and_si128(_mm_mullo_epi16(v, p), ff), three), 8), one)
+            _mm_storeu_si128((__m128i *)(wv + k * 16), _mm_packs_epi16(HS_DIGIT(alo), HS_DIGIT(ahi)));
+            _mm_storel_epi64((__m128i *)(wv + 80 + k * 8), _mm_packs_epi16(HS_DIGIT(blo), HS_DIGIT(bhi)));
+#undef HS_DIGIT
+        }
+        ptq_qh(blk, wv);
+        __m256 acc = _mm256_setzero_ps();
+        for (int s = 0; s < 4; s++) {
+            const uint8_t *ab = a + (b * 4 + (size_t)s) * 34;
+            __m256i w32 = _mm256_loadu_si256((const __m256i *)(wv + s * 32)), a32 = _mm256_loadu_si256((const __m256i *)(ab + 2));
+            __m256i wl = _mm256_cvtepi8_epi16(_mm256_castsi256_si128(w32)), wh = _mm256_cvtepi8_epi16(_mm256_extracti128_si256(w32, 1));
+            __m256i al = _mm256_cvtepi8_epi16(_mm256_castsi256_si128(a32)), ah = _mm256_cvtepi8_epi16(_mm256_extracti128_si256(a32, 1));
+            __m256i p = _mm256_add_epi32(_mm256_madd_epi16(wl, al), _mm256_madd_epi16(wh, ah));
+            acc = _mm256_add_ps(acc, _mm256_mul_ps(_mm256_cvtepi32_ps(p), _mm256_set1_ps(h2f(ab))));
+        }
+        float lanes[8], blk_acc = 0.0f;
+        _mm256_storeu_ps(lanes, acc);
+        for (int i = 0; i < 8; i++) blk_acc += lanes[i];
+        sum += blk_acc * scale;
+    }
+    return sum;
+}
+
+/* AVX-512 arm (ptq1_0.rs:241-308): all 24 qs bytes in one register per digit slot, one 32-element
+ * sub-block per vpmaddwd, sixteen fp32 lanes per block summed left to right. */
+__attribute__((target("avx2,fma,f16c,avx512f,avx512bw,avx512vl"))) static float ptq_avx512(const uint8_t *w, const uint8_t *a, size_t n) {
+    static const int16_t pow3[5] = {1, 3, 9, 27, 81};
+    const __m512i ff = _mm512_set1_epi16(0xFF), three = _mm512_set1_epi16(3), one = _mm512_set1_epi16(1);
+    int8_t wv[128];
+    float sum = 0.0f;
+    for (size_t b = 0; b < n / 128; b++) {
+        const uint8_t *blk = w + b * 28;
+        float scale = h2f(blk + 26);
+        __m512i bytes16 = _mm512_cvtepu8_epi16(_mm256_maskz_loadu_epi8((__mmask32)0x00FFFFFFu, blk));
+        for (int k = 0; k < 5; k++) {
+            __m512i t = _mm512_and_si512(_mm512_mullo_epi16(bytes16, _mm512_set1_epi16(pow3[k])), ff);
+            __m256i packed = _mm512_cvtepi16_epi8(_mm512_sub_epi16(_mm512_srli_epi16(_mm512_mullo_epi16(t, three), 8), one));
+            _mm_storeu_si128((__m128i *)(wv + k * 16), _mm256_castsi256_si128(packed));
+            _mm_storel_epi64((__m128i *)(wv + 80 + k * 8), _mm256_extracti128_si256(packed, 1));
+        }
+        ptq_qh(blk, wv);
+        __m512 acc = _mm512_setzero_ps();
+        for (int s = 0; s < 4; s++) {
+            const uint8_t *ab = a + (b * 4 + (size_t)s) * 34;
+            __m512i w16 = _mm512_cvtepi8_epi16(_mm256_loadu_si256((const __m256i *)(wv + s * 32)));
+            __m512i a16 = _mm512_cvtepi8_epi16(_mm256_loadu_si256((const __m256i *)(ab + 2)));
+            acc = _mm512_add_ps(acc, _mm512_mul_ps(_mm512_cvtepi32_ps(_mm512_madd_epi16(w16, a16)), _mm512_set1_ps(h2f(ab))));
+        }
+        float lanes[16], blk_acc = 0.0f;
+        _mm512_storeu_ps(lanes, acc);
+        for (int i = 0; i < 16; i++) blk_acc += lanes[i];
+        sum += blk_acc * scale;
+    }
+    return sum;
+}
+
+static float ptq_scalar(const uint8_t *w, const uint8_t *a, size_t n) {
+    static const unsigned pow3[5] = {1, 3, 9, 27, 81};
+    int8_t wv[128];
+    float sum = 0.0f;
+    for (size_t b = 0; b < n / 128; b++) {
+        const uint8_t *blk = w + b * 28;
+        for (int k = 0; k < 5; k++) {
+            for (int m = 0; m < 16; m++) wv[k * 16 + m] = (int8_t)(((((blk[m] * pow3[k]) & 255u) * 3u) >> 8) - 1);
+            for (int m = 0; m < 8; m++) wv[80 + k * 8 + m] = (int8_t)(((((blk[16 + m] * pow3[k]) & 255u) * 3u) >> 8) - 1);
+        }
+        ptq_qh(blk, wv);
+        float acc = 0.0f;
+        for (int s = 0; s < 4; s++) {
+            const uint8_t *ab = a + (b * 4 + (size_t)s) * 34;
+            int32_t d = 0;
+            for (int i = 0; i < 32; i++) d += (int32_t)wv[s * 32 + i] * (int32_t)(int8_t)ab[2 + i];
+            acc += (float)d * half_scalar(ab);
+        }
+        sum += acc * half_scalar(blk + 26);
+    }
+    return sum;
+}
+
+/* -------------------------------------------------- K-quants x f32 ------- */
+
+/* Eight lanes, lane j takes elements 8t + j with a fused multiply-add, lanes reduced
+ * ((l0+l4)+(l2+l6))+((l1+l5)+(l3+l7)) -- the order the scalar oracle assumes for `wide`'s reduce_add. */
+T_AVX2 static inline float reduce8_ps(__m256 v) {
+    __m128 lo = _mm256_castps256_ps128(v), hi = _mm256_extractf128_ps(v, 1);
+    __m128 s = _mm_add_ps(lo, hi);                        /* l0+l4, l1+l5, l2+l6, l3+l7 */
+    __m128 t = _mm_add_ps(s, _mm_movehl_ps(s, s));        /* (l0+l4)+(l2+l6), (l1+l5)+(l3+l7) */
+    return _mm_cvtss_f32(_mm_add_ss(t, _mm_shuffle_ps(t, t, 1)));
+}
+
+/* dot_q4_k_f32 (q4_k.rs:51-96); `a` carries the f32 activation row. */
+T_AVX2 static float q4k_f32(const uint8_t *w, const uint8_t *a, size_t n) {
+    const float *x = (const float *)a;
+    float sum = 0.0f;
+    for (size_t b = 0; b < n / 256; b++) {
+        const uint8_t *bp = w + b * 144;
+        float d = h2f(bp), dmin = h2f(bp + 2);
+        uint8_t sc[8], mn[8];
+        for (int i = 0; i < 4; i++) {
+            uint8_t s0 = bp[4 + 3 * i], s1 = bp[5 + 3 * i], s2 = bp[6 + 3 * i];
+            sc[2 * i] = s0 & 63;
+            mn[2 * i] = (uint8_t)((s0 >> 6) | ((s1 & 15) << 2));
+            sc[2 * i + 1] = (uint8_t)((s1 >> 4) | ((s2 & 3) << 4));
+            mn[2 * i + 1] = (s2 >> 2) & 63;
+        }
+        for (int sb = 0; sb < 8; sb++) {
+            float scale = (float)sc[sb] * d, minv = (float)mn[sb] * dmin;
+            __m256 vs = _mm256_set1_ps(scale), vm = _mm256_set1_ps(minv), acc = _mm256_setzero_ps();
+            const uint8_t *qs = bp + 16 + sb * 16;
+            const float *xs = x + b * 256 + (size_t)sb * 32;
+            for (int t = 0; t < 4; t++) {
+                float nib[8];
+                for (int j = 0; j < 8; j++) {
+                    int i = t * 8 + j;
+                    uint8_t byte = qs[i >> 1];
+                    nib[j] = (float)((i & 1) ? (byte >> 4) : (byte & 15));
+                }
+                __m256 val = _mm256_sub_ps(_mm256_mul_ps(_mm256_loadu_ps(nib), vs), vm);
+                acc = _mm256_fmadd_ps(val, _mm256_loadu_ps(xs + t * 8), acc);
+            }
+            sum += reduce8_ps(acc);
+        }
+    }
+    return sum;
+}
+
+/* dot_q6_k_f32 (qk_quant.rs:141-176). */
+T_AVX2 static float q6k_f32(const uint8_t *w, const uint8_t *a, size_t n) {
+    const float *x = (const float *)a;
+    float sum = 0.0f;
+    for (size_t b = 0; b < n / 256; b++) {
+        const uint8_t *bp = w + b * 210;
+        float d = h2f(bp + 208);
+        for (int sb = 0; sb < 16; sb++) {
+            float scale = (float)(int8_t)bp[192 + sb] * d;
+            __m256 vs = _mm256_set1_ps(scale);
+            for (int g = 0; g < 2; g++) {
+                float q[8];
+                for (int j = 0; j < 8; j++) {
+                    int i = sb * 16 + g * 8 + j;
+                    uint8_t ql = bp[i >> 1];
+                    int low4 = (i & 1) ? (ql >> 4) : (ql & 15);
+                    int high2 = (bp[128 + (i >> 2)] >> (2 * (i & 3))) & 3;
+                    q[j] = (float)((low4 | (high2 << 4)) - 32);
+                }
+                __m256 val = _mm256_mul_ps(_mm256_loadu_ps(q), vs);
+                __m256 prod = _mm256_fmadd_ps(val, _mm256_loadu_ps(x + b * 256 + (size_t)sb * 16 + g * 8), _mm256_setzero_ps());
+                sum += reduce8_ps(prod);
+            }
+        }
+    }
+    return sum;
+}
+
 typedef float (*dot1_fn)(const uint8_t *, const uint8_t *, size_t);
 typedef void (*dot2_fn)(const uint8_t *, const uint8_t *, const uint8_t *, size_t, float *, float *);
 
-enum { K_Q1 = 0, K_Q2 = 1, K_Q8 = 2 };
+enum { K_Q1 = 0, K_Q2 = 1, K_Q8 = 2, K_PTQ = 3, K_Q4K = 4, K_Q6K = 5 };
 
 static int kind_of(int dtype) {
     switch (dtype) {
         case 39: case 41: case 43: return K_Q1;
         case 42: case 142: return K_Q2;
         case 8: return K_Q8;
+        case 143: return K_PTQ;
+        case 12: return K_Q4K;
+        case 14: return K_Q6K;
         default: return -1;
     }
 }
@@ -379,6 +576,18 @@ static dot1_fn pick1(int kind, const char **name) {
         if (vnni256_ok()) { *name = "vnni256"; return q2_vnni256; }
         *name = "scalar";
         return q2_scalar;
+    }
+    if (kind == K_PTQ) {
+        if (!g_ptq_ready) { build_ptq_tables(); g_ptq_ready = 1; }
+        if (full_width() && g_has_avx512vl) { *name = "avx512"; return ptq_avx512; }
+        if (avx2_ok()) { *name = "avx2"; return ptq_avx2; }
+        *name = "scalar";
+        return ptq_scalar;
+    }
+    if (kind == K_Q4K || kind == K_Q6K) {
+        if (!avx2_ok()) { *name = "none"; return 0; }  /* the shipped baseline target has AVX2 + FMA */
+        *name = "wide_f32x8_fma";
+        return kind == K_Q4K ? q4k_f32 : q6k_f32;
     }
     *name = "scalar";
     return q8_scalar;
@@ -526,7 +735,8 @@ HS_API void hs_pool_stop(void) {
 }
 
 /* par_dot_rows_batched (seq_len == 1: par_dot_rows).  Returns 0, -1 for a dtype
- * without a Q8_0 dot, -2 if the pool was not started. */
+ * without a dot here, -2 if the pool was not started.  For Q4_K / Q6_K (ids 12, 14) a_ptr holds f32 rows and
+ * q8_stride is their stride in bytes (the per-row loop of matmul.rs:270-280 and its per-token repetition). */
 HS_API int hs_par_dot_rows_batched(int dtype, size_t n, size_t seq_len, size_t q8_stride, const uint8_t *w_base,
                                    const uint8_t *a_ptr, float *out, size_t row_bytes, size_t n_cols) {
     int kind = kind_of(dtype);
@@ -536,6 +746,7 @@ HS_API int hs_par_dot_rows_batched(int dtype, size_t n, size_t seq_len, size_t q
     const char *nm;
     job_t j = {n, seq_len, q8_stride, row_bytes, n_cols, 0, w_base, a_ptr, out, pick1(kind, &nm),
                seq_len > 1 ? pick2(kind) : 0};
+    if (!j.f1) return -1;
     j.tile = 1048576 / row_bytes;
     if (j.tile < 1) j.tile = 1;
     if (g_pool.nthreads <= 1) {

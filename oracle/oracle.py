@@ -231,3 +231,16 @@ def quantize_ptq1_0(x: np.ndarray) -> np.ndarray:
 
 def dot_ptq1_0_f32(w_row: np.ndarray, x: np.ndarray, n: int) -> float:
     return float(lib().ho_dot_ptq1_0_f32(_u8(np.ascontiguousarray(w_row)), _f32(np.ascontiguousarray(x, dtype=np.float32)), n))
+
+
+def simd_matmul_kquant_f32(dtype: int, w: np.ndarray, x: np.ndarray, n_rows: int, n_cols: int,
+                           out: np.ndarray | None = None) -> np.ndarray:
+    """Q4_K / Q6_K rows against f32 activations through the restated eight-lane FMA loops and the pool."""
+    x2 = np.ascontiguousarray(x.reshape(1, -1) if x.ndim == 1 else x, dtype=np.float32)
+    if out is None:
+        out = np.zeros((x2.shape[0], n_rows), dtype=np.float32)
+    rb = byte_size(dtype, n_cols)
+    rc = simd().hs_par_dot_rows_batched(dtype, n_rows, x2.shape[0], x2.shape[1] * 4, _u8(w),
+                                        x2.ctypes.data_as(_u8p), _f32(out), rb, n_cols)
+    assert rc == 0, rc
+    return out

@@ -189,7 +189,7 @@ def test_simd_baseline_agrees_with_scalar_oracle(oracle):
     S = oracle.simd()
     S.hs_pool_start(2)
     try:
-        for dt in (43, 42, 8):
+        for dt in (43, 42, 8, 143):
             n_rows, n_cols = 70, 2048
             w = synth.weights(dt, n_rows, n_cols, seed=31 + dt, allow_code3=True)
             a = oracle.quantize_q8_0(synth.activations(3, n_cols, seed=32))
@@ -198,6 +198,28 @@ def test_simd_baseline_agrees_with_scalar_oracle(oracle):
             assert got.shape == want.shape == (3, n_rows)
             err = np.abs(got - want)
             assert (err <= 1e-4 * np.maximum(1.0, np.abs(want))).all(), (dt, err.max())
-            assert S.hs_selected_kernel(dt).decode() in ("vnni256", "avx2_shuffle", "vnni512x2", "avx2_lut", "scalar")
+            assert S.hs_selected_kernel(dt).decode() in ("vnni256", "avx2_shuffle", "vnni512x2", "avx2_lut", "scalar",
+                                                          "avx512", "avx2")
+        # K-quants: the same eight-lane order as the scalar oracle, so the bits agree
+        for dt in (12, 14):
+            n_rows, n_cols = 37, 1024
+            w = synth.weights(dt, n_rows, n_cols, seed=41 + dt)
+            x = synth.activations(2, n_cols, seed=42)
+            want = oracle.matmul_kquant_f32(dt, w, x, n_rows, n_cols)
+            got = oracle.simd_matmul_kquant_f32(dt, w, x, n_rows, n_cols)
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), dt
     finally:
         S.hs_pool_stop()
+
+
+def test_ptq1_0_simd_arms_share_the_integer_dots(oracle):
+    """hs_dot for id 143 on rows with one non-zero activation block isolates the integer sub-block sums."""
+    from hearth_b200 import synth
+    n = 1152
+    w = synth.weights(143, 5, n, seed=3)
+    a = oracle.quantize_q8_0(synth.activations(1, n, seed=4))[0]
+    S = oracle.simd()
+    for r in range(5):
+        got = S.hs_dot(143, w[r].ctypes.data_as(oracle._u8p), a.ctypes.data_as(oracle._u8p), n)
+        want = oracle.dot_rows_batched(143, w[r:r + 1], a, 1, n)[0, 0]
+        assert abs(got - want) <= 1e-4 * max(1.0, abs(want))
