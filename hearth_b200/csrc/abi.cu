@@ -192,7 +192,7 @@ int dot_rows_launch(const hb200_weight* w, const hb200_act* a, size_t seq_len, f
         set_error("K-quant weights take f32 activations; use hb200_matmul_f32[_dev]");
         return HB200_ERR_UNSUPPORTED;
     }
-    // Five or more tokens of a 1-/2-bit weight go to the tensor cores; up to four stay on the streaming dp4a kernel.
+    // GEMM_TC_MIN_TOKENS or more tokens of a 1-/2-bit weight go to the tensor cores; fewer run as passes of the streaming dp4a kernel.
     if (seq_len >= (size_t)GEMM_TC_MIN_TOKENS && (w->kind == KIND_Q1 || w->kind == KIND_Q2) && a->has_qmap && w->nb > 0)
         return launch_gemm_tc(w->kind, a->qmap, w->bits, w->scales, a->d, a->ld_b, (int)w->n_rows, w->nb, (int)seq_len, out,
                               (int)ld_out, g_ctx.d_status, st);

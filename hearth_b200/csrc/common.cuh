@@ -136,7 +136,7 @@ int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const 
 int gemv_dp4a_ctas_per_sm(int m);  // resident CTAs per SM the kernel for m tokens is built for
 int gemv_dp4a_prepare();  // sets the dynamic shared-memory attributes once
 
-// gemm_tc.cu: tcgen05 kind::i8 path for 5 or more tokens (Q1_0 / Q2_0).  `amap` points at a CUtensorMap over the
+// gemm_tc.cu: tcgen05 kind::i8 path for GEMM_TC_MIN_TOKENS or more tokens (Q1_0 / Q2_0).  `amap` points at a CUtensorMap over the
 // activation's int8 plane ([max_seq][ld_q] bytes, box 128 x 128, SWIZZLE_128B).  `status` is a device word that
 // receives a non-zero code if a bounded wait inside the kernel expires.
 // Below this many tokens, passes of the streaming dp4a kernel (four tokens each) are faster than one 128-token

@@ -429,10 +429,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
         }
         if (tok_ok && !*abort_flag) {
             float* op = args.out + (size_t)tok * args.ld_out + rbase;
+            if (rbase + 16 <= args.n_rows && (reinterpret_cast<uintptr_t>(op) & 15) == 0) {
+                // 64 contiguous bytes per thread: four 16-byte stores instead of sixteen 4-byte ones
 #pragma unroll
-            for (int c = 0; c < 8; c++) {
-                if (rbase + 2 * c < args.n_rows) op[2 * c] = sum[c].x;
-                if (rbase + 2 * c + 1 < args.n_rows) op[2 * c + 1] = sum[c].y;
+                for (int c = 0; c < 4; c++)
+                    reinterpret_cast<float4*>(op)[c] = make_float4(sum[2 * c].x, sum[2 * c].y, sum[2 * c + 1].x, sum[2 * c + 1].y);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 8; c++) {
+                    if (rbase + 2 * c < args.n_rows) op[2 * c] = sum[c].x;
+                    if (rbase + 2 * c + 1 < args.n_rows) op[2 * c + 1] = sum[c].y;
+                }
             }
         }
     }
