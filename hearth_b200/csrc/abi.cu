@@ -72,7 +72,9 @@ struct hb200_batch {
     std::vector<BatchEntry> entries;
     std::vector<BatchGroup> groups;
     std::vector<BatchEntry> kquant;  // K-quant ops launch on their own
-    std::vector<BatchEntry> tensor;  // ops with five or more tokens: tensor-core kernel, one launch each
+    std::vector<BatchEntry> tensor;  // ops for the tensor-core kernel (GEMM_TC_MIN_TOKENS tokens or more)
+    struct TcGroup { int kind = 0; TcMat* mats_dev = nullptr; int* chunks_dev = nullptr; int n_tiles = 0, grid = 0; };
+    std::vector<TcGroup> tc_groups;  // one persistent launch per weight kind
     // host-input path: distinct activations in order of first use, a staging buffer for their f32 rows
     std::vector<hb200_act_t> acts;
     std::vector<size_t> act_seq;       // rows used of each
@@ -121,6 +123,8 @@ int encode_qmap(hb200_act* a) {
                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return HB200_ERR_CUDA; }
+    if (!a->qmap_dev) HB_CUDA(cudaMalloc(&a->qmap_dev, sizeof(a->qmap)));
+    HB_CUDA(cudaMemcpy(a->qmap_dev, a->qmap, sizeof(a->qmap), cudaMemcpyHostToDevice));
     a->has_qmap = true;
     return 0;
 }
@@ -194,8 +198,8 @@ int dot_rows_launch(const hb200_weight* w, const hb200_act* a, size_t seq_len, f
     }
     // GEMM_TC_MIN_TOKENS or more tokens of a 1-/2-bit weight go to the tensor cores; fewer run as passes of the streaming dp4a kernel.
     if (seq_len >= (size_t)GEMM_TC_MIN_TOKENS && (w->kind == KIND_Q1 || w->kind == KIND_Q2) && a->has_qmap && w->nb > 0)
-        return launch_gemm_tc(w->kind, a->qmap, w->bits, w->scales, a->d, a->ld_b, (int)w->n_rows, w->nb, (int)seq_len, out,
-                              (int)ld_out, g_ctx.d_status, st);
+        return launch_gemm_tc(w->kind, a->qmap_dev, w->bits, w->scales, a->d, a->ld_b, (int)w->n_rows, w->nb, (int)seq_len, out,
+                              (int)ld_out, g_ctx.sm_count, g_ctx.d_status, st);
     for (size_t tok0 = 0; tok0 < seq_len; tok0 += GEMV_MAX_M) {
         const int m = (int)((seq_len - tok0) < (size_t)GEMV_MAX_M ? (seq_len - tok0) : GEMV_MAX_M);
         DotOp op;
@@ -530,6 +534,7 @@ extern "C" int hb200_act_free(hb200_act_t a) {
     if (a->q) cudaFree(a->q);
     if (a->d) cudaFree(a->d);
     if (a->sums) cudaFree(a->sums);
+    if (a->qmap_dev) cudaFree(a->qmap_dev);
     delete a;
     return HB200_OK;
     HB_GUARD_END
@@ -894,7 +899,7 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
     std::map<std::pair<int, int>, Acc> acc;
     for (const BatchEntry& e : b->entries) {
         if (e.seq_len >= (size_t)GEMM_TC_MIN_TOKENS && (e.w->kind == KIND_Q1 || e.w->kind == KIND_Q2) && e.a->has_qmap && e.w->nb > 0) {
-            b->tensor.push_back(e);  // tensor-core kernel: one launch per op
+            b->tensor.push_back(e);  // tensor-core kernel: all such ops of one kind share a launch
             continue;
         }
         for (size_t tok0 = 0; tok0 < e.seq_len; tok0 += GEMV_MAX_M) {
@@ -936,6 +941,42 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
         HB_CUDA(cudaMalloc(&g.chunks_dev, chunks.size() * sizeof(int)));
         HB_CUDA(cudaMemcpy(g.chunks_dev, chunks.data(), chunks.size() * sizeof(int), cudaMemcpyHostToDevice));
         b->groups.push_back(g);
+    }
+    // Tensor-core ops: per weight kind one list of matrices whose 128 x 64 tiles are numbered consecutively, and
+    // contiguous runs of tiles per CTA balanced by 128-column blocks (plus a fixed share per tile for its fill and drain).
+    for (int kind : {KIND_Q1, KIND_Q2}) {
+        std::vector<TcMat> mats;
+        std::vector<int> cost;
+        int n_tiles = 0;
+        for (const BatchEntry& e : b->tensor) {
+            if (e.w->kind != kind) continue;
+            TcMat m;
+            gemm_tc_fill(m, e.a->qmap_dev, e.w->bits, e.w->scales, e.a->d, e.a->ld_b, (int)e.w->n_rows, e.w->nb, (int)e.seq_len, e.out,
+                         (int)e.ld_out, n_tiles);
+            for (int t = m.tile_begin; t < m.tile_end; t++) cost.push_back(e.w->nb + 4);
+            n_tiles = m.tile_end;
+            mats.push_back(m);
+        }
+        if (n_tiles == 0) continue;
+        hb200_batch::TcGroup g;
+        g.kind = kind;
+        g.n_tiles = n_tiles;
+        g.grid = n_tiles < g_ctx.sm_count ? n_tiles : g_ctx.sm_count;
+        long long total_cost = 0;
+        for (int c : cost) total_cost += c;
+        std::vector<int> chunks(g.grid + 1, n_tiles);
+        chunks[0] = 0;
+        long long run = 0;
+        int next_c = 1;
+        for (int i = 0; i < n_tiles && next_c < g.grid; i++) {
+            run += cost[i];
+            while (next_c < g.grid && run * g.grid >= total_cost * next_c) chunks[next_c++] = i + 1;
+        }
+        HB_CUDA(cudaMalloc(&g.mats_dev, mats.size() * sizeof(TcMat)));
+        HB_CUDA(cudaMemcpy(g.mats_dev, mats.data(), mats.size() * sizeof(TcMat), cudaMemcpyHostToDevice));
+        HB_CUDA(cudaMalloc(&g.chunks_dev, chunks.size() * sizeof(int)));
+        HB_CUDA(cudaMemcpy(g.chunks_dev, chunks.data(), chunks.size() * sizeof(int), cudaMemcpyHostToDevice));
+        b->tc_groups.push_back(g);
     }
     // Host-input path: one staging buffer for every distinct activation's f32 rows and one descriptor list for the
     // list quantizer.  K-quant ops read f32 from the activation's own area, so those rows are also copied there.
@@ -994,10 +1035,8 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
                                    pt.n > 1 ? &pt : nullptr)))
             return rc;
     }
-    for (const BatchEntry& e : b->tensor)
-        if ((rc = launch_gemm_tc(e.w->kind, e.a->qmap, e.w->bits, e.w->scales, e.a->d, e.a->ld_b, (int)e.w->n_rows, e.w->nb,
-                                 (int)e.seq_len, e.out, (int)e.ld_out, g_ctx.d_status, st)))
-            return rc;
+    for (const hb200_batch::TcGroup& g : b->tc_groups)
+        if ((rc = launch_gemm_tc_list(g.kind, g.mats_dev, g.chunks_dev, g.n_tiles, g.grid, g_ctx.d_status, st))) return rc;
     for (const BatchEntry& e : b->kquant)
         if ((rc = launch_kquant_gemv(e.w->kind, e.w->kq, e.w->d16, (int)e.w->n_rows, (int)e.w->n_cols, e.w->nb, e.w->n_panels, e.a->x,
                                      (int)e.seq_len, e.out, (int)e.ld_out, g_ctx.sm_count, st)))
@@ -1033,7 +1072,7 @@ extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const 
 
 extern "C" int hb200_batch_launch_count(hb200_batch_t b) {
     if (!b || !b->sealed) return 0;
-    return (int)(b->groups.size() + b->kquant.size() + b->tensor.size());
+    return (int)(b->groups.size() + b->kquant.size() + b->tc_groups.size());
 }
 
 extern "C" int hb200_batch_free(hb200_batch_t b) {
@@ -1042,6 +1081,10 @@ extern "C" int hb200_batch_free(hb200_batch_t b) {
     for (BatchGroup& g : b->groups) {
         if (g.ops_dev) cudaFree(g.ops_dev);
         if (g.items_dev) cudaFree(g.items_dev);
+        if (g.chunks_dev) cudaFree(g.chunks_dev);
+    }
+    for (hb200_batch::TcGroup& g : b->tc_groups) {
+        if (g.mats_dev) cudaFree(g.mats_dev);
         if (g.chunks_dev) cudaFree(g.chunks_dev);
     }
     if (b->x_stage) cudaFree(b->x_stage);

@@ -142,8 +142,26 @@ int gemv_dp4a_prepare();  // sets the dynamic shared-memory attributes once
 // Below this many tokens, passes of the streaming dp4a kernel (four tokens each) are faster than one 128-token
 // tensor-core tile that is mostly empty (measured crossover on B200: about 44 tokens for Q2_0, later for Q1_0).
 constexpr int GEMM_TC_MIN_TOKENS = 48;
-int launch_gemm_tc(int kind, const void* amap, const uint4* bits, const void* scales, const float* ad, int ld_b, int n_rows,
-                   int nb, int seq_len, float* out, int ld_out, int* status, cudaStream_t st);
+// One matrix of a tensor-core launch.  amap: a CUtensorMap in device memory.  Tiles (128 tokens x 64 rows) of the
+// matrices of a launch are numbered consecutively, tile_begin .. tile_end - 1 belonging to this one.
+struct TcMat {
+    const uint4* bits;
+    const void* scales;
+    const float* ad;
+    float* out;
+    const void* amap;
+    int n_rows, nb, seq_len, ld_out, ld_b;
+    int tok_tiles, tile_begin, tile_end;
+};
+int gemm_tc_tiles(int n_rows, int seq_len);
+void gemm_tc_fill(TcMat& m, const void* amap_dev, const uint4* bits, const void* scales, const float* ad, int ld_b, int n_rows,
+                  int nb, int seq_len, float* out, int ld_out, int tile_begin);
+// One matrix: persistent CTAs (at most sm_count) take its tiles in turn.
+int launch_gemm_tc(int kind, const void* amap_dev, const uint4* bits, const void* scales, const float* ad, int ld_b, int n_rows,
+                   int nb, int seq_len, float* out, int ld_out, int sm_count, int* status, cudaStream_t st);
+// Many matrices of one kind in one launch: mats_dev[...] in device memory, chunks_dev[grid + 1] gives CTA c the tiles
+// chunks[c] .. chunks[c+1]-1.
+int launch_gemm_tc_list(int kind, const TcMat* mats_dev, const int* chunks_dev, int n_tiles, int grid, int* status, cudaStream_t st);
 int gemm_tc_prepare();
 
 // kquant.cu: Q4_K / Q6_K weights are re-tiled at upload into 32-row panels of interleaved 16-byte pieces

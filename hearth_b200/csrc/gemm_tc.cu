@@ -41,13 +41,15 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
-struct TcArgs {
-    const uint4* bits;
-    const void* scales;
-    const float* ad;   // activation block scales, ld_b floats per token
-    float* out;
-    int* status;       // device word: 0 ok, otherwise the code of the first wait that expired
-    int n_rows, nb, seq_len, ld_out, ld_b;
+// What one launch works through: `mats` (device memory, n_tiles tiles in all) or, when mats is null, the one matrix
+// `single`.  With `chunks` ([gridDim.x + 1] tile indices) CTA c owns tiles chunks[c] .. chunks[c+1]-1, a contiguous
+// run balanced by block count; without, CTA c takes tiles c, c + gridDim.x, ...
+struct TcLaunch {
+    const TcMat* mats;
+    const int* chunks;
+    int* status;  // device word: 0 ok, otherwise the code of the first wait that expired
+    int n_tiles;
+    TcMat single;
 };
 
 // ---- PTX wrappers -----------------------------------------------------------------------------------------------
@@ -192,9 +194,83 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
 }
 
+// Tile t of the launch: which matrix, which 128 tokens, which 64 rows.  Tiles of a matrix are numbered with the
+// token tile fastest, so CTAs working side by side read different activation tiles and the same weights.
+struct TileRef {
+    const TcMat* m;
+    int tok0, row0;
+};
+
+struct TileWalk {
+    const TcLaunch* L;
+    int i;     // how many tiles of this CTA have been handed out
+    int mi;    // matrix cursor (tiles come in increasing order)
+    __device__ __forceinline__ void init(const TcLaunch* l) { L = l; i = 0; mi = 0; }
+    __device__ __forceinline__ bool next(TileRef& r) {
+        int t;
+        if (L->chunks) {
+            t = L->chunks[blockIdx.x] + i;
+            if (t >= L->chunks[blockIdx.x + 1]) return false;
+        } else {
+            t = (int)blockIdx.x + i * (int)gridDim.x;
+            if (t >= L->n_tiles) return false;
+        }
+        i++;
+        const TcMat* m = &L->single;
+        if (L->mats) {
+            while (t >= L->mats[mi].tile_end) mi++;
+            m = &L->mats[mi];
+        }
+        const int lt = t - m->tile_begin;
+        r.m = m;
+        r.tok0 = (lt % m->tok_tiles) * TOK_TILE;
+        r.row0 = (lt / m->tok_tiles) * ROW_TILE;
+        return true;
+    }
+};
+
+// Position of an unpack warp in the stream of blocks of this CTA (all tiles, in order): g counts blocks from the
+// CTA's first one and selects every ring slot and barrier phase.
+template <int KIND>
+struct UnpackCursor {
+    TileWalk walk;
+    bool valid;
+    int g, blk, nb;
+    const uint4* tp0;                // packed pieces of block 0 of the tile's row groups
+    const unsigned char* sp0;        // f16 scales of block 0
+    __device__ __forceinline__ void load_tile() {
+        constexpr int RPG = rows_per_group(KIND);
+        constexpr int SPT = scales_per_tile(KIND);
+        TileRef r;
+        valid = walk.next(r);
+        if (!valid) return;
+        nb = r.m->nb;
+        const int rg0 = r.row0 / RPG;  // first row group of the tile; a tile never straddles a 32-row-group panel
+        const size_t tile0 = (size_t)(rg0 >> 5) * nb;
+        const int lane0 = rg0 & 31;
+        tp0 = r.m->bits + tile0 * 256 + lane0;
+        sp0 = reinterpret_cast<const unsigned char*>(r.m->scales) + (tile0 * 32 + lane0) * SPT * 2;
+    }
+    __device__ __forceinline__ void init(const TcLaunch* l, int first) {
+        walk.init(l);
+        g = 0;
+        blk = 0;
+        load_tile();
+        advance(first);
+    }
+    __device__ __forceinline__ void advance(int n) {
+        g += n;
+        blk += n;
+        while (valid && blk >= nb) {
+            blk -= nb;
+            load_tile();
+        }
+    }
+};
+
 template <int KIND>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
+gemm_tc_kernel(const __grid_constant__ TcLaunch L) {
     constexpr int RPG = rows_per_group(KIND);
     constexpr int SPT = scales_per_tile(KIND);
     constexpr int RGS = ROW_TILE / RPG;  // row groups per tile: 8 (Q1_0) or 16 (Q2_0)
@@ -205,10 +281,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
     volatile int* abort_flag = &bars->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Token tiles vary fastest across the grid: CTAs that run at the same time then read different activation tiles.
-    const int tok0 = blockIdx.x * TOK_TILE;
-    const int row0 = blockIdx.y * ROW_TILE;
-    const int nb = args.nb;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; i++) {
@@ -232,27 +304,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
 
+    // Every role walks the same sequence of tiles and, inside a tile, of 128-column blocks; g numbers the blocks of
+    // the CTA across tiles, so the rings and their barrier phases simply keep turning from one tile into the next
+    // and the producers start on the next tile while the promotion warps are still finishing the previous one.
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer (one lane)
         if (lane == 0) {
-            int issued = 0;
-            for (int blk = 0; blk < nb; blk++) {
-                const int st = blk % STAGES;
-                if (blk >= STAGES &&
-                    !mbar_wait(smem_u32(&bars->empty[st]), ((blk / STAGES) - 1) & 1, abort_flag, args.status, 1))
-                    break;
-                const uint32_t bar = smem_u32(&bars->full[st]);
-                mbar_expect_tx(bar, A_BYTES);
-                tma_load_2d(smem_u32(tiles + st * STAGE_BYTES), &amap, blk * 128, tok0, bar);
-                issued = blk + 1;
+            TileWalk walk;
+            walk.init(&L);
+            TileRef tr;
+            int g = 0;
+            bool ok = true;
+            while (ok && walk.next(tr)) {
+                const int nb = tr.m->nb;
+                const CUtensorMap* amap = static_cast<const CUtensorMap*>(tr.m->amap);
+                for (int blk = 0; blk < nb; blk++, g++) {
+                    const int st = g % STAGES;
+                    if (g >= STAGES && !mbar_wait(smem_u32(&bars->empty[st]), ((g / STAGES) - 1) & 1, abort_flag, L.status, 1)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bar = smem_u32(&bars->full[st]);
+                    mbar_expect_tx(bar, A_BYTES);
+                    tma_load_2d(smem_u32(tiles + st * STAGE_BYTES), amap, blk * 128, tr.tok0, bar);
+                }
             }
             if (*abort_flag) {
                 // Do not leave the CTA with bulk copies in flight: wait (bounded) for the ones already issued.  If the
                 // unpack warps have stopped arriving the phase cannot complete, so this loop simply runs out.
-                const int first = issued > STAGES ? issued - STAGES : 0;
-                for (int blk = first; blk < issued; blk++) {
-                    const uint32_t bar = smem_u32(&bars->full[blk % STAGES]);
-                    for (uint32_t i = 0; i < (SPIN_LIMIT >> 8) && !mbar_try(bar, (blk / STAGES) & 1); i++) {
+                const int first = g > STAGES ? g - STAGES : 0;
+                for (int q = first; q < g; q++) {
+                    const uint32_t bar = smem_u32(&bars->full[q % STAGES]);
+                    for (uint32_t i = 0; i < (SPIN_LIMIT >> 8) && !mbar_try(bar, (q / STAGES) & 1); i++) {
                     }
                 }
             }
@@ -262,53 +345,65 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
         // Two issuing threads halve the serial cost of the waits and commits per block; each owns one accumulator set.
         if (lane == 0) {
             const int par = warp - 1;
-            for (int blk = par; blk < nb; blk += 2) {
-                const int st = blk % STAGES, buf = par;
-                if (!mbar_wait(smem_u32(&bars->full[st]), (blk / STAGES) & 1, abort_flag, args.status, 2)) break;
-                if (blk >= 2 && !mbar_wait(smem_u32(&bars->tmem_empty[buf]), ((blk >> 1) - 1) & 1, abort_flag, args.status, 4)) break;
-                tc_fence_after();
-                const uint32_t a_addr = smem_u32(tiles + st * STAGE_BYTES);
-                const uint32_t b_addr = a_addr + A_BYTES;
+            TileWalk walk;
+            walk.init(&L);
+            TileRef tr;
+            int g = 0;
+            bool ok = true;
+            while (ok && walk.next(tr)) {
+                const int nb = tr.m->nb;
+                for (int blk = 0; blk < nb; blk++, g++) {
+                    if ((g & 1) != par) continue;
+                    const int st = g % STAGES, buf = par;
+                    if (!mbar_wait(smem_u32(&bars->full[st]), (g / STAGES) & 1, abort_flag, L.status, 2)) { ok = false; break; }
+                    if (g >= 2 && !mbar_wait(smem_u32(&bars->tmem_empty[buf]), ((g >> 1) - 1) & 1, abort_flag, L.status, 4)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + st * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
-                for (int s = 0; s < 4; s++)  // one K=32 MMA per sub-block; +32 B inside the 128 B swizzle row
-                    tc_mma_i8(tmem_base + buf * 256 + s * ROW_TILE, make_desc(a_addr + s * 32), make_desc(b_addr + s * 32), IDESC);
-                tc_commit(smem_u32(&bars->empty[st]));       // the stage may be refilled once these MMAs have read it
-                tc_commit(smem_u32(&bars->tmem_full[buf]));  // the accumulators are complete
+                    for (int s = 0; s < 4; s++)  // one K=32 MMA per sub-block; +32 B inside the 128 B swizzle row
+                        tc_mma_i8(tmem_base + buf * 256 + s * ROW_TILE, make_desc(a_addr + s * 32), make_desc(b_addr + s * 32), IDESC);
+                    tc_commit(smem_u32(&bars->empty[st]));       // the stage may be refilled once these MMAs have read it
+                    tc_commit(smem_u32(&bars->tmem_full[buf]));  // the accumulators are complete
+                }
             }
         }
     } else if (warp < 3 + UNPACK_WARPS) {
         // ---------------------------------------------------------------- unpack (4 warps, one block each in turn)
         // The expansion of one block is a long serial chain (ring wait, stage wait, expand, proxy fence, arrive), so
-        // four warps run four such chains side by side: warp w owns blocks w, w+4, ...  Packed codes and scales of a
-        // warp's next block stream into its two ring slots with cp.async while it expands the current one.
+        // four warps run four such chains side by side: warp w owns blocks w, w+4, ... of the CTA's block stream.
+        // Packed codes and scales of a warp's next two blocks stream into its two ring slots with cp.async while it
+        // expands the current one.
         const int uw = warp - 3;
-        const int rg0 = row0 / RPG;  // first row group of the tile; a tile never straddles a 32-row-group panel
-        const size_t tile0 = (size_t)(rg0 >> 5) * nb;
-        const int lane0 = rg0 & 31;
-        auto issue = [&](int blk) {
-            if (blk < nb) {
-                const int slot = blk % PSLOTS;
-                const uint4* tp = args.bits + (tile0 + blk) * 256;
+        UnpackCursor<KIND> cur, pf;
+        cur.init(&L, uw);
+        pf = cur;
+        auto issue = [&](const UnpackCursor<KIND>& c) {
+            if (c.valid) {
+                const int slot = c.g % PSLOTS;
+                const uint4* tp = c.tp0 + (size_t)c.blk * 256;
 #pragma unroll
                 for (int k = 0; k < RGS * 8 / 32; k++) {
                     const int pi = lane + k * 32;  // piece: row group pi >> 3, piece pi & 7 of its tile
-                    cp_async16(&bars->packed[slot][pi * 16], tp + (pi & 7) * 32 + lane0 + (pi >> 3));
+                    cp_async16(&bars->packed[slot][pi * 16], tp + (pi & 7) * 32 + (pi >> 3));
                 }
                 if (lane < 8)  // RGS * SPT f16 = 128 bytes
-                    cp_async16(&bars->pscale[slot][lane * 16],
-                               reinterpret_cast<const unsigned char*>(args.scales) + ((tile0 + blk) * 32 + lane0) * SPT * 2 + lane * 16);
+                    cp_async16(&bars->pscale[slot][lane * 16], c.sp0 + (size_t)c.blk * 32 * SPT * 2 + lane * 16);
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        issue(uw);
-        issue(uw + UNPACK_WARPS);
-        for (int blk = uw; blk < nb; blk += UNPACK_WARPS) {
-            const int st = blk % STAGES, slot = blk % PSLOTS;
+        issue(pf);
+        pf.advance(UNPACK_WARPS);
+        issue(pf);
+        pf.advance(UNPACK_WARPS);
+        for (; cur.valid; cur.advance(UNPACK_WARPS)) {
+            const int g = cur.g;
+            const int st = g % STAGES, slot = g % PSLOTS;
             asm volatile("cp.async.wait_group 1;" ::: "memory");  // this block's group has landed (the next one may be in flight)
             __syncwarp();
             bool ok = true;
-            if (blk >= STAGES) {
-                if (lane == 0) ok = mbar_wait(smem_u32(&bars->empty[st]), ((blk / STAGES) - 1) & 1, abort_flag, args.status, 5);
+            if (g >= STAGES) {
+                if (lane == 0) ok = mbar_wait(smem_u32(&bars->empty[st]), ((g / STAGES) - 1) & 1, abort_flag, L.status, 5);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
             if (!ok) break;
@@ -351,12 +446,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
                 const int row = lane + 32 * k;
                 const int rgl = row / RPG, r = row % RPG;
                 const unsigned short h = *reinterpret_cast<const unsigned short*>(&bars->pscale[slot][(rgl * SPT + r) * 2]);
-                bars->wscale[blk % SCALE_SLOTS][row] = __half2float(__ushort_as_half(h));
+                bars->wscale[g % SCALE_SLOTS][row] = __half2float(__ushort_as_half(h));
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // make the generic-proxy writes visible to the MMA
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->full[st]));
-            issue(blk + 2 * UNPACK_WARPS);  // refills the slot just consumed (same slot index modulo PSLOTS = 8)
+            issue(pf);  // refills the slot just consumed (the cursor is two of this warp's blocks ahead: same slot modulo PSLOTS = 8)
+            pf.advance(UNPACK_WARPS);
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     } else {
@@ -364,81 +460,89 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap amap, const TcArgs args) {
         const int e = warp - (3 + UNPACK_WARPS);
         const int quarter = warp & 3;   // TMEM lanes this warp may read: 32*(warp % 4) ..
         const int cg = e >> 2;          // which 16 of the 64 columns (weight rows); the four warps of a quarter differ in cg
-        const int tok = tok0 + quarter * 32 + lane;
-        const bool tok_ok = tok < args.seq_len;
-        const float* adp = args.ad + (size_t)(tok_ok ? tok : 0) * args.ld_b;
-        const int rbase = row0 + cg * 16;  // first weight row of this thread's columns
-        // A warp none of whose 32 tokens exist only keeps the barrier protocol going.
-        const bool warp_has_tokens = (tok0 + quarter * 32) < args.seq_len;
-        float2 sum[8];
+        TileWalk walk;
+        walk.init(&L);
+        TileRef tr;
+        int g = 0;
+        bool ok = true;
+        while (ok && walk.next(tr)) {
+            const TcMat* M = tr.m;
+            const int nb = M->nb, n_rows = M->n_rows;
+            const int tok = tr.tok0 + quarter * 32 + lane;
+            const bool tok_ok = tok < M->seq_len;
+            const float* adp = M->ad + (size_t)(tok_ok ? tok : 0) * M->ld_b;
+            const int rbase = tr.row0 + cg * 16;  // first weight row of this thread's columns
+            // A warp none of whose 32 tokens exist only keeps the barrier protocol going.
+            const bool warp_has_tokens = (tr.tok0 + quarter * 32) < M->seq_len;
+            float2 sum[8];
 #pragma unroll
-        for (int c = 0; c < 8; c++) sum[c] = make_float2(0.0f, 0.0f);
-        float4 as_next = (nb > 0) ? *reinterpret_cast<const float4*>(adp) : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int c = 0; c < 8; c++) sum[c] = make_float2(0.0f, 0.0f);
+            float4 as_next = (nb > 0) ? *reinterpret_cast<const float4*>(adp) : make_float4(0.f, 0.f, 0.f, 0.f);
 
-        for (int blk = 0; blk < nb; blk++) {
-            const int buf = blk & 1;
-            const float4 as4 = as_next;
-            if (blk + 1 < nb) as_next = *reinterpret_cast<const float4*>(adp + 4 * (blk + 1));
-            bool ok = true;
-            if (lane == 0) ok = mbar_wait(smem_u32(&bars->tmem_full[buf]), (blk >> 1) & 1, abort_flag, args.status, 6);
-            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-            if (!ok) break;
-            tc_fence_after();
-            if (warp_has_tokens) {
-                const float asv[4] = {as4.x, as4.y, as4.z, as4.w};
-                const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256 + cg * 16;
-                const float4* wsp = reinterpret_cast<const float4*>(&bars->wscale[blk % SCALE_SLOTS][cg * 16]);
-                // Two halves of eight columns: the four sub-block sums of a half are fetched together, the accumulator
-                // set is handed back to the MMA issuer as soon as the second half sits in registers.
+            for (int blk = 0; blk < nb; blk++, g++) {
+                const int buf = g & 1;
+                const float4 as4 = as_next;
+                if (blk + 1 < nb) as_next = *reinterpret_cast<const float4*>(adp + 4 * (blk + 1));
+                if (lane == 0) ok = mbar_wait(smem_u32(&bars->tmem_full[buf]), (g >> 1) & 1, abort_flag, L.status, 6);
+                ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                if (!ok) break;
+                tc_fence_after();
+                if (warp_has_tokens) {
+                    const float asv[4] = {as4.x, as4.y, as4.z, as4.w};
+                    const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256 + cg * 16;
+                    const float4* wsp = reinterpret_cast<const float4*>(&bars->wscale[g % SCALE_SLOTS][cg * 16]);
+                    // Two halves of eight columns: the four sub-block sums of a half are fetched together, the accumulator
+                    // set is handed back to the MMA issuer as soon as the second half sits in registers.
 #pragma unroll
-                for (int hf = 0; hf < 2; hf++) {
-                    uint32_t v[4][8];
+                    for (int hf = 0; hf < 2; hf++) {
+                        uint32_t v[4][8];
 #pragma unroll
-                    for (int s4 = 0; s4 < 4; s4++) tc_ld8(tbase + s4 * ROW_TILE + hf * 8, v[s4]);
-                    tc_wait_ld8(v[0]);
-                    tc_pin8(v[1]);
-                    tc_pin8(v[2]);
-                    tc_pin8(v[3]);
-                    if (hf == 1) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[buf]));
-                    }
-                    // block_acc = fma(I0,a0,0), fma(I1,a1,.), fma(I2,a2,.), fma(I3,a3,.); then sum += block_acc * w_scale,
-                    // rounded separately (q2_0.rs:545-573, q1_0g128.rs:1026-1051)
+                        for (int s4 = 0; s4 < 4; s4++) tc_ld8(tbase + s4 * ROW_TILE + hf * 8, v[s4]);
+                        tc_wait_ld8(v[0]);
+                        tc_pin8(v[1]);
+                        tc_pin8(v[2]);
+                        tc_pin8(v[3]);
+                        if (hf == 1) {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[buf]));
+                        }
+                        // block_acc = fma(I0,a0,0), fma(I1,a1,.), fma(I2,a2,.), fma(I3,a3,.); then sum += block_acc * w_scale,
+                        // rounded separately (q2_0.rs:545-573, q1_0g128.rs:1026-1051)
 #pragma unroll
-                    for (int c4 = 0; c4 < 2; c4++) {
-                        const float4 wd = wsp[hf * 2 + c4];
+                        for (int c4 = 0; c4 < 2; c4++) {
+                            const float4 wd = wsp[hf * 2 + c4];
 #pragma unroll
-                        for (int hh = 0; hh < 2; hh++) {
-                            const int c = 4 * c4 + 2 * hh;
-                            float2 acc = make_float2(0.0f, 0.0f);
+                            for (int hh = 0; hh < 2; hh++) {
+                                const int c = 4 * c4 + 2 * hh;
+                                float2 acc = make_float2(0.0f, 0.0f);
 #pragma unroll
-                            for (int s4 = 0; s4 < 4; s4++)
-                                acc = ffma2(make_float2((float)(int)v[s4][c], (float)(int)v[s4][c + 1]), make_float2(asv[s4], asv[s4]), acc);
-                            const float2 w2 = hh ? make_float2(wd.z, wd.w) : make_float2(wd.x, wd.y);
-                            sum[hf * 4 + (c >> 1)] = fadd2(sum[hf * 4 + (c >> 1)], fmul2(acc, w2));
+                                for (int s4 = 0; s4 < 4; s4++)
+                                    acc = ffma2(make_float2((float)(int)v[s4][c], (float)(int)v[s4][c + 1]), make_float2(asv[s4], asv[s4]), acc);
+                                const float2 w2 = hh ? make_float2(wd.z, wd.w) : make_float2(wd.x, wd.y);
+                                sum[hf * 4 + (c >> 1)] = fadd2(sum[hf * 4 + (c >> 1)], fmul2(acc, w2));
+                            }
                         }
                     }
+                } else {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[buf]));
                 }
-            } else {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[buf]));
             }
-        }
-        if (tok_ok && !*abort_flag) {
-            float* op = args.out + (size_t)tok * args.ld_out + rbase;
-            if (rbase + 16 <= args.n_rows && (reinterpret_cast<uintptr_t>(op) & 15) == 0) {
-                // 64 contiguous bytes per thread: four 16-byte stores instead of sixteen 4-byte ones
+            if (ok && tok_ok && !*abort_flag) {
+                float* op = M->out + (size_t)tok * M->ld_out + rbase;
+                if (rbase + 16 <= n_rows && (reinterpret_cast<uintptr_t>(op) & 15) == 0) {
+                    // 64 contiguous bytes per thread: four 16-byte stores instead of sixteen 4-byte ones
 #pragma unroll
-                for (int c = 0; c < 4; c++)
-                    reinterpret_cast<float4*>(op)[c] = make_float4(sum[2 * c].x, sum[2 * c].y, sum[2 * c + 1].x, sum[2 * c + 1].y);
-            } else {
+                    for (int c = 0; c < 4; c++)
+                        reinterpret_cast<float4*>(op)[c] = make_float4(sum[2 * c].x, sum[2 * c].y, sum[2 * c + 1].x, sum[2 * c + 1].y);
+                } else {
 #pragma unroll
-                for (int c = 0; c < 8; c++) {
-                    if (rbase + 2 * c < args.n_rows) op[2 * c] = sum[c].x;
-                    if (rbase + 2 * c + 1 < args.n_rows) op[2 * c + 1] = sum[c].y;
+                    for (int c = 0; c < 8; c++) {
+                        if (rbase + 2 * c < n_rows) op[2 * c] = sum[c].x;
+                        if (rbase + 2 * c + 1 < n_rows) op[2 * c + 1] = sum[c].y;
+                    }
                 }
             }
         }
@@ -462,19 +566,43 @@ int gemm_tc_prepare() {
     return 0;
 }
 
-int launch_gemm_tc(int kind, const void* amap, const uint4* bits, const void* scales, const float* ad, int ld_b, int n_rows,
-                   int nb, int seq_len, float* out, int ld_out, int* status, cudaStream_t st) {
-    if (n_rows <= 0 || seq_len <= 0) return 0;
-    TcArgs a;
-    a.bits = bits; a.scales = scales; a.ad = ad; a.out = out; a.status = status;
-    a.n_rows = n_rows; a.nb = nb; a.seq_len = seq_len; a.ld_out = ld_out; a.ld_b = ld_b;
-    dim3 grid((seq_len + TOK_TILE - 1) / TOK_TILE, (n_rows + ROW_TILE - 1) / ROW_TILE);
-    const CUtensorMap& map = *static_cast<const CUtensorMap*>(amap);
-    if (kind == KIND_Q1) gemm_tc_kernel<KIND_Q1><<<grid, TC_THREADS, TC_SMEM, st>>>(map, a);
-    else if (kind == KIND_Q2) gemm_tc_kernel<KIND_Q2><<<grid, TC_THREADS, TC_SMEM, st>>>(map, a);
+int gemm_tc_tiles(int n_rows, int seq_len) {
+    return ((seq_len + TOK_TILE - 1) / TOK_TILE) * ((n_rows + ROW_TILE - 1) / ROW_TILE);
+}
+
+void gemm_tc_fill(TcMat& m, const void* amap_dev, const uint4* bits, const void* scales, const float* ad, int ld_b, int n_rows,
+                  int nb, int seq_len, float* out, int ld_out, int tile_begin) {
+    m.bits = bits; m.scales = scales; m.ad = ad; m.out = out; m.amap = amap_dev;
+    m.n_rows = n_rows; m.nb = nb; m.seq_len = seq_len; m.ld_out = ld_out; m.ld_b = ld_b;
+    m.tok_tiles = (seq_len + TOK_TILE - 1) / TOK_TILE;
+    m.tile_begin = tile_begin;
+    m.tile_end = tile_begin + gemm_tc_tiles(n_rows, seq_len);
+}
+
+static int run_tc(int kind, const TcLaunch& L, int grid, cudaStream_t st) {
+    if (kind == KIND_Q1) gemm_tc_kernel<KIND_Q1><<<grid, TC_THREADS, TC_SMEM, st>>>(L);
+    else if (kind == KIND_Q2) gemm_tc_kernel<KIND_Q2><<<grid, TC_THREADS, TC_SMEM, st>>>(L);
     else { set_error("gemm_tc: kind %d has no tensor-core kernel", kind); return -7; }
     HB_CUDA(cudaGetLastError());
     return 0;
+}
+
+int launch_gemm_tc(int kind, const void* amap_dev, const uint4* bits, const void* scales, const float* ad, int ld_b, int n_rows,
+                   int nb, int seq_len, float* out, int ld_out, int sm_count, int* status, cudaStream_t st) {
+    if (n_rows <= 0 || seq_len <= 0) return 0;
+    TcLaunch L;
+    L.mats = nullptr; L.chunks = nullptr; L.status = status;
+    gemm_tc_fill(L.single, amap_dev, bits, scales, ad, ld_b, n_rows, nb, seq_len, out, ld_out, 0);
+    L.n_tiles = L.single.tile_end;
+    return run_tc(kind, L, L.n_tiles < sm_count ? L.n_tiles : sm_count, st);
+}
+
+int launch_gemm_tc_list(int kind, const TcMat* mats_dev, const int* chunks_dev, int n_tiles, int grid, int* status, cudaStream_t st) {
+    if (n_tiles <= 0 || grid <= 0) return 0;
+    TcLaunch L;
+    L.mats = mats_dev; L.chunks = chunks_dev; L.status = status; L.n_tiles = n_tiles;
+    L.single = TcMat{};
+    return run_tc(kind, L, grid, st);
 }
 
 }  // namespace hb200

@@ -24,7 +24,8 @@ struct hb200_act {
     int8_t* q = nullptr;
     float* d = nullptr;
     float* sums = nullptr;
-    alignas(64) unsigned char qmap[128] = {};  // CUtensorMap over the int8 plane (tcgen05 path)
+    alignas(64) unsigned char qmap[128] = {};  // CUtensorMap over the int8 plane (tcgen05 path), host copy
+    void* qmap_dev = nullptr;                  // the same 128 bytes in device memory, where the kernel reads them
     bool has_qmap = false;
 };
 

@@ -274,7 +274,7 @@ def test_error_behaviour(hb):
     E = hb.Hb200Error
     w = synth.weights(Q1_0, 4, 256, seed=1)
     with pytest.raises(E) as e:
-        hb.Weight.upload(143, 4, 256, w)  # PTQ1_0: outside this path
+        hb.Weight.upload(13, 4, 256, w)  # Q5_K: outside this path
     assert e.value.code == -3
     with pytest.raises(E) as e:
         hb.Weight.upload(Q1_0, 5, 256, w)  # byte count mismatch
