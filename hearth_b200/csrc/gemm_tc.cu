@@ -355,16 +355,21 @@ gemm_tc_kernel(const __grid_constant__ TcLaunch L) {
                 for (int blk = 0; blk < nb; blk++, g++) {
                     if ((g & 1) != par) continue;
                     const int st = g % STAGES, buf = par;
+                    // Everything the issue needs is computed before the waits: between the moment the promotion warps
+                    // hand the accumulator set back and the commit only four MMA and two commit instructions remain
+                    // (this thread shares its scheduler with busy warps, so every extra instruction here costs many cycles).
+                    const uint32_t a_addr = smem_u32(tiles + st * STAGE_BYTES);
+                    const uint64_t ad0 = make_desc(a_addr), bd0 = make_desc(a_addr + A_BYTES);
+                    const uint32_t d0 = tmem_base + buf * 256;
+                    const uint32_t bar_full = smem_u32(&bars->tmem_full[buf]), bar_empty = smem_u32(&bars->empty[st]);
                     if (!mbar_wait(smem_u32(&bars->full[st]), (g / STAGES) & 1, abort_flag, L.status, 2)) { ok = false; break; }
                     if (g >= 2 && !mbar_wait(smem_u32(&bars->tmem_empty[buf]), ((g >> 1) - 1) & 1, abort_flag, L.status, 4)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(tiles + st * STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + A_BYTES;
 #pragma unroll
-                    for (int s = 0; s < 4; s++)  // one K=32 MMA per sub-block; +32 B inside the 128 B swizzle row
-                        tc_mma_i8(tmem_base + buf * 256 + s * ROW_TILE, make_desc(a_addr + s * 32), make_desc(b_addr + s * 32), IDESC);
-                    tc_commit(smem_u32(&bars->empty[st]));       // the stage may be refilled once these MMAs have read it
-                    tc_commit(smem_u32(&bars->tmem_full[buf]));  // the accumulators are complete
+                    for (int s = 0; s < 4; s++)  // one K=32 MMA per sub-block; +32 B inside the 128 B swizzle row = +2 in the address field
+                        tc_mma_i8(d0 + s * ROW_TILE, ad0 + 2 * s, bd0 + 2 * s, IDESC);
+                    tc_commit(bar_full);   // the accumulators are complete (first: the promotion warps wait on this one)
+                    tc_commit(bar_empty);  // the stage may be refilled once these MMAs have read it
                 }
             }
         }
