@@ -72,7 +72,7 @@ struct hb200_batch {
     std::vector<BatchEntry> entries;
     std::vector<BatchGroup> groups;
     std::vector<BatchEntry> kquant;  // K-quant ops launch on their own
-    std::vector<BatchEntry> tensor;  // ops for the tensor-core kernel (GEMM_TC_MIN_TOKENS tokens or more)
+    std::vector<BatchEntry> tensor;  // ops for the tensor-core kernel (see gemm_tc_wanted)
     struct TcGroup { int kind = 0; TcMat* mats_dev = nullptr; int* chunks_dev = nullptr; int n_tiles = 0, grid = 0; };
     std::vector<TcGroup> tc_groups;  // one persistent launch per weight kind
     // host-input path: distinct activations in order of first use, a staging buffer for their f32 rows
@@ -196,8 +196,8 @@ int dot_rows_launch(const hb200_weight* w, const hb200_act* a, size_t seq_len, f
         set_error("K-quant weights take f32 activations; use hb200_matmul_f32[_dev]");
         return HB200_ERR_UNSUPPORTED;
     }
-    // GEMM_TC_MIN_TOKENS or more tokens of a 1-/2-bit weight go to the tensor cores; fewer run as passes of the streaming dp4a kernel.
-    if (seq_len >= (size_t)GEMM_TC_MIN_TOKENS && (w->kind == KIND_Q1 || w->kind == KIND_Q2) && a->has_qmap && w->nb > 0)
+    // Prefill-sized token counts of a 1-/2-bit weight go to the tensor cores; fewer run as passes of the streaming dp4a kernel.
+    if (gemm_tc_wanted(w->kind, seq_len) && a->has_qmap && w->nb > 0)
         return launch_gemm_tc(w->kind, a->qmap_dev, w->bits, w->scales, a->d, a->ld_b, (int)w->n_rows, w->nb, (int)seq_len, out,
                               (int)ld_out, g_ctx.sm_count, g_ctx.d_status, st);
     for (size_t tok0 = 0; tok0 < seq_len; tok0 += GEMV_MAX_M) {
@@ -328,8 +328,8 @@ extern "C" const char* hb200_selected_kernel(int dtype, size_t seq_len) {
     const int kind = kind_of(dtype);
     if (seq_len == 0) return "none";
     switch (kind) {
-        case KIND_Q1: return seq_len >= (size_t)GEMM_TC_MIN_TOKENS ? "gemm_tcgen05_i8_q1_0" : "gemv_dp4a_q1_0";
-        case KIND_Q2: return seq_len >= (size_t)GEMM_TC_MIN_TOKENS ? "gemm_tcgen05_i8_q2_0" : "gemv_dp4a_q2_0";
+        case KIND_Q1: return gemm_tc_wanted(kind, seq_len) ? "gemm_tcgen05_i8_q1_0" : "gemv_dp4a_q1_0";
+        case KIND_Q2: return gemm_tc_wanted(kind, seq_len) ? "gemm_tcgen05_i8_q2_0" : "gemv_dp4a_q2_0";
         case KIND_Q8: return "gemv_dp4a_q8_0";
         case KIND_Q4K: return "kquant_gemv_q4_k_f32";
         case KIND_Q6K: return "kquant_gemv_q6_k_f32";
@@ -889,7 +889,7 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
     if (b->peers.n > 1) {
         if (!b->kquant.empty()) { set_error("peer-store batches carry Q8_0-activation ops only"); return HB200_ERR_UNSUPPORTED; }
         for (const BatchEntry& e : b->entries)
-            if (e.seq_len >= (size_t)GEMM_TC_MIN_TOKENS && (e.w->kind == KIND_Q1 || e.w->kind == KIND_Q2)) {
+            if (gemm_tc_wanted(e.w->kind, e.seq_len)) {
                 set_error("peer-store batches take at most %d tokens per op", GEMM_TC_MIN_TOKENS - 1);
                 return HB200_ERR_UNSUPPORTED;
             }
@@ -898,7 +898,7 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
     struct Acc { std::vector<DotOp> first; std::vector<DotItem> second; std::vector<int> cost; };
     std::map<std::pair<int, int>, Acc> acc;
     for (const BatchEntry& e : b->entries) {
-        if (e.seq_len >= (size_t)GEMM_TC_MIN_TOKENS && (e.w->kind == KIND_Q1 || e.w->kind == KIND_Q2) && e.a->has_qmap && e.w->nb > 0) {
+        if (gemm_tc_wanted(e.w->kind, e.seq_len) && e.a->has_qmap && e.w->nb > 0) {
             b->tensor.push_back(e);  // tensor-core kernel: all such ops of one kind share a launch
             continue;
         }

@@ -136,12 +136,18 @@ int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const 
 int gemv_dp4a_ctas_per_sm(int m);  // resident CTAs per SM the kernel for m tokens is built for
 int gemv_dp4a_prepare();  // sets the dynamic shared-memory attributes once
 
-// gemm_tc.cu: tcgen05 kind::i8 path for GEMM_TC_MIN_TOKENS or more tokens (Q1_0 / Q2_0).  `amap` points at a CUtensorMap over the
+// gemm_tc.cu: tcgen05 kind::i8 path for prefill-sized token counts (Q1_0 / Q2_0), see gemm_tc_wanted.  `amap` points at a CUtensorMap over the
 // activation's int8 plane ([max_seq][ld_q] bytes, box 128 x 128, SWIZZLE_128B).  `status` is a device word that
 // receives a non-zero code if a bounded wait inside the kernel expires.
-// Below this many tokens, passes of the streaming dp4a kernel (four tokens each) are faster than one 128-token
-// tensor-core tile that is mostly empty (measured crossover on B200: about 44 tokens for Q2_0, later for Q1_0).
-constexpr int GEMM_TC_MIN_TOKENS = 48;
+// Below these token counts, passes of the streaming dp4a kernel (four tokens each) are faster than 128-token
+// tensor-core tiles that are mostly empty.  Measured on B200 on the 27B layer set: a tensor-core pass costs what six
+// dp4a passes of Q2_0 cost (24 tokens), or four of Q1_0, whose dp4a kernel is slower.
+constexpr int GEMM_TC_MIN_TOKENS_Q2 = 25;
+constexpr int GEMM_TC_MIN_TOKENS_Q1 = 17;
+constexpr int GEMM_TC_MIN_TOKENS = GEMM_TC_MIN_TOKENS_Q1;  // no tensor-core launch below this, whatever the kind
+inline bool gemm_tc_wanted(int kind, size_t seq_len) {
+    return (kind == KIND_Q1 && seq_len >= (size_t)GEMM_TC_MIN_TOKENS_Q1) || (kind == KIND_Q2 && seq_len >= (size_t)GEMM_TC_MIN_TOKENS_Q2);
+}
 // One matrix of a tensor-core launch.  amap: a CUtensorMap in device memory.  Tiles (128 tokens x 64 rows) of the
 // matrices of a launch are numbered consecutively, tile_begin .. tile_end - 1 belonging to this one.
 struct TcMat {

@@ -1,5 +1,5 @@
 // Prefill / multi-token matmul on the 5th-generation tensor cores: tcgen05.mma kind::i8 with TMEM
-// accumulators, for Q1_0 and Q2_0 / PQ2_0 weights against 48 or more Q8_0 activations (prefill).
+// accumulators, for Q1_0 (17 tokens or more) and Q2_0 / PQ2_0 (25 or more) weights against Q8_0 activations (prefill).
 //
 // Replaces ThreadPool::par_dot_rows_batched over the paired-token kernels
 // (hearth-llm/src/pool.rs:40-80, :568-618; hearth-quant/src/q1_0g128.rs:396-502, q2_0.rs:408-492) and keeps
@@ -10,13 +10,16 @@
 // Because every sub-block carries its own activation scale the accumulator can never run deeper than K=32:
 // the tensor pipe is waiting on this fp32 promotion, not the other way round.
 //
-// Tile: 128 tokens (TMEM lanes) x 64 weight rows (TMEM columns) per CTA, K walked in 128-column blocks.
-//   warp 0      TMA producer: int8 activation tile 128 tokens x 128 B per block (SWIZZLE_128B, K-major)
+// Persistent kernel: one CTA per SM walks a run of tiles (128 tokens = TMEM lanes, 64 weight rows = TMEM columns),
+// possibly of many matrices; every tile's K is walked in 128-column blocks and the rings keep turning across tiles.
+//   warp 0      TMA producer: int8 activation tile 128 tokens x 128 B per block (SWIZZLE_128B, K-major); the tensor
+//               map of the tile's activation is read from device memory
 //   warps 1-2   TMEM allocation (warp 1) + MMA issue, one thread each: warp 1 the even blocks, warp 2 the odd ones;
 //               4 MMAs (128x64x32) per block into 4 x 64 columns of that issuer's accumulator set
 //   warps 3-6   unpack, each warp every fourth block: packed codes arrive through a cp.async ring; 64 rows x 128 columns
 //               of 1-/2-bit codes -> int8 {-1,+1} / {-1,0,+1,+2} in the same swizzled K-major layout, 128-bit stores
-//   warps 7-22  promotion: tcgen05.ld 16 columns x 4 sub-blocks at a time, thread = token, 16 running sums per thread
+//   warps 7-22  promotion: tcgen05.ld 16 columns x 4 sub-blocks at a time, thread = token, 16 running sums per thread,
+//               64 contiguous output bytes per thread at the end of a tile
 // Two accumulator sets (2 x 256 TMEM columns) let the MMAs of block b+1 run under the promotion of block b;
 // a 4-stage shared-memory ring decouples TMA / unpack from the MMA issue.
 // Every wait on an mbarrier is bounded; on expiry the CTA records a status code, stops issuing, drains its
