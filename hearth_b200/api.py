@@ -65,6 +65,13 @@ def _stream_ptr(stream) -> C.c_void_p:
     return C.c_void_p(int(stream.cuda_stream))
 
 
+def measure_i8_peak() -> float:
+    """Dense int8 tensor-core rate of the device in use, measured, in TOP/s."""
+    v = C.c_double()
+    check(_l.load().hb200_measure_i8_peak(C.byref(v)))
+    return float(v.value)
+
+
 class Weight:
     """A weight tensor resident on the device (GpuCompute::upload_bytes residency)."""
 

@@ -298,6 +298,16 @@ extern "C" int hb200_shutdown(void) {
 extern "C" const char* hb200_last_error(void) { return g_last_error.c_str(); }
 extern "C" int hb200_sm_count(void) { return g_ctx.ready ? g_ctx.sm_count : 0; }
 
+extern "C" int hb200_measure_i8_peak(double* tops) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!tops) { set_error("null output"); return HB200_ERR_NULL; }
+    if ((rc = measure_i8_peak(g_ctx.sm_count, g_ctx.d_status, g_ctx.stream, tops))) return rc;
+    return check_device_status();
+    HB_GUARD_END
+}
+
 // ---------------------------------------------------------------- geometry --
 
 extern "C" size_t hb200_block_size(int dtype) {

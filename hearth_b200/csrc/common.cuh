@@ -170,6 +170,9 @@ int launch_gemm_tc(int kind, const void* amap_dev, const uint4* bits, const void
 int launch_gemm_tc_list(int kind, const TcMat* mats_dev, const int* chunks_dev, int n_tiles, int grid, int* status, cudaStream_t st);
 int gemm_tc_prepare();
 
+// tc_peak.cu: dense kind::i8 tensor-core rate of this GPU, measured (TOP/s).
+int measure_i8_peak(int sm_count, int* status, cudaStream_t st, double* tops);
+
 // kquant.cu: Q4_K / Q6_K weights are re-tiled at upload into 32-row panels of interleaved 16-byte pieces
 // (layout described in kquant.cu); d16 holds Q6_K's per-block f16 scale and is null for Q4_K.
 size_t kquant_pieces_per_block(int kind);

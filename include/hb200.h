@@ -82,6 +82,11 @@ HB200_API int hb200_shutdown(void);
 HB200_API const char *hb200_last_error(void);
 /* Number of streaming multiprocessors of the bound device (sizing of grids). */
 HB200_API int hb200_sm_count(void);
+/* Measures the dense int8 tensor-core rate of the device in use (a run of
+ * tcgen05.mma kind::i8 with resident operands on every SM) and returns it in
+ * TOP/s: the denominator for the prefill kernel's roofline fraction.  No
+ * reference counterpart; takes about ten milliseconds. */
+HB200_API int hb200_measure_i8_peak(double *tops);
 
 /* ---- block geometry ----------------------------------------------------- */
 

@@ -94,3 +94,10 @@ def test_prefill_shape_sampled_rows(hb, oracle):
             check(got, oracle.dot_rows_batched(Q1_0, w, a, n_rows, n_cols), "k projection, 512 tokens")
         else:
             check(got[toks], oracle.dot_rows_batched(Q1_0, w, a[toks], n_rows, n_cols), "gate projection, sampled tokens")
+
+
+def test_int8_peak_measurement_is_plausible(hb):
+    """A bare run of kind::i8 MMAs: between the promotion-bound kernel's rate and the 4.5 POP/s nominal figure."""
+    tops = hb.measure_i8_peak()
+    assert 1000.0 < tops < 5000.0, tops
+    hb.check_status()
