@@ -181,6 +181,22 @@ def _as_torch_f32(ptr: int, n: int, device):
     return torch.as_tensor(h, device=device)
 
 
+def argmax_f32_dev(x_dev, n: int | None = None, stream=None) -> int:
+    """GpuCompute::argmax_f32 (hearth-compute/src/lib.rs:338): index of the largest value of a CUDA f32 tensor."""
+    import torch
+    assert x_dev.is_cuda and x_dev.dtype == torch.float32 and x_dev.is_contiguous()
+    idx = C.c_uint32()
+    check(_l.load().hb200_argmax_f32_dev(C.c_void_p(x_dev.data_ptr()), x_dev.numel() if n is None else n, C.byref(idx),
+                                         _stream_ptr(stream)))
+    return int(idx.value)
+
+
+def argmax_f32_dev_async(x_dev, index_dev, n: int | None = None, stream=None) -> None:
+    """The same without a synchronisation; index_dev is a CUDA int32 / uint32 tensor of one element."""
+    check(_l.load().hb200_argmax_f32_dev_async(C.c_void_p(x_dev.data_ptr()), x_dev.numel() if n is None else n,
+                                               C.c_void_p(index_dev.data_ptr()), _stream_ptr(stream)))
+
+
 # ---- host-buffer calls --------------------------------------------------------------------------
 
 def quantize_q8_0(x: np.ndarray) -> np.ndarray:

@@ -103,6 +103,7 @@ struct Context {
     size_t d_out_bytes = 0;
     hb200_act_t act = nullptr;
     int* d_status = nullptr;  // device word set by kernels whose bounded waits expire
+    void* d_argmax = nullptr;  // ticket + partial results of the argmax kernel, then one result word
 };
 Context g_ctx;
 
@@ -275,6 +276,8 @@ extern "C" int hb200_init(int device) {
     }
     HB_CUDA(cudaMalloc(&g_ctx.d_status, sizeof(int)));
     HB_CUDA(cudaMemset(g_ctx.d_status, 0, sizeof(int)));
+    HB_CUDA(cudaMalloc(&g_ctx.d_argmax, argmax_scratch_bytes() + 256));
+    HB_CUDA(cudaMemset(g_ctx.d_argmax, 0, argmax_scratch_bytes() + 256));
     g_ctx.ready = true;
     return HB200_OK;
     HB_GUARD_END
@@ -289,6 +292,8 @@ extern "C" int hb200_shutdown(void) {
     if (g_ctx.d_in) cudaFree(g_ctx.d_in);
     if (g_ctx.d_out) cudaFree(g_ctx.d_out);
     if (g_ctx.d_status) cudaFree(g_ctx.d_status);
+    if (g_ctx.d_argmax) cudaFree(g_ctx.d_argmax);
+    g_ctx.d_argmax = nullptr;
     if (g_ctx.stream) cudaStreamDestroy(g_ctx.stream);
     g_ctx = Context();
     return HB200_OK;
@@ -681,6 +686,39 @@ extern "C" int hb200_matmul_f32_dev(hb200_weight_t w, hb200_act_t a, size_t seq_
     rc = launch_quantize_q8_0(a->x, (int)seq_len, (int)a->n_cols, a->q, a->d, a->sums, a->ld_q, a->ld_b, nullptr, 0, st);
     if (rc) return rc;
     return dot_rows_launch(w, a, seq_len, out_dev, ld_out, st);
+    HB_GUARD_END
+}
+
+// ------------------------------------------------------------------ argmax --
+
+static int argmax_check(size_t n) {
+    if (n == 0) { set_error("argmax of an empty row"); return HB200_ERR_BAD_SHAPE; }
+    if (n > (size_t)ARGMAX_CHUNK * ARGMAX_MAX_CHUNKS) { set_error("argmax of %zu values (limit %zu)", n, (size_t)ARGMAX_CHUNK * ARGMAX_MAX_CHUNKS); return HB200_ERR_TOO_LARGE; }
+    return 0;
+}
+
+extern "C" int hb200_argmax_f32_dev_async(const float* x_dev, size_t n, uint32_t* index_dev, void* stream) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!x_dev || !index_dev) { set_error("null pointer"); return HB200_ERR_NULL; }
+    if ((rc = argmax_check(n))) return rc;
+    return launch_argmax(x_dev, n, g_ctx.d_argmax, index_dev, (cudaStream_t)stream);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_argmax_f32_dev(const float* x_dev, size_t n, uint32_t* index_out, void* stream) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!x_dev || !index_out) { set_error("null pointer"); return HB200_ERR_NULL; }
+    if ((rc = argmax_check(n))) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t* res = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(g_ctx.d_argmax) + argmax_scratch_bytes());
+    if ((rc = launch_argmax(x_dev, n, g_ctx.d_argmax, res, st))) return rc;
+    HB_CUDA(cudaMemcpyAsync(index_out, res, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+    HB_CUDA(cudaStreamSynchronize(st));
+    return HB200_OK;
     HB_GUARD_END
 }
 

@@ -170,6 +170,13 @@ int launch_gemm_tc(int kind, const void* amap_dev, const uint4* bits, const void
 int launch_gemm_tc_list(int kind, const TcMat* mats_dev, const int* chunks_dev, int n_tiles, int grid, int* status, cudaStream_t st);
 int gemm_tc_prepare();
 
+// argmax.cu: lowest index of the largest value (the reference's greedy-sampling reduction).  `scratch` is
+// argmax_scratch_bytes() of zero-initialised device memory owned by the caller, reused by every call on one stream.
+constexpr int ARGMAX_CHUNK = 2048;
+constexpr int ARGMAX_MAX_CHUNKS = 1 << 15;  // up to 64 Mi values
+size_t argmax_scratch_bytes();
+int launch_argmax(const float* x, size_t n, void* scratch, uint32_t* out_dev, cudaStream_t st);
+
 // tc_peak.cu: dense kind::i8 tensor-core rate of this GPU, measured (TOP/s).
 int measure_i8_peak(int sm_count, int* status, cudaStream_t st, double* tops);
 

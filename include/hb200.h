@@ -165,6 +165,16 @@ HB200_API int hb200_act_silu_mul_q8_dev(hb200_act_t a, const float *gate_dev, co
 HB200_API int hb200_act_hadamard_quantize_dev(hb200_act_t a, const float *x_dev, const float *signs_dev,
                                               size_t block_size, size_t seq_len, float *rotated_dev, void *stream);
 
+/* GpuCompute::argmax_f32 (hearth-compute/src/lib.rs:338-450, shader
+ * hearth-compute/src/shaders/argmax.wgsl): index of the largest of n f32 values
+ * in device memory, lowest index on ties, NaN never wins, 0 if no value
+ * exceeds -FLT_MAX.  Synchronises `stream` and returns the index on the host,
+ * as the reference's call does; four bytes cross the bus. */
+HB200_API int hb200_argmax_f32_dev(const float *x_dev, size_t n, uint32_t *index_out, void *stream);
+/* The same, without synchronising: the index lands in device memory.  Calls
+ * on different streams must not overlap (one scratch area per context). */
+HB200_API int hb200_argmax_f32_dev_async(const float *x_dev, size_t n, uint32_t *index_dev, void *stream);
+
 /* ---- host-buffer calls (the reference's own call shapes) ---------------- */
 
 /* quantize_q8_0_into / par_quantize with host buffers

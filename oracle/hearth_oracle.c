@@ -766,3 +766,45 @@ HO_API void ho_silu_mul_q8(const float *gate, const float *up, uint8_t *q8_out, 
         }
     }
 }
+
+/* ------------------------------------------------------------------ argmax -- */
+
+/* GpuCompute::argmax_f32 with its shader (hearth-compute/src/lib.rs:338-450,
+ * hearth-compute/src/shaders/argmax.wgsl), executed literally: workgroups of
+ * 128 threads x 16 consecutive elements, each thread scanning with strict '>'
+ * from -3.4028235e38 (index 0 when nothing is larger), a tree over the 128
+ * thread results (offsets 64..1, strict '>' takes the upper entry), then the
+ * host loop over the workgroup results with strict '>' from -inf. */
+HO_API uint32_t ho_argmax_f32(const float *data, size_t n) {
+    const size_t ept = 16, wg = 128, per_wg = ept * wg;
+    size_t num_wgs = (n + per_wg - 1) / per_wg;
+    uint32_t best_idx = 0;
+    float best_val = -INFINITY;
+    for (size_t g = 0; g < num_wgs; g++) {
+        float wmax[128];
+        uint32_t widx[128];
+        for (size_t t = 0; t < wg; t++) {
+            size_t start = g * per_wg + t * ept, end = start + ept < n ? start + ept : n;
+            float my_max = -3.4028235e+38f;
+            uint32_t my_idx = 0;
+            for (size_t i = start; i < end; i++)
+                if (data[i] > my_max) {
+                    my_max = data[i];
+                    my_idx = (uint32_t)i;
+                }
+            wmax[t] = my_max;
+            widx[t] = my_idx;
+        }
+        for (size_t off = 64; off > 0; off >>= 1)
+            for (size_t t = 0; t < off; t++)
+                if (wmax[t + off] > wmax[t]) {
+                    wmax[t] = wmax[t + off];
+                    widx[t] = widx[t + off];
+                }
+        if (wmax[0] > best_val) {
+            best_val = wmax[0];
+            best_idx = widx[0];
+        }
+    }
+    return best_idx;
+}

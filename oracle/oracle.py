@@ -72,6 +72,8 @@ def lib() -> C.CDLL:
                                               C.c_size_t, C.c_size_t]
         L.ho_matmul_kquant_f32.restype = C.c_int
         L.ho_matmul_kquant_f32.argtypes = [C.c_int, C.c_size_t, C.c_size_t, _u8p, _f32p, _f32p, C.c_size_t]
+        L.ho_argmax_f32.restype = C.c_uint32
+        L.ho_argmax_f32.argtypes = [_f32p, C.c_size_t]
         L.ho_quantize_ptq1_0.restype = None
         L.ho_quantize_ptq1_0.argtypes = [_f32p, C.c_size_t, _u8p]
         L.ho_hadamard_rotate.restype = None
@@ -244,3 +246,9 @@ def simd_matmul_kquant_f32(dtype: int, w: np.ndarray, x: np.ndarray, n_rows: int
                                         x2.ctypes.data_as(_u8p), _f32(out), rb, n_cols)
     assert rc == 0, rc
     return out
+
+
+def argmax_f32(x: np.ndarray) -> int:
+    """GpuCompute::argmax_f32 executed literally on the CPU."""
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
+    return int(lib().ho_argmax_f32(_f32(x), x.size))
