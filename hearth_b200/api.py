@@ -9,6 +9,7 @@ library; a missing library or device raises.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import numpy as np
 
@@ -179,6 +180,68 @@ def _as_torch_f32(ptr: int, n: int, device):
     h = _Holder()
     h.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 3}
     return torch.as_tensor(h, device=device)
+
+
+class Gguf:
+    """A mapped GGUF model file (hearth_gguf::GgufFile, hearth-gguf/src/gguf.rs:137-259).  Parsing needs no device."""
+
+    def __init__(self, path: str):
+        self._h = C.c_void_p()
+        check(_l.load().hb200_gguf_open(os.fsencode(path), C.byref(self._h)))
+        L = _l.load()
+        self.version = int(L.hb200_gguf_version(self._h))
+        self.data_offset = int(L.hb200_gguf_data_offset(self._h))
+        self.tensors = []
+        for i in range(L.hb200_gguf_tensor_count(self._h)):
+            name, dt, nd, off, nb = C.c_char_p(), C.c_int(), C.c_size_t(), C.c_uint64(), C.c_size_t()
+            shape = (C.c_uint64 * 8)()
+            check(L.hb200_gguf_tensor_info(self._h, i, C.byref(name), C.byref(dt), C.byref(nd), shape, C.byref(off), C.byref(nb)))
+            self.tensors.append(dict(name=name.value.decode(), dtype=dt.value, shape=[int(shape[k]) for k in range(nd.value)],
+                                     offset=int(off.value), bytes=int(nb.value)))
+
+    def find_tensor(self, name: str) -> int:
+        idx = C.c_size_t()
+        check(_l.load().hb200_gguf_find_tensor(self._h, name.encode(), C.byref(idx)))
+        return int(idx.value)
+
+    def tensor_data(self, index: int) -> np.ndarray:
+        p, n = C.c_void_p(), C.c_size_t()
+        check(_l.load().hb200_gguf_tensor_data(self._h, index, C.byref(p), C.byref(n)))
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(n.value,)).copy()
+
+    def upload(self, name_or_index) -> "Weight":
+        i = self.find_tensor(name_or_index) if isinstance(name_or_index, str) else int(name_or_index)
+        h = C.c_void_p()
+        check(_l.load().hb200_gguf_upload_tensor(self._h, i, C.byref(h)))
+        t = self.tensors[i]
+        return Weight(h, t["dtype"], t["shape"][1] if len(t["shape"]) > 1 else 1, t["shape"][0])
+
+    def meta_u64(self, key: str) -> int:
+        v = C.c_uint64()
+        check(_l.load().hb200_gguf_meta_u64(self._h, key.encode(), C.byref(v)))
+        return int(v.value)
+
+    def meta_f64(self, key: str) -> float:
+        v = C.c_double()
+        check(_l.load().hb200_gguf_meta_f64(self._h, key.encode(), C.byref(v)))
+        return float(v.value)
+
+    def meta_str(self, key: str) -> str:
+        p, n = C.c_char_p(), C.c_size_t()
+        check(_l.load().hb200_gguf_meta_str(self._h, key.encode(), C.byref(p), C.byref(n)))
+        return C.string_at(p, n.value).decode("utf-8", "replace")
+
+    def meta_array_f32(self, key: str) -> np.ndarray:
+        n = C.c_size_t()
+        check(_l.load().hb200_gguf_meta_array_f32(self._h, key.encode(), None, 0, C.byref(n)))
+        out = np.zeros(n.value, dtype=np.float32)
+        check(_l.load().hb200_gguf_meta_array_f32(self._h, key.encode(), _np_ptr(out), out.size, C.byref(n)))
+        return out
+
+    def close(self) -> None:
+        if self._h:
+            _l.load().hb200_gguf_close(self._h)
+            self._h = None
 
 
 def argmax_f32_dev(x_dev, n: int | None = None, stream=None) -> int:

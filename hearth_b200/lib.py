@@ -17,7 +17,8 @@ Q8_0, Q4_K, Q6_K, Q1_0_G128_LEGACY, Q1_0, Q2_0, Q1_0_G128, PQ2_0, PTQ1_0 = 8, 12
 STATUS = {
     0: "HB200_OK", -1: "HB200_ERR_NOT_INITIALIZED", -2: "HB200_ERR_NO_DEVICE", -3: "HB200_ERR_BAD_DTYPE",
     -4: "HB200_ERR_BAD_SHAPE", -5: "HB200_ERR_NULL", -6: "HB200_ERR_CUDA", -7: "HB200_ERR_UNSUPPORTED",
-    -8: "HB200_ERR_TOO_LARGE", -9: "HB200_ERR_TIMEOUT",
+    -8: "HB200_ERR_TOO_LARGE", -9: "HB200_ERR_TIMEOUT", -10: "HB200_ERR_IO", -11: "HB200_ERR_BAD_FORMAT",
+    -12: "HB200_ERR_NOT_FOUND",
 }
 
 _vp = C.c_void_p
@@ -52,6 +53,20 @@ SIGNATURES = {
     "hb200_act_hadamard_quantize_dev": (_int, [_vp, _vp, _vp, _sz, _sz, _vp, _vp]),
     "hb200_argmax_f32_dev": (_int, [_vp, _sz, C.POINTER(C.c_uint32), _vp]),
     "hb200_argmax_f32_dev_async": (_int, [_vp, _sz, _vp, _vp]),
+    "hb200_gguf_open": (_int, [C.c_char_p, C.POINTER(_vp)]),
+    "hb200_gguf_close": (_int, [_vp]),
+    "hb200_gguf_version": (C.c_uint32, [_vp]),
+    "hb200_gguf_data_offset": (C.c_uint64, [_vp]),
+    "hb200_gguf_tensor_count": (_sz, [_vp]),
+    "hb200_gguf_tensor_info": (_int, [_vp, _sz, C.POINTER(C.c_char_p), C.POINTER(_int), C.POINTER(_sz), C.POINTER(C.c_uint64),
+                                      C.POINTER(C.c_uint64), C.POINTER(_sz)]),
+    "hb200_gguf_find_tensor": (_int, [_vp, C.c_char_p, C.POINTER(_sz)]),
+    "hb200_gguf_tensor_data": (_int, [_vp, _sz, C.POINTER(_vp), C.POINTER(_sz)]),
+    "hb200_gguf_upload_tensor": (_int, [_vp, _sz, C.POINTER(_vp)]),
+    "hb200_gguf_meta_u64": (_int, [_vp, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "hb200_gguf_meta_f64": (_int, [_vp, C.c_char_p, C.POINTER(C.c_double)]),
+    "hb200_gguf_meta_str": (_int, [_vp, C.c_char_p, C.POINTER(C.c_char_p), C.POINTER(_sz)]),
+    "hb200_gguf_meta_array_f32": (_int, [_vp, C.c_char_p, _vp, _sz, C.POINTER(_sz)]),
     "hb200_quantize_q8_0": (_int, [_vp, _sz, _sz, _vp]),
     "hb200_rms_norm_q8": (_int, [_vp, _vp, C.c_float, _vp, _sz, _sz]),
     "hb200_silu_mul_q8": (_int, [_vp, _vp, _vp, _sz, _sz]),

@@ -52,7 +52,10 @@ typedef enum hb200_status {
     HB200_ERR_CUDA = -6,           /* a CUDA runtime call failed; see hb200_last_error */
     HB200_ERR_UNSUPPORTED = -7,    /* valid request this build has no kernel for */
     HB200_ERR_TOO_LARGE = -8,      /* exceeds a stated fixed capacity */
-    HB200_ERR_TIMEOUT = -9         /* a bounded device-side wait ran out */
+    HB200_ERR_TIMEOUT = -9,        /* a bounded device-side wait ran out */
+    HB200_ERR_IO = -10,            /* a file could not be opened or mapped */
+    HB200_ERR_BAD_FORMAT = -11,    /* not a GGUF file this reader understands, or truncated */
+    HB200_ERR_NOT_FOUND = -12      /* no tensor / metadata key of that name */
 } hb200_status;
 
 /* GGML type ids accepted, as the reference parses them
@@ -72,6 +75,7 @@ enum {
 typedef struct hb200_weight *hb200_weight_t; /* resident weight matrix */
 typedef struct hb200_act *hb200_act_t;       /* resident activation (f32 and Q8_0 forms) */
 typedef struct hb200_batch *hb200_batch_t;   /* recorded list of dot-row ops, one launch */
+typedef struct hb200_gguf *hb200_gguf_t;     /* a mapped GGUF model file */
 
 /* ---- lifecycle ---------------------------------------------------------- */
 
@@ -308,6 +312,39 @@ HB200_API int hb200_check_status(void);
 
 /* ---- stream helper ------------------------------------------------------ */
 HB200_API int hb200_stream_synchronize(void *stream);
+
+/* ---- GGUF reader (host only; needs no device) ---------------------------- */
+
+/* hearth_gguf::GgufFile::open (hearth-gguf/src/gguf.rs:137-224): maps the file
+ * read-only and parses header, metadata and tensor infos (GGUF version 2 or
+ * 3).  Errors: HB200_ERR_IO, HB200_ERR_BAD_FORMAT (magic, version, truncation),
+ * HB200_ERR_BAD_DTYPE (a tensor type id the reference's GgmlDType::from_id
+ * rejects, hearth-gguf/src/ggml.rs:58-103). */
+HB200_API int hb200_gguf_open(const char *path, hb200_gguf_t *out);
+HB200_API int hb200_gguf_close(hb200_gguf_t g);
+HB200_API uint32_t hb200_gguf_version(hb200_gguf_t g);
+HB200_API uint64_t hb200_gguf_data_offset(hb200_gguf_t g);
+HB200_API size_t hb200_gguf_tensor_count(hb200_gguf_t g);
+/* TensorInfo (hearth-gguf/src/tensor.rs): any output may be null.  shape has
+ * the innermost dimension first; bytes = byte_size of the tensor, 0 for a type
+ * outside this path (F32, F16 and BF16 are sized too). */
+HB200_API int hb200_gguf_tensor_info(hb200_gguf_t g, size_t index, const char **name, int *dtype_id, size_t *n_dims,
+                                     uint64_t shape[8], uint64_t *offset, size_t *bytes);
+/* GgufFile::find_tensor (gguf.rs:236). */
+HB200_API int hb200_gguf_find_tensor(hb200_gguf_t g, const char *name, size_t *index);
+/* GgufFile::tensor_data (gguf.rs:226-230): a pointer into the mapping. */
+HB200_API int hb200_gguf_tensor_data(hb200_gguf_t g, size_t index, const uint8_t **data, size_t *bytes);
+/* Uploads a one- or two-dimensional tensor as a resident weight: shape[0]
+ * columns, shape[1] rows (TensorEntry::n_cols / n_rows,
+ * hearth-llm/src/model/tensor.rs:57-71).  Needs hb200_init. */
+HB200_API int hb200_gguf_upload_tensor(hb200_gguf_t g, size_t index, hb200_weight_t *out);
+/* GgufFile::meta_u32 / meta_u64 / meta_bool, meta_f32, meta_str, meta_array
+ * (gguf.rs:240-258).  HB200_ERR_NOT_FOUND for a missing key, HB200_ERR_BAD_DTYPE
+ * for a value of another kind. */
+HB200_API int hb200_gguf_meta_u64(hb200_gguf_t g, const char *key, uint64_t *out);
+HB200_API int hb200_gguf_meta_f64(hb200_gguf_t g, const char *key, double *out);
+HB200_API int hb200_gguf_meta_str(hb200_gguf_t g, const char *key, const char **out, size_t *len);
+HB200_API int hb200_gguf_meta_array_f32(hb200_gguf_t g, const char *key, float *out, size_t capacity, size_t *count);
 
 #ifdef __cplusplus
 }
