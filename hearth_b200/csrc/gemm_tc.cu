@@ -80,10 +80,14 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false (after recording `code`) if the phase did not complete or the CTA is aborting.
+// BACKOFF_NS > 0 puts the thread to sleep between polls: the roles that wait long (copy producer, unpack, MMA issue)
+// would otherwise spend issue slots that the promotion warps of the same scheduler need.
+template <int BACKOFF_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
     for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
         if (mbar_try(bar, parity)) return true;
         if ((i & 7) == 7 && *abort_flag) return false;
+        if (BACKOFF_NS > 0) __nanosleep(BACKOFF_NS);
     }
     *abort_flag = 1;
     atomicCAS(status, 0, code);
@@ -323,7 +327,7 @@ gemm_tc_kernel(const __grid_constant__ TcLaunch L) {
                 const CUtensorMap* amap = static_cast<const CUtensorMap*>(tr.m->amap);
                 for (int blk = 0; blk < nb; blk++, g++) {
                     const int st = g % STAGES;
-                    if (g >= STAGES && !mbar_wait(smem_u32(&bars->empty[st]), ((g / STAGES) - 1) & 1, abort_flag, L.status, 1)) {
+                    if (g >= STAGES && !mbar_wait<200>(smem_u32(&bars->empty[st]), ((g / STAGES) - 1) & 1, abort_flag, L.status, 1)) {
                         ok = false;
                         break;
                     }
@@ -365,8 +369,8 @@ gemm_tc_kernel(const __grid_constant__ TcLaunch L) {
                     const uint64_t ad0 = make_desc(a_addr), bd0 = make_desc(a_addr + A_BYTES);
                     const uint32_t d0 = tmem_base + buf * 256;
                     const uint32_t bar_full = smem_u32(&bars->tmem_full[buf]), bar_empty = smem_u32(&bars->empty[st]);
-                    if (!mbar_wait(smem_u32(&bars->full[st]), (g / STAGES) & 1, abort_flag, L.status, 2)) { ok = false; break; }
-                    if (g >= 2 && !mbar_wait(smem_u32(&bars->tmem_empty[buf]), ((g >> 1) - 1) & 1, abort_flag, L.status, 4)) { ok = false; break; }
+                    if (!mbar_wait<100>(smem_u32(&bars->full[st]), (g / STAGES) & 1, abort_flag, L.status, 2)) { ok = false; break; }
+                    if (g >= 2 && !mbar_wait<50>(smem_u32(&bars->tmem_empty[buf]), ((g >> 1) - 1) & 1, abort_flag, L.status, 4)) { ok = false; break; }
                     tc_fence_after();
 #pragma unroll
                     for (int s = 0; s < 4; s++)  // one K=32 MMA per sub-block; +32 B inside the 128 B swizzle row = +2 in the address field
@@ -411,7 +415,7 @@ gemm_tc_kernel(const __grid_constant__ TcLaunch L) {
             __syncwarp();
             bool ok = true;
             if (g >= STAGES) {
-                if (lane == 0) ok = mbar_wait(smem_u32(&bars->empty[st]), ((g / STAGES) - 1) & 1, abort_flag, L.status, 5);
+                if (lane == 0) ok = mbar_wait<200>(smem_u32(&bars->empty[st]), ((g / STAGES) - 1) & 1, abort_flag, L.status, 5);
                 ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             }
             if (!ok) break;
