@@ -75,6 +75,8 @@ struct hb200_batch {
     std::vector<BatchEntry> tensor;  // ops for the tensor-core kernel (see gemm_tc_wanted)
     struct TcGroup { int kind = 0; TcMat* mats_dev = nullptr; int* chunks_dev = nullptr; int n_tiles = 0, grid = 0; };
     std::vector<TcGroup> tc_groups;  // one persistent launch per weight kind
+    struct KqGroup { int kind = 0, mt = 0; KqMat* mats_dev = nullptr; int* chunks_dev = nullptr; int n_items = 0, grid = 0; };
+    std::vector<KqGroup> kq_groups;  // K-quant ops: one launch per (kind, tokens per pass)
     // host-input path: distinct activations in order of first use, a staging buffer for their f32 rows
     std::vector<hb200_act_t> acts;
     std::vector<size_t> act_seq;       // rows used of each
@@ -1026,6 +1028,45 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
         HB_CUDA(cudaMemcpy(g.chunks_dev, chunks.data(), chunks.size() * sizeof(int), cudaMemcpyHostToDevice));
         b->tc_groups.push_back(g);
     }
+    // K-quant ops: per (kind, tokens per pass) one list of matrices whose items (32-row panel x token tile) are numbered
+    // consecutively, and contiguous runs of items per CTA balanced by rounds.
+    for (int kind : {KIND_Q4K, KIND_Q6K})
+        for (int mt : {1, 2, 4}) {
+            std::vector<KqMat> mats;
+            std::vector<int> cost;
+            int n_items = 0;
+            for (const BatchEntry& e : b->kquant) {
+                if (e.w->kind != kind || kquant_tokens_per_pass((int)e.seq_len) != mt) continue;
+                KqMat m;
+                m.kq = e.w->kq; m.d16 = e.w->d16; m.x = e.a->x; m.out = e.out;
+                m.n_rows = (int)e.w->n_rows; m.n_cols = (int)e.w->n_cols; m.nblk = e.w->nb; m.n_panels = e.w->n_panels;
+                m.seq_len = (int)e.seq_len; m.ld_out = (int)e.ld_out;
+                m.item_begin = n_items;
+                m.item_end = n_items + kquant_items(m.n_panels, m.seq_len);
+                for (int t = m.item_begin; t < m.item_end; t++) cost.push_back(kquant_rounds(kind, m.nblk));
+                n_items = m.item_end;
+                mats.push_back(m);
+            }
+            if (n_items == 0) continue;
+            hb200_batch::KqGroup g;
+            g.kind = kind; g.mt = mt; g.n_items = n_items;
+            g.grid = kquant_grid(kind, mt, g_ctx.sm_count, n_items);
+            long long total_cost = 0;
+            for (int c : cost) total_cost += c;
+            std::vector<int> chunks(g.grid + 1, n_items);
+            chunks[0] = 0;
+            long long run = 0;
+            int next_c = 1;
+            for (int i = 0; i < n_items && next_c < g.grid; i++) {
+                run += cost[i];
+                while (next_c < g.grid && run * g.grid >= total_cost * next_c) chunks[next_c++] = i + 1;
+            }
+            HB_CUDA(cudaMalloc(&g.mats_dev, mats.size() * sizeof(KqMat)));
+            HB_CUDA(cudaMemcpy(g.mats_dev, mats.data(), mats.size() * sizeof(KqMat), cudaMemcpyHostToDevice));
+            HB_CUDA(cudaMalloc(&g.chunks_dev, chunks.size() * sizeof(int)));
+            HB_CUDA(cudaMemcpy(g.chunks_dev, chunks.data(), chunks.size() * sizeof(int), cudaMemcpyHostToDevice));
+            b->kq_groups.push_back(g);
+        }
     // Host-input path: one staging buffer for every distinct activation's f32 rows and one descriptor list for the
     // list quantizer.  K-quant ops read f32 from the activation's own area, so those rows are also copied there.
     {
@@ -1085,10 +1126,8 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
     }
     for (const hb200_batch::TcGroup& g : b->tc_groups)
         if ((rc = launch_gemm_tc_list(g.kind, g.mats_dev, g.chunks_dev, g.n_tiles, g.grid, g_ctx.d_status, st))) return rc;
-    for (const BatchEntry& e : b->kquant)
-        if ((rc = launch_kquant_gemv(e.w->kind, e.w->kq, e.w->d16, (int)e.w->n_rows, (int)e.w->n_cols, e.w->nb, e.w->n_panels, e.a->x,
-                                     (int)e.seq_len, e.out, (int)e.ld_out, g_ctx.sm_count, st)))
-            return rc;
+    for (const hb200_batch::KqGroup& g : b->kq_groups)
+        if ((rc = launch_kquant_gemv_list(g.kind, g.mt, g.mats_dev, g.chunks_dev, g.n_items, g.grid, st))) return rc;
     return HB200_OK;
     HB_GUARD_END
 }
@@ -1120,7 +1159,7 @@ extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const 
 
 extern "C" int hb200_batch_launch_count(hb200_batch_t b) {
     if (!b || !b->sealed) return 0;
-    return (int)(b->groups.size() + b->kquant.size() + b->tc_groups.size());
+    return (int)(b->groups.size() + b->kq_groups.size() + b->tc_groups.size());
 }
 
 extern "C" int hb200_batch_free(hb200_batch_t b) {
@@ -1132,6 +1171,10 @@ extern "C" int hb200_batch_free(hb200_batch_t b) {
         if (g.chunks_dev) cudaFree(g.chunks_dev);
     }
     for (hb200_batch::TcGroup& g : b->tc_groups) {
+        if (g.mats_dev) cudaFree(g.mats_dev);
+        if (g.chunks_dev) cudaFree(g.chunks_dev);
+    }
+    for (hb200_batch::KqGroup& g : b->kq_groups) {
         if (g.mats_dev) cudaFree(g.mats_dev);
         if (g.chunks_dev) cudaFree(g.chunks_dev);
     }

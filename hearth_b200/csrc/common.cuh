@@ -185,8 +185,24 @@ int measure_i8_peak(int sm_count, int* status, cudaStream_t st, double* tops);
 size_t kquant_pieces_per_block(int kind);
 int launch_kquant_repack(int kind, const uint8_t* raw, size_t row_bytes, int n_rows, int nblk, int n_panels, uint4* kq,
                          unsigned short* d16, cudaStream_t st);
+// One matrix of a K-quant launch; items item_begin .. item_end - 1 of the launch belong to it
+// (item = panel * token tiles + token tile).
+struct KqMat {
+    const uint4* kq;
+    const unsigned short* d16;  // Q6_K only
+    const float* x;             // [seq_len][n_cols]
+    float* out;
+    int n_rows, n_cols, nblk, n_panels, seq_len, ld_out;
+    int item_begin, item_end;
+};
 int launch_kquant_gemv(int kind, const uint4* kq, const unsigned short* d16, int n_rows, int n_cols, int nblk, int n_panels,
                        const float* x, int seq_len, float* out, int ld_out, int sm_count, cudaStream_t st);
+// Many matrices of one kind and one tokens-per-pass class (1, 2 or 4) in one launch.
+int kquant_tokens_per_pass(int seq_len);
+int kquant_items(int n_panels, int seq_len);
+int kquant_rounds(int kind, int nblk);
+int kquant_grid(int kind, int mt, int sm_count, int n_items);
+int launch_kquant_gemv_list(int kind, int mt, const KqMat* mats_dev, const int* chunks_dev, int n_items, int grid, cudaStream_t st);
 int kquant_prepare();
 
 }  // namespace hb200

@@ -63,13 +63,17 @@ struct KqSmem {
     alignas(16) float term[2][TERMS][MT][32];
 };
 
-struct KqArgs {
-    const uint4* kq;
-    const unsigned short* d16;  // Q6_K only
-    const float* x;             // [seq_len][n_cols]
-    float* out;
-    int n_rows, n_cols, nblk, n_panels, seq_len, ld_out;
+// What one launch works through: `mats` (device memory) or, when mats is null, the one matrix `single`.  Items are
+// numbered across the matrices (item = panel * token tiles + token tile inside its matrix); with `chunks`
+// ([gridDim.x + 1] item indices) CTA c owns items chunks[c] .. chunks[c+1]-1, a contiguous run balanced by rounds;
+// without, the items are split evenly.
+struct KqLaunch {
+    const KqMat* mats;
+    const int* chunks;
+    int n_items;
+    KqMat single;
 };
+using KqArgs = KqMat;
 
 // ---- one-time re-tiling -------------------------------------------------------------------------------------------
 
@@ -106,30 +110,72 @@ __global__ void kq_repack_kernel(const uint8_t* __restrict__ raw, size_t row_byt
 
 // ---- the matvec ------------------------------------------------------------------------------------------------
 
+// Items of a matrix: item = panel * token tiles + token tile, so the token tiles of one 32-row panel follow each other
+// and re-read its weights while they are still in cache.
+template <int MT>
+__device__ __forceinline__ int kq_tiles(const KqMat& a) { return (a.seq_len + MT - 1) / MT; }
+
+// One step of a CTA's work: round r of item `item` of matrix m.
+struct KqStep {
+    const KqMat* m;
+    int item;     // item index inside its matrix
+    int r;        // round inside the item
+    int rounds;   // rounds of an item of this matrix
+};
+
 template <int KIND, int MT>
-__global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_constant__ KqArgs a, int n_items) {
+__global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_constant__ KqLaunch L) {
     using G = KqGeom<KIND>;
     using S = KqSmem<KIND, MT>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     S& sm = *reinterpret_cast<S*>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nblk = a.nblk;
-    const int rounds = max(1, (nblk + G::BLK_PER_ROUND - 1) / G::BLK_PER_ROUND);
 
-    // This CTA's contiguous run of items; item = token_tile * n_panels + panel.
-    const int it0 = (int)(((long long)n_items * blockIdx.x) / gridDim.x);
-    const int it1 = (int)(((long long)n_items * (blockIdx.x + 1)) / gridDim.x);
+    // This CTA's contiguous run of items.
+    int it0, it1;
+    if (L.chunks) {
+        it0 = L.chunks[blockIdx.x];
+        it1 = L.chunks[blockIdx.x + 1];
+    } else {
+        it0 = (int)(((long long)L.n_items * blockIdx.x) / gridDim.x);
+        it1 = (int)(((long long)L.n_items * (blockIdx.x + 1)) / gridDim.x);
+    }
     if (it0 >= it1) return;
-    const int total = (it1 - it0) * rounds;
 
-    auto stage = [&](int item, int r, int buf) {
-        const int tok0 = (item / a.n_panels) * MT;
+    int mi = 0;  // matrix cursor of the step generator (items come in increasing order)
+    auto rounds_of = [&](const KqMat* m) { return max(1, (m->nblk + G::BLK_PER_ROUND - 1) / G::BLK_PER_ROUND); };
+    auto first_step = [&](int gitem) {
+        KqStep st;
+        st.m = &L.single;
+        if (L.mats) {
+            while (gitem >= L.mats[mi].item_end) mi++;
+            st.m = &L.mats[mi];
+        }
+        st.item = gitem - st.m->item_begin;
+        st.r = 0;
+        st.rounds = rounds_of(st.m);
+        return st;
+    };
+    // gnext: the global index of the item after the one `st` belongs to
+    auto next_step = [&](const KqStep& st, int& gitem) {
+        KqStep n = st;
+        if (++n.r == st.rounds) {
+            gitem++;
+            if (gitem < it1) n = first_step(gitem);
+        }
+        return n;
+    };
+
+    auto stage = [&](const KqStep& st, int buf) {
+        const KqMat& a = *st.m;
+        const int tok0 = (st.item % kq_tiles<MT>(a)) * MT;
         constexpr int PIECES = G::CH / 4;
+        const bool vec_ok = ((a.n_cols & 3) == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
         for (int idx = tid; idx < MT * PIECES; idx += KQ_THREADS) {
             const int m = idx / PIECES, p = idx % PIECES;
-            const int col = r * G::CH + p * 4;
+            const int col = st.r * G::CH + p * 4;
             float* dst = &sm.x[buf][m][p * 4];
-            if (tok0 + m < a.seq_len && col + 3 < a.n_cols && ((a.n_cols & 3) == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0)) {
+            if (tok0 + m < a.seq_len && col + 3 < a.n_cols && vec_ok) {
                 cp_async16(dst, a.x + (size_t)(tok0 + m) * a.n_cols + col);
             } else {
 #pragma unroll
@@ -141,11 +187,12 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
 
     uint4 wn[G::NW];
     uint32_t dn = 0;
-    auto load_w = [&](int item, int r) {
-        const int panel = item % a.n_panels;
-        const int blk = (KIND == KIND_Q4K) ? (r * 8 + warp) : (r * 2 + (warp >> 2));
-        if (blk < nblk) {
-            const size_t base = ((size_t)panel * nblk + blk);
+    auto load_w = [&](const KqStep& st) {
+        const KqMat& a = *st.m;
+        const int panel = st.item / kq_tiles<MT>(a);
+        const int blk = (KIND == KIND_Q4K) ? (st.r * 8 + warp) : (st.r * 2 + (warp >> 2));
+        if (blk < a.nblk) {
+            const size_t base = ((size_t)panel * a.nblk + blk);
             const uint4* p = a.kq + base * G::NP * 32 + lane;
             if (KIND == KIND_Q4K) {
 #pragma unroll
@@ -162,15 +209,22 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
     };
 
     float run = 0.0f;  // thread tid < MT*32 owns the chain of (token tid/32, row tid%32)
-    auto replay = [&](int item, int r, int buf) {
+    auto replay = [&](const KqStep& st, int buf) {
         if (tid < MT * 32) {
+            const KqMat& a = *st.m;
             const int m = tid >> 5, row = tid & 31;
-            const int nvalid = min(TERMS, G::TERMS_PER_BLK * (nblk - r * G::BLK_PER_ROUND));
+            const int nvalid = min(TERMS, G::TERMS_PER_BLK * (a.nblk - st.r * G::BLK_PER_ROUND));
             float acc = run;
-            for (int k = 0; k < nvalid; k++) acc = __fadd_rn(acc, sm.term[buf][k][m][row]);
-            if (r == rounds - 1) {
-                const int grow = (item % a.n_panels) * 32 + row;
-                const int tok = (item / a.n_panels) * MT + m;
+            int k = 0;
+            for (; k + 4 <= nvalid; k += 4) {  // loads first, then the ordered adds
+                const float t0 = sm.term[buf][k][m][row], t1 = sm.term[buf][k + 1][m][row];
+                const float t2 = sm.term[buf][k + 2][m][row], t3 = sm.term[buf][k + 3][m][row];
+                acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, t0), t1), t2), t3);
+            }
+            for (; k < nvalid; k++) acc = __fadd_rn(acc, sm.term[buf][k][m][row]);
+            if (st.r == st.rounds - 1) {
+                const int grow = (st.item / kq_tiles<MT>(a)) * 32 + row;
+                const int tok = (st.item % kq_tiles<MT>(a)) * MT + m;
                 if (grow < a.n_rows && tok < a.seq_len) a.out[(size_t)tok * a.ld_out + grow] = acc;
                 acc = 0.0f;
             }
@@ -178,25 +232,27 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
         }
     };
 
-    stage(it0, 0, 0);
-    load_w(it0, 0);
-    int item = it0, r = 0, pitem = it0, pr = 0;
-    for (int t = 0; t < total; t++) {
+    int gitem = it0;
+    KqStep cur = first_step(gitem), prev = cur;
+    stage(cur, 0);
+    load_w(cur);
+    for (int t = 0; gitem < it1; t++) {
         cp_async_commit_wait_all();
         __syncthreads();
         uint4 w[G::NW];
 #pragma unroll
         for (int i = 0; i < G::NW; i++) w[i] = wn[i];
         const uint32_t dcur = dn;
-        int nitem = item, nr = r + 1;
-        if (nr == rounds) { nr = 0; nitem = item + 1; }
-        if (t + 1 < total) {
-            stage(nitem, nr, (t + 1) & 1);
-            load_w(nitem, nr);
+        int gnext = gitem;
+        const KqStep nxt = next_step(cur, gnext);
+        if (gnext < it1) {
+            stage(nxt, (t + 1) & 1);
+            load_w(nxt);
         }
-        if (t > 0) replay(pitem, pr, (t - 1) & 1);
+        if (t > 0) replay(prev, (t - 1) & 1);
 
         const int buf = t & 1;
+        const int nblk = cur.m->nblk, r = cur.r;
         if (KIND == KIND_Q4K) {
             const int blk = r * 8 + warp;
             if (blk < nblk) {
@@ -212,6 +268,10 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
                     if ((sb & 1) == 0) { sc = s0 & 0x3F; mn = (s0 >> 6) | ((s1 & 0x0F) << 2); }
                     else { sc = (s1 >> 4) | ((s2 & 0x03) << 4); mn = (s2 >> 2) & 0x3F; }
                     const float scf = __fmul_rn((float)sc, d), mnf = __fmul_rn((float)mn, dmin);
+                    // nibble -> float without a shift, a mask and a convert per weight: a byte permute drops the nibble
+                    // into the mantissa of 2^23 (0x4B0000nn = 8388608 + n), and fma(2^23 + n, scf, -(2^23 * scf)) is the
+                    // correctly rounded n * scf, i.e. the same bits as the separate multiply (2^23 * scf is exact).
+                    const float c0 = __fmul_rn(-8388608.0f, scf);
                     const uint4 qv = w[1 + sb];
                     const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
                     float lanes[MT][8];
@@ -219,11 +279,7 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
                     for (int m = 0; m < MT; m++)
 #pragma unroll
                         for (int j = 0; j < 8; j++) lanes[m][j] = 0.0f;
-#pragma unroll
-                    for (int tt = 0; tt < 4; tt++) {  // elements 8tt..8tt+7 of the sub-block live in word tt
-                        float v[8];
-#pragma unroll
-                        for (int j = 0; j < 8; j++) v[j] = __fsub_rn(__fmul_rn((float)((qw[tt] >> (4 * j)) & 0xF), scf), mnf);
+                    auto accumulate = [&](int tt, const float (&v)[8]) {
 #pragma unroll
                         for (int m = 0; m < MT; m++) {
                             const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][warp * 256 + sb * 32 + tt * 8]);
@@ -232,6 +288,27 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
                             lanes[m][2] = fmaf(v[2], x0.z, lanes[m][2]); lanes[m][3] = fmaf(v[3], x0.w, lanes[m][3]);
                             lanes[m][4] = fmaf(v[4], x1.x, lanes[m][4]); lanes[m][5] = fmaf(v[5], x1.y, lanes[m][5]);
                             lanes[m][6] = fmaf(v[6], x1.z, lanes[m][6]); lanes[m][7] = fmaf(v[7], x1.w, lanes[m][7]);
+                        }
+                    };
+                    if (fabsf(scf) <= 3.0e38f) {
+#pragma unroll
+                        for (int tt = 0; tt < 4; tt++) {  // elements 8tt..8tt+7 of the sub-block live in word tt
+                            float v[8];
+                            const uint32_t ev = qw[tt] & 0x0F0F0F0Fu, od = (qw[tt] >> 4) & 0x0F0F0F0Fu;  // elements 0,2,4,6 / 1,3,5,7
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                const float nf = __uint_as_float(__byte_perm((j & 1) ? od : ev, 0x4B000000u, 0x7540u + (j >> 1)));
+                                v[j] = __fsub_rn(fmaf(nf, scf, c0), mnf);
+                            }
+                            accumulate(tt, v);
+                        }
+                    } else {  // an infinite or NaN scale: the literal multiply, so that inf and NaN come out where the reference has them
+#pragma unroll
+                        for (int tt = 0; tt < 4; tt++) {
+                            float v[8];
+#pragma unroll
+                            for (int j = 0; j < 8; j++) v[j] = __fsub_rn(__fmul_rn((float)((qw[tt] >> (4 * j)) & 0xF), scf), mnf);
+                            accumulate(tt, v);
                         }
                     }
 #pragma unroll
@@ -270,36 +347,35 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
                 }
             }
         }
-        pitem = item; pr = r;
-        item = nitem; r = nr;
+        prev = cur;
+        cur = nxt;
+        gitem = gnext;
+        if (gitem >= it1) {
+            __syncthreads();
+            replay(prev, t & 1);
+        }
     }
-    __syncthreads();
-    replay(pitem, pr, (total - 1) & 1);
 }
 
 // Resident CTAs per SM of each instantiation, measured by the occupancy API at prepare time: the grid of the
 // persistent kernel is sized to exactly one wave.
 int g_kq_ctas[2][5] = {};
 
+int kq_items(const KqMat& m, int mt) { return ((m.seq_len + mt - 1) / mt) * m.n_panels; }
+
 template <int KIND, int MT>
-int launch_mt(const KqArgs& a, int sm_count, cudaStream_t st) {
-    const int tiles = (a.seq_len + MT - 1) / MT;
-    const int n_items = tiles * a.n_panels;
-    if (n_items <= 0) return 0;
-    const size_t smem = sizeof(KqSmem<KIND, MT>);
-    const int per_sm = g_kq_ctas[KIND == KIND_Q4K ? 0 : 1][MT] > 0 ? g_kq_ctas[KIND == KIND_Q4K ? 0 : 1][MT] : 1;
-    int grid = sm_count * per_sm;
-    if (grid > n_items) grid = n_items;
-    kq_gemv_kernel<KIND, MT><<<grid, KQ_THREADS, smem, st>>>(a, n_items);
+int launch_mt(const KqLaunch& L, int grid, cudaStream_t st) {
+    if (L.n_items <= 0 || grid <= 0) return 0;
+    kq_gemv_kernel<KIND, MT><<<grid, KQ_THREADS, sizeof(KqSmem<KIND, MT>), st>>>(L);
     HB_CUDA(cudaGetLastError());
     return 0;
 }
 
 template <int KIND>
-int launch_kind(const KqArgs& a, int sm_count, cudaStream_t st) {
-    if (a.seq_len == 1) return launch_mt<KIND, 1>(a, sm_count, st);
-    if (a.seq_len == 2) return launch_mt<KIND, 2>(a, sm_count, st);
-    return launch_mt<KIND, 4>(a, sm_count, st);
+int launch_kind(const KqLaunch& L, int mt, int grid, cudaStream_t st) {
+    if (mt == 1) return launch_mt<KIND, 1>(L, grid, st);
+    if (mt == 2) return launch_mt<KIND, 2>(L, grid, st);
+    return launch_mt<KIND, 4>(L, grid, st);
 }
 
 template <int KIND, int MT>
@@ -338,14 +414,49 @@ int launch_kquant_repack(int kind, const uint8_t* raw, size_t row_bytes, int n_r
     return 0;
 }
 
+int kquant_tokens_per_pass(int seq_len) { return seq_len == 1 ? 1 : (seq_len == 2 ? 2 : 4); }
+
+int kquant_items(int n_panels, int seq_len) {
+    const int mt = kquant_tokens_per_pass(seq_len);
+    return ((seq_len + mt - 1) / mt) * n_panels;
+}
+
+int kquant_rounds(int kind, int nblk) {
+    const int per = (kind == KIND_Q4K) ? 8 : 2;
+    const int r = (nblk + per - 1) / per;
+    return r > 0 ? r : 1;
+}
+
+int kquant_grid(int kind, int mt, int sm_count, int n_items) {
+    const int per_sm = g_kq_ctas[kind == KIND_Q4K ? 0 : 1][mt] > 0 ? g_kq_ctas[kind == KIND_Q4K ? 0 : 1][mt] : 1;
+    const int grid = sm_count * per_sm;
+    return grid > n_items ? n_items : grid;
+}
+
 int launch_kquant_gemv(int kind, const uint4* kq, const unsigned short* d16, int n_rows, int n_cols, int nblk, int n_panels,
                        const float* x, int seq_len, float* out, int ld_out, int sm_count, cudaStream_t st) {
     if (n_rows <= 0 || seq_len <= 0) return 0;
-    KqArgs a;
+    KqLaunch L;
+    L.mats = nullptr; L.chunks = nullptr;
+    KqMat& a = L.single;
     a.kq = kq; a.d16 = d16; a.x = x; a.out = out;
     a.n_rows = n_rows; a.n_cols = n_cols; a.nblk = nblk; a.n_panels = n_panels; a.seq_len = seq_len; a.ld_out = ld_out;
-    if (kind == KIND_Q4K) return launch_kind<KIND_Q4K>(a, sm_count, st);
-    if (kind == KIND_Q6K) return launch_kind<KIND_Q6K>(a, sm_count, st);
+    const int mt = kquant_tokens_per_pass(seq_len);
+    a.item_begin = 0;
+    a.item_end = L.n_items = kquant_items(n_panels, seq_len);
+    const int grid = kquant_grid(kind, mt, sm_count, L.n_items);
+    if (kind == KIND_Q4K) return launch_kind<KIND_Q4K>(L, mt, grid, st);
+    if (kind == KIND_Q6K) return launch_kind<KIND_Q6K>(L, mt, grid, st);
+    set_error("kquant_gemv: kind %d", kind);
+    return -7;
+}
+
+int launch_kquant_gemv_list(int kind, int mt, const KqMat* mats_dev, const int* chunks_dev, int n_items, int grid, cudaStream_t st) {
+    KqLaunch L;
+    L.mats = mats_dev; L.chunks = chunks_dev; L.n_items = n_items;
+    L.single = KqMat{};
+    if (kind == KIND_Q4K) return launch_kind<KIND_Q4K>(L, mt, grid, st);
+    if (kind == KIND_Q6K) return launch_kind<KIND_Q6K>(L, mt, grid, st);
     set_error("kquant_gemv: kind %d", kind);
     return -7;
 }
