@@ -182,6 +182,22 @@ def _as_torch_f32(ptr: int, n: int, device):
     return torch.as_tensor(h, device=device)
 
 
+def dequant_matmul_f32act(w: "Weight", x: np.ndarray, accum: np.ndarray | None = None) -> np.ndarray:
+    """GpuCompute::dequant_matmul_fused / _batch (hearth-compute/src/lib.rs:483, :1153): f32 activations, the shaders'
+    arithmetic; with `accum` the add-in-place form (lib.rs:1123).  f32 [batch, n_rows]."""
+    x2 = _rows(x)
+    out = np.zeros((x2.shape[0], w.n_rows), dtype=np.float32) if accum is None else np.array(accum, dtype=np.float32).reshape(x2.shape[0], w.n_rows)
+    check(_l.load().hb200_matmul_f32act(w._h, _np_ptr(x2), x2.shape[0], _np_ptr(out), 0 if accum is None else 1))
+    return out
+
+
+def dequant_matmul_f32act_dev(w: "Weight", x_dev, seq_len: int, out_dev, ld_out: int | None = None, accumulate: bool = False,
+                              stream=None) -> None:
+    """Device-buffer form; ld_out > n_rows lets gate|up or q|k|v share one output buffer (fused_gate_up, fused_qkv)."""
+    check(_l.load().hb200_matmul_f32act_dev(w._h, C.c_void_p(x_dev.data_ptr()), seq_len, C.c_void_p(out_dev.data_ptr()),
+                                            w.n_rows if ld_out is None else ld_out, 1 if accumulate else 0, _stream_ptr(stream)))
+
+
 class Gguf:
     """A mapped GGUF model file (hearth_gguf::GgufFile, hearth-gguf/src/gguf.rs:137-259).  Parsing needs no device."""
 

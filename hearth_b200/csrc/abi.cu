@@ -691,6 +691,53 @@ extern "C" int hb200_matmul_f32_dev(hb200_weight_t w, hb200_act_t a, size_t seq_
     HB_GUARD_END
 }
 
+// ------------------------------------------------- f32-activation matmul --
+
+static int f32act_check(hb200_weight_t w, size_t seq_len, size_t ld_out) {
+    if (!w) { set_error("null weight handle"); return HB200_ERR_NULL; }
+    if (w->dtype == HB200_PTQ1_0 || (w->kind != KIND_Q1 && w->kind != KIND_Q2)) {
+        set_error("f32-activation matmul: GGML type %d has no shader counterpart (Q1_0, Q1_0_G128 and Q2_0 do)", w->dtype);
+        return HB200_ERR_UNSUPPORTED;
+    }
+    if (seq_len > 65535) { set_error("f32-activation matmul of %zu tokens (limit 65535)", seq_len); return HB200_ERR_TOO_LARGE; }
+    if (ld_out < w->n_rows) { set_error("ld_out %zu smaller than n_rows %zu", ld_out, w->n_rows); return HB200_ERR_BAD_SHAPE; }
+    return 0;
+}
+
+extern "C" int hb200_matmul_f32act_dev(hb200_weight_t w, const float* x_dev, size_t seq_len, float* out_dev, size_t ld_out,
+                                       int accumulate, void* stream) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if ((rc = f32act_check(w, seq_len, ld_out))) return rc;
+    if (!x_dev || !out_dev) { set_error("null pointer"); return HB200_ERR_NULL; }
+    if (seq_len == 0 || w->n_rows == 0) return HB200_OK;
+    return launch_f32act(w->kind, w->bits, w->scales, (int)w->n_rows, (int)w->n_cols, w->nb, w->n_panels, x_dev, (int)seq_len,
+                         out_dev, (int)ld_out, accumulate != 0, (cudaStream_t)stream);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_matmul_f32act(hb200_weight_t w, const float* x, size_t seq_len, float* out, int accumulate) {
+    HB_GUARD_BEGIN
+    int rc = need_ctx();
+    if (rc) return rc;
+    if ((rc = f32act_check(w, seq_len, w ? w->n_rows : 0))) return rc;
+    if (seq_len == 0 || w->n_rows == 0) return HB200_OK;
+    if (!x || !out) { set_error("null buffer"); return HB200_ERR_NULL; }
+    const size_t in_bytes = seq_len * w->n_cols * sizeof(float), out_bytes = seq_len * w->n_rows * sizeof(float);
+    if ((rc = grow(&g_ctx.d_in, &g_ctx.d_in_bytes, in_bytes))) return rc;
+    if ((rc = grow(&g_ctx.d_out, &g_ctx.d_out_bytes, out_bytes))) return rc;
+    cudaStream_t st = g_ctx.stream;
+    HB_CUDA(cudaMemcpyAsync(g_ctx.d_in, x, in_bytes, cudaMemcpyHostToDevice, st));
+    if (accumulate) HB_CUDA(cudaMemcpyAsync(g_ctx.d_out, out, out_bytes, cudaMemcpyHostToDevice, st));
+    if ((rc = launch_f32act(w->kind, w->bits, w->scales, (int)w->n_rows, (int)w->n_cols, w->nb, w->n_panels, (const float*)g_ctx.d_in,
+                            (int)seq_len, (float*)g_ctx.d_out, (int)w->n_rows, accumulate != 0, st))) return rc;
+    HB_CUDA(cudaMemcpyAsync(out, g_ctx.d_out, out_bytes, cudaMemcpyDeviceToHost, st));
+    HB_CUDA(cudaStreamSynchronize(st));
+    return HB200_OK;
+    HB_GUARD_END
+}
+
 // ------------------------------------------------------------------ argmax --
 
 static int argmax_check(size_t n) {

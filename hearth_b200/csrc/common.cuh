@@ -177,6 +177,10 @@ constexpr int ARGMAX_MAX_CHUNKS = 1 << 15;  // up to 64 Mi values
 size_t argmax_scratch_bytes();
 int launch_argmax(const float* x, size_t n, void* scratch, uint32_t* out_dev, cudaStream_t st);
 
+// f32act.cu: the shaders' f32-activation matmul on the panel layout (Q1_0 / Q2_0 kinds).  accumulate: out += result.
+int launch_f32act(int kind, const uint4* bits, const void* scales, int n_rows, int n_cols, int nb, int n_panels, const float* x,
+                  int seq_len, float* out, int ld_out, bool accumulate, cudaStream_t st);
+
 // tc_peak.cu: dense kind::i8 tensor-core rate of this GPU, measured (TOP/s).
 int measure_i8_peak(int sm_count, int* status, cudaStream_t st, double* tops);
 

@@ -51,6 +51,8 @@ SIGNATURES = {
     "hb200_act_rms_norm_q8_dev": (_int, [_vp, _vp, _vp, C.c_float, _sz, _vp]),
     "hb200_act_silu_mul_q8_dev": (_int, [_vp, _vp, _vp, _sz, _vp]),
     "hb200_act_hadamard_quantize_dev": (_int, [_vp, _vp, _vp, _sz, _sz, _vp, _vp]),
+    "hb200_matmul_f32act_dev": (_int, [_vp, _vp, _sz, _vp, _sz, _int, _vp]),
+    "hb200_matmul_f32act": (_int, [_vp, _vp, _sz, _vp, _int]),
     "hb200_argmax_f32_dev": (_int, [_vp, _sz, C.POINTER(C.c_uint32), _vp]),
     "hb200_argmax_f32_dev_async": (_int, [_vp, _sz, _vp, _vp]),
     "hb200_gguf_open": (_int, [C.c_char_p, C.POINTER(_vp)]),

@@ -169,6 +169,23 @@ HB200_API int hb200_act_silu_mul_q8_dev(hb200_act_t a, const float *gate_dev, co
 HB200_API int hb200_act_hadamard_quantize_dev(hb200_act_t a, const float *x_dev, const float *signs_dev,
                                               size_t block_size, size_t seq_len, float *rotated_dev, void *stream);
 
+/* f32-activation matmul with the arithmetic of the reference's GPU shaders:
+ * GpuCompute::dequant_matmul_fused (seq_len = 1), dequant_matmul_batch
+ * ([seq_len][n_cols] in, [seq_len][n_rows] out) and, with accumulate != 0,
+ * dequant_matmul_fused_add_inplace (out += result)
+ * (hearth-compute/src/lib.rs:483-507, :1153-1173, :1123-1151; shaders
+ * q1_0_matmul.wgsl, q2_0_matmul.wgsl and their _batch / _add_inplace forms).
+ * fused_gate_up / fused_qkv (lib.rs:1237, :1364) are two or three such calls
+ * on one x with ld_out letting them share an output buffer.  Q1_0, Q1_0_G128
+ * and Q2_0 / PQ2_0 weights only, as QuantKind has them (lib.rs:25-49); other
+ * types return HB200_ERR_UNSUPPORTED, the analogue of the reference's None.
+ * The activation is NOT quantized on this path, so results differ from
+ * hb200_matmul_f32 (which follows the CPU path). */
+HB200_API int hb200_matmul_f32act_dev(hb200_weight_t w, const float *x_dev, size_t seq_len, float *out_dev, size_t ld_out,
+                                      int accumulate, void *stream);
+/* The same with host buffers; with accumulate != 0 `out` is read, too. */
+HB200_API int hb200_matmul_f32act(hb200_weight_t w, const float *x, size_t seq_len, float *out, int accumulate);
+
 /* GpuCompute::argmax_f32 (hearth-compute/src/lib.rs:338-450, shader
  * hearth-compute/src/shaders/argmax.wgsl): index of the largest of n f32 values
  * in device memory, lowest index on ties, NaN never wins, 0 if no value

@@ -808,3 +808,58 @@ HO_API uint32_t ho_argmax_f32(const float *data, size_t n) {
     }
     return best_idx;
 }
+
+/* ----------------------------------- f32-activation mode (the GPU shaders) -- */
+
+/* f16_to_f32 of the matmul shaders (hearth-compute/src/shaders/q1_0_matmul.wgsl:26-32):
+ * sign | (exp + 112) << 23 | mant << 13 with no special cases, so zero and
+ * subnormal halves come out as 2^-15 * (1 + mant/1024) and exp = 31 as a finite
+ * number.  Equal to the IEEE value for every normal half. */
+static inline float shader_h2f(const uint8_t *p) {
+    uint32_t lo = p[0], hi = p[1];
+    uint32_t sign = (hi >> 7) & 1u, exp = (hi >> 2) & 0x1Fu, mant = ((hi & 3u) << 8) | lo;
+    uint32_t bits = (sign << 31) | ((exp + 112u) << 23) | (mant << 13);
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+/* One weight row against one f32 activation row, as q1_0_matmul.wgsl:38-97 and
+ * q2_0_matmul.wgsl:48-106 compute it (the batch, add-in-place and fused
+ * gate/up and q/k/v shaders repeat the same arithmetic): per 128-column block
+ * partial[i] = w_i * x_i, a tree over the 128 partials (offsets 64, 32, .. 1,
+ * partial[i] += partial[i + offset]), then sum = sum + partial[0] * w_scale
+ * with the product and the sum rounded separately. */
+HO_API float ho_dot_f32act(int dtype, const uint8_t *w, const float *x, size_t n) {
+    int q1 = (dtype == HO_Q1_0 || dtype == HO_Q1_0_G128 || dtype == HO_Q1_0_G128_LEGACY);
+    size_t bb = q1 ? 18 : 34, blocks = n / 128;
+    float sum = 0.0f;
+    for (size_t b = 0; b < blocks; b++) {
+        const uint8_t *blk = w + b * bb;
+        float w_scale = shader_h2f(blk);
+        float partial[128];
+        for (size_t i = 0; i < 128; i++) {
+            float wv = q1 ? (float)q1_sign(blk + 2, i) : (float)q2_val(blk + 2, i);
+            partial[i] = wv * x[b * 128 + i];
+        }
+        for (size_t off = 64; off > 0; off >>= 1)
+            for (size_t i = 0; i < off; i++) partial[i] = partial[i] + partial[i + off];
+        sum = sum + partial[0] * w_scale;
+    }
+    return sum;
+}
+
+/* dequant_matmul_fused (n = 1), dequant_matmul_batch ([batch x k] in, [batch x m]
+ * out) and dequant_matmul_fused_add_inplace (out[row] = out[row] + sum)
+ * (hearth-compute/src/lib.rs:483-507, :1153-1173, :1123-1151). */
+HO_API int ho_matmul_f32act(int dtype, size_t m, size_t batch, const uint8_t *w_base, const float *x, float *out, size_t k,
+                            int add_inplace) {
+    size_t row_bytes = ho_byte_size(dtype, k);
+    if (dtype != HO_Q1_0 && dtype != HO_Q1_0_G128 && dtype != HO_Q1_0_G128_LEGACY && dtype != HO_Q2_0 && dtype != HO_PQ2_0) return -1;
+    for (size_t s = 0; s < batch; s++)
+        for (size_t row = 0; row < m; row++) {
+            float v = ho_dot_f32act(dtype, w_base + row * row_bytes, x + s * k, k);
+            out[s * m + row] = add_inplace ? out[s * m + row] + v : v;
+        }
+    return 0;
+}

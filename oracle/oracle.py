@@ -72,6 +72,8 @@ def lib() -> C.CDLL:
                                               C.c_size_t, C.c_size_t]
         L.ho_matmul_kquant_f32.restype = C.c_int
         L.ho_matmul_kquant_f32.argtypes = [C.c_int, C.c_size_t, C.c_size_t, _u8p, _f32p, _f32p, C.c_size_t]
+        L.ho_matmul_f32act.restype = C.c_int
+        L.ho_matmul_f32act.argtypes = [C.c_int, C.c_size_t, C.c_size_t, _u8p, _f32p, _f32p, C.c_size_t, C.c_int]
         L.ho_argmax_f32.restype = C.c_uint32
         L.ho_argmax_f32.argtypes = [_f32p, C.c_size_t]
         L.ho_quantize_ptq1_0.restype = None
@@ -252,3 +254,12 @@ def argmax_f32(x: np.ndarray) -> int:
     """GpuCompute::argmax_f32 executed literally on the CPU."""
     x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
     return int(lib().ho_argmax_f32(_f32(x), x.size))
+
+
+def matmul_f32act(dtype: int, w: np.ndarray, x: np.ndarray, n_rows: int, n_cols: int, accum: np.ndarray | None = None) -> np.ndarray:
+    """The GPU shaders' f32-activation matmul (dequant_matmul_fused / _batch / _add_inplace): f32 [batch, n_rows]."""
+    x2 = np.ascontiguousarray(x.reshape(1, -1) if x.ndim == 1 else x, dtype=np.float32)
+    out = np.zeros((x2.shape[0], n_rows), dtype=np.float32) if accum is None else np.array(accum, dtype=np.float32).reshape(x2.shape[0], n_rows)
+    rc = lib().ho_matmul_f32act(dtype, n_rows, x2.shape[0], _u8(np.ascontiguousarray(w)), _f32(x2), _f32(out), n_cols, 0 if accum is None else 1)
+    assert rc == 0
+    return out
