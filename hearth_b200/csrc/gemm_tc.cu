@@ -115,25 +115,6 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr)
-        : "memory");
-}
 __device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&v)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
@@ -141,32 +122,16 @@ __device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&v)[8]) {
                  : "memory");
 }
 #define HB_R8(v) "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7])
+// Waits for every outstanding tcgen05.ld of this thread.  The loaded registers are listed as read-write operands so
+// that the compiler cannot schedule a use of them (or a spill) ahead of the wait; tc_pin8 gives the same guarantee to
+// further arrays covered by that wait.
 __device__ __forceinline__ void tc_wait_ld8(uint32_t (&v)[8]) { asm volatile("tcgen05.wait::ld.sync.aligned;" : HB_R8(v)::"memory"); }
 __device__ __forceinline__ void tc_pin8(uint32_t (&v)[8]) { asm volatile("" : HB_R8(v)::"memory"); }
 
-#define HB_R16(v)                                                                                                   \
-    "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), \
-        "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
-// Waits for every outstanding tcgen05.ld of this thread; the registers are read-write operands so that no use of them
-// can be scheduled ahead of the wait.  tc_pin16 gives the same guarantee to further arrays covered by that wait.
-__device__ __forceinline__ void tc_wait_ld16(uint32_t (&v)[16]) { asm volatile("tcgen05.wait::ld.sync.aligned;" : HB_R16(v)::"memory"); }
-__device__ __forceinline__ void tc_pin16(uint32_t (&v)[16]) { asm volatile("" : HB_R16(v)::"memory"); }
 
-#define HB_R32(v)                                                                                                    \
-    "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),  \
-        "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]),  \
-        "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]),  \
-        "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31])
-// Waits for every outstanding tcgen05.ld of this thread.  The loaded registers are listed as read-write operands so
-// that the compiler cannot schedule a use of them ahead of the wait.
-__device__ __forceinline__ void tc_wait_ld(uint32_t (&v)[32]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" : HB_R32(v)::"memory");
-}
-// Same ordering guarantee for a second register array covered by the same wait.
-__device__ __forceinline__ void tc_pin(uint32_t (&v)[32]) { asm volatile("" : HB_R32(v)::"memory"); }
-
-// Pairs of fp32 lanes.  Written as two scalar IEEE operations each: the packed sm_100 forms (fma/mul/add .f32x2) did not
-// reproduce the scalar results bit for bit in the sum across blocks, so they are not used.
+// Pairs of fp32 lanes, written as two scalar IEEE operations each.  The packed sm_100 forms are not used: ptxas 12.9
+// contracts mul.rn.f32x2 followed by add.rn.f32x2 into a fused multiply-add (the scalar forms with .rn are kept apart),
+// which changes the bits of the running sum; and the packed forms issue over two cycles, so they save little.
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) { return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y)); }
 __device__ __forceinline__ float2 fmul2(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
 __device__ __forceinline__ float2 fadd2(float2 a, float2 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }

@@ -31,7 +31,6 @@ namespace hb200 {
 namespace {
 
 constexpr int KQ_THREADS = 256;
-constexpr int KQ_WARPS = 8;
 constexpr int TERMS = 64;  // ordered terms per row and round
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
