@@ -425,7 +425,7 @@ def run_ours(args, cfg, rank, world, local_rank):
             "clocks": clocks,
             "roofline": roof,
             "e2e": ({"value": (total_ops(cfg) / (e2e_ms * 1e-3) / 1e12) if is_prefill(cfg) else ab["weights"] / (e2e_ms * 1e-3) / 1e9, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                     "ms_per_step": e2e_ms, "call": "hb200_batch_run_host: one H2D of the step's inputs, list quantize, recorded batch, one D2H; pinned host buffers"} if e2e_ms else None),
+                     "ms_per_step": e2e_ms, "call": "hb200_batch_run_host: the step's inputs up, list quantize, recorded batch, every output back; pinned host buffers; single-token steps run as eight pipelined runs (upload, compute and readback streams)"} if e2e_ms else None),
         }
         if ms_nccl:
             line["nccl_allgather_variant"] = {"ms_per_step": ms_nccl / args.steps,

@@ -89,6 +89,19 @@ struct hb200_batch {
     PeerTable peers = {};   // n > 1: outputs go to every rank's buffer
     int epoch = 0;
     bool sealed = false;
+    // Pipelined host path: the ops in the order they were added, and sub-batches over contiguous runs of them, each
+    // with the activations it is the first to use and the span of output floats it writes.
+    std::vector<std::pair<int, size_t>> order;  // (0: entries, 1: kquant; index in that list)
+    bool is_child = false;
+    struct Segment {
+        hb200_batch* ops = nullptr;
+        size_t act_lo = 0, act_hi = 0;   // activations first used here: indices into acts
+        int q_lo = 0, q_hi = 0;          // their descriptors in qdescs_dev
+        const float* out_lo = nullptr;   // device span [out_lo, out_hi) written by these ops
+        const float* out_hi = nullptr;
+    };
+    std::vector<Segment> segments;
+    std::vector<cudaEvent_t> seg_in, seg_done;
 };
 
 namespace {
@@ -106,6 +119,7 @@ struct Context {
     hb200_act_t act = nullptr;
     int* d_status = nullptr;  // device word set by kernels whose bounded waits expire
     void* d_argmax = nullptr;  // ticket + partial results of the argmax kernel, then one result word
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;  // the pipelined host path: uploads and readbacks beside the compute stream
 };
 Context g_ctx;
 
@@ -297,6 +311,9 @@ extern "C" int hb200_shutdown(void) {
     if (g_ctx.d_argmax) cudaFree(g_ctx.d_argmax);
     g_ctx.d_argmax = nullptr;
     if (g_ctx.stream) cudaStreamDestroy(g_ctx.stream);
+    if (g_ctx.copy_in) cudaStreamDestroy(g_ctx.copy_in);
+    if (g_ctx.copy_out) cudaStreamDestroy(g_ctx.copy_out);
+    g_ctx.copy_in = g_ctx.copy_out = nullptr;
     g_ctx = Context();
     return HB200_OK;
     HB_GUARD_END
@@ -968,8 +985,8 @@ extern "C" int hb200_batch_add(hb200_batch_t b, hb200_weight_t w, hb200_act_t a,
     if (!out_dev) { set_error("null output"); return HB200_ERR_NULL; }
     if (seq_len == 0 || w->n_rows == 0) return HB200_OK;
     BatchEntry e{w, a, seq_len, out_dev, ld_out};
-    if (w->kind == KIND_Q4K || w->kind == KIND_Q6K) b->kquant.push_back(e);
-    else b->entries.push_back(e);
+    if (w->kind == KIND_Q4K || w->kind == KIND_Q6K) { b->order.push_back({1, b->kquant.size()}); b->kquant.push_back(e); }
+    else { b->order.push_back({0, b->entries.size()}); b->entries.push_back(e); }
     size_t ai = 0;
     for (; ai < b->acts.size(); ai++)
         if (b->acts[ai] == a) break;
@@ -977,6 +994,94 @@ extern "C" int hb200_batch_add(hb200_batch_t b, hb200_weight_t w, hb200_act_t a,
     else if (seq_len > b->act_seq[ai]) b->act_seq[ai] = seq_len;
     return HB200_OK;
     HB_GUARD_END
+}
+
+extern "C" int hb200_batch_seal(hb200_batch_t b);
+extern "C" int hb200_batch_free(hb200_batch_t b);
+
+// Splits a sealed batch into sub-batches over contiguous runs of its ops (in the order they were added), balanced by
+// weight bytes, for the pipelined host path: while the GPU works on one run the next one's inputs arrive and the
+// previous one's outputs leave.  Only done when the runs write disjoint, ascending spans of the output buffer (one
+// token per op, as in decode); otherwise the batch keeps the single-copy path.
+static int build_segments(hb200_batch* b) {
+    const size_t n_ops = b->order.size();
+    if (n_ops < 32) return 0;
+    auto entry_of = [&](size_t i) -> const BatchEntry& { return b->order[i].first ? b->kquant[b->order[i].second] : b->entries[b->order[i].second]; };
+    for (size_t i = 0; i < n_ops; i++)
+        if (entry_of(i).seq_len != 1) return 0;
+    const int n_seg = 8;
+    std::vector<size_t> bytes(n_ops);
+    size_t total = 0;
+    for (size_t i = 0; i < n_ops; i++) { bytes[i] = entry_of(i).w->resident_bytes; total += bytes[i]; }
+    std::vector<size_t> cut(n_seg + 1, n_ops);
+    cut[0] = 0;
+    size_t run = 0;
+    int next = 1;
+    for (size_t i = 0; i < n_ops && next < n_seg; i++) {
+        run += bytes[i];
+        while (next < n_seg && run * n_seg >= total * next) cut[next++] = i + 1;
+    }
+    std::vector<hb200_batch::Segment> segs;
+    size_t act_seen = 0;  // activations are listed in order of first use, so each run's new ones are a contiguous range
+    const float* prev_hi = nullptr;
+    for (int k = 0; k < n_seg; k++) {
+        if (cut[k] >= cut[k + 1]) continue;
+        hb200_batch::Segment sg;
+        sg.ops = new hb200_batch();
+        sg.ops->is_child = true;
+        size_t act_max = act_seen;
+        for (size_t i = cut[k]; i < cut[k + 1]; i++) {
+            const BatchEntry& e = entry_of(i);
+            (b->order[i].first ? sg.ops->kquant : sg.ops->entries).push_back(e);
+            const float* lo = e.out;
+            const float* hi = e.out + e.w->n_rows;
+            if (!sg.out_lo || lo < sg.out_lo) sg.out_lo = lo;
+            if (!sg.out_hi || hi > sg.out_hi) sg.out_hi = hi;
+            for (size_t ai = 0; ai < b->acts.size(); ai++)
+                if (b->acts[ai] == e.a && ai + 1 > act_max) act_max = ai + 1;
+        }
+        sg.act_lo = act_seen;
+        sg.act_hi = act_max;
+        act_seen = act_max;
+        segs.push_back(sg);
+    }
+    bool ok = true;
+    for (const auto& sg : segs) {
+        if (prev_hi && sg.out_lo < prev_hi) ok = false;  // spans must not interleave
+        prev_hi = sg.out_hi;
+    }
+    // descriptor ranges: qdescs_dev lists the activations that feed Q8_0 ops, in activation order
+    {
+        std::vector<int> qidx(b->acts.size() + 1, 0);
+        int q = 0;
+        for (size_t ai = 0; ai < b->acts.size(); ai++) {
+            qidx[ai] = q;
+            bool q8_user = false;
+            for (const BatchEntry& e : b->entries) q8_user = q8_user || e.a == b->acts[ai];
+            for (const BatchEntry& e : b->tensor) q8_user = q8_user || e.a == b->acts[ai];
+            if (q8_user) q++;
+        }
+        qidx[b->acts.size()] = q;
+        for (auto& sg : segs) { sg.q_lo = qidx[sg.act_lo]; sg.q_hi = qidx[sg.act_hi]; }
+    }
+    int rc = 0;
+    if (ok)
+        for (auto& sg : segs)
+            if ((rc = hb200_batch_seal(sg.ops))) { ok = false; break; }
+    if (!ok) {
+        for (auto& sg : segs) hb200_batch_free(sg.ops);
+        return rc;
+    }
+    b->segments = segs;
+    b->seg_in.resize(segs.size());
+    b->seg_done.resize(segs.size());
+    for (size_t k = 0; k < segs.size(); k++) {
+        HB_CUDA(cudaEventCreateWithFlags(&b->seg_in[k], cudaEventDisableTiming));
+        HB_CUDA(cudaEventCreateWithFlags(&b->seg_done[k], cudaEventDisableTiming));
+    }
+    if (!g_ctx.copy_in) HB_CUDA(cudaStreamCreateWithFlags(&g_ctx.copy_in, cudaStreamNonBlocking));
+    if (!g_ctx.copy_out) HB_CUDA(cudaStreamCreateWithFlags(&g_ctx.copy_out, cudaStreamNonBlocking));
+    return 0;
 }
 
 extern "C" int hb200_batch_seal(hb200_batch_t b) {
@@ -1148,6 +1253,10 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
             HB_CUDA(cudaMemcpy(b->qdescs_dev, qd.data(), qd.size() * sizeof(QuantDesc), cudaMemcpyHostToDevice));
         }
     }
+    if (!b->is_child && b->peers.n <= 1) {
+        int rc2 = build_segments(b);
+        if (rc2) return rc2;
+    }
     b->sealed = true;
     return HB200_OK;
     HB_GUARD_END
@@ -1190,6 +1299,39 @@ extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const 
     if (!b->sealed) { set_error("batch is not sealed"); return HB200_ERR_BAD_SHAPE; }
     if ((b->input_floats && !x_host) || (out_floats && (!out_dev_base || !out_host))) { set_error("null buffer"); return HB200_ERR_NULL; }
     cudaStream_t st = g_ctx.stream;
+    if (!b->segments.empty() && out_floats) {
+        // Pipelined: uploads on one stream, quantize + matvec on the compute stream, readbacks on a third; run k's
+        // compute overlaps run k+1's upload and run k-1's readback.  Every stream is drained before returning.
+        const float* base = out_dev_base;
+        bool spans_ok = true;
+        for (const auto& sg : b->segments) spans_ok = spans_ok && sg.out_lo >= base && sg.out_hi <= base + out_floats;
+        if (spans_ok) {
+            for (size_t k = 0; k < b->segments.size(); k++) {
+                const auto& sg = b->segments[k];
+                if (sg.act_hi > sg.act_lo) {
+                    const size_t f_lo = b->act_offset[sg.act_lo];
+                    const size_t f_hi = sg.act_hi < b->acts.size() ? b->act_offset[sg.act_hi] : b->input_floats;
+                    HB_CUDA(cudaMemcpyAsync(b->x_stage + f_lo, x_host + f_lo, (f_hi - f_lo) * sizeof(float), cudaMemcpyHostToDevice, g_ctx.copy_in));
+                }
+                HB_CUDA(cudaEventRecord(b->seg_in[k], g_ctx.copy_in));
+                HB_CUDA(cudaStreamWaitEvent(st, b->seg_in[k], 0));
+                if (b->has_kquant_inputs)
+                    for (size_t i = sg.act_lo; i < sg.act_hi; i++)
+                        HB_CUDA(cudaMemcpyAsync(b->acts[i]->x, b->x_stage + b->act_offset[i], b->act_seq[i] * b->acts[i]->n_cols * sizeof(float),
+                                                cudaMemcpyDeviceToDevice, st));
+                if (sg.q_hi > sg.q_lo && (rc = launch_quantize_q8_0_list(b->qdescs_dev + sg.q_lo, sg.q_hi - sg.q_lo, b->q_max_chunks, b->q_max_seq, st))) return rc;
+                if ((rc = hb200_batch_launch(sg.ops, st))) return rc;
+                HB_CUDA(cudaEventRecord(b->seg_done[k], st));
+                HB_CUDA(cudaStreamWaitEvent(g_ctx.copy_out, b->seg_done[k], 0));
+                HB_CUDA(cudaMemcpyAsync(out_host + (sg.out_lo - base), sg.out_lo, (size_t)(sg.out_hi - sg.out_lo) * sizeof(float), cudaMemcpyDeviceToHost,
+                                        g_ctx.copy_out));
+            }
+            HB_CUDA(cudaStreamSynchronize(g_ctx.copy_out));
+            HB_CUDA(cudaStreamSynchronize(st));
+            if (!b->tensor.empty()) return check_device_status();
+            return HB200_OK;
+        }
+    }
     if (b->input_floats) HB_CUDA(cudaMemcpyAsync(b->x_stage, x_host, b->input_floats * sizeof(float), cudaMemcpyHostToDevice, st));
     if (b->has_kquant_inputs)
         for (size_t i = 0; i < b->acts.size(); i++)
@@ -1225,6 +1367,9 @@ extern "C" int hb200_batch_free(hb200_batch_t b) {
         if (g.mats_dev) cudaFree(g.mats_dev);
         if (g.chunks_dev) cudaFree(g.chunks_dev);
     }
+    for (auto& sg : b->segments) hb200_batch_free(sg.ops);
+    for (cudaEvent_t e : b->seg_in) cudaEventDestroy(e);
+    for (cudaEvent_t e : b->seg_done) cudaEventDestroy(e);
     if (b->x_stage) cudaFree(b->x_stage);
     if (b->qdescs_dev) cudaFree(b->qdescs_dev);
     delete b;

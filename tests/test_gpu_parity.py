@@ -397,3 +397,66 @@ def test_batch_run_from_host_buffers(hb, oracle):
             a.free()
         for W in Ws:
             W.free()
+
+
+def test_batch_run_host_pipelined(hb, oracle):
+    """Forty single-token ops: hb200_batch_run_host splits them into runs and overlaps upload, compute and readback.
+    Same results as the oracle, and the same on every repetition (buffers are reused)."""
+    import torch
+    dev = torch.device("cuda:0")
+    kinds = [Q2_0, Q1_0, Q8_0, Q6_K, Q4_K]
+    specs = []
+    for i in range(40):
+        dt = kinds[i % len(kinds)]
+        k = 512 if dt in (Q4_K, Q6_K) else (1152 if i % 3 else 2048)
+        specs.append((dt, 40 + 8 * (i % 7), k, i // 2))            # two ops share each activation
+    n_acts = 20
+    widths = {}
+    for dt, n, k, g in specs:
+        widths.setdefault(g, k)
+    # ops of one activation must agree on its width: give every op the width of its group
+    specs = [(dt, n, widths[g], g) for dt, n, k, g in specs]
+    specs = [(dt, n, k, g) for dt, n, k, g in specs if not (dt in (Q4_K, Q6_K) and k % 256)]
+    xs = {g: synth.activations(1, k, seed=700 + g) for g, k in widths.items()}
+    acts = {g: hb.Act(1, k) for g, k in widths.items()}
+    ws = [synth.weights(dt, n, k, seed=800 + i, allow_code3=True) for i, (dt, n, k, _) in enumerate(specs)]
+    Ws = [hb.Weight.upload(dt, n, k, w) for (dt, n, k, _), w in zip(specs, ws)]
+    total = sum(n for _, n, _, _ in specs)
+    out_dev = torch.zeros((1, total), dtype=torch.float32, device=dev)
+    batch = hb.Batch()
+    off = 0
+    for (dt, n, k, g), W in zip(specs, Ws):
+        batch.add(W, acts[g], 1, out_dev[:, off:], ld_out=total)
+        off += n
+    batch.seal()
+    order = []
+    for _, _, _, g in specs:
+        if g not in order:
+            order.append(g)
+    pieces = []
+    for g in order:                                              # first-use order, each start 16-byte aligned
+        pieces.append(xs[g].reshape(-1))
+        pad = (-xs[g].size) % 4
+        if pad:
+            pieces.append(np.zeros(pad, dtype=np.float32))
+    x_host = np.concatenate(pieces)
+    assert batch.input_floats == x_host.size
+    out_host = np.zeros((1, total), dtype=np.float32)
+    try:
+        for rep in range(3):
+            out_host[:] = np.nan
+            batch.run_host(x_host, out_dev, out_host)
+            off = 0
+            for (dt, n, k, g), w in zip(specs, ws):
+                if dt in (Q4_K, Q6_K):
+                    want = oracle.matmul_kquant_f32(dt, w, xs[g], n, k)
+                else:
+                    want = oracle.dot_rows_batched(dt, w, oracle.quantize_q8_0(xs[g]), n, k)
+                assert_bits_equal(out_host[:, off:off + n], want, f"pipelined run_host op dtype {dt} rep {rep}")
+                off += n
+    finally:
+        batch.free()
+        for a in acts.values():
+            a.free()
+        for W in Ws:
+            W.free()
