@@ -134,3 +134,42 @@ def test_two_real_ranks_over_nvlink(oracle):
         assert p.exitcode == 0
     for r in range(world):
         assert (got[r].view(np.uint32) == want.view(np.uint32)).all(), f"rank {r}"
+
+
+def test_absent_rank_ends_in_a_timeout_status_not_a_hang(hb, oracle):
+    """Failure detection without a fault: rank 0 waits (bounded) for the flag of a rank that never launches.  The wait
+    runs out, the kernel returns, the next status check reports HB200_ERR_TIMEOUT, and the context stays usable."""
+    import time
+    import torch
+    dev = torch.device("cuda:0")
+    seq = 1
+    want, _ = _expected(oracle, seq)
+    total = want.shape[1]
+    bufs = [hb.PeerBuffer.alloc(seq * total) for _ in range(2)]
+    batch, acts, Ws = _build_rank(hb, torch, dev, 0, 2, seq, bufs, wait=True)
+    try:
+        t0 = time.perf_counter()
+        batch.launch()
+        torch.cuda.synchronize()
+        assert time.perf_counter() - t0 < 30.0
+        with pytest.raises(hb.Hb200Error) as e:
+            hb.check_status()
+        assert e.value.code == -9
+        hb.check_status()                      # the status word was cleared
+        # rank 0's own rows are in place all the same, and the library still works
+        got = bufs[0].tensor(dev).view(seq, total).cpu().numpy()
+        coff = 0
+        for dt, n, k in SPECS:
+            lo, hi = shard_rows(n, 0, 2)
+            assert (got[:, coff + lo:coff + hi].view(np.uint32) == want[:, coff + lo:coff + hi].view(np.uint32)).all()
+            coff += n
+        x = synth.activations(1, 256, seed=1)
+        assert (hb.quantize_q8_0(x) == oracle.quantize_q8_0(x)).all()
+    finally:
+        batch.free()
+        for a in acts.values():
+            a.free()
+        for W in Ws:
+            W.free()
+        for b in bufs:
+            b.close()
