@@ -322,7 +322,7 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
                     for (int r = 0; r < peers.n; r++) {
                         unsigned spins = 0;
                         while (mine[r] - peers.epoch < 0) {  // epochs only grow; the difference also survives wrap-around
-                            if (++spins > (1u << 24)) {
+                            if (++spins > (1u << 21)) {  // about a second and a half
                                 atomicCAS(peers.status, 0, 100 + r);
                                 break;
                             }
