@@ -150,7 +150,8 @@ HB200_API int hb200_act_store_q8_0_dev(hb200_act_t a, uint8_t *q8_dev, size_t se
  *
  * ops::rms_norm_q8_batch (hearth-llm/src/ops.rs:442-504): x_dev is
  * f32 [seq_len][n_cols], weight_dev f32 [n_cols]; n_cols <= 32768.  Bit-exact
- * with the reference given the eight-lane reduction order stated in DESIGN. */
+ * with the reference given the eight-lane reduction order
+ * ((l0+l4)+(l2+l6))+((l1+l5)+(l3+l7)) assumed for `wide`'s reduce_add. */
 HB200_API int hb200_act_rms_norm_q8_dev(hb200_act_t a, const float *x_dev, const float *weight_dev, float eps,
                                         size_t seq_len, void *stream);
 /* ops::silu_mul_q8 (hearth-llm/src/ops.rs:273-306) per token: gate_dev and
