@@ -151,6 +151,12 @@ constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(ROW_
 
 constexpr int SCALE_SLOTS = 8;  // ring of per-block weight scales (f32); deeper than the tile ring, see the unpack loop
 constexpr int PSLOTS = 8;       // ring of packed weight bytes (cp.async): two slots per unpack warp
+// One unpack warp per stage: a stage's blocks g, g + STAGES, ... are then produced by one warp, in order.  With two
+// producers on a stage the later one could find the stage's `empty` barrier two phases behind the one it waits for,
+// and a parity wait cannot tell a phase from the one two before it: it would pass at once and overwrite a tile in use.
+// (Five stages with five unpack warps were measured too: the same times as four, so the smaller kernel stays.)
+static_assert(UNPACK_WARPS == STAGES, "every stage needs exactly one producer warp");
+static_assert(PSLOTS == 2 * UNPACK_WARPS, "two packed-byte slots per unpack warp");
 struct Barriers {
     uint64_t full[STAGES], empty[STAGES];
     uint64_t tmem_full[2], tmem_empty[2];

@@ -304,8 +304,8 @@ HB200_API size_t hb200_batch_input_floats(hb200_batch_t b);
  * (hearth-llm/src/pool.rs:321-323) is applied here across GPUs, one process
  * per GPU.  Instead of gathering output slices with a collective after the
  * kernel, a sharded batch can store every output value straight into the
- * same place of every rank's output buffer over NVLink (ordinary peer stores,
- * no multicast) and close with a flag exchange.
+ * same place of every rank's output buffer over NVLink (ordinary peer stores
+ * only) and close with a flag exchange.
  *
  * hb200_peer_alloc: device buffer of `bytes` for the assembled outputs plus a
  *   small control block; `handle` (64 bytes) identifies it to other processes.
