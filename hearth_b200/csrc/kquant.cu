@@ -26,6 +26,8 @@
 // adds the terms in order, one round behind.  Up to four tokens share one pass over the weights.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace hb200 {
 
 namespace {
@@ -70,6 +72,7 @@ struct KqLaunch {
     const KqMat* mats;
     const int* chunks;
     int n_items;
+    uint32_t magic;  // 0x4B000000 (2^23 as a float), kept a run-time value: as a literal it was re-materialised before every byte permute
     KqMat single;
 };
 using KqArgs = KqMat;
@@ -257,62 +260,57 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
             if (blk < nblk) {
                 const float d = h2f_bits(w[0].x & 0xffffu), dmin = h2f_bits(w[0].x >> 16);
                 const uint32_t sw[3] = {w[0].y, w[0].z, w[0].w};  // the 12 scale bytes
+                const uint32_t magic = L.magic;
+                // FAST: nibble -> float without a shift, a mask and a convert per weight: a byte permute drops the nibble
+                // into the mantissa of 2^23 (0x4B0000nn = 8388608 + n), and fma(2^23 + n, scf, -(2^23 * scf)) is the
+                // correctly rounded n * scf, i.e. the same bits as the separate multiply (2^23 * scf is exact).  That
+                // needs a finite scf = sc * d, i.e. a finite d; a block whose d is infinite or NaN takes the literal
+                // multiply, so that inf and NaN come out where the reference has them.
+                auto block_body = [&](auto fast_tag) {
+                    constexpr bool FAST = decltype(fast_tag)::value;
 #pragma unroll
-                for (int sb = 0; sb < 8; sb++) {
-                    const int i3 = (sb >> 1) * 3;
-                    const uint32_t s0 = (sw[i3 >> 2] >> (8 * (i3 & 3))) & 0xff;
-                    const uint32_t s1 = (sw[(i3 + 1) >> 2] >> (8 * ((i3 + 1) & 3))) & 0xff;
-                    const uint32_t s2 = (sw[(i3 + 2) >> 2] >> (8 * ((i3 + 2) & 3))) & 0xff;
-                    uint32_t sc, mn;
-                    if ((sb & 1) == 0) { sc = s0 & 0x3F; mn = (s0 >> 6) | ((s1 & 0x0F) << 2); }
-                    else { sc = (s1 >> 4) | ((s2 & 0x03) << 4); mn = (s2 >> 2) & 0x3F; }
-                    const float scf = __fmul_rn((float)sc, d), mnf = __fmul_rn((float)mn, dmin);
-                    // nibble -> float without a shift, a mask and a convert per weight: a byte permute drops the nibble
-                    // into the mantissa of 2^23 (0x4B0000nn = 8388608 + n), and fma(2^23 + n, scf, -(2^23 * scf)) is the
-                    // correctly rounded n * scf, i.e. the same bits as the separate multiply (2^23 * scf is exact).
-                    const float c0 = __fmul_rn(-8388608.0f, scf);
-                    const uint4 qv = w[1 + sb];
-                    const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
-                    float lanes[MT][8];
-#pragma unroll
-                    for (int m = 0; m < MT; m++)
-#pragma unroll
-                        for (int j = 0; j < 8; j++) lanes[m][j] = 0.0f;
-                    auto accumulate = [&](int tt, const float (&v)[8]) {
-#pragma unroll
-                        for (int m = 0; m < MT; m++) {
-                            const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][warp * 256 + sb * 32 + tt * 8]);
-                            const float4 x0 = xp[0], x1 = xp[1];
-                            lanes[m][0] = fmaf(v[0], x0.x, lanes[m][0]); lanes[m][1] = fmaf(v[1], x0.y, lanes[m][1]);
-                            lanes[m][2] = fmaf(v[2], x0.z, lanes[m][2]); lanes[m][3] = fmaf(v[3], x0.w, lanes[m][3]);
-                            lanes[m][4] = fmaf(v[4], x1.x, lanes[m][4]); lanes[m][5] = fmaf(v[5], x1.y, lanes[m][5]);
-                            lanes[m][6] = fmaf(v[6], x1.z, lanes[m][6]); lanes[m][7] = fmaf(v[7], x1.w, lanes[m][7]);
-                        }
-                    };
-                    if (fabsf(scf) <= 3.0e38f) {
+                    for (int sb = 0; sb < 8; sb++) {
+                        const int i3 = (sb >> 1) * 3;
+                        const uint32_t s0 = (sw[i3 >> 2] >> (8 * (i3 & 3))) & 0xff;
+                        const uint32_t s1 = (sw[(i3 + 1) >> 2] >> (8 * ((i3 + 1) & 3))) & 0xff;
+                        const uint32_t s2 = (sw[(i3 + 2) >> 2] >> (8 * ((i3 + 2) & 3))) & 0xff;
+                        uint32_t sc, mn;
+                        if ((sb & 1) == 0) { sc = s0 & 0x3F; mn = (s0 >> 6) | ((s1 & 0x0F) << 2); }
+                        else { sc = (s1 >> 4) | ((s2 & 0x03) << 4); mn = (s2 >> 2) & 0x3F; }
+                        const float scf = __fmul_rn((float)sc, d), mnf = __fmul_rn((float)mn, dmin);
+                        const float c0 = __fmul_rn(-8388608.0f, scf);
+                        const uint4 qv = w[1 + sb];
+                        const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+                        float lanes[MT][8];
 #pragma unroll
                         for (int tt = 0; tt < 4; tt++) {  // elements 8tt..8tt+7 of the sub-block live in word tt
                             float v[8];
-                            const uint32_t ev = qw[tt] & 0x0F0F0F0Fu, od = (qw[tt] >> 4) & 0x0F0F0F0Fu;  // elements 0,2,4,6 / 1,3,5,7
+                            if (FAST) {
+                                const uint32_t ev = qw[tt] & 0x0F0F0F0Fu, od = (qw[tt] >> 4) & 0x0F0F0F0Fu;  // elements 0,2,4,6 / 1,3,5,7
 #pragma unroll
-                            for (int j = 0; j < 8; j++) {
-                                const float nf = __uint_as_float(__byte_perm((j & 1) ? od : ev, 0x4B000000u, 0x7540u + (j >> 1)));
-                                v[j] = __fsub_rn(fmaf(nf, scf, c0), mnf);
+                                for (int j = 0; j < 8; j++) {
+                                    const float nf = __uint_as_float(__byte_perm((j & 1) ? od : ev, magic, 0x7540u + (j >> 1)));
+                                    v[j] = __fsub_rn(fmaf(nf, scf, c0), mnf);
+                                }
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; j++) v[j] = __fsub_rn(__fmul_rn((float)((qw[tt] >> (4 * j)) & 0xF), scf), mnf);
                             }
-                            accumulate(tt, v);
-                        }
-                    } else {  // an infinite or NaN scale: the literal multiply, so that inf and NaN come out where the reference has them
 #pragma unroll
-                        for (int tt = 0; tt < 4; tt++) {
-                            float v[8];
+                            for (int m = 0; m < MT; m++) {
+                                const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][warp * 256 + sb * 32 + tt * 8]);
+                                const float4 x0 = xp[0], x1 = xp[1];
+                                const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
-                            for (int j = 0; j < 8; j++) v[j] = __fsub_rn(__fmul_rn((float)((qw[tt] >> (4 * j)) & 0xF), scf), mnf);
-                            accumulate(tt, v);
+                                for (int j = 0; j < 8; j++) lanes[m][j] = fmaf(v[j], xs[j], tt == 0 ? 0.0f : lanes[m][j]);
+                            }
                         }
+#pragma unroll
+                        for (int m = 0; m < MT; m++) sm.term[buf][warp * 8 + sb][m][lane] = reduce8(lanes[m]);
                     }
-#pragma unroll
-                    for (int m = 0; m < MT; m++) sm.term[buf][warp * 8 + sb][m][lane] = reduce8(lanes[m]);
-                }
+                };
+                if (fabsf(d) <= 65504.0f) block_body(std::true_type{});
+                else block_body(std::false_type{});
             }
         } else {
             const int blk = r * 2 + (warp >> 2), q = warp & 3;
@@ -436,7 +434,7 @@ int launch_kquant_gemv(int kind, const uint4* kq, const unsigned short* d16, int
                        const float* x, int seq_len, float* out, int ld_out, int sm_count, cudaStream_t st) {
     if (n_rows <= 0 || seq_len <= 0) return 0;
     KqLaunch L;
-    L.mats = nullptr; L.chunks = nullptr;
+    L.mats = nullptr; L.chunks = nullptr; L.magic = 0x4B000000u;
     KqMat& a = L.single;
     a.kq = kq; a.d16 = d16; a.x = x; a.out = out;
     a.n_rows = n_rows; a.n_cols = n_cols; a.nblk = nblk; a.n_panels = n_panels; a.seq_len = seq_len; a.ld_out = ld_out;
@@ -452,7 +450,7 @@ int launch_kquant_gemv(int kind, const uint4* kq, const unsigned short* d16, int
 
 int launch_kquant_gemv_list(int kind, int mt, const KqMat* mats_dev, const int* chunks_dev, int n_items, int grid, cudaStream_t st) {
     KqLaunch L;
-    L.mats = mats_dev; L.chunks = chunks_dev; L.n_items = n_items;
+    L.mats = mats_dev; L.chunks = chunks_dev; L.n_items = n_items; L.magic = 0x4B000000u;
     L.single = KqMat{};
     if (kind == KIND_Q4K) return launch_kind<KIND_Q4K>(L, mt, grid, st);
     if (kind == KIND_Q6K) return launch_kind<KIND_Q6K>(L, mt, grid, st);
