@@ -17,12 +17,15 @@
 //   panel = 32 consecutive rows; the 16-byte pieces of one 256-column block are interleaved over the rows,
 //   piece p of (panel, blk) for lane l at kq[((panel*nblk + blk)*NP + p)*32 + l], so a warp reads 512
 //   contiguous bytes per piece.  Q4_K: NP = 9 (header with d, dmin and the 12 scale bytes; one piece of
-//   nibbles per 32-element sub-block).  Q6_K: NP = 13 (8 of ql, 4 of qh, 1 of int8 scales) and the f16 d of
-//   every block in a separate array d16[(panel*nblk + blk)*32 + l].
+//   nibbles per 32-element sub-block).  Q6_K: NP = 13: the 256 six-bit values (low nibble from ql, high two bits
+//   from qh) re-coded at upload into one 6-bit stream, element e at stream bits 6e..6e+5 (12 pieces, three per
+//   64-element quarter), then 1 piece of int8 scales; the f16 d of every block in a separate array
+//   d16[(panel*nblk + blk)*32 + l].  Same 210 bytes per block; the stream lets a field be turned into a float by
+//   one logic operation (no nibble / bit-pair merge per weight).
 //
 // Kernel: lane = row, so all lanes of a warp use the same columns and x comes from shared memory as
 // broadcasts; a warp takes one block (Q4_K) or a quarter block (Q6_K) per round, eight warps make 64 ordered
-// terms per row and round; next round's pieces are prefetched into registers; one thread per (token, row)
+// terms per row and round; next round's pieces are loaded into the registers of the pieces just used up; one thread per (token, row)
 // adds the terms in order, one round behind.  Up to four tokens share one pass over the weights.
 #include "common.cuh"
 
@@ -33,7 +36,6 @@ namespace hb200 {
 namespace {
 
 constexpr int KQ_THREADS = 256;
-constexpr int TERMS = 64;  // ordered terms per row and round
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -49,19 +51,24 @@ __device__ __forceinline__ float reduce8(const float* l) {
     return __fadd_rn(__fadd_rn(q0, q2), __fadd_rn(q1, q3));
 }
 
-template <int KIND>
+template <int KIND, int MT = 1>
 struct KqGeom {
     static constexpr int NP = (KIND == KIND_Q4K) ? 9 : 13;           // pieces per block
-    static constexpr int BLK_PER_ROUND = (KIND == KIND_Q4K) ? 8 : 2;  // blocks the eight warps cover per round
+    // Q6_K: 64-element quarters a warp takes per round.  Two make a round long enough to carry its fixed cost (step
+    // bookkeeping, barrier, ordered replay); with four tokens per pass the term buffer of two would not leave room
+    // for two CTAs per SM.
+    static constexpr int H = (MT <= 2) ? 2 : 1;
+    static constexpr int BLK_PER_ROUND = (KIND == KIND_Q4K) ? 8 : 2 * H;  // blocks the eight warps cover per round
     static constexpr int CH = BLK_PER_ROUND * 256;                    // columns of x per round
-    static constexpr int NW = (KIND == KIND_Q4K) ? 9 : 4;             // pieces a thread holds per round
+    static constexpr int NW = (KIND == KIND_Q4K) ? 9 : 3 * H + 1;     // pieces a thread holds per round
     static constexpr int TERMS_PER_BLK = (KIND == KIND_Q4K) ? 8 : 32;
+    static constexpr int TERMS = BLK_PER_ROUND * TERMS_PER_BLK;       // ordered terms per row and round
 };
 
 template <int KIND, int MT>
 struct KqSmem {
-    alignas(16) float x[2][MT][KqGeom<KIND>::CH];
-    alignas(16) float term[2][TERMS][MT][32];
+    alignas(16) float x[2][MT][KqGeom<KIND, MT>::CH];
+    alignas(16) float4 term[2][KqGeom<KIND, MT>::TERMS / 4][MT][32];  // four consecutive ordered terms of a row side by side
 };
 
 // What one launch works through: `mats` (device memory) or, when mats is null, the one matrix `single`.  Items are
@@ -95,15 +102,32 @@ __global__ void kq_repack_kernel(const uint8_t* __restrict__ raw, size_t row_byt
     const int row = panel * 32 + lane;
     uint32_t w[4] = {0, 0, 0, 0};
     if (row < n_rows) {
-        const uint8_t* src = raw + (size_t)row * row_bytes + (size_t)blk * BB + p * 16;  // 2-byte aligned at least
+        const uint8_t* blkp = raw + (size_t)row * row_bytes + (size_t)blk * BB;
+        if (KIND == KIND_Q6K && p < 12) {
+            // Words 4p..4p+3 of the block's 6-bit stream: element e (its low nibble from ql, its two high bits from qh,
+            // qk_quant.rs:141-176) sits at stream bits 6e..6e+5.
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const unsigned short lo = *reinterpret_cast<const unsigned short*>(src + 4 * k);
-            const unsigned short hi = *reinterpret_cast<const unsigned short*>(src + 4 * k + 2);
-            w[k] = (uint32_t)lo | ((uint32_t)hi << 16);
+            for (int k = 0; k < 4; k++) {
+                const int bit0 = 32 * (4 * p + k);
+                uint32_t word = 0;
+                for (int e = bit0 / 6; e <= (bit0 + 31) / 6; e++) {
+                    const uint32_t ql = blkp[e >> 1], qh = blkp[128 + (e >> 2)];
+                    const uint32_t v = ((e & 1) ? (ql >> 4) : (ql & 0x0F)) | (((qh >> ((e & 3) << 1)) & 0x03) << 4);
+                    const int pos = 6 * e - bit0;
+                    word |= pos >= 0 ? (v << pos) : (v >> -pos);
+                }
+                w[k] = word;
+            }
+        } else {
+            const uint8_t* src = blkp + (KIND == KIND_Q6K ? 192 : p * 16);  // 2-byte aligned at least
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const unsigned short lo = *reinterpret_cast<const unsigned short*>(src + 4 * k);
+                const unsigned short hi = *reinterpret_cast<const unsigned short*>(src + 4 * k + 2);
+                w[k] = (uint32_t)lo | ((uint32_t)hi << 16);
+            }
         }
-        if (KIND == KIND_Q6K && p == 0)
-            d16[pb * 32 + lane] = *reinterpret_cast<const unsigned short*>(raw + (size_t)row * row_bytes + (size_t)blk * BB + 208);
+        if (KIND == KIND_Q6K && p == 0) d16[pb * 32 + lane] = *reinterpret_cast<const unsigned short*>(blkp + 208);
     } else if (KIND == KIND_Q6K && p == 0) {
         d16[pb * 32 + lane] = 0;
     }
@@ -120,14 +144,21 @@ __device__ __forceinline__ int kq_tiles(const KqMat& a) { return (a.seq_len + MT
 // One step of a CTA's work: round r of item `item` of matrix m.
 struct KqStep {
     const KqMat* m;
-    int item;     // item index inside its matrix
     int r;        // round inside the item
     int rounds;   // rounds of an item of this matrix
+    int panel;    // the item's 32-row panel and first token (one division per item, none per round)
+    int tok0;
+    int nblk;
 };
 
+// Resident CTAs per SM the register allocation of the Q6_K kernels is held to (0: none given).  The Q4_K kernels are
+// left to the allocator: told any number it schedules more aggressively and spills.
 template <int KIND, int MT>
-__global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_constant__ KqLaunch L) {
-    using G = KqGeom<KIND>;
+constexpr int kq_min_ctas() { return KIND == KIND_Q6K ? (MT == 1 ? 3 : 2) : 0; }
+
+template <int KIND, int MT>
+__global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_kernel(const __grid_constant__ KqLaunch L) {
+    using G = KqGeom<KIND, MT>;
     using S = KqSmem<KIND, MT>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     S& sm = *reinterpret_cast<S*>(smem_raw);
@@ -145,7 +176,6 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
     if (it0 >= it1) return;
 
     int mi = 0;  // matrix cursor of the step generator (items come in increasing order)
-    auto rounds_of = [&](const KqMat* m) { return max(1, (m->nblk + G::BLK_PER_ROUND - 1) / G::BLK_PER_ROUND); };
     auto first_step = [&](int gitem) {
         KqStep st;
         st.m = &L.single;
@@ -153,9 +183,12 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
             while (gitem >= L.mats[mi].item_end) mi++;
             st.m = &L.mats[mi];
         }
-        st.item = gitem - st.m->item_begin;
+        const int item = gitem - st.m->item_begin, tiles = kq_tiles<MT>(*st.m);
+        st.panel = item / tiles;
+        st.tok0 = (item - st.panel * tiles) * MT;
+        st.nblk = st.m->nblk;
         st.r = 0;
-        st.rounds = rounds_of(st.m);
+        st.rounds = max(1, (st.nblk + G::BLK_PER_ROUND - 1) / G::BLK_PER_ROUND);
         return st;
     };
     // gnext: the global index of the item after the one `st` belongs to
@@ -170,7 +203,7 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
 
     auto stage = [&](const KqStep& st, int buf) {
         const KqMat& a = *st.m;
-        const int tok0 = (st.item % kq_tiles<MT>(a)) * MT;
+        const int tok0 = st.tok0;
         constexpr int PIECES = G::CH / 4;
         const bool vec_ok = ((a.n_cols & 3) == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
         for (int idx = tid; idx < MT * PIECES; idx += KQ_THREADS) {
@@ -187,26 +220,38 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
         }
     };
 
-    uint4 wn[G::NW];
-    uint32_t dn = 0;
-    auto load_w = [&](const KqStep& st) {
-        const KqMat& a = *st.m;
-        const int panel = st.item / kq_tiles<MT>(a);
-        const int blk = (KIND == KIND_Q4K) ? (st.r * 8 + warp) : (st.r * 2 + (warp >> 2));
-        if (blk < a.nblk) {
-            const size_t base = ((size_t)panel * a.nblk + blk);
-            const uint4* p = a.kq + base * G::NP * 32 + lane;
-            if (KIND == KIND_Q4K) {
+    // Weight registers: w[] holds the pieces of the current round.  Q6_K refills it piece by piece, each piece as soon
+    // as its last use in the current round is behind, with the piece the next round needs (one set of registers, no
+    // copies; a load has most of a round to arrive).  Q4_K fetches the next round's nine pieces up front into a
+    // second set and copies: refilled in place (one by one, or in two bursts) it executed 6 % fewer instructions but
+    // issued at 63 % instead of 69 %, or spilled.  piece_ptr: this thread's first piece of a step; a step without a
+    // block for this warp (the ragged last round, or no next step at all) points at the matrix's first block instead,
+    // so that the refills need no branch: what they fetch then is never used.
+    uint4 w[G::NW];
+    uint32_t dcur = 0;
+    const int uq0 = warp * G::H;  // Q6_K: the first of this warp's quarters among the round's 8 H
+    auto block_of = [&](const KqStep& st) { return (KIND == KIND_Q4K) ? (st.r * 8 + warp) : (st.r * G::BLK_PER_ROUND + (uq0 >> 2)); };
+    auto piece_ptr = [&](const KqStep& st) -> const uint4* {
+        const int blk = block_of(st);
+        const size_t base = blk < st.nblk ? ((size_t)st.panel * st.nblk + blk) : 0;
+        return st.m->kq + (base * G::NP + (KIND == KIND_Q4K ? 0 : 3 * (uq0 & 3))) * 32 + lane;
+    };
+    // Q6_K: the scale piece is number 12 of the block (the pointer stands at piece 3q), d sits in its own array.
+    auto q6_scales = [&](const uint4* p) { return __ldg(p + (12 - 3 * (uq0 & 3)) * 32); };
+    auto q6_d = [&](const KqStep& st) -> uint32_t {
+        const int blk = block_of(st);
+        const size_t base = blk < st.nblk ? ((size_t)st.panel * st.nblk + blk) : 0;
+        return __ldg(st.m->d16 + base * 32 + lane);
+    };
+    auto load_all = [&](const uint4* p, const KqStep& st) {
+        if (KIND == KIND_Q4K) {
 #pragma unroll
-                for (int i = 0; i < 9; i++) wn[i] = __ldg(p + i * 32);
-            } else {
-                const int q = warp & 3;
-                wn[0] = __ldg(p + (2 * q) * 32);
-                wn[1] = __ldg(p + (2 * q + 1) * 32);
-                wn[2] = __ldg(p + (8 + q) * 32);
-                wn[3] = __ldg(p + 12 * 32);
-                dn = __ldg(a.d16 + base * 32 + lane);
-            }
+            for (int i = 0; i < 9; i++) w[i] = __ldg(p + i * 32);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 3 * G::H; i++) w[i] = __ldg(p + i * 32);
+            w[3 * G::H] = q6_scales(p);
+            dcur = q6_d(st);
         }
     };
 
@@ -215,18 +260,15 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
         if (tid < MT * 32) {
             const KqMat& a = *st.m;
             const int m = tid >> 5, row = tid & 31;
-            const int nvalid = min(TERMS, G::TERMS_PER_BLK * (a.nblk - st.r * G::BLK_PER_ROUND));
+            const int nvalid = min(G::TERMS, G::TERMS_PER_BLK * (st.nblk - st.r * G::BLK_PER_ROUND));
             float acc = run;
-            int k = 0;
-            for (; k + 4 <= nvalid; k += 4) {  // loads first, then the ordered adds
-                const float t0 = sm.term[buf][k][m][row], t1 = sm.term[buf][k + 1][m][row];
-                const float t2 = sm.term[buf][k + 2][m][row], t3 = sm.term[buf][k + 3][m][row];
-                acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, t0), t1), t2), t3);
+            for (int k = 0; k < nvalid / 4; k++) {  // nvalid is a multiple of eight
+                const float4 t = sm.term[buf][k][m][row];
+                acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, t.x), t.y), t.z), t.w);
             }
-            for (; k < nvalid; k++) acc = __fadd_rn(acc, sm.term[buf][k][m][row]);
             if (st.r == st.rounds - 1) {
-                const int grow = (st.item / kq_tiles<MT>(a)) * 32 + row;
-                const int tok = (st.item % kq_tiles<MT>(a)) * MT + m;
+                const int grow = st.panel * 32 + row;
+                const int tok = st.tok0 + m;
                 if (grow < a.n_rows && tok < a.seq_len) a.out[(size_t)tok * a.ld_out + grow] = acc;
                 acc = 0.0f;
             }
@@ -237,24 +279,30 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
     int gitem = it0;
     KqStep cur = first_step(gitem), prev = cur;
     stage(cur, 0);
-    load_w(cur);
+    load_all(piece_ptr(cur), cur);
     for (int t = 0; gitem < it1; t++) {
         cp_async_commit_wait_all();
         __syncthreads();
-        uint4 w[G::NW];
+        // The next step is worked out twice, here for the fetches and again at the end of the round to move on, so
+        // that it does not occupy registers across the arithmetic in between.
+        const uint4* pn;  // next round's pieces of this thread (after the last step it has no block: an idle fetch)
+        uint32_t dnext = 0;
+        {
+            int gnext = gitem;
+            const KqStep nxt = next_step(cur, gnext);
+            if (gnext < it1) stage(nxt, (t + 1) & 1);
+            pn = piece_ptr(nxt);
+            if (KIND == KIND_Q6K) dnext = q6_d(nxt);
+        }
+        uint4 wn[KIND == KIND_Q4K ? 9 : 1];
+        if (KIND == KIND_Q4K) {  // fetched up front into a second set of registers (see the note at w[])
 #pragma unroll
-        for (int i = 0; i < G::NW; i++) w[i] = wn[i];
-        const uint32_t dcur = dn;
-        int gnext = gitem;
-        const KqStep nxt = next_step(cur, gnext);
-        if (gnext < it1) {
-            stage(nxt, (t + 1) & 1);
-            load_w(nxt);
+            for (int i = 0; i < 9; i++) wn[i] = __ldg(pn + i * 32);
         }
         if (t > 0) replay(prev, (t - 1) & 1);
 
         const int buf = t & 1;
-        const int nblk = cur.m->nblk, r = cur.r;
+        const int nblk = cur.nblk, r = cur.r;
         if (KIND == KIND_Q4K) {
             const int blk = r * 8 + warp;
             if (blk < nblk) {
@@ -279,8 +327,7 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
                         else { sc = (s1 >> 4) | ((s2 & 0x03) << 4); mn = (s2 >> 2) & 0x3F; }
                         const float scf = __fmul_rn((float)sc, d), mnf = __fmul_rn((float)mn, dmin);
                         const float c0 = __fmul_rn(-8388608.0f, scf);
-                        const uint4 qv = w[1 + sb];
-                        const uint32_t qw[4] = {qv.x, qv.y, qv.z, qv.w};
+                        const uint32_t qw[4] = {w[1 + sb].x, w[1 + sb].y, w[1 + sb].z, w[1 + sb].w};
                         float lanes[MT][8];
 #pragma unroll
                         for (int tt = 0; tt < 4; tt++) {  // elements 8tt..8tt+7 of the sub-block live in word tt
@@ -306,47 +353,80 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
                             }
                         }
 #pragma unroll
-                        for (int m = 0; m < MT; m++) sm.term[buf][warp * 8 + sb][m][lane] = reduce8(lanes[m]);
+                        for (int m = 0; m < MT; m++)  // scalar stores into the float4 slots: no registers held across sub-blocks
+                            reinterpret_cast<float*>(&sm.term[buf][warp * 2 + (sb >> 2)][m][lane])[sb & 3] = reduce8(lanes[m]);
                     }
                 };
                 if (fabsf(d) <= 65504.0f) block_body(std::true_type{});
                 else block_body(std::false_type{});
             }
         } else {
-            const int blk = r * 2 + (warp >> 2), q = warp & 3;
+            const int blk = r * G::BLK_PER_ROUND + (uq0 >> 2);
             if (blk < nblk) {
                 const float d = h2f_bits(dcur);
-                const uint32_t qlw[8] = {w[0].x, w[0].y, w[0].z, w[0].w, w[1].x, w[1].y, w[1].z, w[1].w};
-                const uint32_t qhw[4] = {w[2].x, w[2].y, w[2].z, w[2].w};
-                const uint32_t scw = (q == 0) ? w[3].x : (q == 1 ? w[3].y : (q == 2 ? w[3].z : w[3].w));
+                const uint32_t magic = L.magic;
+                uint32_t scw[G::H];
 #pragma unroll
-                for (int u = 0; u < 8; u++) {
-                    const int sci = (int)(int8_t)((scw >> (8 * (u >> 1))) & 0xff);
-                    const float sd = __fmul_rn((float)sci, d);
-                    const uint32_t qh16 = (qhw[u >> 1] >> (16 * (u & 1))) & 0xffffu;
-                    float qf[8];
+                for (int h = 0; h < G::H; h++) {
+                    const int q = (uq0 + h) & 3;
+                    const uint4& sp = w[3 * G::H];
+                    scw[h] = (q == 0) ? sp.x : (q == 1 ? sp.y : (q == 2 ? sp.z : sp.w));
+                }
+                w[3 * G::H] = q6_scales(pn);
+                float tq[MT][4];
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const int quant = (int)(((qlw[u] >> (4 * j)) & 0xF) | (((qh16 >> (2 * j)) & 3) << 4)) - 32;
-                        qf[j] = __fmul_rn((float)quant, sd);
-                    }
+                for (int h = 0; h < G::H; h++) {
 #pragma unroll
-                    for (int m = 0; m < MT; m++) {
-                        const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][(warp >> 2) * 256 + q * 64 + u * 8]);
-                        const float4 x0 = xp[0], x1 = xp[1];
-                        float lanes[8];
-                        lanes[0] = fmaf(qf[0], x0.x, 0.0f); lanes[1] = fmaf(qf[1], x0.y, 0.0f);
-                        lanes[2] = fmaf(qf[2], x0.z, 0.0f); lanes[3] = fmaf(qf[3], x0.w, 0.0f);
-                        lanes[4] = fmaf(qf[4], x1.x, 0.0f); lanes[5] = fmaf(qf[5], x1.y, 0.0f);
-                        lanes[6] = fmaf(qf[6], x1.z, 0.0f); lanes[7] = fmaf(qf[7], x1.w, 0.0f);
-                        sm.term[buf][warp * 8 + u][m][lane] = reduce8(lanes);
+                    for (int g = 0; g < 4; g++) {  // 16 elements = 96 stream bits = words 3g..3g+2 of the quarter, one int8 scale
+                        const int sci = (int)(int8_t)((scw[h] >> (8 * g)) & 0xff);
+                        const float sd = __fmul_rn((float)sci, d);
+                        // A field that sits s bits up in a word is used in place: (word & 0x3F << s) | 2^23 is the float
+                        // 2^23 + quant * 2^s, minus (2^23 + 32 * 2^s) is (quant - 32) * 2^s exactly, and times sd / 2^s
+                        // rounds as (quant - 32) * sd does (the factor is a power of two, sd / 4096 stays normal).
+                        const float mul[3] = {sd, __fmul_rn(sd, 0.015625f), __fmul_rn(sd, 0.000244140625f)};
+                        auto word = [&](int i) { const uint4& v = w[i >> 2]; return (i & 3) == 0 ? v.x : ((i & 3) == 1 ? v.y : ((i & 3) == 2 ? v.z : v.w)); };
+                        const uint32_t A = word(12 * h + 3 * g), B = word(12 * h + 3 * g + 1), C = word(12 * h + 3 * g + 2);
+                        // windows of three fields each, at stream bits 0, 18, 36, 54, 72 and (one field) 90
+                        const uint32_t win[6] = {A, __funnelshift_r(A, B, 18), B >> 4, __funnelshift_r(B, C, 22), C >> 8, C >> 26};
+                        float qf[16];
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {
+                            const int s6 = 6 * (i % 3);
+                            const float f = __uint_as_float((win[i / 3] & (0x3Fu << s6)) | magic);
+                            qf[i] = __fmul_rn(__fadd_rn(f, -(8388608.0f + (float)(32 << s6))), mul[i % 3]);
+                        }
+#pragma unroll
+                        for (int hh = 0; hh < 2; hh++) {
+                            const int u = 2 * g + hh;  // the quarter's u-th run of eight elements
+#pragma unroll
+                            for (int m = 0; m < MT; m++) {
+                                const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][(uq0 + h) * 64 + u * 8]);
+                                const float4 x0 = xp[0], x1 = xp[1];
+                                float lanes[8];
+                                lanes[0] = fmaf(qf[8 * hh + 0], x0.x, 0.0f); lanes[1] = fmaf(qf[8 * hh + 1], x0.y, 0.0f);
+                                lanes[2] = fmaf(qf[8 * hh + 2], x0.z, 0.0f); lanes[3] = fmaf(qf[8 * hh + 3], x0.w, 0.0f);
+                                lanes[4] = fmaf(qf[8 * hh + 4], x1.x, 0.0f); lanes[5] = fmaf(qf[8 * hh + 5], x1.y, 0.0f);
+                                lanes[6] = fmaf(qf[8 * hh + 6], x1.z, 0.0f); lanes[7] = fmaf(qf[8 * hh + 7], x1.w, 0.0f);
+                                tq[m][u & 3] = reduce8(lanes);
+                                if ((u & 3) == 3) sm.term[buf][(uq0 + h) * 2 + (u >> 2)][m][lane] = make_float4(tq[m][0], tq[m][1], tq[m][2], tq[m][3]);
+                            }
+                        }
+                        if (g >= 1) w[3 * h + g - 1] = __ldg(pn + (3 * h + g - 1) * 32);  // group g ends in the quarter's piece g - 1
                     }
                 }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 3 * G::H; i++) w[i] = __ldg(pn + i * 32);
+                w[3 * G::H] = q6_scales(pn);
             }
+            dcur = dnext;
+        }
+        if (KIND == KIND_Q4K) {
+#pragma unroll
+            for (int i = 0; i < 9; i++) w[i] = wn[i];
         }
         prev = cur;
-        cur = nxt;
-        gitem = gnext;
+        cur = next_step(cur, gitem);
         if (gitem >= it1) {
             __syncthreads();
             replay(prev, t & 1);
@@ -357,8 +437,6 @@ __global__ void __launch_bounds__(KQ_THREADS) kq_gemv_kernel(const __grid_consta
 // Resident CTAs per SM of each instantiation, measured by the occupancy API at prepare time: the grid of the
 // persistent kernel is sized to exactly one wave.
 int g_kq_ctas[2][5] = {};
-
-int kq_items(const KqMat& m, int mt) { return ((m.seq_len + mt - 1) / mt) * m.n_panels; }
 
 template <int KIND, int MT>
 int launch_mt(const KqLaunch& L, int grid, cudaStream_t st) {

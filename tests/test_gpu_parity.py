@@ -194,7 +194,8 @@ def test_row_range_upload_is_the_pool_row_split(hb, oracle):
 # ---------------------------------------------------------------------------------- K-quants
 
 @pytest.mark.parametrize("dtype", [Q4_K, Q6_K])
-@pytest.mark.parametrize("n_rows,n_cols,seq_len", [(64, 4096, 1), (37, 512, 3), (5, 14336, 2), (1, 256, 1)])
+@pytest.mark.parametrize("n_rows,n_cols,seq_len", [(64, 4096, 1), (37, 512, 3), (5, 14336, 2), (1, 256, 1),
+                                                    (33, 1280, 9), (40, 768, 5), (70, 2304, 1), (3, 1792, 2)])
 def test_kquant_f32_matvec(hb, oracle, dtype, n_rows, n_cols, seq_len):
     """Tolerance-level parity (the 8-lane reduce order is an assumption shared with the oracle)."""
     w = synth.weights(dtype, n_rows, n_cols, seed=dtype + n_rows)
@@ -205,6 +206,31 @@ def test_kquant_f32_matvec(hb, oracle, dtype, n_rows, n_cols, seq_len):
         want = oracle.matmul_kquant_f32(dtype, w, x, n_rows, n_cols)
         np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
         assert (got.view(np.uint32) == want.view(np.uint32)).all(), "same order, same bits expected"
+    finally:
+        W.free()
+
+
+@pytest.mark.parametrize("dtype", [Q4_K, Q6_K])
+@pytest.mark.parametrize("seq_len", [1, 3])
+def test_kquant_non_finite_block_scales(hb, oracle, dtype, seq_len):
+    """Blocks whose f16 d (or dmin) is inf or NaN leave the fast nibble-to-float path: inf and NaN must come out in the
+    rows the reference puts them in, and every other row keeps its bits."""
+    n_rows, n_cols = 40, 1024
+    w = synth.weights(dtype, n_rows, n_cols, seed=77).copy()
+    bb, d_off = (144, 0) if dtype == Q4_K else (210, 208)
+    inf16, nan16, ninf16 = 0x7C00, 0x7E00, 0xFC00
+    for row, blk, bits, off in [(3, 0, inf16, d_off), (7, 2, nan16, d_off), (11, 3, ninf16, d_off), (12, 1, inf16, 2 if dtype == Q4_K else d_off)]:
+        o = blk * bb + off
+        w[row, o], w[row, o + 1] = bits & 0xFF, bits >> 8
+    x = synth.activations(seq_len, n_cols, seed=5)
+    W = hb.Weight.upload(dtype, n_rows, n_cols, w)
+    try:
+        got = hb.matmul(W, x)
+        want = oracle.matmul_kquant_f32(dtype, w, x, n_rows, n_cols)
+        assert (np.isnan(got) == np.isnan(want)).all()
+        fin = ~np.isnan(want)
+        assert (got[fin].view(np.uint32) == want[fin].view(np.uint32)).all()
+        assert not np.isfinite(want[:, [3, 7, 11, 12]]).all(), "the case must exercise non-finite outputs"
     finally:
         W.free()
 
