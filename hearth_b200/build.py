@@ -16,7 +16,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libhearth_b200.so")
 
-SOURCES = ["abi.cu", "quantize.cu", "producers.cu", "repack.cu", "gemv_dp4a.cu", "kquant.cu", "noalloc.cu", "gemm_tc.cu", "tc_peak.cu", "argmax.cu", "gguf.cu", "f32act.cu"]
+SOURCES = ["abi.cu", "quantize.cu", "producers.cu", "repack.cu", "gemv_dp4a.cu", "kquant.cu", "noalloc.cu", "gemm_tc.cu", "gemm_tc_rows.cu", "tc_peak.cu", "argmax.cu", "gguf.cu", "f32act.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

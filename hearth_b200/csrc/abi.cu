@@ -72,8 +72,9 @@ struct hb200_batch {
     std::vector<BatchEntry> entries;
     std::vector<BatchGroup> groups;
     std::vector<BatchEntry> kquant;  // K-quant ops launch on their own
-    std::vector<BatchEntry> tensor;  // ops for the tensor-core kernel (see gemm_tc_wanted)
-    struct TcGroup { int kind = 0; TcMat* mats_dev = nullptr; int* chunks_dev = nullptr; int n_tiles = 0, grid = 0; };
+    std::vector<BatchEntry> tensor;       // ops for the prefill tensor-core kernel (see dot_path)
+    std::vector<BatchEntry> tensor_rows;  // ops for the few-token tensor-core kernel
+    struct TcGroup { int kind = 0; bool rows = false; TcMat* mats_dev = nullptr; int* chunks_dev = nullptr; int n_tiles = 0, grid = 0; };
     std::vector<TcGroup> tc_groups;  // one persistent launch per weight kind
     struct KqGroup { int kind = 0, mt = 0; KqMat* mats_dev = nullptr; int* chunks_dev = nullptr; int n_items = 0, grid = 0; };
     std::vector<KqGroup> kq_groups;  // K-quant ops: one launch per (kind, tokens per pass)
@@ -128,20 +129,27 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode_tiled = nullptr;
 
-// Tensor map over an activation's int8 plane: [max_seq rows][ld_q bytes], box 128 rows x 128 bytes, 128-byte swizzle.
-int encode_qmap(hb200_act* a) {
-    if (!g_encode_tiled) { a->has_qmap = false; return 0; }
-    static_assert(sizeof(CUtensorMap) <= sizeof(a->qmap), "tensor map storage");
+// Tensor maps over an activation's int8 plane: [max_seq rows][ld_q bytes], 128-byte swizzle, boxes of 128 rows x 128
+// bytes (prefill kernel) and 32 rows x 128 bytes (few-token kernel).
+static int encode_one_qmap(hb200_act* a, unsigned char* host, void** dev, cuuint32_t box_rows) {
     const cuuint64_t dims[2] = {(cuuint64_t)a->ld_q, (cuuint64_t)a->max_seq};
     const cuuint64_t strides[1] = {(cuuint64_t)a->ld_q};
-    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t box[2] = {128, box_rows};
     const cuuint32_t estr[2] = {1, 1};
-    CUresult r = g_encode_tiled(reinterpret_cast<CUtensorMap*>(a->qmap), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->q, dims, strides, box,
+    CUresult r = g_encode_tiled(reinterpret_cast<CUtensorMap*>(host), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a->q, dims, strides, box,
                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with code %d", (int)r); return HB200_ERR_CUDA; }
-    if (!a->qmap_dev) HB_CUDA(cudaMalloc(&a->qmap_dev, sizeof(a->qmap)));
-    HB_CUDA(cudaMemcpy(a->qmap_dev, a->qmap, sizeof(a->qmap), cudaMemcpyHostToDevice));
+    if (!*dev) HB_CUDA(cudaMalloc(dev, 128));
+    HB_CUDA(cudaMemcpy(*dev, host, 128, cudaMemcpyHostToDevice));
+    return 0;
+}
+int encode_qmap(hb200_act* a) {
+    if (!g_encode_tiled) { a->has_qmap = false; return 0; }
+    static_assert(sizeof(CUtensorMap) <= sizeof(a->qmap), "tensor map storage");
+    int rc;
+    if ((rc = encode_one_qmap(a, a->qmap, &a->qmap_dev, 128))) return rc;
+    if ((rc = encode_one_qmap(a, a->qmap32, &a->qmap32_dev, GEMM_TCR_TOK_TILE))) return rc;
     a->has_qmap = true;
     return 0;
 }
@@ -208,13 +216,29 @@ int check_pair(const hb200_weight* w, const hb200_act* a, size_t seq_len, size_t
 
 namespace {
 
+// Which kernel a Q8_0-activation op runs on: the streaming dp4a kernel (passes of four tokens), the few-token
+// tensor-core kernel (rows on the MMA's M side) or the prefill tensor-core kernel (tokens on the M side).
+enum DotPath { PATH_DP4A = 0, PATH_TC_ROWS = 1, PATH_TC = 2 };
+DotPath dot_path(const hb200_weight* w, const hb200_act* a, size_t seq_len) {
+    static const char* force = getenv("HB200_FORCE_PATH");
+    if (!a->has_qmap || w->nb <= 0 || (w->kind != KIND_Q1 && w->kind != KIND_Q2)) return PATH_DP4A;
+    if (force) return (DotPath)atoi(force);
+    if (gemm_tcr_wanted(w->kind, seq_len)) return PATH_TC_ROWS;
+    if (gemm_tc_wanted(w->kind, seq_len)) return PATH_TC;
+    return PATH_DP4A;
+}
+
 int dot_rows_launch(const hb200_weight* w, const hb200_act* a, size_t seq_len, float* out, size_t ld_out, cudaStream_t st) {
     if (w->kind == KIND_Q4K || w->kind == KIND_Q6K) {
         set_error("K-quant weights take f32 activations; use hb200_matmul_f32[_dev]");
         return HB200_ERR_UNSUPPORTED;
     }
     // Prefill-sized token counts of a 1-/2-bit weight go to the tensor cores; fewer run as passes of the streaming dp4a kernel.
-    if (gemm_tc_wanted(w->kind, seq_len) && a->has_qmap && w->nb > 0)
+    const DotPath path = dot_path(w, a, seq_len);
+    if (path == PATH_TC_ROWS)
+        return launch_gemm_tcr(w->kind, a->qmap32_dev, w->bits, w->scales, a->d, a->ld_b, (int)w->n_rows, w->nb, (int)seq_len, out,
+                               (int)ld_out, g_ctx.sm_count, g_ctx.d_status, st);
+    if (path == PATH_TC)
         return launch_gemm_tc(w->kind, a->qmap_dev, w->bits, w->scales, a->d, a->ld_b, (int)w->n_rows, w->nb, (int)seq_len, out,
                               (int)ld_out, g_ctx.sm_count, g_ctx.d_status, st);
     for (size_t tok0 = 0; tok0 < seq_len; tok0 += GEMV_MAX_M) {
@@ -279,6 +303,7 @@ extern "C" int hb200_init(int device) {
     if ((rc = gemv_dp4a_prepare())) return rc;
     if ((rc = kquant_prepare())) return rc;
     if ((rc = gemm_tc_prepare())) return rc;
+    if ((rc = gemm_tcr_prepare())) return rc;
     if ((rc = producers_prepare())) return rc;
     {
         void* fn = nullptr;
@@ -362,8 +387,8 @@ extern "C" const char* hb200_selected_kernel(int dtype, size_t seq_len) {
     const int kind = kind_of(dtype);
     if (seq_len == 0) return "none";
     switch (kind) {
-        case KIND_Q1: return gemm_tc_wanted(kind, seq_len) ? "gemm_tcgen05_i8_q1_0" : "gemv_dp4a_q1_0";
-        case KIND_Q2: return gemm_tc_wanted(kind, seq_len) ? "gemm_tcgen05_i8_q2_0" : "gemv_dp4a_q2_0";
+        case KIND_Q1: return gemm_tcr_wanted(kind, seq_len) ? "gemm_tcgen05_i8_rows_q1_0" : (gemm_tc_wanted(kind, seq_len) ? "gemm_tcgen05_i8_q1_0" : "gemv_dp4a_q1_0");
+        case KIND_Q2: return gemm_tcr_wanted(kind, seq_len) ? "gemm_tcgen05_i8_rows_q2_0" : (gemm_tc_wanted(kind, seq_len) ? "gemm_tcgen05_i8_q2_0" : "gemv_dp4a_q2_0");
         case KIND_Q8: return "gemv_dp4a_q8_0";
         case KIND_Q4K: return "kquant_gemv_q4_k_f32";
         case KIND_Q6K: return "kquant_gemv_q6_k_f32";
@@ -569,6 +594,7 @@ extern "C" int hb200_act_free(hb200_act_t a) {
     if (a->d) cudaFree(a->d);
     if (a->sums) cudaFree(a->sums);
     if (a->qmap_dev) cudaFree(a->qmap_dev);
+    if (a->qmap32_dev) cudaFree(a->qmap32_dev);
     delete a;
     return HB200_OK;
     HB_GUARD_END
@@ -910,7 +936,7 @@ extern "C" int hb200_dot_rows_batched(hb200_weight_t w, const uint8_t* a_q8, siz
     if ((rc = dot_rows_launch(w, g_ctx.act, seq_len, (float*)g_ctx.d_out, w->n_rows, g_ctx.stream))) return rc;
     HB_CUDA(cudaMemcpyAsync(out, g_ctx.d_out, out_bytes, cudaMemcpyDeviceToHost, g_ctx.stream));
     HB_CUDA(cudaStreamSynchronize(g_ctx.stream));
-    if (seq_len >= (size_t)GEMM_TC_MIN_TOKENS) return check_device_status();
+    if (seq_len >= (size_t)GEMM_TCR_MIN_TOKENS_Q1) return check_device_status();
     return HB200_OK;
     HB_GUARD_END
 }
@@ -934,7 +960,7 @@ extern "C" int hb200_matmul_f32(hb200_weight_t w, const float* x, size_t seq_len
     if ((rc = hb200_matmul_f32_dev(w, g_ctx.act, seq_len, (float*)g_ctx.d_out, w->n_rows, g_ctx.stream))) return rc;
     HB_CUDA(cudaMemcpyAsync(out, g_ctx.d_out, out_bytes, cudaMemcpyDeviceToHost, g_ctx.stream));
     HB_CUDA(cudaStreamSynchronize(g_ctx.stream));
-    if (seq_len >= (size_t)GEMM_TC_MIN_TOKENS) return check_device_status();
+    if (seq_len >= (size_t)GEMM_TCR_MIN_TOKENS_Q1) return check_device_status();
     return HB200_OK;
     HB_GUARD_END
 }
@@ -1132,10 +1158,11 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
     struct Acc { std::vector<DotOp> first; std::vector<DotItem> second; std::vector<int> cost; };
     std::map<std::pair<int, int>, Acc> acc;
     for (const BatchEntry& e : b->entries) {
-        if (gemm_tc_wanted(e.w->kind, e.seq_len) && e.a->has_qmap && e.w->nb > 0) {
-            b->tensor.push_back(e);  // tensor-core kernel: all such ops of one kind share a launch
-            continue;
-        }
+        // tensor-core kernels: all such ops of one kind share a launch (a peer-store batch stays on the streaming kernel,
+        // the only one with that epilogue)
+        const DotPath path = b->peers.n > 1 ? PATH_DP4A : dot_path(e.w, e.a, e.seq_len);
+        if (path == PATH_TC) { b->tensor.push_back(e); continue; }
+        if (path == PATH_TC_ROWS) { b->tensor_rows.push_back(e); continue; }
         for (size_t tok0 = 0; tok0 < e.seq_len; tok0 += GEMV_MAX_M) {
             const int m = (int)((e.seq_len - tok0) < (size_t)GEMV_MAX_M ? (e.seq_len - tok0) : GEMV_MAX_M);
             auto& slot = acc[{e.w->kind, m}];
@@ -1171,15 +1198,20 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
     }
     // Tensor-core ops: per weight kind one list of matrices whose 128 x 64 tiles are numbered consecutively, and
     // contiguous runs of tiles per CTA balanced by 128-column blocks (plus a fixed share per tile for its fill and drain).
+    for (int rows = 0; rows < 2; rows++)
     for (int kind : {KIND_Q1, KIND_Q2}) {
         std::vector<TcMat> mats;
         std::vector<int> cost;
         int n_tiles = 0;
-        for (const BatchEntry& e : b->tensor) {
+        for (const BatchEntry& e : (rows ? b->tensor_rows : b->tensor)) {
             if (e.w->kind != kind) continue;
             TcMat m;
-            gemm_tc_fill(m, e.a->qmap_dev, e.w->bits, e.w->scales, e.a->d, e.a->ld_b, (int)e.w->n_rows, e.w->nb, (int)e.seq_len, e.out,
-                         (int)e.ld_out, n_tiles);
+            if (rows)
+                gemm_tcr_fill(m, e.a->qmap32_dev, e.w->bits, e.w->scales, e.a->d, e.a->ld_b, (int)e.w->n_rows, e.w->nb, (int)e.seq_len,
+                              e.out, (int)e.ld_out, n_tiles);
+            else
+                gemm_tc_fill(m, e.a->qmap_dev, e.w->bits, e.w->scales, e.a->d, e.a->ld_b, (int)e.w->n_rows, e.w->nb, (int)e.seq_len, e.out,
+                             (int)e.ld_out, n_tiles);
             for (int t = m.tile_begin; t < m.tile_end; t++) cost.push_back(e.w->nb + 4);
             n_tiles = m.tile_end;
             mats.push_back(m);
@@ -1187,6 +1219,7 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
         if (n_tiles == 0) continue;
         hb200_batch::TcGroup g;
         g.kind = kind;
+        g.rows = rows != 0;
         g.n_tiles = n_tiles;
         g.grid = n_tiles < g_ctx.sm_count ? n_tiles : g_ctx.sm_count;
         const std::vector<int> chunks = balanced_chunks(cost, g.grid);
@@ -1288,7 +1321,8 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
             return rc;
     }
     for (const hb200_batch::TcGroup& g : b->tc_groups)
-        if ((rc = launch_gemm_tc_list(g.kind, g.mats_dev, g.chunks_dev, g.n_tiles, g.grid, g_ctx.d_status, st))) return rc;
+        if ((rc = (g.rows ? launch_gemm_tcr_list : launch_gemm_tc_list)(g.kind, g.mats_dev, g.chunks_dev, g.n_tiles, g.grid, g_ctx.d_status, st)))
+            return rc;
     for (const hb200_batch::KqGroup& g : b->kq_groups)
         if ((rc = launch_kquant_gemv_list(g.kind, g.mt, g.mats_dev, g.chunks_dev, g.n_items, g.grid, st))) return rc;
     return HB200_OK;
@@ -1335,7 +1369,7 @@ extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const 
             }
             HB_CUDA(cudaStreamSynchronize(g_ctx.copy_out));
             HB_CUDA(cudaStreamSynchronize(st));
-            if (!b->tensor.empty()) return check_device_status();
+            if (!b->tensor.empty() || !b->tensor_rows.empty()) return check_device_status();
             return HB200_OK;
         }
     }
@@ -1348,7 +1382,7 @@ extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const 
     if ((rc = hb200_batch_launch(b, st))) return rc;
     if (out_floats) HB_CUDA(cudaMemcpyAsync(out_host, out_dev_base, out_floats * sizeof(float), cudaMemcpyDeviceToHost, st));
     HB_CUDA(cudaStreamSynchronize(st));
-    if (!b->tensor.empty()) return check_device_status();
+    if (!b->tensor.empty() || !b->tensor_rows.empty()) return check_device_status();
     return HB200_OK;
     HB_GUARD_END
 }

@@ -141,7 +141,8 @@ int gemv_dp4a_prepare();  // sets the dynamic shared-memory attributes once
 // receives a non-zero code if a bounded wait inside the kernel expires.
 // Below these token counts, passes of the streaming dp4a kernel (four tokens each) are faster than 128-token
 // tensor-core tiles that are mostly empty.  Measured on B200 on the 27B layer set: a tensor-core pass costs what six
-// dp4a passes of Q2_0 cost (24 tokens), or four of Q1_0, whose dp4a kernel is slower.
+// dp4a passes of Q2_0 cost (24 tokens), or four of Q1_0, whose dp4a kernel is slower.  (With the few-token kernel
+// below taking everything up to 64 tokens, these two limits only matter where that kernel is not available.)
 constexpr int GEMM_TC_MIN_TOKENS_Q2 = 25;
 constexpr int GEMM_TC_MIN_TOKENS_Q1 = 17;
 constexpr int GEMM_TC_MIN_TOKENS = GEMM_TC_MIN_TOKENS_Q1;  // no tensor-core launch below this, whatever the kind
@@ -169,6 +170,29 @@ int launch_gemm_tc(int kind, const void* amap_dev, const uint4* bits, const void
 // chunks[c] .. chunks[c+1]-1.
 int launch_gemm_tc_list(int kind, const TcMat* mats_dev, const int* chunks_dev, int n_tiles, int grid, int* status, cudaStream_t st);
 int gemm_tc_prepare();
+
+// gemm_tc_rows.cu: the same arithmetic with the weight rows on the MMA's M side (tiles of 128 rows x 32 tokens), for
+// token counts between the streaming kernel's and the prefill kernel's.  `amap32` points at a CUtensorMap over the
+// activation's int8 plane with a box of 32 rows x 128 bytes.  Same TcMat, same status word.
+constexpr int GEMM_TCR_TOK_TILE = 32;
+constexpr int GEMM_TCR_ROW_TILE = 128;
+// Measured on B200 (matrices of 17408 x 5120, 5120 x 17408, 12288 x 4096, 1024 x 5120): two passes of the streaming
+// kernel (eight tokens) cost what one pass of this kernel costs for Q1_0, three passes (twelve tokens) for Q2_0, whose
+// streaming kernel is faster; from 65 tokens on the 128-token tiles of the prefill kernel are ahead.
+constexpr int GEMM_TCR_MIN_TOKENS_Q1 = 7;
+constexpr int GEMM_TCR_MIN_TOKENS_Q2 = 12;
+constexpr int GEMM_TCR_MAX_TOKENS = 64;
+inline bool gemm_tcr_wanted(int kind, size_t seq_len) {
+    return seq_len <= (size_t)GEMM_TCR_MAX_TOKENS &&
+           ((kind == KIND_Q1 && seq_len >= (size_t)GEMM_TCR_MIN_TOKENS_Q1) || (kind == KIND_Q2 && seq_len >= (size_t)GEMM_TCR_MIN_TOKENS_Q2));
+}
+int gemm_tcr_tiles(int n_rows, int seq_len);
+void gemm_tcr_fill(TcMat& m, const void* amap32_dev, const uint4* bits, const void* scales, const float* ad, int ld_b, int n_rows,
+                   int nb, int seq_len, float* out, int ld_out, int tile_begin);
+int launch_gemm_tcr(int kind, const void* amap32_dev, const uint4* bits, const void* scales, const float* ad, int ld_b, int n_rows,
+                    int nb, int seq_len, float* out, int ld_out, int sm_count, int* status, cudaStream_t st);
+int launch_gemm_tcr_list(int kind, const TcMat* mats_dev, const int* chunks_dev, int n_tiles, int grid, int* status, cudaStream_t st);
+int gemm_tcr_prepare();
 
 // argmax.cu: lowest index of the largest value (the reference's greedy-sampling reduction).  `scratch` is
 // argmax_scratch_bytes() of zero-initialised device memory owned by the caller, reused by every call on one stream.

@@ -24,9 +24,7 @@
 // a 4-stage shared-memory ring decouples TMA / unpack from the MMA issue.
 // Every wait on an mbarrier is bounded; on expiry the CTA records a status code, stops issuing, drains its
 // outstanding bulk copies, frees its TMEM and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace hb200 {
 
@@ -42,7 +40,6 @@ constexpr int A_BYTES = TOK_TILE * 128;  // 16 KiB
 constexpr int B_BYTES = ROW_TILE * 128;  // 8 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 // What one launch works through: `mats` (device memory, n_tiles tiles in all) or, when mats is null, the one matrix
 // `single`.  With `chunks` ([gridDim.x + 1] tile indices) CTA c owns tiles chunks[c] .. chunks[c+1]-1, a contiguous
@@ -55,79 +52,6 @@ struct TcLaunch {
     TcMat single;
 };
 
-// ---- PTX wrappers -----------------------------------------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false (after recording `code`) if the phase did not complete or the CTA is aborting.
-// BACKOFF_NS > 0 puts the thread to sleep between polls: the roles that wait long (copy producer, unpack, MMA issue)
-// would otherwise spend issue slots that the promotion warps of the same scheduler need.
-template <int BACKOFF_NS = 0>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
-        if (mbar_try(bar, parity)) return true;
-        if ((i & 7) == 7 && *abort_flag) return false;
-        if (BACKOFF_NS > 0) __nanosleep(BACKOFF_NS);
-    }
-    *abort_flag = 1;
-    atomicCAS(status, 0, code);
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-        "l"(map), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(0u)  // p = false: D = A*B, no accumulation
-        : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&v)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                 : "r"(taddr)
-                 : "memory");
-}
-#define HB_R8(v) "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7])
-// Waits for every outstanding tcgen05.ld of this thread.  The loaded registers are listed as read-write operands so
-// that the compiler cannot schedule a use of them (or a spill) ahead of the wait; tc_pin8 gives the same guarantee to
-// further arrays covered by that wait.
-__device__ __forceinline__ void tc_wait_ld8(uint32_t (&v)[8]) { asm volatile("tcgen05.wait::ld.sync.aligned;" : HB_R8(v)::"memory"); }
-__device__ __forceinline__ void tc_pin8(uint32_t (&v)[8]) { asm volatile("" : HB_R8(v)::"memory"); }
-
 
 // Pairs of fp32 lanes, written as two scalar IEEE operations each.  The packed sm_100 forms are not used: ptxas 12.9
 // contracts mul.rn.f32x2 followed by add.rn.f32x2 into a fused multiply-add (the scalar forms with .rn are kept apart),
@@ -136,17 +60,6 @@ __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) { return m
 __device__ __forceinline__ float2 fmul2(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
 __device__ __forceinline__ float2 fadd2(float2 a, float2 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }
 
-// K-major, SWIZZLE_128B shared-memory matrix descriptor: rows of 128 B, 8-row groups 1024 B apart.
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr >> 4) & 0x3FFF);  // start address
-    d |= (uint64_t)1 << 16;                  // leading byte offset (unused for swizzled K-major; canonical value 1)
-    d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                  // descriptor version for sm_100
-    d |= (uint64_t)2 << 61;                  // SWIZZLE_128B
-    return d;
-}
-// kind::i8, D = S32, A and B signed int8, both K-major, M = 128, N = 64.
 constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(ROW_TILE >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
 constexpr int SCALE_SLOTS = 8;  // ring of per-block weight scales (f32); deeper than the tile ring, see the unpack loop
@@ -166,11 +79,6 @@ struct Barriers {
     alignas(16) unsigned char packed[PSLOTS][2048];  // 64 rows x 128 columns of codes: 1 KiB (Q1_0) or 2 KiB (Q2_0)
     alignas(16) unsigned char pscale[PSLOTS][128];   // their f16 scales
 };
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    const uint32_t sa = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
-}
 
 // Tile t of the launch: which matrix, which 128 tokens, which 64 rows.  Tiles of a matrix are numbered with the
 // token tile fastest, so CTAs working side by side read different activation tiles and the same weights.

@@ -26,6 +26,8 @@ struct hb200_act {
     float* sums = nullptr;
     alignas(64) unsigned char qmap[128] = {};  // CUtensorMap over the int8 plane (tcgen05 path), host copy
     void* qmap_dev = nullptr;                  // the same 128 bytes in device memory, where the kernel reads them
+    alignas(64) unsigned char qmap32[128] = {};  // the same plane with a box of 32 rows (few-token tensor-core kernel)
+    void* qmap32_dev = nullptr;
     bool has_qmap = false;
 };
 
