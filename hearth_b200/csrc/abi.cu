@@ -220,9 +220,7 @@ namespace {
 // tensor-core kernel (rows on the MMA's M side) or the prefill tensor-core kernel (tokens on the M side).
 enum DotPath { PATH_DP4A = 0, PATH_TC_ROWS = 1, PATH_TC = 2 };
 DotPath dot_path(const hb200_weight* w, const hb200_act* a, size_t seq_len) {
-    static const char* force = getenv("HB200_FORCE_PATH");
     if (!a->has_qmap || w->nb <= 0 || (w->kind != KIND_Q1 && w->kind != KIND_Q2)) return PATH_DP4A;
-    if (force) return (DotPath)atoi(force);
     if (gemm_tcr_wanted(w->kind, seq_len)) return PATH_TC_ROWS;
     if (gemm_tc_wanted(w->kind, seq_len)) return PATH_TC;
     return PATH_DP4A;
