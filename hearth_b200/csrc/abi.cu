@@ -1140,6 +1140,18 @@ static std::vector<int> balanced_chunks(const std::vector<int>& cost, int grid) 
     return chunks;
 }
 
+extern "C" int hb200_plan_chunks(const int* cost, size_t n_items, int grid, int* chunks) {
+    HB_GUARD_BEGIN
+    if ((!cost && n_items) || !chunks) { set_error("null buffer"); return HB200_ERR_NULL; }
+    if (grid <= 0) { set_error("grid must be positive"); return HB200_ERR_BAD_SHAPE; }
+    for (size_t i = 0; i < n_items; i++)
+        if (cost[i] < 0) { set_error("negative cost"); return HB200_ERR_BAD_SHAPE; }
+    const std::vector<int> c = balanced_chunks(std::vector<int>(cost, cost + n_items), grid);
+    for (int i = 0; i <= grid; i++) chunks[i] = c[i];
+    return HB200_OK;
+    HB_GUARD_END
+}
+
 extern "C" int hb200_batch_seal(hb200_batch_t b) {
     HB_GUARD_BEGIN
     if (!b) { set_error("null batch"); return HB200_ERR_NULL; }

@@ -34,6 +34,7 @@ SIGNATURES = {
     "hb200_block_size": (_sz, [_int]),
     "hb200_block_bytes": (_sz, [_int]),
     "hb200_measure_i8_peak": (_int, [C.POINTER(C.c_double)]),
+    "hb200_plan_chunks": (_int, [C.POINTER(C.c_int), C.c_size_t, _int, C.POINTER(C.c_int)]),
     "hb200_byte_size": (_sz, [_int, _sz]),
     "hb200_selected_kernel": (C.c_char_p, [_int, _sz]),
     "hb200_weight_upload": (_int, [_int, _sz, _sz, _vp, _sz, C.POINTER(_vp)]),

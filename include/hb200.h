@@ -91,6 +91,14 @@ HB200_API int hb200_sm_count(void);
  * TOP/s: the denominator for the prefill kernel's roofline fraction.  No
  * reference counterpart; takes about ten milliseconds. */
 HB200_API int hb200_measure_i8_peak(double *tops);
+/* The split of a work list over persistent CTAs that hb200_batch_seal uses:
+ * n_items items with the given costs, in order, become `grid` contiguous
+ * runs whose largest total cost is as small as contiguity allows;
+ * chunks[c] .. chunks[c+1]-1 are the items of CTA c (chunks has grid + 1
+ * entries, trailing runs may be empty).  Needs no device.  The reference
+ * splits rows evenly over its threads (hearth-llm/src/pool.rs:321-323); here
+ * an item is a whole panel of rows whose cost depends on its matrix. */
+HB200_API int hb200_plan_chunks(const int *cost, size_t n_items, int grid, int *chunks);
 
 /* ---- block geometry ----------------------------------------------------- */
 
