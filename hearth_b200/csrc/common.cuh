@@ -176,10 +176,11 @@ int gemm_tc_prepare();
 // activation's int8 plane with a box of 32 rows x 128 bytes.  Same TcMat, same status word.
 constexpr int GEMM_TCR_TOK_TILE = 32;
 constexpr int GEMM_TCR_ROW_TILE = 128;
-// Measured on B200 (matrices of 17408 x 5120, 5120 x 17408, 12288 x 4096, 1024 x 5120): two passes of the streaming
-// kernel (eight tokens) cost what one pass of this kernel costs for Q1_0, three passes (twelve tokens) for Q2_0, whose
-// streaming kernel is faster; from 65 tokens on the 128-token tiles of the prefill kernel are ahead.
-constexpr int GEMM_TCR_MIN_TOKENS_Q1 = 7;
+// Measured on B200 on whole layer sets in one launch (8B Q1_0: two streaming passes, eight tokens, 1.45 ms against
+// 1.90 ms here; 27B PQ2_0: 4.7 ms against 5.7 ms): up to two full passes of the streaming kernel and a partial one are
+// cheaper than one pass of this kernel, whose time hardly depends on the token count; from 65 tokens on the
+// 128-token tiles of the prefill kernel are ahead.
+constexpr int GEMM_TCR_MIN_TOKENS_Q1 = 11;
 constexpr int GEMM_TCR_MIN_TOKENS_Q2 = 12;
 constexpr int GEMM_TCR_MAX_TOKENS = 64;
 inline bool gemm_tcr_wanted(int kind, size_t seq_len) {

@@ -1,4 +1,4 @@
-// Few-token matmul (batched decode, 5 .. 64 tokens) on the tensor cores with the WEIGHT ROWS on the MMA's M side:
+// Few-token matmul (batched decode, about 11 .. 64 tokens) on the tensor cores with the WEIGHT ROWS on the MMA's M side:
 // tcgen05.mma kind::i8, 128 weight rows = TMEM lanes, 32 tokens = TMEM columns, for Q1_0 and Q2_0 / PQ2_0 / PTQ1_0
 // weights against Q8_0 activations.
 //

@@ -162,6 +162,7 @@ CONFIGS = {
     "c4_pq2_27b_m16": dict(dtype=PQ2_0, shapes=layer_shapes(5120, 17408, 1024), layers=64, seq_len=16),
     "c4_pq2_27b_m32": dict(dtype=PQ2_0, shapes=layer_shapes(5120, 17408, 1024), layers=64, seq_len=32),
     "c4_pq2_27b_m32_2layers": dict(dtype=PQ2_0, shapes=layer_shapes(5120, 17408, 1024), layers=2, seq_len=32),
+    "c2_q1_8b_m8": dict(dtype=Q1_0, shapes=layer_shapes(4096, 12288, 1024), layers=36, seq_len=8),
     "c2_q1_8b_m32": dict(dtype=Q1_0, shapes=layer_shapes(4096, 12288, 1024), layers=36, seq_len=32),
 }
 

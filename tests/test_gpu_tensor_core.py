@@ -1,5 +1,5 @@
 """GPU parity tests for the two tcgen05 (tensor-core) matmuls of Q1_0 / Q2_0 weights: the few-token kernel with the
-weight rows on the MMA's M side (7 .. 64 tokens of Q1_0, 12 .. 64 of Q2_0) and the prefill kernel with the tokens on
+weight rows on the MMA's M side (11 .. 64 tokens of Q1_0, 12 .. 64 of Q2_0) and the prefill kernel with the tokens on
 the M side (more than 64).  Fewer tokens run as passes of the streaming decode kernel; a few such cases are kept
 here on purpose.
 
@@ -27,10 +27,10 @@ def check(got, want, what):
 @pytest.mark.parametrize("n_rows,n_cols,seq_len", [
     (64, 128, 48), (200, 2048, 65), (264, 1152, 128), (1000, 2048, 130), (96, 6144, 49), (8, 256, 300), (520, 2048, 33),
     (130, 1152, 17), (130, 1152, 25), (72, 256, 24), (72, 256, 16),
-    (300, 1152, 5), (300, 1152, 7), (129, 128, 8), (300, 1152, 12), (300, 1152, 13), (128, 2304, 31), (1, 256, 32), (257, 640, 64), (384, 1152, 96), (100, 512, 97),
+    (300, 1152, 5), (300, 1152, 7), (129, 128, 8), (300, 1152, 10), (300, 1152, 11), (300, 1152, 12), (300, 1152, 13), (128, 2304, 31), (1, 256, 32), (257, 640, 64), (384, 1152, 96), (100, 512, 97),
     (64, 128, 4), (700, 4096, 40), (260, 384, 200)])
 def test_tensor_core_matches_oracle(hb, oracle, dtype, n_rows, n_cols, seq_len):
-    min_tokens = 7 if dtype == Q1_0 else 12
+    min_tokens = 11 if dtype == Q1_0 else 12
     name = hb.selected_kernel(dtype, seq_len)
     assert name.startswith("gemm_tcgen05_i8" if seq_len >= min_tokens else "gemv_dp4a")
     assert ("_rows_" in name) == (min_tokens <= seq_len <= 64)
