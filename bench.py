@@ -7,9 +7,15 @@ A step is one pass of the decode (or prefill) layer set: every projection of
 every layer of the named model shape against synthetic Q8_0 activations.  The
 metric is the reference benchmark's own (hearth-llm/examples/benchk.rs:162,
 :198): packed weight bytes streamed per second.  With N > 1 every weight is
-row-sharded over the ranks (rank r holds rows [r*ceil(n/N), ...)) and each step
-ends with an NCCL all-gather of the output slices, so the total work is fixed
-("strong" scaling).  Prints one JSON line on rank 0.
+row-sharded over the ranks (rank r holds rows [r*ceil(n/N), ...)); by default the
+decode kernel itself stores every output into all ranks' buffers over NVLink
+(peer stores and a flag exchange; --gather nccl runs an NCCL all-gather of the
+output slices after the kernel instead), so the total work is fixed ("strong"
+scaling).  What the ranks assemble is compared across ranks and with the CPU
+checker before anything is timed.  The default run also times the other
+workloads of the metric (prefill, the 8B and 1.7B decode sets, the K-quant
+configuration) and reports them under "secondary".  Prints one JSON line on
+rank 0.
 """
 from __future__ import annotations
 
@@ -213,6 +219,187 @@ def run_reference(args, cfg, rank):
 
 # ------------------------------------------------------------------------------------------ GPU arm
 
+GROUP_OF = {"q": 0, "k": 0, "v": 0, "o": 1, "gate": 2, "up": 2, "down": 3}
+FORMAT_NAME = {41: "Q1_0", 43: "Q1_0_G128", 42: "Q2_0", 142: "PQ2_0", 143: "PTQ1_0", 8: "Q8_0", 12: "Q4_K", 14: "Q6_K"}
+NOMINAL_HBM_GBS = 8000.0  # the figure the path's brief quotes its decode target against
+
+# Workloads timed after the headline one and reported under "secondary" (device-timed, inputs resident):
+# the prefill half of the metric, the decode shapes the 70 % target is quoted on, the 1.7B sets, the K-quant
+# configuration at its three token counts, a Q8_0-weight set, and the single 6144 x 2048 matvec.
+SECONDARY_1GPU = ["c2_q1_8b_prefill", "c2_q1_8b_decode", "c2_q2_8b_decode", "c1_q1_1p7b_decode", "c1_q2_1p7b_decode",
+                  "c3_q4k_m1", "c3_q4k_m8", "c3_q4k_m32", "c3_q6k_m1", "c3_q6k_m8", "c3_q6k_m32", "c1_q8_1p7b_decode",
+                  "c4_pq2_27b_m32", "c0_q1_single_x160"]
+SECONDARY_MULTI = ["c4_pq2_27b_m32"]
+
+
+def weight_seed(li: int, ti: int, rank: int) -> int:
+    return 1000 * (li + 1) + 10 * ti + rank
+
+
+class Workload:
+    """One configuration resident on this rank: its row shard of every weight, one activation per input-sharing group
+    of each layer (q|k|v read one vector, o another, gate|up a third, down a fourth, hearth-llm/src/model/mod.rs:527-775)
+    and the recorded batch that writes a packed [M, slice_rows] buffer."""
+
+    def __init__(self, hb, torch, cfg, rank, world, dev):
+        self.hb, self.torch, self.cfg, self.rank, self.world, self.dev = hb, torch, cfg, rank, world, dev
+        M, dtype = cfg["seq_len"], cfg["dtype"]
+        self.M = M
+        self.weights, self.acts, self.act_offset = [], {}, {}
+        self.slice_rows = 0
+        for li in range(cfg["layers"]):
+            for ti, (_, n_rows, n_cols) in enumerate(cfg["shapes"]):
+                lo, hi = shard_rows(n_rows, rank, world)
+                packed = synth.weights_torch(dtype, hi - lo, n_cols, seed=weight_seed(li, ti, rank), device=dev)
+                self.weights.append((hb.Weight.upload_dev(dtype, hi - lo, n_cols, packed), -(-n_rows // world)))
+                del packed
+                self.slice_rows += -(-n_rows // world)
+        torch.cuda.synchronize()
+        self.out_local = torch.zeros((M, self.slice_rows), dtype=torch.float32, device=dev)
+        self.batch = hb.Batch()
+        off, i, x_off = 0, 0, 0
+        for li in range(cfg["layers"]):
+            for ti, (name, n_rows, n_cols) in enumerate(cfg["shapes"]):
+                W, pad_rows = self.weights[i]
+                i += 1
+                key = (li, GROUP_OF.get(name, ti))
+                if W.n_rows > 0:
+                    if key not in self.acts:
+                        self.acts[key] = hb.Act(M, n_cols)
+                        self.act_offset[key] = x_off            # the batch lists inputs in order of first use, 16-byte aligned
+                        x_off = (x_off + M * n_cols + 3) & ~3
+                    self.batch.add(W, self.acts[key], M, self.out_local[:, off:], ld_out=self.slice_rows)
+                off += pad_rows
+        self.batch.seal()
+        assert self.batch.input_floats == x_off, (self.batch.input_floats, x_off)
+        rng = np.random.Generator(np.random.PCG64(4242))
+        self.x_pinned = torch.from_numpy(rng.standard_normal(max(x_off, 1), dtype=np.float32)).pin_memory()
+        self.out_pinned = torch.zeros((M, self.slice_rows), dtype=torch.float32).pin_memory()
+        # uploads and quantizes the activations once, so that device-only steps have their inputs resident
+        self.batch.run_host(self.x_pinned.numpy(), self.out_local, self.out_pinned.numpy())
+
+    def free(self):
+        self.batch.free()
+        for a in self.acts.values():
+            a.free()
+        for W, _ in self.weights:
+            W.free()
+        self.weights, self.acts = [], {}
+        del self.out_local
+        self.torch.cuda.empty_cache()
+
+
+def roofline_of(hb, cfg, ms_per_step, world):
+    """(metric, unit, value, roofline dict) of one device-timed step of cfg."""
+    ab = algorithmic_bytes(cfg)
+    total_alg = ab["weights"] + ab["activations"] + ab["outputs"]
+    kernel = hb.selected_kernel(cfg["dtype"], cfg["seq_len"])
+    if is_prefill(cfg):
+        value = total_ops(cfg) / (ms_per_step * 1e-3) / 1e12
+        tpeak, tsrc = tensor_peak(hb)
+        per_rank = value / world
+        return PREFILL_METRIC, PREFILL_UNIT, value, {
+            "bound": "tensor", "achieved": per_rank, "peak": tpeak, "unit": "TOP/s", "frac": per_rank / tpeak, "traffic": None,
+            "kernel": kernel, "peak_source": tsrc, "ops_per_step": total_ops(cfg),
+            "weight_stream_gbs": ab["weights"] / (ms_per_step * 1e-3) / 1e9}
+    peak, peak_src = measured_peaks()
+    per_rank_alg = total_alg / world
+    achieved = per_rank_alg / (ms_per_step * 1e-3) / 1e9
+    return METRIC, UNIT, ab["weights"] / (ms_per_step * 1e-3) / 1e9, {
+        "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+        "frac_of_nominal_8tbs": achieved / NOMINAL_HBM_GBS, "traffic": None, "kernel": kernel, "peak_source": peak_src,
+        "algorithmic_bytes_per_launch": per_rank_alg}
+
+
+def time_secondary(hb, torch, dist, name, rank, world, dev, stream, steps):
+    """Device-timed steps of one more workload (weights generated, timed, freed).  N > 1: row shards + NCCL gather."""
+    cfg = synth.CONFIGS[name]
+    wl = Workload(hb, torch, cfg, rank, world, dev)
+    out_all = torch.zeros((world * wl.M, wl.slice_rows), dtype=torch.float32, device=dev) if world > 1 else None
+
+    def step():
+        wl.batch.launch(stream)
+        if world > 1:
+            with torch.cuda.stream(stream):
+                dist.all_gather_into_tensor(out_all, wl.out_local)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(3):
+        step()
+    barrier()
+    hb.check_status()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / steps
+    launches = wl.batch.launch_count
+    wl.free()
+    metric, unit, value, roof = roofline_of(hb, cfg, ms, world)
+    ab = algorithmic_bytes(cfg)
+    entry = {"workload": name, "format": FORMAT_NAME.get(cfg["dtype"], str(cfg["dtype"])), "tokens": cfg["seq_len"],
+             "metric": metric, "value": value, "unit": unit, "ms_per_step": ms, "steps": steps, "gpu_launches_per_step": launches,
+             "weight_bytes": ab["weights"], "kernel": roof["kernel"],
+             "roofline": {k: roof[k] for k in ("bound", "achieved", "peak", "unit", "frac") if k in roof},
+             "l2": "per-GPU inputs exceed the 126 MB L2" if ab["weights"] / world > 126e6 else "inputs fit in L2"}
+    if "frac_of_nominal_8tbs" in roof:
+        entry["roofline"]["frac_of_nominal_8tbs"] = roof["frac_of_nominal_8tbs"]
+    if world > 1:
+        entry["gather"] = "NCCL all-gather of output slices"
+    if name.startswith("c0_q1_single_x"):
+        n = cfg["layers"]
+        entry["note"] = (f"the single 6144 x 2048 Q1_0 matvec (1.77 MB, shorter than a launch and L2-resident when repeated) is "
+                         f"timed as one launch over {n} distinct copies of the weight ({ab['weights'] / 1e6:.0f} MB, more than "
+                         f"twice the L2), and reported per matrix")
+        entry["us_per_matrix"] = ms * 1e3 / n
+    return entry
+
+
+def shared_pinned(torch, name, n_floats, rank, world, dist):
+    """One float32 host buffer shared by all ranks of the node (a file in /dev/shm mapped by every process) and
+    page-locked in each of them, so that each rank's readback lands in its own part of ONE host buffer.
+    Returns (numpy array, page-locked?, cleanup)."""
+    import mmap
+    nbytes = max(n_floats, 1) * 4
+    path = os.path.join("/dev/shm", name)
+    if rank == 0:
+        with open(path, "wb") as f:
+            f.truncate(nbytes)
+    if world > 1:
+        dist.barrier()
+    f = open(path, "r+b")
+    mm = mmap.mmap(f.fileno(), nbytes)
+    f.close()
+    arr = np.frombuffer(mm, dtype=np.float32, count=n_floats)
+    rt = torch.cuda.cudart()
+    try:
+        registered = int(rt.cudaHostRegister(arr.ctypes.data, nbytes, 0)) == 0
+    except RuntimeError:
+        registered = False
+
+    def cleanup():
+        if registered:
+            rt.cudaHostUnregister(arr.ctypes.data)
+        if world > 1:
+            dist.barrier()
+        if rank == 0:
+            try:
+                os.unlink(path)
+            except OSError:
+                pass
+    return arr, registered, cleanup
+
+
 def run_ours(args, cfg, rank, world, local_rank):
     import torch
     import torch.distributed as dist
@@ -230,58 +417,28 @@ def run_ours(args, cfg, rank, world, local_rank):
     dtype = cfg["dtype"]
     stream = torch.cuda.Stream(device=dev)
 
-    # ---- resident data: this rank's row shard of every weight, one activation per distinct input width
-    weights, acts = [], {}
-    slice_rows = 0
-    for li in range(cfg["layers"]):
-        for ti, (_, n_rows, n_cols) in enumerate(cfg["shapes"]):
-            lo, hi = shard_rows(n_rows, rank, world)
-            packed = synth.weights_torch(dtype, hi - lo, n_cols, seed=1000 * (li + 1) + 10 * ti + rank, device=dev)
-            weights.append((hb.Weight.upload_dev(dtype, hi - lo, n_cols, packed), -(-n_rows // world)))
-            del packed
-            slice_rows += -(-n_rows // world)
-    torch.cuda.synchronize()
-    # One activation per input-sharing group of each layer, as in the model: q|k|v read one vector, o another,
-    # gate|up a third, down a fourth (hearth-llm/src/model/mod.rs:527-775).
-    group_of = {"q": 0, "k": 0, "v": 0, "o": 1, "gate": 2, "up": 2, "down": 3}
-
-    # outputs: one packed buffer per rank [M, slice_rows]; gathered into [world, M, slice_rows]
-    out_local = torch.zeros((M, slice_rows), dtype=torch.float32, device=dev)
+    wl = Workload(hb, torch, cfg, rank, world, dev)
+    batch, acts, weights, out_local, slice_rows = wl.batch, wl.acts, wl.weights, wl.out_local, wl.slice_rows
+    x_pinned, out_pinned = wl.x_pinned, wl.out_pinned
     out_all = torch.zeros((world * M, slice_rows), dtype=torch.float32, device=dev) if world > 1 else None  # [world][M][slice]
-    batch = hb.Batch()
-    off = 0
-    i = 0
-    for li in range(cfg["layers"]):
-        for ti, (name, n_rows, n_cols) in enumerate(cfg["shapes"]):
-            W, pad_rows = weights[i]
-            i += 1
-            key = (li, group_of.get(name, ti))
-            if key not in acts:
-                acts[key] = hb.Act(M, n_cols)
-            if W.n_rows > 0:
-                batch.add(W, acts[key], M, out_local[:, off:], ld_out=slice_rows)
-            off += pad_rows
-    batch.seal()
-    # all inputs of a step in one pinned host buffer, outputs in another (the end-to-end leg copies both every step)
-    rng = np.random.Generator(np.random.PCG64(4242))
-    x_pinned = torch.from_numpy(rng.standard_normal(batch.input_floats, dtype=np.float32)).pin_memory()
-    out_pinned = torch.zeros((M, slice_rows), dtype=torch.float32).pin_memory()
-    batch.run_host(x_pinned.numpy(), out_local, out_pinned.numpy())  # uploads and quantizes the activations once
     launches_per_step = batch.launch_count
 
     # Fused gather (N > 1, up to four tokens): a second recording of the same ops whose outputs go straight into
-    # every rank's assembled [M, sum of n_rows] buffer.
+    # every rank's assembled [M, sum of n_rows] buffer.  Every buffer holds two such areas, written by alternate
+    # launches, so a rank that runs one step ahead never overwrites what a slower rank still reads.
     fused = None
     use_fused = world > 1 and args.gather == "fused" and M <= 4
+    full_cols = sum(n for _, n, _ in cfg["shapes"]) * cfg["layers"]
+    area = (M * full_cols + 3) & ~3
     if use_fused:
-        full_cols = sum(n for _, n, _ in cfg["shapes"]) * cfg["layers"]
-        mine = hb.PeerBuffer.alloc(M * full_cols)
+        mine = hb.PeerBuffer.alloc(2 * area)
         handles = [None] * world
         dist.all_gather_object(handles, mine.handle)
-        bufs = [mine if r == rank else hb.PeerBuffer.open(handles[r], M * full_cols) for r in range(world)]
-        full_local = mine.tensor(dev).view(M, full_cols)
+        bufs = [mine if r == rank else hb.PeerBuffer.open(handles[r], 2 * area) for r in range(world)]
+        full_both = mine.tensor(dev)
+        full_area0 = full_both[:M * full_cols].view(M, full_cols)
         fused = hb.Batch()
-        fused.set_peers(rank, bufs, wait=True)
+        fused.set_peers(rank, bufs, wait=True, area_floats=area)
         coff, i = 0, 0
         for li in range(cfg["layers"]):
             for ti, (name, n_rows, n_cols) in enumerate(cfg["shapes"]):
@@ -289,10 +446,14 @@ def run_ours(args, cfg, rank, world, local_rank):
                 i += 1
                 lo, hi = shard_rows(n_rows, rank, world)
                 if hi > lo:
-                    fused.add(W, acts[(li, group_of.get(name, ti))], M, full_local[:, coff + lo:], ld_out=full_cols)
+                    fused.add(W, acts[(li, GROUP_OF.get(name, ti))], M, full_area0[:, coff + lo:], ld_out=full_cols)
                 coff += n_rows
         fused.seal()
         launches_per_step = fused.launch_count
+
+        def full_latest():
+            a = fused.peer_area
+            return full_both[a * area:a * area + M * full_cols].view(M, full_cols)
 
     def step_nccl():
         batch.launch(stream)
@@ -314,6 +475,75 @@ def run_ours(args, cfg, rank, world, local_rank):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
+
+    # ---- N > 1: what the ranks assembled is checked before anything is timed.  Every rank must hold the same bits,
+    # and rank 0 recomputes whole row shards of three matrices (first, middle and last rank's) with the CPU checker
+    # from the seeds the shards were generated with.
+    multi_check, assembled_host = None, None
+    if world > 1:
+        hb.check_status()
+        if use_fused:
+            mine_full = full_latest().clone()
+        else:
+            g = out_all.view(world, M, slice_rows)
+            parts, off = [], 0
+            for li in range(cfg["layers"]):
+                for ti, (name, n_rows, n_cols) in enumerate(cfg["shapes"]):
+                    chunk = -(-n_rows // world)
+                    for r in range(world):
+                        lo, hi = shard_rows(n_rows, r, world)
+                        if hi > lo:
+                            parts.append(g[r][:, off:off + (hi - lo)])
+                    off += chunk
+            mine_full = torch.cat(parts, dim=1).contiguous()
+        ref_full = mine_full.clone()
+        dist.broadcast(ref_full, 0)
+        diff = (mine_full.view(torch.int32) != ref_full.view(torch.int32)).sum().to(torch.float64).reshape(1)
+        nan_count = torch.isnan(mine_full).sum().to(torch.float64).reshape(1)
+        dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+        dist.all_reduce(nan_count, op=dist.ReduceOp.MAX)
+        identical = float(diff.item()) == 0.0 and float(nan_count.item()) == 0.0
+        rows_checked, oracle_ok = 0, True
+        if rank == 0 and dtype not in (12, 14):
+            from oracle import oracle as O  # the CPU checker, used as a checker
+            O.build()
+            n_l, n_t = cfg["layers"], len(cfg["shapes"])
+            picks = [(0, min(1, n_t - 1), 0), (n_l // 2, min(4, n_t - 1), world // 2), (n_l - 1, n_t - 1, world - 1)]
+            col_of = {}
+            coff = 0
+            for li in range(n_l):
+                for ti, (_, n_rows, _) in enumerate(cfg["shapes"]):
+                    col_of[(li, ti)] = coff
+                    coff += n_rows
+            host_full = assembled_host = mine_full.cpu().numpy()
+            xh = x_pinned.numpy()
+            for li, ti, r in picks:
+                name, n_rows, n_cols = cfg["shapes"][ti]
+                lo, hi = shard_rows(n_rows, r, world)
+                if hi <= lo:
+                    continue
+                hi = min(hi, lo + 512)
+                w = synth.weights_torch(dtype, shard_rows(n_rows, r, world)[1] - lo, n_cols, seed=weight_seed(li, ti, r), device=dev)
+                w = w.cpu().numpy().reshape(-1, synth.row_bytes(dtype, n_cols))[:hi - lo]
+                xo = wl.act_offset[(li, GROUP_OF.get(name, ti))]
+                q8 = O.quantize_q8_0(xh[xo:xo + M * n_cols].reshape(M, n_cols))
+                want = O.dot_rows_batched(dtype, np.ascontiguousarray(w), q8, hi - lo, n_cols)
+                c0 = col_of[(li, ti)] + lo
+                got = np.ascontiguousarray(host_full[:, c0:c0 + (hi - lo)])
+                oracle_ok = oracle_ok and bool((got.view(np.uint32) == want.view(np.uint32)).all())
+                rows_checked += hi - lo
+        flag = torch.tensor([1.0 if oracle_ok else 0.0, float(rows_checked)], dtype=torch.float64, device=dev)
+        dist.broadcast(flag, 0)
+        oracle_ok, rows_checked = bool(flag[0].item() > 0), int(flag[1].item())
+        multi_check = {"ranks_identical": identical, "oracle_rows_checked": rows_checked, "oracle_bits_equal": oracle_ok,
+                       "assembled_floats": int(mine_full.numel())}
+        del mine_full, ref_full
+        if not identical or not oracle_ok:
+            if rank == 0:
+                print(json.dumps({"error": "multi-GPU value check failed", "multi_gpu_check": multi_check}))
+            dist.barrier()
+            raise SystemExit(3)
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -362,27 +592,29 @@ def run_ours(args, cfg, rank, world, local_rank):
     ms, ms_nccl = float(t[0].item()), (float(t[1].item()) if ms_nccl else None)
     ms_per_step = ms / args.steps
 
-    # ---- end to end through the host-buffer entry point: every step copies all inputs from pinned host memory,
-    # quantizes, runs the recorded batch, (all-gathers) and copies the results back to pinned host memory.
-    e2e_ms, h2d, d2h = None, 0, 0
+    # ---- end to end through the host-buffer entry point: every step copies this rank's inputs from pinned host
+    # memory, quantizes, runs the recorded batch and copies the results back to pinned host memory.  The consumer is
+    # the host, so with N > 1 no device-side gather is needed: every rank reads back only the rows it computed, into
+    # its own part of ONE page-locked host buffer shared by all ranks ([rank][M][slice]); the step is complete when
+    # every rank's part has landed (barrier at the end of the timed region, maximum over ranks).
+    e2e_ms, h2d, d2h, e2e_note = None, 0, 0, None
     if not args.quick:
-        xh, oh = x_pinned.numpy(), out_pinned.numpy()
-        out_all_pinned = torch.zeros((world * M, slice_rows), dtype=torch.float32).pin_memory() if world > 1 else None
-        empty = np.zeros(0, dtype=np.float32)
-        full_pinned = torch.zeros((M, full_cols), dtype=torch.float32).pin_memory() if use_fused else None
+        xh = x_pinned.numpy()
+        cleanup = None
+        if world == 1:
+            oh = out_pinned.numpy()
+        else:
+            shared, registered, cleanup = shared_pinned(torch, f"hb200_bench_{os.environ.get('MASTER_PORT', '0')}",
+                                                        world * M * slice_rows, rank, world, dist)
+            oh = shared[rank * M * slice_rows:(rank + 1) * M * slice_rows].reshape(M, slice_rows)
+            e2e_note = ("every rank reads back its own row slices into its part of one shared page-locked host buffer"
+                        if registered else "shared host buffer could not be page-locked; pageable copies")
 
         def e2e_step():
-            if world == 1:
-                batch.run_host(xh, out_local, oh)
-            elif use_fused:
-                fused.run_host(xh, full_local, full_pinned.numpy())  # the kernel itself assembles every rank's outputs
-            else:
-                batch.run_host(xh, out_local, empty)           # inputs in, compute; results stay on the device
-                dist.all_gather_into_tensor(out_all, out_local)
-                out_all_pinned.copy_(out_all, non_blocking=True)
-                torch.cuda.synchronize()
+            batch.run_host(xh, out_local, oh)
         e2e_steps = max(1, min(args.steps, 20 if M <= 4 else 3))
-        e2e_step()
+        for _ in range(2):
+            e2e_step()
         barrier()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
@@ -393,41 +625,56 @@ def run_ours(args, cfg, rank, world, local_rank):
         if world > 1:
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e2e_ms = float(tt.item()) / e2e_steps * 1e3
-        h2d = batch.input_floats * 4
-        d2h = (full_pinned.numel() if use_fused else (out_all_pinned.numel() if world > 1 else out_pinned.numel())) * 4
+        # bytes summed over the ranks: every rank uploads every input (activations are replicated), each output once
+        counts = torch.tensor([float(batch.input_floats * 4), float(M * slice_rows * 4)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(counts, op=dist.ReduceOp.SUM)
+        h2d, d2h = int(counts[0].item()), int(counts[1].item())
+        if world > 1:
+            barrier()
+            if rank == 0 and assembled_host is not None:
+                # the shared host buffer must now hold, rank by rank, the rows the device-side assembly holds
+                same, off, col = True, 0, 0
+                parts = shared.reshape(world, M, slice_rows)
+                for li in range(cfg["layers"]):
+                    for ti, (name, n_rows, n_cols) in enumerate(cfg["shapes"]):
+                        for r in range(world):
+                            lo, hi = shard_rows(n_rows, r, world)
+                            if hi > lo:
+                                same = same and bool((parts[r][:, off:off + (hi - lo)].view(np.uint32) ==
+                                                      assembled_host[:, col + lo:col + hi].view(np.uint32)).all())
+                        off += -(-n_rows // world)
+                        col += n_rows
+                multi_check["host_buffer_equals_device_assembly"] = same
+            cleanup()
+
+    # ---- the other workloads of the metric
+    secondary = []
+    if not args.quick and not args.no_secondary and args.workload == DEFAULT_WORKLOAD:
+        for name in (SECONDARY_1GPU if world == 1 else SECONDARY_MULTI):
+            c2 = synth.CONFIGS[name]
+            k = 3 if c2["seq_len"] >= 128 else (10 if c2["seq_len"] > 4 else 20)
+            try:
+                secondary.append(time_secondary(hb, torch, dist, name, rank, world, dev, stream, k))
+            except Exception as e:  # noqa: BLE001 - one failed extra workload must not lose the headline line
+                secondary.append({"workload": name, "error": f"{type(e).__name__}: {e}"})
 
     if rank == 0:
         ab = algorithmic_bytes(cfg)
-        total_alg = ab["weights"] + ab["activations"] + ab["outputs"]
-        value = ab["weights"] / (ms_per_step * 1e-3) / 1e9
-        peak, peak_src = measured_peaks()
-        per_rank_alg = total_alg / world
-        achieved = per_rank_alg / (ms_per_step * 1e-3) / 1e9
-        metric, unit = METRIC, UNIT
-        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "kernel": hb.selected_kernel(dtype, M), "peak_source": peak_src,
-                "algorithmic_bytes_per_launch": per_rank_alg}
+        metric, unit, value, roof = roofline_of(hb, cfg, ms_per_step, world)
         if dtype in (42, 142) and M <= 4:
             # dram__bytes_read + dram__bytes_write of gemv_dp4a_kernel<Q2_0> from the ncu capture summarised in
             # profiles/gemv_dp4a_q2_0__c1_1p7b_decode.md (1.7B layer set, 1.008 x its algorithmic bytes), scaled to this
             # launch by algorithmic bytes: every launch streams each weight byte exactly once.
-            roof["traffic"] = 1.008 * per_rank_alg
+            roof["traffic"] = 1.008 * roof["algorithmic_bytes_per_launch"]
             roof["traffic_source"] = "ncu capture of the same kernel on the 1.7B layer set, scaled by algorithmic bytes"
-        if is_prefill(cfg):
-            metric, unit = PREFILL_METRIC, PREFILL_UNIT
-            value = total_ops(cfg) / (ms_per_step * 1e-3) / 1e12
-            tpeak, tsrc = tensor_peak(hb)
-            per_rank_tops = value / world
-            roof = {"bound": "tensor", "achieved": per_rank_tops, "peak": tpeak, "unit": "TOP/s", "frac": per_rank_tops / tpeak,
-                    "traffic": None, "kernel": hb.selected_kernel(dtype, M), "peak_source": tsrc,
-                    "ops_per_step": total_ops(cfg), "weight_stream_gbs": ab["weights"] / (ms_per_step * 1e-3) / 1e9}
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "int8 x {1,2}-bit -> int32, fp32 scales", "data": "synthetic",
-            "config": {"workload": args.workload, "format": {41: "Q1_0", 43: "Q1_0_G128", 42: "Q2_0", 142: "PQ2_0", 143: "PTQ1_0", 8: "Q8_0", 12: "Q4_K", 14: "Q6_K"}.get(dtype, str(dtype)),
+            "config": {"workload": args.workload, "format": FORMAT_NAME.get(dtype, str(dtype)),
                        "tokens": M, "layers": cfg["layers"], "matrices_per_step": cfg["layers"] * len(cfg["shapes"]),
-                       "weight_bytes": ab["weights"], "parallelism": f"rows/{world}" + ((" + outputs stored to all ranks from the kernel (peer stores, flag exchange)" if use_fused
+                       "weight_bytes": ab["weights"], "parallelism": f"rows/{world}" + ((" + outputs stored to all ranks from the kernel (peer stores, flag exchange, two output areas)" if use_fused
                                                                 else " + NCCL all-gather of output slices") if world > 1 else ""),
                        "l2": "per-GPU inputs exceed the 126 MB L2" if ab["weights"] / world > 126e6 else "inputs fit in L2",
                        "launch": "one recorded batch (work list) per step"},
@@ -435,11 +682,17 @@ def run_ours(args, cfg, rank, world, local_rank):
             "clocks": clocks,
             "roofline": roof,
             "e2e": ({"value": (total_ops(cfg) / (e2e_ms * 1e-3) / 1e12) if is_prefill(cfg) else ab["weights"] / (e2e_ms * 1e-3) / 1e9, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                     "ms_per_step": e2e_ms, "call": "hb200_batch_run_host: the step's inputs up, list quantize, recorded batch, every output back; pinned host buffers; single-token steps run as eight pipelined runs (upload, compute and readback streams)"} if e2e_ms else None),
+                     "ms_per_step": e2e_ms, "bytes_counted": "summed over ranks",
+                     "call": "hb200_batch_run_host on every rank: the step's inputs up, list quantize, recorded batch, the rank's own outputs back; pinned host buffers; single-token steps run as eight pipelined runs (upload, compute and readback streams)"
+                             + ("; " + e2e_note if e2e_note else "")} if e2e_ms else None),
         }
+        if multi_check:
+            line["multi_gpu_check"] = multi_check
         if ms_nccl:
             line["nccl_allgather_variant"] = {"ms_per_step": ms_nccl / args.steps,
                                               "value": ab["weights"] / (ms_nccl / args.steps * 1e-3) / 1e9, "unit": UNIT}
+        if secondary:
+            line["secondary"] = secondary
         if world == 1 and not args.no_cpu and not args.quick:
             arm = CpuArm(cfg, 0, 1)
             t0 = time.perf_counter()
@@ -477,6 +730,7 @@ def main():
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: 'fused' stores every output into all ranks' buffers from the kernel (peer stores + flag "
                          "exchange); 'nccl' runs an all-gather of the output slices after the kernel")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the extra workloads reported under 'secondary'")
     ap.add_argument("--quick", action="store_true",
                     help="kernel timing only: no clock-sampling burst, no end-to-end leg, no CPU leg (for profiler runs)")
     args = ap.parse_args()

@@ -54,6 +54,28 @@ def selected_kernel(dtype: int, seq_len: int = 1) -> str:
     return _l.load().hb200_selected_kernel(dtype, seq_len).decode()
 
 
+def _text_call(fn, dtypes) -> str:
+    arr = (C.c_int * len(dtypes))(*dtypes)
+    need = C.c_size_t()
+    rc = fn(arr, len(dtypes), None, 0, C.byref(need))
+    if rc not in (0, -8):
+        check(rc)
+    buf = C.create_string_buffer(need.value + 1)
+    check(fn(arr, len(dtypes), buf, need.value + 1, C.byref(need)))
+    return buf.value.decode()
+
+
+def dispatch_report(dtypes) -> dict:
+    """hearth_quant::dispatch_report (hearth-quant/src/lib.rs:449-473): kernels per weight format and token range."""
+    import json
+    return json.loads(_text_call(_l.load().hb200_dispatch_report, list(dtypes)))
+
+
+def dispatch_banner(dtypes) -> str:
+    """DispatchReport::banner (hearth-quant/src/lib.rs:438-447)."""
+    return _text_call(_l.load().hb200_dispatch_banner, list(dtypes))
+
+
 def _np_ptr(a: np.ndarray) -> C.c_void_p:
     assert a.flags["C_CONTIGUOUS"]
     return C.c_void_p(a.ctypes.data)
@@ -405,11 +427,17 @@ class Batch:
         check(_l.load().hb200_batch_add(self._h, w._h, a._h, seq_len, C.c_void_p(out_dev.data_ptr()),
                                         ld_out if ld_out is not None else w.n_rows))
 
-    def set_peers(self, my_rank: int, buffers: list, wait: bool = True) -> None:
-        """Row-sharded run: buffers[r] is rank r's PeerBuffer (local or opened); outputs are stored into all of them."""
+    def set_peers(self, my_rank: int, buffers: list, wait: bool = True, area_floats: int = 0) -> None:
+        """Row-sharded run: buffers[r] is rank r's PeerBuffer (local or opened); outputs are stored into all of them.
+        area_floats > 0: every buffer holds two output areas that far apart, written by alternate launches."""
         arr = (C.c_void_p * len(buffers))(*[C.c_void_p(b.ptr) for b in buffers])
-        check(_l.load().hb200_batch_set_peers(self._h, len(buffers), my_rank, arr, 1 if wait else 0))
+        check(_l.load().hb200_batch_set_peers(self._h, len(buffers), my_rank, arr, area_floats * 4, 1 if wait else 0))
         self._keep.append(buffers)
+
+    @property
+    def peer_area(self) -> int:
+        """Index (0 or 1) of the output area the latest launch wrote."""
+        return int(_l.load().hb200_batch_peer_area(self._h))
 
     def seal(self) -> None:
         check(_l.load().hb200_batch_seal(self._h))
@@ -459,8 +487,13 @@ class PeerBuffer:
         return cls(int(p.value), n_floats, None, False)
 
     def tensor(self, device):
-        """The output area as a torch float32 tensor (no copy)."""
+        """The output area(s) as a torch float32 tensor (no copy)."""
         return _as_torch_f32(self.ptr, self.n_floats, device)
+
+    def flags(self, device):
+        """The eight epoch flags of the control block in front of the output area (int32, no copy)."""
+        import torch
+        return _as_torch_f32(self.ptr - 512, 8, device).view(torch.int32)
 
     def close(self) -> None:
         if self.ptr:

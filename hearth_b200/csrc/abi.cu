@@ -35,6 +35,7 @@ void set_error(const char* fmt, ...) {
     va_end(ap);
     g_last_error = buf;
 }
+int bound_device();
 }  // namespace hb200
 
 #define HB_GUARD_BEGIN try {
@@ -88,6 +89,7 @@ struct hb200_batch {
     int q_max_chunks = 0, q_max_seq = 0, n_qacts = 0;
     bool has_kquant_inputs = false;
     PeerTable peers = {};   // n > 1: outputs go to every rank's buffer
+    size_t peer_area_floats = 0;  // two output areas this far apart, written in turn (0: one area)
     int epoch = 0;
     bool sealed = false;
     // Pipelined host path: the ops in the order they were added, and sub-batches over contiguous runs of them, each
@@ -117,7 +119,8 @@ struct Context {
     size_t d_in_bytes = 0;
     uint8_t* d_out = nullptr;
     size_t d_out_bytes = 0;
-    hb200_act_t act = nullptr;
+    hb200_act_t act = nullptr;                // the one in use, an entry of `acts`
+    std::map<size_t, hb200_act_t> acts;       // by width
     int* d_status = nullptr;  // device word set by kernels whose bounded waits expire
     void* d_argmax = nullptr;  // ticket + partial results of the argmax kernel, then one result word
     cudaStream_t copy_in = nullptr, copy_out = nullptr;  // the pipelined host path: uploads and readbacks beside the compute stream
@@ -263,15 +266,34 @@ int check_device_status() {
     return 0;
 }
 
+// The activation the host-buffer calls stage their input in: one per width, kept for the life of the context (a
+// model alternates between a handful of widths - d_model, the FFN width - so nothing is allocated or freed after the
+// first call of each), replaced only when a call brings more tokens than it holds.
 int ensure_ctx_act(size_t seq_len, size_t n_cols) {
     if (g_ctx.act && g_ctx.act->n_cols == n_cols && g_ctx.act->max_seq >= seq_len) return 0;
-    if (g_ctx.act) { hb200_act_free(g_ctx.act); g_ctx.act = nullptr; }
-    return hb200_act_create(seq_len, n_cols, &g_ctx.act);
+    g_ctx.act = nullptr;
+    auto it = g_ctx.acts.find(n_cols);
+    if (it != g_ctx.acts.end() && it->second->max_seq >= seq_len) { g_ctx.act = it->second; return 0; }
+    if (it != g_ctx.acts.end()) { hb200_act_free(it->second); g_ctx.acts.erase(it); }
+    if (g_ctx.acts.size() >= 16) {  // a caller cycling through many widths: keep the cache bounded
+        for (auto& kv : g_ctx.acts) hb200_act_free(kv.second);
+        g_ctx.acts.clear();
+    }
+    hb200_act_t fresh = nullptr;
+    const int rc = hb200_act_create(seq_len, n_cols, &fresh);
+    if (rc) return rc;
+    g_ctx.acts[n_cols] = fresh;
+    g_ctx.act = fresh;
+    return 0;
 }
 
 }  // namespace
 
 // --------------------------------------------------------------- lifecycle --
+
+namespace hb200 {
+int bound_device() { return g_ctx.ready ? g_ctx.device : -1; }
+}  // namespace hb200
 
 extern "C" int hb200_init(int device) {
     HB_GUARD_BEGIN
@@ -327,7 +349,9 @@ extern "C" int hb200_shutdown(void) {
     if (!g_ctx.ready) return HB200_OK;
     cudaSetDevice(g_ctx.device);
     cudaDeviceSynchronize();
-    if (g_ctx.act) { hb200_act_free(g_ctx.act); g_ctx.act = nullptr; }
+    for (auto& kv : g_ctx.acts) hb200_act_free(kv.second);
+    g_ctx.acts.clear();
+    g_ctx.act = nullptr;
     if (g_ctx.d_in) cudaFree(g_ctx.d_in);
     if (g_ctx.d_out) cudaFree(g_ctx.d_out);
     if (g_ctx.d_status) cudaFree(g_ctx.d_status);
@@ -392,6 +416,107 @@ extern "C" const char* hb200_selected_kernel(int dtype, size_t seq_len) {
         case KIND_Q6K: return "kquant_gemv_q6_k_f32";
         default: return "none";
     }
+}
+
+// hearth_quant::dispatch_report (hearth-quant/src/lib.rs:449-473): for every distinct format of the list, the runs
+// of token counts served by one kernel, found by asking hb200_selected_kernel (the last run is open-ended).
+namespace {
+const char* dtype_name(int dtype) {  // GgmlDType::name (hearth-gguf/src/ggml.rs:178-224)
+    switch (dtype) {
+        case HB200_Q8_0: return "Q8_0";
+        case HB200_Q4_K: return "Q4_K";
+        case HB200_Q6_K: return "Q6_K";
+        case HB200_Q1_0: return "Q1_0";
+        case HB200_Q2_0: return "Q2_0";
+        case HB200_Q1_0_G128: case HB200_Q1_0_G128_LEGACY: return "Q1_0_G128";
+        case HB200_PQ2_0: return "PQ2_0";
+        case HB200_PTQ1_0: return "PTQ1_0";
+        default: return nullptr;
+    }
+}
+struct KernelRun { size_t lo, hi; const char* kernel; };  // hi == 0: open-ended
+std::vector<KernelRun> kernel_runs(int dtype) {
+    std::vector<KernelRun> runs;
+    const size_t probe_to = (size_t)GEMM_TCR_MAX_TOKENS + 2;  // beyond the last threshold nothing changes
+    for (size_t m = 1; m <= probe_to; m++) {
+        const char* k = hb200_selected_kernel(dtype, m);
+        if (runs.empty() || strcmp(runs.back().kernel, k) != 0) runs.push_back({m, m, k});
+        else runs.back().hi = m;
+    }
+    runs.back().hi = 0;
+    return runs;
+}
+std::vector<int> distinct_formats(const int* dtypes, size_t n) {
+    std::vector<int> out;
+    for (size_t i = 0; i < n; i++) {
+        const char* nm = dtype_name(dtypes[i]);
+        if (!nm || kind_of(dtypes[i]) == KIND_NONE) continue;
+        bool seen = false;
+        for (int d : out) seen = seen || strcmp(dtype_name(d), nm) == 0;
+        if (!seen) out.push_back(dtypes[i]);
+    }
+    return out;
+}
+std::string lower(const char* s) {
+    std::string r(s);
+    for (char& c : r) if (c >= 'A' && c <= 'Z') c = (char)(c - 'A' + 'a');
+    return r;
+}
+int emit_text(const std::string& text, char* buf, size_t cap, size_t* needed) {
+    if (needed) *needed = text.size();
+    if (!buf || cap < text.size() + 1) {
+        set_error("text of %zu bytes does not fit a buffer of %zu", text.size() + 1, cap);
+        return HB200_ERR_TOO_LARGE;
+    }
+    memcpy(buf, text.c_str(), text.size() + 1);
+    return HB200_OK;
+}
+std::string device_name() {
+    if (!g_ctx.ready) return "none";
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, g_ctx.device) != cudaSuccess) return "unknown";
+    return prop.name;
+}
+std::string range_text(const KernelRun& r) {
+    char t[48];
+    if (r.hi == 0) snprintf(t, sizeof(t), "%zu+", r.lo);
+    else if (r.hi == r.lo) snprintf(t, sizeof(t), "%zu", r.lo);
+    else snprintf(t, sizeof(t), "%zu-%zu", r.lo, r.hi);
+    return t;
+}
+}  // namespace
+
+extern "C" int hb200_dispatch_report(const int* dtypes, size_t n_dtypes, char* json, size_t cap, size_t* needed) {
+    HB_GUARD_BEGIN
+    if (!dtypes && n_dtypes) { set_error("null dtype list"); return HB200_ERR_NULL; }
+    std::string js = "{\"device\": \"" + device_name() + "\", \"sm\": \"" + (g_ctx.ready ? "10.0" : "none") + "\", \"sm_count\": " +
+                     std::to_string(g_ctx.ready ? g_ctx.sm_count : 0) + ", \"kernels\": {";
+    bool first = true;
+    for (int d : distinct_formats(dtypes, n_dtypes)) {
+        js += std::string(first ? "" : ", ") + "\"" + lower(dtype_name(d)) + "\": [";
+        first = false;
+        const std::vector<KernelRun> runs = kernel_runs(d);
+        for (size_t i = 0; i < runs.size(); i++)
+            js += std::string(i ? ", " : "") + "{\"tokens\": \"" + range_text(runs[i]) + "\", \"kernel\": \"" + runs[i].kernel + "\"}";
+        js += "]";
+    }
+    js += "}}";
+    return emit_text(js, json, cap, needed);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_dispatch_banner(const int* dtypes, size_t n_dtypes, char* text, size_t cap, size_t* needed) {
+    HB_GUARD_BEGIN
+    if (!dtypes && n_dtypes) { set_error("null dtype list"); return HB200_ERR_NULL; }
+    std::string b = "[kernel]";
+    for (int d : distinct_formats(dtypes, n_dtypes)) {
+        b += std::string(" ") + dtype_name(d) + "=";
+        const std::vector<KernelRun> runs = kernel_runs(d);
+        for (size_t i = 0; i < runs.size(); i++) b += std::string(i ? "," : "") + runs[i].kernel + "(" + range_text(runs[i]) + ")";
+    }
+    b += " . " + device_name() + " . " + (g_ctx.ready ? "sm_100 . " + std::to_string(g_ctx.sm_count) + " SMs" : "no device bound");
+    return emit_text(b, text, cap, needed);
+    HB_GUARD_END
 }
 
 // ----------------------------------------------------------------- weights --
@@ -556,11 +681,15 @@ extern "C" int hb200_weight_info(hb200_weight_t w, int* dtype, size_t* n_rows, s
 
 extern "C" int hb200_act_create(size_t max_seq_len, size_t n_cols, hb200_act_t* out) {
     HB_GUARD_BEGIN
-    int rc = need_ctx();
-    if (rc) return rc;
     if (!out) { set_error("null output handle"); return HB200_ERR_NULL; }
     if (n_cols == 0 || max_seq_len == 0) { set_error("activation of %zu x %zu", max_seq_len, n_cols); return HB200_ERR_BAD_SHAPE; }
-    if (n_cols > (1u << 24) || max_seq_len > (1u << 20)) { set_error("activation %zu x %zu too large", max_seq_len, n_cols); return HB200_ERR_TOO_LARGE; }
+    // the per-token kernels put the token index in gridDim.y
+    if (n_cols > (1u << 24) || max_seq_len > HB200_MAX_SEQ_LEN) {
+        set_error("activation %zu x %zu too large (at most %d tokens of %u columns)", max_seq_len, n_cols, HB200_MAX_SEQ_LEN, 1u << 24);
+        return HB200_ERR_TOO_LARGE;
+    }
+    int rc = need_ctx();
+    if (rc) return rc;
     hb200_act* a = new hb200_act();
     a->max_seq = max_seq_len;
     a->n_cols = n_cols;
@@ -1319,17 +1448,23 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
     if (!b) { set_error("null batch"); return HB200_ERR_NULL; }
     if (!b->sealed) { set_error("batch is not sealed"); return HB200_ERR_BAD_SHAPE; }
     cudaStream_t st = (cudaStream_t)stream;
-    for (const BatchGroup& g : b->groups)
-    {
-        PeerTable pt = b->peers;
-        if (pt.n > 1) {
-            pt.epoch = ++b->epoch;
-            pt.status = g_ctx.d_status;
-        }
+    // A peer launch is one epoch, however many kernels it takes: they run in stream order, each makes its peer stores
+    // visible before it ends, and the last one alone runs the flag exchange.  A rank whose shard is empty still
+    // publishes, so that the epochs of all ranks advance together.
+    PeerTable pt = b->peers;
+    if (pt.n > 1) {
+        pt.epoch = ++b->epoch;
+        pt.status = g_ctx.d_status;
+        pt.area_off = b->peer_area_floats ? (long long)((pt.epoch - 1) & 1) * (long long)b->peer_area_floats : 0;
+    }
+    for (size_t gi = 0; gi < b->groups.size(); gi++) {
+        const BatchGroup& g = b->groups[gi];
+        pt.publish = (gi + 1 == b->groups.size()) ? 1 : 0;
         if ((rc = launch_gemv_dp4a(g.kind, g.m, false, g.ops_dev, g.items_dev, g.chunks_dev, g.grid, g.n_items, nullptr, st,
                                    pt.n > 1 ? &pt : nullptr)))
             return rc;
     }
+    if (pt.n > 1 && b->groups.empty() && (rc = launch_peer_publish(pt, st))) return rc;
     for (const hb200_batch::TcGroup& g : b->tc_groups)
         if ((rc = (g.rows ? launch_gemm_tcr_list : launch_gemm_tc_list)(g.kind, g.mats_dev, g.chunks_dev, g.n_tiles, g.grid, g_ctx.d_status, st)))
             return rc;
@@ -1390,6 +1525,7 @@ extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const 
                                     cudaMemcpyDeviceToDevice, st));
     if ((rc = launch_quantize_q8_0_list(b->qdescs_dev, b->n_qacts, b->q_max_chunks, b->q_max_seq, st))) return rc;
     if ((rc = hb200_batch_launch(b, st))) return rc;
+    if (b->peers.n > 1 && b->peer_area_floats) out_dev_base += (size_t)((b->epoch - 1) & 1) * b->peer_area_floats;
     if (out_floats) HB_CUDA(cudaMemcpyAsync(out_host, out_dev_base, out_floats * sizeof(float), cudaMemcpyDeviceToHost, st));
     HB_CUDA(cudaStreamSynchronize(st));
     if (!b->tensor.empty() || !b->tensor_rows.empty()) return check_device_status();
@@ -1478,7 +1614,7 @@ extern "C" int hb200_peer_close(void* data_dev) {
     HB_GUARD_END
 }
 
-extern "C" int hb200_batch_set_peers(hb200_batch_t b, int n_ranks, int my_rank, void* const* data, int wait) {
+extern "C" int hb200_batch_set_peers(hb200_batch_t b, int n_ranks, int my_rank, void* const* data, size_t area_bytes, int wait) {
     HB_GUARD_BEGIN
     if (!b || !data) { set_error("null argument"); return HB200_ERR_NULL; }
     if (b->sealed) { set_error("set the peers before sealing the batch"); return HB200_ERR_BAD_SHAPE; }
@@ -1491,10 +1627,17 @@ extern "C" int hb200_batch_set_peers(hb200_batch_t b, int n_ranks, int my_rank, 
         if (!data[r]) { set_error("null buffer for rank %d", r); return HB200_ERR_NULL; }
         pt.data[r] = static_cast<float*>(data[r]);
     }
+    if (area_bytes % 16) { set_error("area_bytes %zu is not a multiple of 16", area_bytes); return HB200_ERR_BAD_SHAPE; }
     pt.n = n_ranks; pt.me = my_rank; pt.wait = wait ? 1 : 0;
     b->peers = pt;
+    b->peer_area_floats = area_bytes / sizeof(float);
     return HB200_OK;
     HB_GUARD_END
+}
+
+extern "C" int hb200_batch_peer_area(hb200_batch_t b) {
+    if (!b || b->peers.n <= 1 || !b->peer_area_floats || b->epoch == 0) return 0;
+    return (b->epoch - 1) & 1;
 }
 
 extern "C" int hb200_check_status(void) {

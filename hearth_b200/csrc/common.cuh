@@ -23,7 +23,7 @@
 //    rounded up to 1024, padding zero), block scales d[ld_b] (ld_b = ld_q/32; the
 //    stored f16 widened to f32) and block sums sum[ld_b] (sum of the 32 int8 as f32).
 //
-//  Weights, Q4_K / Q6_K: the reference's bytes unchanged (rows contiguous).
+//  Weights, Q4_K / Q6_K: re-tiled at upload into 32-row panels of interleaved 16-byte pieces (layout in kquant.cu).
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -56,18 +56,23 @@ struct DotOp {
 };
 
 // Peer buffers of a row-sharded launch.  Every rank owns one buffer of identical layout: a 512-byte control block
-// (int flags[8] at byte 0: flags[r] = last epoch rank r finished writing here; int counter at byte 256) followed by the
-// output area.  A kernel stores each output value at the same offset in every rank's output area (plain peer stores),
-// then the last CTA publishes `epoch` in every rank's flags[me] and, if `wait` is set, waits with a bound until all
-// ranks have published theirs here.
+// (int flags[8] at byte 0: flags[r] = last epoch rank r finished writing here; int counter at byte 256) followed by
+// one or two output areas.  A kernel stores each output value at the same offset in every rank's output area (plain
+// peer stores).  One batch launch is one epoch, whatever the number of kernels it takes: only the launch's last kernel
+// has `publish` set, and its last CTA writes `epoch` into every rank's flags[me] and, if `wait` is set, waits with a
+// bound until all ranks have published theirs here.  With two areas, launch number e writes area (e - 1) & 1
+// (`area_off` floats beyond the area-0 address), so a rank that is one launch ahead never overwrites what a slower
+// rank's consumer is still reading.
 constexpr int MAX_PEERS = 8;
 constexpr int PEER_CTRL_BYTES = 512;
 struct PeerTable {
-    float* data[MAX_PEERS];  // output areas; data[me] is local
+    float* data[MAX_PEERS];  // output areas (area 0); data[me] is local
+    long long area_off;      // floats added to every store address of this launch
     int n;                   // ranks (0 or 1: not sharded, plain local stores)
     int me;
     int epoch;
     int wait;
+    int publish;             // this kernel closes the launch: flag exchange after its last CTA
     int* status;             // device word for an expired wait
 };
 
@@ -76,6 +81,8 @@ typedef int2 DotItem;
 
 // Error plumbing shared by the .cu files.
 void set_error(const char* fmt, ...);
+// Ordinal of the device hb200_init bound this process to; -1 before it succeeded.
+int bound_device();
 #define HB_CUDA(expr)                                                                        \
     do {                                                                                     \
         cudaError_t _e = (expr);                                                             \
@@ -134,6 +141,9 @@ constexpr int GEMV_MAX_M = 4;  // tokens one dp4a launch handles per op
 int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const DotItem* items_dev, const int* chunks_dev,
                      int grid, int n_items, const DotOp* single, cudaStream_t st, const PeerTable* peers = nullptr);
 int gemv_dp4a_ctas_per_sm(int m);  // resident CTAs per SM the kernel for m tokens is built for
+// The flag exchange alone (one thread): closes a peer launch of a rank whose shard is empty, so that every rank
+// publishes every epoch.
+int launch_peer_publish(const PeerTable& peers, cudaStream_t st);
 int gemv_dp4a_prepare();  // sets the dynamic shared-memory attributes once
 
 // gemm_tc.cu: tcgen05 kind::i8 path for prefill-sized token counts (Q1_0 / Q2_0), see gemm_tc_wanted.  `amap` points at a CUtensorMap over the

@@ -77,6 +77,31 @@ struct Smem {
 constexpr int MAGIC_I = 0x4B400000;
 constexpr float MAGIC_F = 12582912.0f;
 
+// Raises this rank's flag in every rank's control block, then (optionally) waits, with a bound, for the other ranks'
+// flags here.  One thread.
+__device__ __forceinline__ void peer_flag_exchange(const PeerTable& peers) {
+    int* ctrl_me = reinterpret_cast<int*>(reinterpret_cast<char*>(peers.data[peers.me]) - PEER_CTRL_BYTES);
+    __threadfence_system();
+    for (int p = 0; p < peers.n; p++) {
+        volatile int* f = reinterpret_cast<volatile int*>(reinterpret_cast<char*>(peers.data[p]) - PEER_CTRL_BYTES);
+        f[peers.me] = peers.epoch;
+    }
+    if (peers.wait) {
+        volatile int* mine = reinterpret_cast<volatile int*>(ctrl_me);
+        for (int r = 0; r < peers.n; r++) {
+            unsigned spins = 0;
+            while (mine[r] - peers.epoch < 0) {  // epochs only grow; the difference also survives wrap-around
+                if (++spins > (1u << 21)) {      // about a second and a half
+                    atomicCAS(peers.status, 0, 100 + r);
+                    break;
+                }
+                __nanosleep(64);
+            }
+        }
+        __threadfence_system();
+    }
+}
+
 template <int KIND, int M, bool INT_OUT>
 __global__ void __launch_bounds__(THREADS, (M <= 2 ? 2 : 1))
 gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ items, const int* __restrict__ chunks,
@@ -166,7 +191,7 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
                             float* dst = op.out + (size_t)m * op.ld_out + grow;
                             if (peers.n > 1) {
                                 // the same offset inside every rank's output area: one local and n-1 peer stores
-                                const ptrdiff_t off = dst - peers.data[peers.me];
+                                const ptrdiff_t off = (dst - peers.data[peers.me]) + peers.area_off;
 #pragma unroll
                                 for (int p = 0; p < MAX_PEERS; p++)
                                     if (p < peers.n) peers.data[p][off] = acc;
@@ -302,39 +327,22 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
     }
 
     if (!INT_OUT && peers.n > 1) {
-        // Publish: every CTA makes its peer stores visible system-wide, the last one to finish raises this rank's flag
-        // in every rank's control block, then (optionally) waits, with a bound, for the other ranks' flags here.
+        // Every CTA makes its peer stores visible system-wide; in the kernel that closes the launch the last CTA to
+        // finish then runs the flag exchange.
         __threadfence_system();
         __syncthreads();
-        if (tid == 0) {
-            int* ctrl_me = reinterpret_cast<int*>(reinterpret_cast<char*>(peers.data[peers.me]) - PEER_CTRL_BYTES);
-            int* counter = ctrl_me + 64;
+        if (peers.publish && tid == 0) {
+            int* counter = reinterpret_cast<int*>(reinterpret_cast<char*>(peers.data[peers.me]) - PEER_CTRL_BYTES) + 64;
             const int prev = atomicAdd(counter, 1);
             if (prev == (int)gridDim.x - 1) {
                 *counter = 0;
-                __threadfence_system();
-                for (int p = 0; p < peers.n; p++) {
-                    volatile int* f = reinterpret_cast<volatile int*>(reinterpret_cast<char*>(peers.data[p]) - PEER_CTRL_BYTES);
-                    f[peers.me] = peers.epoch;
-                }
-                if (peers.wait) {
-                    volatile int* mine = reinterpret_cast<volatile int*>(ctrl_me);
-                    for (int r = 0; r < peers.n; r++) {
-                        unsigned spins = 0;
-                        while (mine[r] - peers.epoch < 0) {  // epochs only grow; the difference also survives wrap-around
-                            if (++spins > (1u << 21)) {  // about a second and a half
-                                atomicCAS(peers.status, 0, 100 + r);
-                                break;
-                            }
-                            __nanosleep(64);
-                        }
-                    }
-                    __threadfence_system();
-                }
+                peer_flag_exchange(peers);
             }
         }
     }
 }
+
+__global__ void peer_publish_kernel(const __grid_constant__ PeerTable peers) { peer_flag_exchange(peers); }
 
 template <int KIND, int M, bool INT_OUT>
 int launch_one(const DotOp* ops, const DotItem* items, const int* chunks, int grid, int n_items, const DotOp& single,
@@ -392,6 +400,13 @@ int gemv_dp4a_prepare() {
 }
 
 int gemv_dp4a_ctas_per_sm(int m) { return m <= 2 ? 2 : 1; }
+
+int launch_peer_publish(const PeerTable& peers, cudaStream_t st) {
+    if (peers.n <= 1) return 0;
+    peer_publish_kernel<<<1, 1, 0, st>>>(peers);
+    HB_CUDA(cudaGetLastError());
+    return 0;
+}
 
 int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const DotItem* items_dev, const int* chunks_dev,
                      int grid, int n_items, const DotOp* single, cudaStream_t st, const PeerTable* peers) {

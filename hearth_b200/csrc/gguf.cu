@@ -93,7 +93,7 @@ bool read_value(Reader& r, uint32_t type, MetaValue& v, int depth) {
             if (depth > 4) return false;
             v.elem_type = r.get<uint32_t>();
             const uint64_t count = r.get<uint64_t>();
-            if (!r.ok || count > r.n) return false;  // every element takes at least one byte
+            if (!r.ok || count > r.n - r.pos) return false;  // every element takes at least one of the bytes that remain
             v.items.resize((size_t)count);
             for (auto& it : v.items)
                 if (!read_value(r, v.elem_type, it, depth + 1)) return false;
@@ -135,9 +135,10 @@ extern "C" int hb200_gguf_close(hb200_gguf_t g) {
 }
 
 extern "C" int hb200_gguf_open(const char* path, hb200_gguf_t* out) {
+    hb200_gguf* g = nullptr;  // outside the try block: the catch path must close the file and the mapping too
     try {
         if (!path || !out) { set_error("null path or output handle"); return HB200_ERR_NULL; }
-        hb200_gguf* g = new hb200_gguf();
+        g = new hb200_gguf();
         auto fail = [&](int code) { hb200_gguf_close(g); return code; };
         g->fd = open(path, O_RDONLY);
         if (g->fd < 0) { set_error("cannot open %s: %s", path, strerror(errno)); return fail(HB200_ERR_IO); }
@@ -182,6 +183,7 @@ extern "C" int hb200_gguf_open(const char* path, hb200_gguf_t* out) {
         *out = g;
         return HB200_OK;
     } catch (...) {
+        hb200_gguf_close(g);
         set_error("GGUF: out of memory or malformed file");
         return HB200_ERR_BAD_FORMAT;
     }

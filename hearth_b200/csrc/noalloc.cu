@@ -31,10 +31,19 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[SCRATCH_BYTES];
 constexpr int MAX_DEVICES = 64;
 unsigned char* g_scratch_ptr[MAX_DEVICES] = {};
 
-// Looks up (first call on a device: resolves) the device address of the scratch for the current device.
-int scratch_for_current_device(unsigned char** out) {
+// Looks up (first call on a device: resolves) the device address of the scratch on the device the library is bound
+// to.  The weights, the SM count and the scratch must all belong to that one device, so a calling thread whose
+// current device is another one is refused rather than paired with the wrong GPU's array.  The table below is
+// filled without a lock: two host threads making the FIRST call on a device at the same moment both resolve the
+// same address, which is harmless, but the library as a whole expects calls to be serialised per context anyway.
+int scratch_for_bound_device(unsigned char** out) {
     int dev = -1;
     HB_CUDA(cudaGetDevice(&dev));
+    if (dev != bound_device()) {
+        set_error("the calling thread's current device is %d but the library is bound to device %d; "
+                  "call cudaSetDevice(%d) on this thread first", dev, bound_device(), bound_device());
+        return HB200_ERR_BAD_SHAPE;
+    }
     if (dev < 0 || dev >= MAX_DEVICES) {
         set_error("device ordinal %d outside 0..%d", dev, MAX_DEVICES - 1);
         return HB200_ERR_TOO_LARGE;
@@ -78,7 +87,7 @@ extern "C" int hb200_matmul_f32_noalloc(hb200_weight_t w, const float* x_dev, si
                                       out_dev, (int)ld_out, sms, st);
 
         unsigned char* base = nullptr;
-        int rc = scratch_for_current_device(&base);
+        int rc = scratch_for_bound_device(&base);
         if (rc) return rc;
         // Planes carved from the fixed array: [int8 values][block scales][block sums], row pitch from this call's width.
         hb200_act view;

@@ -37,6 +37,8 @@ SIGNATURES = {
     "hb200_plan_chunks": (_int, [C.POINTER(C.c_int), C.c_size_t, _int, C.POINTER(C.c_int)]),
     "hb200_byte_size": (_sz, [_int, _sz]),
     "hb200_selected_kernel": (C.c_char_p, [_int, _sz]),
+    "hb200_dispatch_report": (_int, [C.POINTER(_int), _sz, C.c_char_p, _sz, C.POINTER(_sz)]),
+    "hb200_dispatch_banner": (_int, [C.POINTER(_int), _sz, C.c_char_p, _sz, C.POINTER(_sz)]),
     "hb200_weight_upload": (_int, [_int, _sz, _sz, _vp, _sz, C.POINTER(_vp)]),
     "hb200_weight_upload_dev": (_int, [_int, _sz, _sz, _vp, _sz, _vp, C.POINTER(_vp)]),
     "hb200_weight_upload_rows": (_int, [_int, _sz, _sz, _vp, _sz, _sz, _sz, C.POINTER(_vp)]),
@@ -93,7 +95,8 @@ SIGNATURES = {
     "hb200_peer_free": (_int, [_vp]),
     "hb200_peer_open": (_int, [_vp, C.POINTER(_vp)]),
     "hb200_peer_close": (_int, [_vp]),
-    "hb200_batch_set_peers": (_int, [_vp, _int, _int, C.POINTER(_vp), _int]),
+    "hb200_batch_set_peers": (_int, [_vp, _int, _int, C.POINTER(_vp), _sz, _int]),
+    "hb200_batch_peer_area": (_int, [_vp]),
     "hb200_check_status": (_int, []),
     "hb200_stream_synchronize": (_int, [_vp]),
 }

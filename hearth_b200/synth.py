@@ -142,6 +142,11 @@ def layer_shapes(d_model: int, ffn: int, kv: int) -> list[tuple[str, int, int]]:
 CONFIGS = {
     # name: dtype, layer shapes, layers, tokens
     "c0_q1_single": dict(dtype=Q1_0, shapes=[("up", 6144, 2048)], layers=1, seq_len=1),
+    # the same matvec over 160 distinct copies of the weight (283 MB, more than twice the L2) in one launch: the way to
+    # time an operation that is shorter than a kernel launch and L2-resident when repeated
+    "c0_q1_single_x160": dict(dtype=Q1_0, shapes=[("up", 6144, 2048)], layers=160, seq_len=1),
+    # Q8_0 weights at the 1.7B shapes (the reference's scalar dot_q8_0_q8_0, hearth-quant/src/q8_0.rs:154-171)
+    "c1_q8_1p7b_decode": dict(dtype=Q8_0, shapes=layer_shapes(2048, 6144, 1024), layers=28, seq_len=1),
     "c1_q2_1p7b_decode": dict(dtype=Q2_0, shapes=layer_shapes(2048, 6144, 1024), layers=28, seq_len=1),
     "c1_q1_1p7b_decode": dict(dtype=Q1_0, shapes=layer_shapes(2048, 6144, 1024), layers=28, seq_len=1),
     "c2_q1_8b_prefill": dict(dtype=Q1_0, shapes=layer_shapes(4096, 12288, 1024), layers=36, seq_len=512),

@@ -115,6 +115,19 @@ HB200_API size_t hb200_byte_size(int dtype, size_t n_cols);
  * 64 tokens, "gemm_tcgen05_i8_*" (tokens on the M side) above. */
 HB200_API const char *hb200_selected_kernel(int dtype, size_t seq_len);
 
+/* hearth_quant::dispatch_report / DispatchReport::banner (hearth-quant/src/lib.rs:426-473): which kernel serves
+ * which token range of each weight format, for a load banner or a service endpoint.  `dtypes` lists the GGML type
+ * ids a model uses; repeats collapse to the first occurrence and ids outside this path are skipped, as in the
+ * reference.  hb200_dispatch_report writes JSON:
+ *   {"device": "...", "sm": "10.0", "sm_count": 148, "kernels": {"q1_0": [{"tokens": "1-10", "kernel": "..."}, ...]}}
+ * (keys are the lowercase format names, as DispatchReport::kernels has them); hb200_dispatch_banner writes the
+ * one-liner "[kernel] Q1_0=gemv_dp4a_q1_0(1-10),...(65+) . NVIDIA B200 . sm_100 . 148 SMs".  Both write at most
+ * `cap` bytes including the terminating zero and store the length needed (without the zero) in *needed (may be
+ * null); a `cap` too small gives HB200_ERR_TOO_LARGE with *needed set.  Without hb200_init the device fields read
+ * "none" / 0 and the table is still reported (it does not depend on the device). */
+HB200_API int hb200_dispatch_report(const int *dtypes, size_t n_dtypes, char *json, size_t cap, size_t *needed);
+HB200_API int hb200_dispatch_banner(const int *dtypes, size_t n_dtypes, char *text, size_t cap, size_t *needed);
+
 /* ---- weights ------------------------------------------------------------ */
 
 /* Replaces GpuCompute::upload_bytes (hearth-compute/src/lib.rs:239) for a
@@ -136,7 +149,10 @@ HB200_API int hb200_weight_info(hb200_weight_t w, int *dtype, size_t *n_rows, si
 
 /* ---- activations -------------------------------------------------------- */
 
-/* A resident activation: up to max_seq_len rows of n_cols values. */
+/* A resident activation: up to max_seq_len rows of n_cols values.  At most HB200_MAX_SEQ_LEN tokens (the per-token
+ * kernels index tokens with a grid dimension); more gives HB200_ERR_TOO_LARGE, from here and from every host-buffer
+ * call that takes a seq_len. */
+#define HB200_MAX_SEQ_LEN 65535
 HB200_API int hb200_act_create(size_t max_seq_len, size_t n_cols, hb200_act_t *out);
 HB200_API int hb200_act_free(hb200_act_t a);
 /* Device address of the f32 [max_seq_len][n_cols] staging area of `a`. */
@@ -277,7 +293,11 @@ HB200_API int hb200_matmul_f32_dev(hb200_weight_t w, hb200_act_t a, size_t seq_l
  * starting any stream capture.  All calls share the one array and it keeps the
  * previous call's contents: every call rewrites the part it reads, but two
  * calls whose kernels overlap on the GPU (different streams, no ordering)
- * race on it.  Serialise them. */
+ * race on it.  Serialise them.  The calling thread's current CUDA device must
+ * be the one hb200_init bound (HB200_ERR_BAD_SHAPE otherwise).  Not thread-safe:
+ * like every call on a context, calls from several host threads must be
+ * serialised by the caller (two threads racing on the very first call of a
+ * device would only resolve the same address twice). */
 #define HB200_NOALLOC_MAX_TOKENS 4
 #define HB200_NOALLOC_MAX_COLS 32768
 HB200_API int hb200_matmul_f32_noalloc(hb200_weight_t w, const float *x_dev, size_t seq_len, float *out_dev,
@@ -323,18 +343,38 @@ HB200_API size_t hb200_batch_input_floats(hb200_batch_t b);
  * hb200_peer_open / hb200_peer_close: map / unmap another rank's buffer.
  * hb200_batch_set_peers: before hb200_batch_seal.  data[r] is rank r's
  *   buffer as seen from this process (data[my_rank] the local one); every op
- *   of the batch must write inside data[my_rank].  With wait != 0 each launch
- *   returns only after all ranks' outputs have landed here (bounded wait,
- *   HB200_ERR_TIMEOUT is reported by the next synchronising call); with
- *   wait == 0 the kernel only publishes.  All ranks must launch the batch the
- *   same number of times. */
+ *   of the batch must write inside data[my_rank].  One buffer serves one batch.
+ *   With wait != 0 each launch returns only after all ranks' outputs have
+ *   landed here (bounded wait, HB200_ERR_TIMEOUT is reported by the next
+ *   synchronising call); with wait == 0 the kernel only publishes.  All ranks
+ *   must launch the batch the same number of times: one launch is one epoch on
+ *   every rank, whatever the number of kernels it takes there, and a rank whose
+ *   row shards are all empty still takes part in the flag exchange.
+ *
+ * Consuming the outputs.  The flag exchange tells a rank that every writer has
+ * finished; it does not tell a writer that every reader has.  With
+ * area_bytes == 0 there is one output area, and no rank may launch step t + 1
+ * before every rank has finished reading step t (synchronise the ranks on the
+ * host).  With area_bytes > 0 every buffer holds two output areas, area_bytes
+ * apart (allocate 2 * area_bytes; a multiple of 16): the ops are recorded
+ * against area 0 and launch number e (counting from 1) stores into area
+ * (e - 1) & 1, hb200_batch_peer_area gives the index of the area the latest
+ * launch wrote, hb200_batch_run_host reads back from it.  A rank can then run
+ * one launch ahead of the slowest one: with wait != 0, launch e + 2 - the next
+ * to write the area of launch e - starts only after this rank's launch e + 1
+ * has seen every rank finish its own launch e + 1, so each rank only has to
+ * order its own reads of launch e before its own launch e + 1 (the same
+ * stream, or an event), which a decode loop does anyway.  With wait == 0
+ * nothing bounds how far ranks drift apart; synchronise on the host. */
 #define HB200_PEER_HANDLE_BYTES 64
 #define HB200_MAX_PEERS 8
 HB200_API int hb200_peer_alloc(size_t bytes, void **data_dev, uint8_t handle[HB200_PEER_HANDLE_BYTES]);
 HB200_API int hb200_peer_free(void *data_dev);
 HB200_API int hb200_peer_open(const uint8_t handle[HB200_PEER_HANDLE_BYTES], void **data_dev);
 HB200_API int hb200_peer_close(void *data_dev);
-HB200_API int hb200_batch_set_peers(hb200_batch_t b, int n_ranks, int my_rank, void *const *data, int wait);
+HB200_API int hb200_batch_set_peers(hb200_batch_t b, int n_ranks, int my_rank, void *const *data, size_t area_bytes,
+                                    int wait);
+HB200_API int hb200_batch_peer_area(hb200_batch_t b);
 /* Reads and clears the device status word: HB200_OK, or HB200_ERR_TIMEOUT if a
  * bounded device-side wait expired since the last check.  Synchronises. */
 HB200_API int hb200_check_status(void);

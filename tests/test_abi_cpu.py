@@ -94,3 +94,37 @@ def test_synthetic_layouts_decode(oracle):
     assert synth.config_weight_bytes("c1_q2_1p7b_decode") == 374341632
     assert synth.config_weight_bytes("c2_q1_8b_prefill") == 976748544
     assert synth.config_weight_bytes("c4_pq2_27b_decode") == 5615124480
+
+
+def test_dispatch_report_and_banner(lib):
+    """hb200_dispatch_report / _banner: the analogue of hearth_quant::dispatch_report (hearth-quant/src/lib.rs:449-473).
+    Keys are lowercase format names, repeats collapse, formats outside the path are skipped; needs no device."""
+    import json
+    from hearth_b200 import api
+    rep = api.dispatch_report([41, 142, 142, 13, 12, 8, 0])
+    assert list(rep["kernels"]) == ["q1_0", "pq2_0", "q4_k", "q8_0"]
+    q1 = rep["kernels"]["q1_0"]
+    assert [r["tokens"] for r in q1] == ["1-10", "11-64", "65+"]
+    for r in q1:
+        lo = int(r["tokens"].rstrip("+").split("-")[0])
+        assert r["kernel"] == lib.hb200_selected_kernel(41, lo).decode()
+    assert rep["kernels"]["q4_k"] == [{"tokens": "1+", "kernel": "kquant_gemv_q4_k_f32"}]
+    banner = api.dispatch_banner([143, 41])
+    assert banner.startswith("[kernel] PTQ1_0=gemv_dp4a_q2_0(1-11),") and " Q1_0=gemv_dp4a_q1_0(1-10)," in banner
+    # a buffer that is too small: the needed length comes back with HB200_ERR_TOO_LARGE
+    need = C.c_size_t()
+    arr = (C.c_int * 1)(41)
+    buf = C.create_string_buffer(8)
+    assert lib.hb200_dispatch_report(arr, 1, buf, 8, C.byref(need)) == -8
+    assert need.value > 8
+    buf = C.create_string_buffer(need.value + 1)
+    assert lib.hb200_dispatch_report(arr, 1, buf, need.value + 1, C.byref(need)) == 0
+    json.loads(buf.value.decode())
+
+
+def test_token_count_limit_is_a_clear_error(lib):
+    """More than HB200_MAX_SEQ_LEN tokens: HB200_ERR_TOO_LARGE with a message, checked before any device work."""
+    h = C.c_void_p()
+    assert lib.hb200_act_create(65536, 128, C.byref(h)) == -8
+    assert b"65535" in lib.hb200_last_error()
+    assert lib.hb200_act_create(0, 128, C.byref(h)) == -4

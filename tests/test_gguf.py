@@ -1,5 +1,6 @@
 """The GGUF reader behind the C ABI against files written by tests/gguf_writer.py: header, metadata, tensor infos
 and data offsets as hearth_gguf::GgufFile reports them (hearth-gguf/src/gguf.rs:137-259); parsing needs no GPU."""
+import os
 import struct
 
 import numpy as np
@@ -84,6 +85,20 @@ def test_malformed_files_are_rejected(api, tmp_path):
     with pytest.raises(api.Hb200Error) as e:
         api.Gguf(str(tmp_path / "does-not-exist.gguf"))
     assert e.value.code == -10
+    # an array whose element count exceeds the bytes that remain, flat and nested, and a huge string length: rejected
+    # before anything of that size is allocated, and (repeated many times) without leaking the mapping or descriptor
+    head = b"GGUF" + struct.pack("<IQQ", 3, 0, 1) + struct.pack("<Q", 1) + b"k" + struct.pack("<I", 9)
+    huge_flat = head + struct.pack("<IQ", 0, 1 << 40) + b"\0" * 64
+    huge_nested = head + struct.pack("<IQ", 9, 2) + struct.pack("<IQ", 0, 1 << 33) + b"\0" * 32
+    huge_str = b"GGUF" + struct.pack("<IQQ", 3, 0, 1) + struct.pack("<Q", 1 << 50) + b"k"
+    n_fds = len(os.listdir("/proc/self/fd"))
+    for _ in range(20):
+        for blob in (huge_flat, huge_nested, huge_str):
+            p.write_bytes(blob)
+            with pytest.raises(api.Hb200Error) as e:
+                api.Gguf(str(p))
+            assert e.value.code == -11
+    assert len(os.listdir("/proc/self/fd")) <= n_fds + 1
     # a tensor type id GgmlDType::from_id does not know (hearth-gguf/src/ggml.rs:58-103)
     gw.write_gguf(str(p), [], [("t", [32], 40, np.zeros(4, np.uint8))])
     with pytest.raises(api.Hb200Error) as e:

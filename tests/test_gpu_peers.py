@@ -29,15 +29,16 @@ def _expected(oracle, seq):
     return np.concatenate(outs, axis=1), xs
 
 
-def _build_rank(hb, torch, dev, rank, world, seq, bufs, wait):
+def _build_rank(hb, torch, dev, rank, world, seq, bufs, wait, specs=None, area_floats=0):
     """Uploads this rank's row shards and records a batch that stores into all of bufs."""
-    total = sum(n for _, n, _ in SPECS)
+    specs = SPECS if specs is None else specs
+    total = sum(n for _, n, _ in specs)
     acts, Ws = {}, []
     batch = hb.Batch()
-    batch.set_peers(rank, bufs, wait=wait)
-    local = bufs[rank].tensor(dev).view(seq, total)
+    batch.set_peers(rank, bufs, wait=wait, area_floats=area_floats)
+    local = bufs[rank].tensor(dev)[:seq * total].view(seq, total)
     coff = 0
-    for i, (dt, n, k) in enumerate(SPECS):
+    for i, (dt, n, k) in enumerate(specs):
         if k not in acts:
             acts[k] = hb.Act(seq, k)
             acts[k].quantize(seq, x_dev=torch.from_numpy(synth.activations(seq, k, seed=900 + k)).to(dev))
@@ -81,6 +82,23 @@ def test_two_emulated_ranks_fill_both_buffers(hb, oracle):
             b.close()
 
 
+def _step_inputs(seq, step):
+    """Activations of one step, by width: they change from step to step so that a stale or early row shows."""
+    return {k: synth.activations(seq, k, seed=900 + k + 7919 * step) for k in sorted({k for _, _, k in SPECS})}
+
+
+def _step_expected(oracle, seq, step):
+    xs = _step_inputs(seq, step)
+    outs = []
+    for i, (dt, n, k) in enumerate(SPECS):
+        w = synth.weights(dt, n, k, seed=800 + i)
+        outs.append(oracle.dot_rows_batched(dt, w, oracle.quantize_q8_0(xs[k]), n, k))
+    return np.concatenate(outs, axis=1)
+
+
+N_STEPS = 6
+
+
 def _real_rank(rank, world, seq, qs, result_q):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -90,7 +108,8 @@ def _real_rank(rank, world, seq, qs, result_q):
     dev = torch.device("cuda", rank)
     hb.init(rank)
     total = sum(n for _, n, _ in SPECS)
-    mine = hb.PeerBuffer.alloc(seq * total)
+    area = seq * total + (-(seq * total)) % 4
+    mine = hb.PeerBuffer.alloc(2 * area)          # two output areas, written by alternate launches
     for r in range(world):
         if r != rank:
             qs[r].put((rank, mine.handle))
@@ -98,12 +117,24 @@ def _real_rank(rank, world, seq, qs, result_q):
     bufs[rank] = mine
     for _ in range(world - 1):
         src, h = qs[rank].get(timeout=60)
-        bufs[src] = hb.PeerBuffer.open(h, seq * total)
-    batch, acts, Ws = _build_rank(hb, torch, dev, rank, world, seq, bufs, wait=True)
-    for _ in range(3):
+        bufs[src] = hb.PeerBuffer.open(h, 2 * area)
+    batch, acts, Ws = _build_rank(hb, torch, dev, rank, world, seq, bufs, wait=True, area_floats=area)
+    results = []
+    stream = torch.cuda.current_stream()
+    for step in range(N_STEPS):
+        # no host-side synchronisation between the ranks from here on: a rank may run one launch ahead of the other,
+        # and the two output areas keep its stores away from what the slower rank still reads
+        for k, x in _step_inputs(seq, step).items():
+            acts[k].quantize(seq, x_dev=torch.from_numpy(x).to(dev))
         batch.launch()
+        got = mine.tensor(dev)[batch.peer_area * area: batch.peer_area * area + seq * total].view(seq, total)
+        results.append(got.to("cpu", non_blocking=False).numpy().copy())  # this rank's read of step `step`, in stream order
+        if rank == 0 and step % 2 == 0:
+            stream.synchronize()
+            import time
+            time.sleep(0.05)                      # let one rank fall behind now and then
     hb.check_status()
-    result_q.put((rank, mine.tensor(dev).view(seq, total).cpu().numpy()))
+    result_q.put((rank, np.stack(results)))
     # leave only between steps, after every rank has its results
     qs[rank].get(timeout=60)
     batch.free()
@@ -119,7 +150,7 @@ def test_two_real_ranks_over_nvlink(oracle):
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     seq, world = 2, 2
-    want, _ = _expected(oracle, seq)
+    want = np.stack([_step_expected(oracle, seq, step) for step in range(N_STEPS)])
     ctx = mp.get_context("spawn")
     qs = [ctx.Queue() for _ in range(world)]
     result_q = ctx.Queue()
@@ -133,7 +164,83 @@ def test_two_real_ranks_over_nvlink(oracle):
         p.join(timeout=60)
         assert p.exitcode == 0
     for r in range(world):
-        assert (got[r].view(np.uint32) == want.view(np.uint32)).all(), f"rank {r}"
+        for step in range(N_STEPS):
+            assert (got[r][step].view(np.uint32) == want[step].view(np.uint32)).all(), f"rank {r}, step {step}"
+
+
+def test_emulated_ranks_with_empty_shards_keep_one_epoch_per_launch(hb, oracle):
+    """One launch is one epoch on every rank, whatever the number of kernels it takes there.  Rank 1's shard of the
+    only Q8_0 matrix is empty (1 row over 2 ranks), so rank 0 launches two kernels per step and rank 1 one; in a
+    second batch every shard of rank 1 is empty and it only runs the flag exchange.  After three launches every
+    control block must read epoch 3 from both ranks."""
+    import torch
+    dev = torch.device("cuda:0")
+    seq = 1
+    for specs in ([(42, 100, 1152), (8, 1, 256)], [(42, 1, 1152), (41, 1, 256)]):
+        total = sum(n for _, n, _ in specs)
+        bufs = [hb.PeerBuffer.alloc(seq * total) for _ in range(2)]
+        built = [_build_rank(hb, torch, dev, r, 2, seq, bufs, wait=False, specs=specs) for r in range(2)]
+        try:
+            for _ in range(3):
+                for batch, _, _ in built:
+                    batch.launch()
+            hb.check_status()
+            for b in bufs:
+                assert b.flags(dev)[:2].tolist() == [3, 3], (specs, b.flags(dev).tolist())
+            want = np.concatenate([oracle.dot_rows_batched(dt, synth.weights(dt, n, k, seed=800 + i),
+                                                           oracle.quantize_q8_0(synth.activations(seq, k, seed=900 + k)), n, k)
+                                   for i, (dt, n, k) in enumerate(specs)], axis=1)
+            for b in bufs:
+                got = b.tensor(dev).view(seq, total).cpu().numpy()
+                assert (got.view(np.uint32) == want.view(np.uint32)).all()
+        finally:
+            for batch, acts, Ws in built:
+                batch.free()
+                for a in acts.values():
+                    a.free()
+                for W in Ws:
+                    W.free()
+            for b in bufs:
+                b.close()
+
+
+def test_emulated_ranks_alternate_output_areas(hb, oracle):
+    """Two output areas per buffer: launch e writes area (e - 1) & 1 and leaves the other one, the previous step's
+    results, untouched.  Inputs change every step."""
+    import torch
+    dev = torch.device("cuda:0")
+    seq = 2
+    total = sum(n for _, n, _ in SPECS)
+    area = seq * total + (-(seq * total)) % 4
+    bufs = [hb.PeerBuffer.alloc(2 * area) for _ in range(2)]
+    built = [_build_rank(hb, torch, dev, r, 2, seq, bufs, wait=False, area_floats=area) for r in range(2)]
+    try:
+        prev = None
+        for step in range(4):
+            want = _step_expected(oracle, seq, step)
+            for batch, acts, _ in built:
+                for k, x in _step_inputs(seq, step).items():
+                    acts[k].quantize(seq, x_dev=torch.from_numpy(x).to(dev))
+                batch.launch()
+            hb.check_status()
+            assert built[0][0].peer_area == built[1][0].peer_area == step & 1
+            for b in bufs:
+                both = b.tensor(dev).cpu().numpy()
+                cur = both[(step & 1) * area:(step & 1) * area + seq * total].reshape(seq, total)
+                assert (cur.view(np.uint32) == want.view(np.uint32)).all(), f"step {step}"
+                if prev is not None:
+                    old = both[((step - 1) & 1) * area:((step - 1) & 1) * area + seq * total].reshape(seq, total)
+                    assert (old.view(np.uint32) == prev.view(np.uint32)).all(), f"step {step}: the previous area changed"
+            prev = want
+    finally:
+        for batch, acts, Ws in built:
+            batch.free()
+            for a in acts.values():
+                a.free()
+            for W in Ws:
+                W.free()
+        for b in bufs:
+            b.close()
 
 
 def test_absent_rank_ends_in_a_timeout_status_not_a_hang(hb, oracle):
