@@ -47,15 +47,19 @@ def _stale(target: str, deps: list[str]) -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    """HB200_NVCC_EXTRA in the environment adds flags (e.g. -DHB200_TC_CHECK for the self-checking tensor-core
+    kernels); a build with extra flags always recompiles everything."""
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()
+    extra = os.environ.get("HB200_NVCC_EXTRA", "").split()
+    force = force or bool(extra)
     headers = _headers()
     jobs = []
     for src in SOURCES:
         s = os.path.join(CSRC, src)
         o = os.path.join(OBJ, src.replace(".cu", ".o"))
         if force or _stale(o, [s] + headers):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             jobs.append((src, cmd))
 
     def run(job):

@@ -12,6 +12,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <new>
@@ -1535,7 +1536,9 @@ extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const 
 
 extern "C" int hb200_batch_launch_count(hb200_batch_t b) {
     if (!b || !b->sealed) return 0;
-    return (int)(b->groups.size() + b->kq_groups.size() + b->tc_groups.size());
+    int n = (int)(b->groups.size() + b->kq_groups.size() + b->tc_groups.size());
+    if (b->peers.n > 1 && b->groups.empty()) n += 1;                         // the flag exchange on its own
+    return n;
 }
 
 extern "C" int hb200_batch_free(hb200_batch_t b) {
