@@ -26,6 +26,33 @@ def init(device: int = 0) -> None:
     _initialized_device = device
 
 
+def init_multi(n_devices: int | None = None, devices: list[int] | None = None) -> int:
+    """One process, several GPUs: binds device slots 0 .. n-1 (to `devices`, default 0 .. n-1) and enables peer access
+    between them.  Returns the number of slots.  Objects are created in the current slot (set_slot)."""
+    global _initialized_device
+    L = _l.load()
+    if devices is None:
+        check(L.hb200_init_multi(int(n_devices)))
+    else:
+        arr = (C.c_int * len(devices))(*devices)
+        check(L.hb200_init_slots(arr, len(devices)))
+    _initialized_device = 0
+    return int(L.hb200_slot_count())
+
+
+def set_slot(slot: int) -> None:
+    check(_l.load().hb200_set_slot(slot))
+
+
+def multi_batch_launch(batches: list, streams: list | None = None) -> None:
+    """hb200_multi_batch_launch: one recorded batch per device slot, launched one after the other by this thread."""
+    arr = (C.c_void_p * len(batches))(*[b._h for b in batches])
+    st = None
+    if streams is not None:
+        st = (C.c_void_p * len(streams))(*[C.c_void_p(int(x.cuda_stream)) if x is not None else C.c_void_p(0) for x in streams])
+    check(_l.load().hb200_multi_batch_launch(arr, len(batches), st))
+
+
 def shutdown() -> None:
     global _initialized_device
     check(_l.load().hb200_shutdown())

@@ -40,6 +40,15 @@ int bound_device();
 }  // namespace hb200
 
 #define HB_GUARD_BEGIN try {
+// First statement of every entry point that takes a weight, an activation or a batch: the object's device slot
+// becomes the current one.
+#define HB_USE(obj)                                   \
+    do {                                              \
+        if (obj) {                                    \
+            const int _rc = use_slot((obj)->slot);    \
+            if (_rc) return _rc;                      \
+        }                                             \
+    } while (0)
 #define HB_GUARD_END                                          \
     }                                                         \
     catch (const std::bad_alloc&) {                           \
@@ -89,6 +98,7 @@ struct hb200_batch {
     QuantDesc* qdescs_dev = nullptr;
     int q_max_chunks = 0, q_max_seq = 0, n_qacts = 0;
     bool has_kquant_inputs = false;
+    int slot = 0;           // device slot the batch (and every weight and activation in it) lives in
     PeerTable peers = {};   // n > 1: outputs go to every rank's buffer
     size_t peer_area_floats = 0;  // two output areas this far apart, written in turn (0: one area)
     int epoch = 0;
@@ -126,7 +136,27 @@ struct Context {
     void* d_argmax = nullptr;  // ticket + partial results of the argmax kernel, then one result word
     cudaStream_t copy_in = nullptr, copy_out = nullptr;  // the pipelined host path: uploads and readbacks beside the compute stream
 };
-Context g_ctx;
+// One context per device slot.  hb200_init binds slot 0; hb200_init_multi binds slots 0 .. n-1 (normally to devices
+// 0 .. n-1) so that ONE host thread - the shape of the reference's dispatcher, hearth-llm/src/pool.rs:398-425 - can
+// drive every GPU of the box.  Every object remembers the slot it was created in, and every call on an object makes
+// that slot (and its CUDA device) current first; calls without an object act on the current slot.
+Context g_ctx_pool[MAX_PEERS];
+int g_n_slots = 0;   // slots bound (0 before any init)
+int g_cur = 0;       // the current slot
+#define g_ctx (g_ctx_pool[g_cur])
+
+// Makes `slot` and its device current.  Objects of a context that has been shut down are refused.
+int use_slot(int slot) {
+    if (slot < 0 || slot >= MAX_PEERS || !g_ctx_pool[slot].ready) {
+        set_error("the object belongs to device slot %d, which is not initialised", slot);
+        return HB200_ERR_NOT_INITIALIZED;
+    }
+    if (slot != g_cur || g_n_slots > 1) {
+        g_cur = slot;
+        HB_CUDA(cudaSetDevice(g_ctx_pool[slot].device));
+    }
+    return 0;
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -207,6 +237,7 @@ void fill_op(DotOp& op, const hb200_weight* w, const hb200_act* a, size_t tok0, 
 
 int check_pair(const hb200_weight* w, const hb200_act* a, size_t seq_len, size_t ld_out) {
     if (!w || !a) { set_error("null weight or activation handle"); return HB200_ERR_NULL; }
+    if (a->slot != w->slot) { set_error("the weight lives in device slot %d, the activation in slot %d", w->slot, a->slot); return HB200_ERR_BAD_SHAPE; }
     if (a->n_cols != w->n_cols) {
         set_error("dim mismatch: weight has %zu columns, activation %zu", w->n_cols, a->n_cols);
         return HB200_ERR_BAD_SHAPE;
@@ -294,13 +325,15 @@ int ensure_ctx_act(size_t seq_len, size_t n_cols) {
 
 namespace hb200 {
 int bound_device() { return g_ctx.ready ? g_ctx.device : -1; }
+int use_slot_of(int slot) { return use_slot(slot); }
 }  // namespace hb200
 
-extern "C" int hb200_init(int device) {
-    HB_GUARD_BEGIN
-    if (g_ctx.ready) {
-        if (g_ctx.device == device) return HB200_OK;
-        set_error("already bound to device %d", g_ctx.device);
+// Binds slot `slot` to CUDA device `device`: stream, status word, scratch, per-device kernel attributes.
+static int init_slot(int slot, int device) {
+    Context& c = g_ctx_pool[slot];
+    if (c.ready) {
+        if (c.device == device) return HB200_OK;
+        set_error("slot %d is already bound to device %d", slot, c.device);
         return HB200_ERR_BAD_SHAPE;
     }
     int n = 0;
@@ -317,16 +350,18 @@ extern "C" int hb200_init(int device) {
         return HB200_ERR_NO_DEVICE;
     }
     HB_CUDA(cudaSetDevice(device));
-    HB_CUDA(cudaStreamCreateWithFlags(&g_ctx.stream, cudaStreamNonBlocking));
-    g_ctx.device = device;
-    g_ctx.sm_count = prop.multiProcessorCount;
+    const int before = g_cur;
+    g_cur = slot;
+    HB_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+    c.device = device;
+    c.sm_count = prop.multiProcessorCount;
     int rc;
     if ((rc = gemv_dp4a_prepare())) return rc;
     if ((rc = kquant_prepare())) return rc;
     if ((rc = gemm_tc_prepare())) return rc;
     if ((rc = gemm_tcr_prepare())) return rc;
     if ((rc = producers_prepare())) return rc;
-    {
+    if (!g_encode_tiled) {
         void* fn = nullptr;
         cudaDriverEntryPointQueryResult qres;
         cudaError_t e2 = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
@@ -336,33 +371,83 @@ extern "C" int hb200_init(int device) {
         }
         g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
     }
-    HB_CUDA(cudaMalloc(&g_ctx.d_status, sizeof(int)));
-    HB_CUDA(cudaMemset(g_ctx.d_status, 0, sizeof(int)));
-    HB_CUDA(cudaMalloc(&g_ctx.d_argmax, argmax_scratch_bytes() + 256));
-    HB_CUDA(cudaMemset(g_ctx.d_argmax, 0, argmax_scratch_bytes() + 256));
-    g_ctx.ready = true;
+    HB_CUDA(cudaMalloc(&c.d_status, sizeof(int)));
+    HB_CUDA(cudaMemset(c.d_status, 0, sizeof(int)));
+    HB_CUDA(cudaMalloc(&c.d_argmax, argmax_scratch_bytes() + 256));
+    HB_CUDA(cudaMemset(c.d_argmax, 0, argmax_scratch_bytes() + 256));
+    c.ready = true;
+    if (slot + 1 > g_n_slots) g_n_slots = slot + 1;
+    g_cur = before;
     return HB200_OK;
+}
+
+extern "C" int hb200_init(int device) {
+    HB_GUARD_BEGIN
+    const int rc = init_slot(0, device);
+    if (rc) return rc;
+    return use_slot(g_n_slots > 1 ? g_cur : 0);
     HB_GUARD_END
 }
 
+extern "C" int hb200_init_slots(const int* devices, int n_slots) {
+    HB_GUARD_BEGIN
+    if (!devices) { set_error("null device list"); return HB200_ERR_NULL; }
+    if (n_slots < 1 || n_slots > MAX_PEERS) { set_error("%d device slots: between 1 and %d", n_slots, MAX_PEERS); return HB200_ERR_BAD_SHAPE; }
+    int rc;
+    for (int i = 0; i < n_slots; i++)
+        if ((rc = init_slot(i, devices[i]))) return rc;
+    // every device may store into every other device's memory (plain peer stores of the row-sharded batches)
+    for (int i = 0; i < n_slots; i++)
+        for (int j = 0; j < n_slots; j++) {
+            if (devices[i] == devices[j]) continue;
+            int can = 0;
+            HB_CUDA(cudaDeviceCanAccessPeer(&can, devices[i], devices[j]));
+            if (!can) { set_error("device %d cannot access device %d", devices[i], devices[j]); return HB200_ERR_UNSUPPORTED; }
+            HB_CUDA(cudaSetDevice(devices[i]));
+            cudaError_t e = cudaDeviceEnablePeerAccess(devices[j], 0);
+            if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+            else if (e != cudaSuccess) { set_error("cudaDeviceEnablePeerAccess(%d -> %d) failed: %s", devices[i], devices[j], cudaGetErrorString(e)); return HB200_ERR_CUDA; }
+        }
+    return use_slot(0);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_init_multi(int n_devices) {
+    int devices[MAX_PEERS];
+    for (int i = 0; i < MAX_PEERS; i++) devices[i] = i;
+    if (n_devices < 1 || n_devices > MAX_PEERS) { set_error("%d devices: between 1 and %d", n_devices, MAX_PEERS); return HB200_ERR_BAD_SHAPE; }
+    return hb200_init_slots(devices, n_devices);
+}
+
+extern "C" int hb200_set_slot(int slot) {
+    HB_GUARD_BEGIN
+    return use_slot(slot);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_slot_count(void) { return g_n_slots; }
+
 extern "C" int hb200_shutdown(void) {
     HB_GUARD_BEGIN
-    if (!g_ctx.ready) return HB200_OK;
-    cudaSetDevice(g_ctx.device);
-    cudaDeviceSynchronize();
-    for (auto& kv : g_ctx.acts) hb200_act_free(kv.second);
-    g_ctx.acts.clear();
-    g_ctx.act = nullptr;
-    if (g_ctx.d_in) cudaFree(g_ctx.d_in);
-    if (g_ctx.d_out) cudaFree(g_ctx.d_out);
-    if (g_ctx.d_status) cudaFree(g_ctx.d_status);
-    if (g_ctx.d_argmax) cudaFree(g_ctx.d_argmax);
-    g_ctx.d_argmax = nullptr;
-    if (g_ctx.stream) cudaStreamDestroy(g_ctx.stream);
-    if (g_ctx.copy_in) cudaStreamDestroy(g_ctx.copy_in);
-    if (g_ctx.copy_out) cudaStreamDestroy(g_ctx.copy_out);
-    g_ctx.copy_in = g_ctx.copy_out = nullptr;
-    g_ctx = Context();
+    for (int slot = 0; slot < MAX_PEERS; slot++) {
+        Context& c = g_ctx_pool[slot];
+        if (!c.ready) continue;
+        cudaSetDevice(c.device);
+        cudaDeviceSynchronize();
+        for (auto& kv : c.acts) hb200_act_free(kv.second);
+        c.acts.clear();
+        c.act = nullptr;
+        if (c.d_in) cudaFree(c.d_in);
+        if (c.d_out) cudaFree(c.d_out);
+        if (c.d_status) cudaFree(c.d_status);
+        if (c.d_argmax) cudaFree(c.d_argmax);
+        if (c.stream) cudaStreamDestroy(c.stream);
+        if (c.copy_in) cudaStreamDestroy(c.copy_in);
+        if (c.copy_out) cudaStreamDestroy(c.copy_out);
+        c = Context();
+    }
+    g_n_slots = 0;
+    g_cur = 0;
     return HB200_OK;
     HB_GUARD_END
 }
@@ -526,6 +611,7 @@ static int weight_build(int dtype, size_t n_rows, size_t n_cols, const uint8_t* 
                         hb200_weight_t* out) {
     const int kind = kind_of(dtype);
     hb200_weight* w = new hb200_weight();
+    w->slot = g_cur;
     w->dtype = dtype;
     w->kind = kind;
     w->n_rows = n_rows;
@@ -659,6 +745,7 @@ extern "C" int hb200_weight_upload_rows(int dtype, size_t n_rows, size_t n_cols,
 
 extern "C" int hb200_weight_free(hb200_weight_t w) {
     HB_GUARD_BEGIN
+    HB_USE(w);
     if (!w) return HB200_OK;
     if (w->bits) cudaFree(w->bits);
     if (w->scales) cudaFree(w->scales);
@@ -692,6 +779,7 @@ extern "C" int hb200_act_create(size_t max_seq_len, size_t n_cols, hb200_act_t* 
     int rc = need_ctx();
     if (rc) return rc;
     hb200_act* a = new hb200_act();
+    a->slot = g_cur;
     a->max_seq = max_seq_len;
     a->n_cols = n_cols;
     a->ld_q = (int)((n_cols + ACT_PAD - 1) / ACT_PAD * ACT_PAD);
@@ -716,6 +804,7 @@ extern "C" int hb200_act_create(size_t max_seq_len, size_t n_cols, hb200_act_t* 
 
 extern "C" int hb200_act_free(hb200_act_t a) {
     HB_GUARD_BEGIN
+    HB_USE(a);
     if (!a) return HB200_OK;
     if (a->x) cudaFree(a->x);
     if (a->q) cudaFree(a->q);
@@ -746,6 +835,7 @@ extern "C" int hb200_act_q8_planes(hb200_act_t a, int8_t** q, float** d, float**
 
 extern "C" int hb200_act_quantize_dev(hb200_act_t a, const float* x_dev, size_t seq_len, void* stream) {
     HB_GUARD_BEGIN
+    HB_USE(a);
     int rc = need_ctx();
     if (rc) return rc;
     if (!a) { set_error("null activation handle"); return HB200_ERR_NULL; }
@@ -757,6 +847,7 @@ extern "C" int hb200_act_quantize_dev(hb200_act_t a, const float* x_dev, size_t 
 
 extern "C" int hb200_act_load_q8_0_dev(hb200_act_t a, const uint8_t* q8_dev, size_t seq_len, size_t q8_stride, void* stream) {
     HB_GUARD_BEGIN
+    HB_USE(a);
     int rc = need_ctx();
     if (rc) return rc;
     if (!a || !q8_dev) { set_error("null handle or pointer"); return HB200_ERR_NULL; }
@@ -769,6 +860,7 @@ extern "C" int hb200_act_load_q8_0_dev(hb200_act_t a, const uint8_t* q8_dev, siz
 
 extern "C" int hb200_act_store_q8_0_dev(hb200_act_t a, uint8_t* q8_dev, size_t seq_len, size_t q8_stride, void* stream) {
     HB_GUARD_BEGIN
+    HB_USE(a);
     int rc = need_ctx();
     if (rc) return rc;
     if (!a || !q8_dev) { set_error("null handle or pointer"); return HB200_ERR_NULL; }
@@ -795,6 +887,7 @@ static int hadamard_check(size_t block_size) {
 extern "C" int hb200_act_rms_norm_q8_dev(hb200_act_t a, const float* x_dev, const float* weight_dev, float eps, size_t seq_len,
                                          void* stream) {
     HB_GUARD_BEGIN
+    HB_USE(a);
     int rc = need_ctx();
     if (rc) return rc;
     if ((rc = producer_check(a, seq_len))) return rc;
@@ -807,6 +900,7 @@ extern "C" int hb200_act_rms_norm_q8_dev(hb200_act_t a, const float* x_dev, cons
 
 extern "C" int hb200_act_silu_mul_q8_dev(hb200_act_t a, const float* gate_dev, const float* up_dev, size_t seq_len, void* stream) {
     HB_GUARD_BEGIN
+    HB_USE(a);
     int rc = need_ctx();
     if (rc) return rc;
     if ((rc = producer_check(a, seq_len))) return rc;
@@ -819,6 +913,7 @@ extern "C" int hb200_act_silu_mul_q8_dev(hb200_act_t a, const float* gate_dev, c
 extern "C" int hb200_act_hadamard_quantize_dev(hb200_act_t a, const float* x_dev, const float* signs_dev, size_t block_size,
                                                size_t seq_len, float* rotated_dev, void* stream) {
     HB_GUARD_BEGIN
+    HB_USE(a);
     int rc = need_ctx();
     if (rc) return rc;
     if ((rc = producer_check(a, seq_len))) return rc;
@@ -836,6 +931,7 @@ extern "C" int hb200_act_hadamard_quantize_dev(hb200_act_t a, const float* x_dev
 
 extern "C" int hb200_dot_rows_dev(hb200_weight_t w, hb200_act_t a, size_t seq_len, float* out_dev, size_t ld_out, void* stream) {
     HB_GUARD_BEGIN
+    HB_USE(w);
     int rc = need_ctx();
     if (rc) return rc;
     if ((rc = check_pair(w, a, seq_len, ld_out))) return rc;
@@ -847,6 +943,7 @@ extern "C" int hb200_dot_rows_dev(hb200_weight_t w, hb200_act_t a, size_t seq_le
 
 extern "C" int hb200_matmul_f32_dev(hb200_weight_t w, hb200_act_t a, size_t seq_len, float* out_dev, size_t ld_out, void* stream) {
     HB_GUARD_BEGIN
+    HB_USE(w);
     int rc = need_ctx();
     if (rc) return rc;
     if ((rc = check_pair(w, a, seq_len, ld_out))) return rc;
@@ -878,6 +975,7 @@ static int f32act_check(hb200_weight_t w, size_t seq_len, size_t ld_out) {
 extern "C" int hb200_matmul_f32act_dev(hb200_weight_t w, const float* x_dev, size_t seq_len, float* out_dev, size_t ld_out,
                                        int accumulate, void* stream) {
     HB_GUARD_BEGIN
+    HB_USE(w);
     int rc = need_ctx();
     if (rc) return rc;
     if ((rc = f32act_check(w, seq_len, ld_out))) return rc;
@@ -890,6 +988,7 @@ extern "C" int hb200_matmul_f32act_dev(hb200_weight_t w, const float* x_dev, siz
 
 extern "C" int hb200_matmul_f32act(hb200_weight_t w, const float* x, size_t seq_len, float* out, int accumulate) {
     HB_GUARD_BEGIN
+    HB_USE(w);
     int rc = need_ctx();
     if (rc) return rc;
     if ((rc = f32act_check(w, seq_len, w ? w->n_rows : 0))) return rc;
@@ -1052,6 +1151,7 @@ static int host_q8_to_act(hb200_weight_t w, const uint8_t* a_q8, size_t seq_len,
 
 extern "C" int hb200_dot_rows_batched(hb200_weight_t w, const uint8_t* a_q8, size_t seq_len, size_t q8_stride, float* out) {
     HB_GUARD_BEGIN
+    HB_USE(w);
     int rc = need_ctx();
     if (rc) return rc;
     if (!w) { set_error("null weight handle"); return HB200_ERR_NULL; }
@@ -1076,6 +1176,7 @@ extern "C" int hb200_dot_rows(hb200_weight_t w, const uint8_t* a_q8, float* out)
 
 extern "C" int hb200_matmul_f32(hb200_weight_t w, const float* x, size_t seq_len, float* out) {
     HB_GUARD_BEGIN
+    HB_USE(w);
     int rc = need_ctx();
     if (rc) return rc;
     if (!w) { set_error("null weight handle"); return HB200_ERR_NULL; }
@@ -1095,6 +1196,7 @@ extern "C" int hb200_matmul_f32(hb200_weight_t w, const float* x, size_t seq_len
 
 extern "C" int hb200_block_dots_i32(hb200_weight_t w, const uint8_t* a_q8, size_t seq_len, size_t q8_stride, int32_t* out) {
     HB_GUARD_BEGIN
+    HB_USE(w);
     int rc = need_ctx();
     if (rc) return rc;
     if (!w) { set_error("null weight handle"); return HB200_ERR_NULL; }
@@ -1126,16 +1228,19 @@ extern "C" int hb200_batch_create(hb200_batch_t* out) {
     if (rc) return rc;
     if (!out) { set_error("null output handle"); return HB200_ERR_NULL; }
     *out = new hb200_batch();
+    (*out)->slot = g_cur;
     return HB200_OK;
     HB_GUARD_END
 }
 
 extern "C" int hb200_batch_add(hb200_batch_t b, hb200_weight_t w, hb200_act_t a, size_t seq_len, float* out_dev, size_t ld_out) {
     HB_GUARD_BEGIN
+    HB_USE(b);
     if (!b) { set_error("null batch"); return HB200_ERR_NULL; }
     if (b->sealed) { set_error("batch is sealed"); return HB200_ERR_BAD_SHAPE; }
     int rc = check_pair(w, a, seq_len, ld_out);
     if (rc) return rc;
+    if (w->slot != b->slot) { set_error("the batch lives in device slot %d, the weight in slot %d", b->slot, w->slot); return HB200_ERR_BAD_SHAPE; }
     if (!out_dev) { set_error("null output"); return HB200_ERR_NULL; }
     if (seq_len == 0 || w->n_rows == 0) return HB200_OK;
     BatchEntry e{w, a, seq_len, out_dev, ld_out};
@@ -1284,6 +1389,7 @@ extern "C" int hb200_plan_chunks(const int* cost, size_t n_items, int grid, int*
 
 extern "C" int hb200_batch_seal(hb200_batch_t b) {
     HB_GUARD_BEGIN
+    HB_USE(b);
     if (!b) { set_error("null batch"); return HB200_ERR_NULL; }
     if (b->sealed) return HB200_OK;
     if (b->peers.n > 1) {
@@ -1444,6 +1550,7 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
 
 extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
     HB_GUARD_BEGIN
+    HB_USE(b);
     int rc = need_ctx();
     if (rc) return rc;
     if (!b) { set_error("null batch"); return HB200_ERR_NULL; }
@@ -1475,11 +1582,23 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
     HB_GUARD_END
 }
 
+extern "C" int hb200_multi_batch_launch(hb200_batch_t const* batches, int n, void* const* streams) {
+    HB_GUARD_BEGIN
+    if (!batches) { set_error("null batch list"); return HB200_ERR_NULL; }
+    for (int i = 0; i < n; i++) {
+        const int rc = hb200_batch_launch(batches[i], streams ? streams[i] : nullptr);
+        if (rc) return rc;
+    }
+    return HB200_OK;
+    HB_GUARD_END
+}
+
 extern "C" size_t hb200_batch_input_floats(hb200_batch_t b) { return (b && b->sealed) ? b->input_floats : 0; }
 
 extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const float* out_dev_base, size_t out_floats,
                                     float* out_host) {
     HB_GUARD_BEGIN
+    HB_USE(b);
     int rc = need_ctx();
     if (rc) return rc;
     if (!b) { set_error("null batch"); return HB200_ERR_NULL; }
@@ -1543,6 +1662,7 @@ extern "C" int hb200_batch_launch_count(hb200_batch_t b) {
 
 extern "C" int hb200_batch_free(hb200_batch_t b) {
     HB_GUARD_BEGIN
+    HB_USE(b);
     if (!b) return HB200_OK;
     for (BatchGroup& g : b->groups) {
         if (g.ops_dev) cudaFree(g.ops_dev);
@@ -1619,6 +1739,7 @@ extern "C" int hb200_peer_close(void* data_dev) {
 
 extern "C" int hb200_batch_set_peers(hb200_batch_t b, int n_ranks, int my_rank, void* const* data, size_t area_bytes, int wait) {
     HB_GUARD_BEGIN
+    HB_USE(b);
     if (!b || !data) { set_error("null argument"); return HB200_ERR_NULL; }
     if (b->sealed) { set_error("set the peers before sealing the batch"); return HB200_ERR_BAD_SHAPE; }
     if (n_ranks < 1 || n_ranks > MAX_PEERS || my_rank < 0 || my_rank >= n_ranks) {

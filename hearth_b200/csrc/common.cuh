@@ -83,6 +83,8 @@ typedef int2 DotItem;
 void set_error(const char* fmt, ...);
 // Ordinal of the device hb200_init bound this process to; -1 before it succeeded.
 int bound_device();
+// Makes device slot `slot` (and its CUDA device) current; an error code if that slot is not initialised.
+int use_slot_of(int slot);
 #define HB_CUDA(expr)                                                                        \
     do {                                                                                     \
         cudaError_t _e = (expr);                                                             \

@@ -66,13 +66,17 @@ int scratch_for_bound_device(unsigned char** out) {
 extern "C" int hb200_matmul_f32_noalloc(hb200_weight_t w, const float* x_dev, size_t seq_len, float* out_dev,
                                         size_t ld_out, void* stream) {
     try {
-        const int sms = hb200_sm_count();
-        if (sms <= 0) {
+        if (hb200_sm_count() <= 0) {
             set_error("hb200_init has not succeeded in this process");
             return HB200_ERR_NOT_INITIALIZED;
         }
         if (!w) { set_error("null weight handle"); return HB200_ERR_NULL; }
+        {
+            const int rc = use_slot_of(w->slot);  // the weight's device slot becomes the current one
+            if (rc) return rc;
+        }
         if (seq_len == 0 || w->n_rows == 0) return HB200_OK;
+        const int sms = hb200_sm_count();
         if (!x_dev || !out_dev) { set_error("null input or output"); return HB200_ERR_NULL; }
         if (ld_out < w->n_rows) { set_error("ld_out %zu is smaller than n_rows %zu", ld_out, w->n_rows); return HB200_ERR_BAD_SHAPE; }
         if (seq_len > MAX_TOKENS || w->n_cols > MAX_COLS) {

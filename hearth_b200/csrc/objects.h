@@ -6,6 +6,7 @@
 #include "common.cuh"
 
 struct hb200_weight {
+    int slot = 0;  // device slot of the context it was uploaded in
     int dtype = 0, kind = hb200::KIND_NONE;
     size_t n_rows = 0, n_cols = 0;
     size_t row_bytes = 0;  // of the reference layout
@@ -18,6 +19,7 @@ struct hb200_weight {
 };
 
 struct hb200_act {
+    int slot = 0;  // device slot of the context it was created in
     size_t max_seq = 0, n_cols = 0;
     int ld_q = 0, ld_b = 0;
     float* x = nullptr;

@@ -28,6 +28,10 @@ _int = C.c_int
 # name -> (restype, argtypes); must list every symbol include/hb200.h declares.
 SIGNATURES = {
     "hb200_init": (_int, [_int]),
+    "hb200_init_multi": (_int, [_int]),
+    "hb200_init_slots": (_int, [C.POINTER(_int), _int]),
+    "hb200_set_slot": (_int, [_int]),
+    "hb200_slot_count": (_int, []),
     "hb200_shutdown": (_int, []),
     "hb200_last_error": (C.c_char_p, []),
     "hb200_sm_count": (_int, []),
@@ -88,6 +92,7 @@ SIGNATURES = {
     "hb200_batch_seal": (_int, [_vp]),
     "hb200_batch_launch": (_int, [_vp, _vp]),
     "hb200_batch_free": (_int, [_vp]),
+    "hb200_multi_batch_launch": (_int, [C.POINTER(_vp), _int, C.POINTER(_vp)]),
     "hb200_batch_launch_count": (_int, [_vp]),
     "hb200_batch_run_host": (_int, [_vp, _vp, _vp, _sz, _vp]),
     "hb200_batch_input_floats": (_sz, [_vp]),

@@ -82,6 +82,23 @@ typedef struct hb200_gguf *hb200_gguf_t;     /* a mapped GGUF model file */
 /* Replaces GpuCompute::new() (hearth-compute/src/lib.rs:127-184): binds the
  * calling process to CUDA device `device`.  Idempotent for the same device. */
 HB200_API int hb200_init(int device);
+/* Single-process use of several GPUs.  The reference is one process with one dispatching thread
+ * (hearth-llm/src/pool.rs:398-425; LlamaModel serialises on one mutex, model/mod.rs:2781-2783), so one host thread
+ * must be able to reach every GPU of the box.  hb200_init_multi binds device slots 0 .. n_devices-1 to CUDA devices
+ * 0 .. n_devices-1 and enables peer access between all of them; hb200_init_slots does the same for an explicit device
+ * list (a device may appear twice: two slots on one GPU emulate two shards where only one GPU is present).  Slots
+ * already bound to the same devices are kept, so the calls are idempotent and may follow hb200_init(0).
+ * Every weight, activation and batch belongs to the slot that was current when it was created (hb200_set_slot
+ * selects it) and every call on such an object switches to its slot and device by itself; a batch takes weights and
+ * activations of its own slot only.  Row-sharded matmuls over the slots: upload the row range of every weight to each
+ * slot (hb200_weight_upload_rows), one batch per slot with hb200_batch_set_peers given the hb200_peer_alloc buffers of
+ * all slots as they are (same process: no handle exchange), then hb200_multi_batch_launch, which launches the batches
+ * one after the other from the calling thread; the kernels run concurrently on their GPUs and exchange flags. */
+HB200_API int hb200_init_multi(int n_devices);
+HB200_API int hb200_init_slots(const int *devices, int n_slots);
+HB200_API int hb200_set_slot(int slot);
+HB200_API int hb200_slot_count(void);
+/* Shuts every slot down. */
 HB200_API int hb200_shutdown(void);
 HB200_API const char *hb200_last_error(void);
 /* Number of streaming multiprocessors of the bound device (sizing of grids). */
@@ -314,6 +331,9 @@ HB200_API int hb200_batch_add(hb200_batch_t b, hb200_weight_t w, hb200_act_t a, 
 HB200_API int hb200_batch_seal(hb200_batch_t b);
 HB200_API int hb200_batch_launch(hb200_batch_t b, void *stream);
 HB200_API int hb200_batch_free(hb200_batch_t b);
+/* hb200_batch_launch of n batches (normally one per device slot), one after the other, on streams[i] (null: the
+ * default stream of each device). */
+HB200_API int hb200_multi_batch_launch(hb200_batch_t const *batches, int n, void *const *streams);
 /* Number of kernel launches one hb200_batch_launch performs. */
 HB200_API int hb200_batch_launch_count(hb200_batch_t b);
 /* A whole recorded step from host memory, the shape of GpuCompute's
