@@ -410,6 +410,18 @@ def matmul(w: Weight, x: np.ndarray) -> np.ndarray:
     return out[0] if x.ndim == 1 else out
 
 
+def matmul_fused(ws: list, x: np.ndarray) -> list:
+    """LlamaModel::matmul_fused2 / matmul_fused_qkv: several weights against one input; one upload and one
+    quantization of x.  Returns one f32 [seq, n_rows_i] (or [n_rows_i]) array per weight."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    x2 = x.reshape(1, -1) if x.ndim == 1 else x
+    outs = [np.zeros((x2.shape[0], w.n_rows), dtype=np.float32) for w in ws]
+    harr = (C.c_void_p * len(ws))(*[w._h for w in ws])
+    oarr = (C.c_void_p * len(ws))(*[C.c_void_p(o.ctypes.data) for o in outs])
+    check(_l.load().hb200_matmul_f32_fused(harr, len(ws), _np_ptr(x2), x2.shape[0], oarr))
+    return [o[0] if x.ndim == 1 else o for o in outs]
+
+
 def block_dots_i32(w: Weight, a_q8: np.ndarray) -> np.ndarray:
     """Exact int32 dots per (token, row, 32-column block): int32 [seq, n_rows, n_cols // 32]."""
     a_q8 = np.ascontiguousarray(a_q8, dtype=np.uint8)

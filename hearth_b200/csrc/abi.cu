@@ -1194,6 +1194,60 @@ extern "C" int hb200_matmul_f32(hb200_weight_t w, const float* x, size_t seq_len
     HB_GUARD_END
 }
 
+extern "C" int hb200_matmul_f32_fused(const hb200_weight_t* ws, size_t n_weights, const float* x, size_t seq_len, float* const* outs) {
+    HB_GUARD_BEGIN
+    if (!ws || !outs) { set_error("null weight or output list"); return HB200_ERR_NULL; }
+    if (n_weights == 0 || seq_len == 0) return HB200_OK;
+    size_t total = 0;
+    for (size_t i = 0; i < n_weights; i++) {
+        if (!ws[i]) { set_error("null weight handle at position %zu", i); return HB200_ERR_NULL; }
+        if (ws[i]->n_cols != ws[0]->n_cols || ws[i]->slot != ws[0]->slot) {
+            // matmul_fused2 / matmul_fused_qkv require one input for all weights (hearth-llm/src/model/matmul.rs:383-567)
+            set_error("Matmul dim mismatch: weight %zu has %zu columns, weight 0 has %zu", i, ws[i]->n_cols, ws[0]->n_cols);
+            return HB200_ERR_BAD_SHAPE;
+        }
+        if (ws[i]->n_rows && !outs[i]) { set_error("null output at position %zu", i); return HB200_ERR_NULL; }
+        total += (ws[i]->n_rows + 3) & ~(size_t)3;  // every weight's columns start 16-byte aligned
+    }
+    HB_USE(ws[0]);
+    int rc = need_ctx();
+    if (rc) return rc;
+    if (!x) { set_error("null input"); return HB200_ERR_NULL; }
+    if (total == 0) return HB200_OK;
+    const size_t n_cols = ws[0]->n_cols;
+    if ((rc = ensure_ctx_act(seq_len, n_cols))) return rc;
+    if ((rc = grow(&g_ctx.d_out, &g_ctx.d_out_bytes, seq_len * total * sizeof(float)))) return rc;
+    hb200_act* a = g_ctx.act;
+    cudaStream_t st = g_ctx.stream;
+    // one upload and one quantization of x for all weights, one buffer [seq_len][sum of rows] for all outputs
+    HB_CUDA(cudaMemcpyAsync(a->x, x, seq_len * n_cols * sizeof(float), cudaMemcpyHostToDevice, st));
+    bool quantized = false, tensor = false;
+    size_t off = 0;
+    for (size_t i = 0; i < n_weights; i++) {
+        hb200_weight* w = ws[i];
+        if (w->n_rows == 0) continue;
+        float* out_dev = reinterpret_cast<float*>(g_ctx.d_out) + off;
+        if (w->kind == KIND_Q4K || w->kind == KIND_Q6K) {
+            if ((rc = launch_kquant_gemv(w->kind, w->kq, w->d16, (int)w->n_rows, (int)w->n_cols, w->nb, w->n_panels, a->x, (int)seq_len,
+                                         out_dev, (int)total, g_ctx.sm_count, st))) return rc;
+        } else {
+            if (!quantized) {
+                if ((rc = launch_quantize_q8_0(a->x, (int)seq_len, (int)n_cols, a->q, a->d, a->sums, a->ld_q, a->ld_b, nullptr, 0, st))) return rc;
+                quantized = true;
+            }
+            tensor = tensor || dot_path(w, a, seq_len) != PATH_DP4A;
+            if ((rc = dot_rows_launch(w, a, seq_len, out_dev, total, st))) return rc;
+        }
+        HB_CUDA(cudaMemcpy2DAsync(outs[i], w->n_rows * sizeof(float), out_dev, total * sizeof(float), w->n_rows * sizeof(float), seq_len,
+                                  cudaMemcpyDeviceToHost, st));
+        off += (w->n_rows + 3) & ~(size_t)3;
+    }
+    HB_CUDA(cudaStreamSynchronize(st));
+    if (tensor) return check_device_status();
+    return HB200_OK;
+    HB_GUARD_END
+}
+
 extern "C" int hb200_block_dots_i32(hb200_weight_t w, const uint8_t* a_q8, size_t seq_len, size_t q8_stride, int32_t* out) {
     HB_GUARD_BEGIN
     HB_USE(w);

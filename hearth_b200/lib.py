@@ -83,6 +83,7 @@ SIGNATURES = {
     "hb200_dot_rows": (_int, [_vp, _vp, _vp]),
     "hb200_dot_rows_batched": (_int, [_vp, _vp, _sz, _sz, _vp]),
     "hb200_matmul_f32": (_int, [_vp, _vp, _sz, _vp]),
+    "hb200_matmul_f32_fused": (_int, [C.POINTER(_vp), _sz, _vp, _sz, C.POINTER(_vp)]),
     "hb200_block_dots_i32": (_int, [_vp, _vp, _sz, _sz, _vp]),
     "hb200_dot_rows_dev": (_int, [_vp, _vp, _sz, _vp, _sz, _vp]),
     "hb200_matmul_f32_dev": (_int, [_vp, _vp, _sz, _vp, _sz, _vp]),

@@ -276,6 +276,13 @@ HB200_API int hb200_dot_rows_batched(hb200_weight_t w, const uint8_t *a_q8, size
  * Q4_K / Q6_K (:270-280, :333-343).  x is [seq_len][n_cols]; out token-major. */
 HB200_API int hb200_matmul_f32(hb200_weight_t w, const float *x, size_t seq_len, float *out);
 
+/* LlamaModel::matmul_fused2 / matmul_fused_qkv (hearth-llm/src/model/matmul.rs:383-464, :469-567): several weights
+ * that read the same input (q|k|v, gate|up).  x is uploaded and quantized once, every weight runs against it, and
+ * outs[i] receives weight i's token-major [seq_len][n_rows_i] result.  All weights must have the same n_cols and live
+ * in the same device slot; unlike the reference's fused calls any mix of formats is accepted. */
+HB200_API int hb200_matmul_f32_fused(const hb200_weight_t *ws, size_t n_weights, const float *x, size_t seq_len,
+                                     float *const *outs);
+
 /* Per-(row, token, 32-block) int32 dots, out[seq_len][n_rows][n_cols/32]:
  * the `dot` / `sumi` integers of q1_0g128.rs:1033-1047, q2_0.rs:553-568,
  * q8_0.rs:164-168, exposed so the integer path can be checked bit for bit. */

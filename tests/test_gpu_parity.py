@@ -294,6 +294,36 @@ def test_device_calls_and_batch_match_host_calls(hb, oracle):
             W.free()
 
 
+def test_fused_matmul_is_one_upload_for_several_weights(hb, oracle):
+    """hb200_matmul_f32_fused (matmul_fused_qkv / matmul_fused2, hearth-llm/src/model/matmul.rs:383-567): q|k|v and a
+    K-quant weight against one input, each result equal to the single-weight call and to the oracle."""
+    n_cols = 2048
+    for seq in (1, 3, 70):
+        x = synth.activations(seq, n_cols, seed=50 + seq)
+        specs = [(Q1_0, 2048), (Q1_0, 1024), (Q2_0, 1022), (Q6_K, 40), (Q8_0, 5)]
+        ws = [synth.weights(dt, n, n_cols, seed=60 + i) for i, (dt, n) in enumerate(specs)]
+        Ws = [hb.Weight.upload(dt, n, n_cols, w) for (dt, n), w in zip(specs, ws)]
+        try:
+            outs = hb.matmul_fused(Ws, x)
+            for (dt, n), w, W, got in zip(specs, ws, Ws, outs):
+                if dt == Q6_K:
+                    want = oracle.matmul_kquant_f32(dt, w, x, n, n_cols)
+                else:
+                    want = oracle.dot_rows_batched(dt, w, oracle.quantize_q8_0(x), n, n_cols)
+                assert_bits_equal(got, want, f"fused, dtype {dt}, {seq} tokens")
+                assert_bits_equal(got, hb.matmul(W, x), "fused equals the single call")
+            with pytest.raises(hb.Hb200Error) as e:
+                other = hb.Weight.upload(Q1_0, 8, 256, synth.weights(Q1_0, 8, 256, seed=1))
+                try:
+                    hb.matmul_fused([Ws[0], other], x)
+                finally:
+                    other.free()
+            assert e.value.code == -4
+        finally:
+            for W in Ws:
+                W.free()
+
+
 # ---------------------------------------------------------------------------------- errors and empties
 
 def test_error_behaviour(hb):
