@@ -27,16 +27,17 @@ def _expected(oracle, seq, step):
                            for i, (dt, n, k) in enumerate(SPECS)], axis=1)
 
 
-def _build(hb, torch, world, devs, seq, wait, area):
+def _build(hb, torch, slots, devs, seq, wait, area):
     """Per slot: row shards, activations, a peer buffer, and a batch that stores into every slot's buffer."""
+    world = len(slots)
     total = sum(n for _, n, _ in SPECS)
     bufs = []
     for r in range(world):
-        hb.set_slot(r)
+        hb.set_slot(slots[r])
         bufs.append(hb.PeerBuffer.alloc(2 * area if area else seq * total))
     built = []
     for r in range(world):
-        hb.set_slot(r)
+        hb.set_slot(slots[r])
         with torch.cuda.device(devs[r]):
             batch = hb.Batch()
             batch.set_peers(r, bufs, wait=wait, area_floats=area)
@@ -74,7 +75,7 @@ def test_two_slots_on_one_device_emulate_two_shards(hb, oracle):
     assert hb.init_multi(devices=[0, 0]) >= 2      # slot 0 is the one the other tests use; slot 1 joins it
     seq = 2
     total = sum(n for _, n, _ in SPECS)
-    bufs, built = _build(hb, torch, 2, [dev, dev], seq, wait=False, area=0)
+    bufs, built = _build(hb, torch, [0, 1], [dev, dev], seq, wait=False, area=0)
     try:
         # an object of another slot is refused, not silently used on the wrong device
         with pytest.raises(hb.Hb200Error) as e:
@@ -104,11 +105,13 @@ def test_two_devices_driven_by_one_host_thread(hb, oracle):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     devs = [torch.device("cuda:0"), torch.device("cuda:1")]
-    hb.init_multi(2)
+    # slot 1 may already be a second slot on device 0 (the emulation test above): the second GPU becomes slot 2
+    hb.init_multi(devices=[0, 0, 1])
+    slots = [0, 2]
     seq = 2
     total = sum(n for _, n, _ in SPECS)
     area = seq * total + (-(seq * total)) % 4
-    bufs, built = _build(hb, torch, 2, devs, seq, wait=True, area=area)
+    bufs, built = _build(hb, torch, slots, devs, seq, wait=True, area=area)
     try:
         for step in range(5):
             want = _expected(oracle, seq, step)
@@ -126,8 +129,8 @@ def test_two_devices_driven_by_one_host_thread(hb, oracle):
             for r, b in enumerate(bufs):
                 got = b.tensor(devs[r])[a * area:a * area + seq * total].view(seq, total).cpu().numpy()
                 assert (got.view(np.uint32) == want.view(np.uint32)).all(), f"device {r}, step {step}"
-        for r in range(2):
-            hb.set_slot(r)
+        for sl in slots:
+            hb.set_slot(sl)
             hb.check_status()
     finally:
         _free(hb, bufs, built)
