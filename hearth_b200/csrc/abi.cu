@@ -1532,7 +1532,7 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
     // K-quant ops: per (kind, tokens per pass) one list of matrices whose items (32-row panel x token tile) are numbered
     // consecutively, and contiguous runs of items per CTA balanced by rounds.
     for (int kind : {KIND_Q4K, KIND_Q6K})
-        for (int mt : {1, 2, 4}) {
+        for (int mt : {1, 2, 4, 8}) {
             std::vector<KqMat> mats;
             std::vector<int> cost;
             int n_items = 0;

@@ -65,10 +65,17 @@ struct KqGeom {
     static constexpr int TERMS = BLK_PER_ROUND * TERMS_PER_BLK;       // ordered terms per row and round
 };
 
+// Term buffers: two, so that the ordered replay of a round runs under the arithmetic of the next one - except for the
+// eight-token pass, whose round is long (eight tokens of arithmetic per expanded weight) and whose replay keeps all
+// 256 threads busy (one chain per (token, row)): there the replay follows its round directly and one buffer is enough,
+// which is what lets eight tokens of x and of terms fit in shared memory at all.
+template <int MT>
+constexpr int kq_term_bufs() { return MT >= 8 ? 1 : 2; }
+
 template <int KIND, int MT>
 struct KqSmem {
     alignas(16) float x[2][MT][KqGeom<KIND, MT>::CH];
-    alignas(16) float4 term[2][KqGeom<KIND, MT>::TERMS / 4][MT][32];  // four consecutive ordered terms of a row side by side
+    alignas(16) float4 term[kq_term_bufs<MT>()][KqGeom<KIND, MT>::TERMS / 4][MT][32];  // four consecutive ordered terms of a row side by side
 };
 
 // What one launch works through: `mats` (device memory) or, when mats is null, the one matrix `single`.  Items are
@@ -154,7 +161,7 @@ struct KqStep {
 // Resident CTAs per SM the register allocation of the Q6_K kernels is held to (0: none given).  The Q4_K kernels are
 // left to the allocator: told any number it schedules more aggressively and spills.
 template <int KIND, int MT>
-constexpr int kq_min_ctas() { return KIND == KIND_Q6K ? (MT == 1 ? 3 : 2) : 0; }
+constexpr int kq_min_ctas() { return KIND == KIND_Q6K ? (MT == 1 ? 3 : (MT >= 8 ? 0 : 2)) : 0; }
 
 template <int KIND, int MT>
 __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_kernel(const __grid_constant__ KqLaunch L) {
@@ -299,9 +306,11 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
 #pragma unroll
             for (int i = 0; i < 9; i++) wn[i] = __ldg(pn + i * 32);
         }
-        if (t > 0) replay(prev, (t - 1) & 1);
+        constexpr bool LATE_REPLAY = kq_term_bufs<MT>() == 2;  // replay one round behind, from the other term buffer
+        if (LATE_REPLAY && t > 0) replay(prev, (t - 1) & 1);
 
         const int buf = t & 1;
+        const int tbuf = LATE_REPLAY ? buf : 0;
         const int nblk = cur.nblk, r = cur.r;
         if (KIND == KIND_Q4K) {
             const int blk = r * 8 + warp;
@@ -328,10 +337,7 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
                         const float scf = __fmul_rn((float)sc, d), mnf = __fmul_rn((float)mn, dmin);
                         const float c0 = __fmul_rn(-8388608.0f, scf);
                         const uint32_t qw[4] = {w[1 + sb].x, w[1 + sb].y, w[1 + sb].z, w[1 + sb].w};
-                        float lanes[MT][8];
-#pragma unroll
-                        for (int tt = 0; tt < 4; tt++) {  // elements 8tt..8tt+7 of the sub-block live in word tt
-                            float v[8];
+                        auto expand8 = [&](int tt, float (&v)[8]) {  // elements 8tt..8tt+7 of the sub-block live in word tt
                             if (FAST) {
                                 const uint32_t ev = qw[tt] & 0x0F0F0F0Fu, od = (qw[tt] >> 4) & 0x0F0F0F0Fu;  // elements 0,2,4,6 / 1,3,5,7
 #pragma unroll
@@ -343,6 +349,32 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
 #pragma unroll
                                 for (int j = 0; j < 8; j++) v[j] = __fsub_rn(__fmul_rn((float)((qw[tt] >> (4 * j)) & 0xF), scf), mnf);
                             }
+                        };
+                        if (MT >= 8) {
+                            // Eight tokens: the 32 values of the sub-block are expanded once into registers, then every token
+                            // runs its eight fused-multiply-add chains over them (one set of chains alive at a time).
+                            float vv[4][8];
+#pragma unroll
+                            for (int tt = 0; tt < 4; tt++) expand8(tt, vv[tt]);
+#pragma unroll
+                            for (int m = 0; m < MT; m++) {
+                                float lanes1[8];
+#pragma unroll
+                                for (int tt = 0; tt < 4; tt++) {
+                                    const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][warp * 256 + sb * 32 + tt * 8]);
+                                    const float4 x0 = xp[0], x1 = xp[1];
+                                    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                                    for (int j = 0; j < 8; j++) lanes1[j] = fmaf(vv[tt][j], xs[j], tt == 0 ? 0.0f : lanes1[j]);
+                                }
+                                reinterpret_cast<float*>(&sm.term[tbuf][warp * 2 + (sb >> 2)][m][lane])[sb & 3] = reduce8(lanes1);
+                            }
+                        } else {
+                        float lanes[MT][8];
+#pragma unroll
+                        for (int tt = 0; tt < 4; tt++) {
+                            float v[8];
+                            expand8(tt, v);
 #pragma unroll
                             for (int m = 0; m < MT; m++) {
                                 const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][warp * 256 + sb * 32 + tt * 8]);
@@ -354,7 +386,8 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
                         }
 #pragma unroll
                         for (int m = 0; m < MT; m++)  // scalar stores into the float4 slots: no registers held across sub-blocks
-                            reinterpret_cast<float*>(&sm.term[buf][warp * 2 + (sb >> 2)][m][lane])[sb & 3] = reduce8(lanes[m]);
+                            reinterpret_cast<float*>(&sm.term[tbuf][warp * 2 + (sb >> 2)][m][lane])[sb & 3] = reduce8(lanes[m]);
+                        }
                     }
                 };
                 if (fabsf(d) <= 65504.0f) block_body(std::true_type{});
@@ -408,7 +441,7 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
                                 lanes[4] = fmaf(qf[8 * hh + 4], x1.x, 0.0f); lanes[5] = fmaf(qf[8 * hh + 5], x1.y, 0.0f);
                                 lanes[6] = fmaf(qf[8 * hh + 6], x1.z, 0.0f); lanes[7] = fmaf(qf[8 * hh + 7], x1.w, 0.0f);
                                 tq[m][u & 3] = reduce8(lanes);
-                                if ((u & 3) == 3) sm.term[buf][(uq0 + h) * 2 + (u >> 2)][m][lane] = make_float4(tq[m][0], tq[m][1], tq[m][2], tq[m][3]);
+                                if ((u & 3) == 3) sm.term[tbuf][(uq0 + h) * 2 + (u >> 2)][m][lane] = make_float4(tq[m][0], tq[m][1], tq[m][2], tq[m][3]);
                             }
                         }
                         if (g >= 1) w[3 * h + g - 1] = __ldg(pn + (3 * h + g - 1) * 32);  // group g ends in the quarter's piece g - 1
@@ -427,7 +460,10 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
         }
         prev = cur;
         cur = next_step(cur, gitem);
-        if (gitem >= it1) {
+        if (!LATE_REPLAY) {  // the round's terms are complete after this barrier; the next round's barrier protects them again
+            __syncthreads();
+            replay(prev, 0);
+        } else if (gitem >= it1) {
             __syncthreads();
             replay(prev, t & 1);
         }
@@ -436,7 +472,7 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
 
 // Resident CTAs per SM of each instantiation, measured by the occupancy API at prepare time: the grid of the
 // persistent kernel is sized to exactly one wave.
-int g_kq_ctas[2][5] = {};
+int g_kq_ctas[2][9] = {};
 
 template <int KIND, int MT>
 int launch_mt(const KqLaunch& L, int grid, cudaStream_t st) {
@@ -450,6 +486,7 @@ template <int KIND>
 int launch_kind(const KqLaunch& L, int mt, int grid, cudaStream_t st) {
     if (mt == 1) return launch_mt<KIND, 1>(L, grid, st);
     if (mt == 2) return launch_mt<KIND, 2>(L, grid, st);
+    if (mt == 8) return launch_mt<KIND, 8>(L, grid, st);
     return launch_mt<KIND, 4>(L, grid, st);
 }
 
@@ -469,9 +506,11 @@ int kquant_prepare() {
     if ((rc = prepare_one<KIND_Q4K, 1>())) return rc;
     if ((rc = prepare_one<KIND_Q4K, 2>())) return rc;
     if ((rc = prepare_one<KIND_Q4K, 4>())) return rc;
+    if ((rc = prepare_one<KIND_Q4K, 8>())) return rc;
     if ((rc = prepare_one<KIND_Q6K, 1>())) return rc;
     if ((rc = prepare_one<KIND_Q6K, 2>())) return rc;
     if ((rc = prepare_one<KIND_Q6K, 4>())) return rc;
+    if ((rc = prepare_one<KIND_Q6K, 8>())) return rc;
     return 0;
 }
 
@@ -489,7 +528,8 @@ int launch_kquant_repack(int kind, const uint8_t* raw, size_t row_bytes, int n_r
     return 0;
 }
 
-int kquant_tokens_per_pass(int seq_len) { return seq_len == 1 ? 1 : (seq_len == 2 ? 2 : 4); }
+// One pass over the weights serves 1, 2, 4 or 8 tokens: from eight tokens on the weights are expanded once per eight.
+int kquant_tokens_per_pass(int seq_len) { return seq_len == 1 ? 1 : (seq_len == 2 ? 2 : (seq_len < 8 ? 4 : 8)); }
 
 int kquant_items(int n_panels, int seq_len) {
     const int mt = kquant_tokens_per_pass(seq_len);
