@@ -47,8 +47,8 @@ def _stale(target: str, deps: list[str]) -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """HB200_NVCC_EXTRA in the environment adds flags (e.g. -DHB200_TC_CHECK for the self-checking tensor-core
-    kernels); a build with extra flags always recompiles everything."""
+    """HB200_NVCC_EXTRA in the environment adds nvcc flags (a -D switch for a measurement build, -Xptxas options); a
+    build with extra flags always recompiles everything."""
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()
     extra = os.environ.get("HB200_NVCC_EXTRA", "").split()

@@ -128,3 +128,19 @@ def test_token_count_limit_is_a_clear_error(lib):
     assert lib.hb200_act_create(65536, 128, C.byref(h)) == -8
     assert b"65535" in lib.hb200_last_error()
     assert lib.hb200_act_create(0, 128, C.byref(h)) == -4
+
+
+def test_device_slots_without_a_device(lib):
+    """hb200_init_multi / hb200_init_slots / hb200_set_slot: clear errors when no GPU is present, nothing bound."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present; this test is about the device-less case")
+    assert lib.hb200_slot_count() == 0
+    assert lib.hb200_init_multi(2) == -2
+    assert lib.hb200_init_multi(0) == -4 and lib.hb200_init_multi(9) == -4
+    arr = (C.c_int * 2)(0, 0)
+    assert lib.hb200_init_slots(arr, 2) == -2
+    assert lib.hb200_init_slots(None, 2) == -5
+    assert lib.hb200_set_slot(1) == -1 and b"slot 1" in lib.hb200_last_error()
+    assert lib.hb200_slot_count() == 0
+    assert lib.hb200_multi_batch_launch(None, 0, None) == -5
