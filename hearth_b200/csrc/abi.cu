@@ -134,6 +134,8 @@ struct Context {
     std::map<size_t, hb200_act_t> acts;       // by width
     int* d_status = nullptr;  // device word set by kernels whose bounded waits expire
     void* d_argmax = nullptr;  // ticket + partial results of the argmax kernel, then one result word
+    uint8_t* d_terms = nullptr;  // per-block terms of the two-phase f32-activation matvec
+    size_t d_terms_bytes = 0;
     cudaStream_t copy_in = nullptr, copy_out = nullptr;  // the pipelined host path: uploads and readbacks beside the compute stream
 };
 // One context per device slot.  hb200_init binds slot 0; hb200_init_multi binds slots 0 .. n-1 (normally to devices
@@ -441,6 +443,7 @@ extern "C" int hb200_shutdown(void) {
         if (c.d_out) cudaFree(c.d_out);
         if (c.d_status) cudaFree(c.d_status);
         if (c.d_argmax) cudaFree(c.d_argmax);
+        if (c.d_terms) cudaFree(c.d_terms);
         if (c.stream) cudaStreamDestroy(c.stream);
         if (c.copy_in) cudaStreamDestroy(c.copy_in);
         if (c.copy_out) cudaStreamDestroy(c.copy_out);
@@ -961,6 +964,21 @@ extern "C" int hb200_matmul_f32_dev(hb200_weight_t w, hb200_act_t a, size_t seq_
 
 // ------------------------------------------------- f32-activation matmul --
 
+// One kernel when (panels x tokens) fills the GPU, otherwise terms and ordered sums in two kernels, so that a single
+// decode matvec spreads over panels x rounds CTAs instead of panels.  The scratch grows on demand (a synchronising
+// allocation the first time a larger product is asked for).
+static int f32act_launch(hb200_weight_t w, const float* x_dev, size_t seq_len, float* out_dev, size_t ld_out, bool accumulate, cudaStream_t st) {
+    const size_t pairs = (size_t)w->n_panels * seq_len;
+    const int rounds = (w->nb + 7) / 8;
+    if (pairs >= (size_t)g_ctx.sm_count || rounds < 2)
+        return launch_f32act(w->kind, w->bits, w->scales, (int)w->n_rows, (int)w->n_cols, w->nb, w->n_panels, x_dev, (int)seq_len, out_dev,
+                             (int)ld_out, accumulate, st);
+    int rc = grow(&g_ctx.d_terms, &g_ctx.d_terms_bytes, f32act_terms_bytes(w->kind, w->nb, w->n_panels, (int)seq_len));
+    if (rc) return rc;
+    return launch_f32act_two_phase(w->kind, w->bits, w->scales, (int)w->n_rows, (int)w->n_cols, w->nb, w->n_panels, x_dev, (int)seq_len,
+                                   out_dev, (int)ld_out, accumulate, reinterpret_cast<float*>(g_ctx.d_terms), st);
+}
+
 static int f32act_check(hb200_weight_t w, size_t seq_len, size_t ld_out) {
     if (!w) { set_error("null weight handle"); return HB200_ERR_NULL; }
     if (w->dtype == HB200_PTQ1_0 || (w->kind != KIND_Q1 && w->kind != KIND_Q2)) {
@@ -981,8 +999,7 @@ extern "C" int hb200_matmul_f32act_dev(hb200_weight_t w, const float* x_dev, siz
     if ((rc = f32act_check(w, seq_len, ld_out))) return rc;
     if (!x_dev || !out_dev) { set_error("null pointer"); return HB200_ERR_NULL; }
     if (seq_len == 0 || w->n_rows == 0) return HB200_OK;
-    return launch_f32act(w->kind, w->bits, w->scales, (int)w->n_rows, (int)w->n_cols, w->nb, w->n_panels, x_dev, (int)seq_len,
-                         out_dev, (int)ld_out, accumulate != 0, (cudaStream_t)stream);
+    return f32act_launch(w, x_dev, seq_len, out_dev, ld_out, accumulate != 0, (cudaStream_t)stream);
     HB_GUARD_END
 }
 
@@ -1000,8 +1017,7 @@ extern "C" int hb200_matmul_f32act(hb200_weight_t w, const float* x, size_t seq_
     cudaStream_t st = g_ctx.stream;
     HB_CUDA(cudaMemcpyAsync(g_ctx.d_in, x, in_bytes, cudaMemcpyHostToDevice, st));
     if (accumulate) HB_CUDA(cudaMemcpyAsync(g_ctx.d_out, out, out_bytes, cudaMemcpyHostToDevice, st));
-    if ((rc = launch_f32act(w->kind, w->bits, w->scales, (int)w->n_rows, (int)w->n_cols, w->nb, w->n_panels, (const float*)g_ctx.d_in,
-                            (int)seq_len, (float*)g_ctx.d_out, (int)w->n_rows, accumulate != 0, st))) return rc;
+    if ((rc = f32act_launch(w, (const float*)g_ctx.d_in, seq_len, (float*)g_ctx.d_out, w->n_rows, accumulate != 0, st))) return rc;
     HB_CUDA(cudaMemcpyAsync(out, g_ctx.d_out, out_bytes, cudaMemcpyDeviceToHost, st));
     HB_CUDA(cudaStreamSynchronize(st));
     return HB200_OK;

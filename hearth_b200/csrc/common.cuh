@@ -218,6 +218,12 @@ int launch_argmax(const float* x, size_t n, void* scratch, uint32_t* out_dev, cu
 int launch_f32act(int kind, const uint4* bits, const void* scales, int n_rows, int n_cols, int nb, int n_panels, const float* x,
                   int seq_len, float* out, int ld_out, bool accumulate, cudaStream_t st);
 
+// The same result in two kernels, for launches that would leave most SMs idle: per-block terms into `terms`
+// (f32act_terms_bytes() of device memory), then the ordered sums.
+size_t f32act_terms_bytes(int kind, int nb, int n_panels, int seq_len);
+int launch_f32act_two_phase(int kind, const uint4* bits, const void* scales, int n_rows, int n_cols, int nb, int n_panels,
+                            const float* x, int seq_len, float* out, int ld_out, bool accumulate, float* terms, cudaStream_t st);
+
 // tc_peak.cu: dense kind::i8 tensor-core rate of this GPU, measured (TOP/s).
 int measure_i8_peak(int sm_count, int* status, cudaStream_t st, double* tops);
 

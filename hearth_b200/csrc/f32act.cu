@@ -168,7 +168,97 @@ __global__ void __launch_bounds__(FA_THREADS) f32act_kernel(const __grid_constan
     }
 }
 
+// Two-phase form for launches with too few (panel, token) pairs to fill the GPU (one decode matvec: 48 panels of a
+// 12288-row matrix on 148 SMs).  The per-block terms are independent; only their addition is ordered.  Phase one takes
+// one round of eight blocks of one panel per CTA, so the grid grows by the number of rounds, and leaves every term in
+// a scratch array; phase two adds each row's terms in block order.  Same terms, same order, same bits.
+// terms[((tok * n_panels + panel) * nb + blk) * ROWS + row]
+template <int KIND>
+__global__ void __launch_bounds__(FA_THREADS) f32act_terms_kernel(const __grid_constant__ FaArgs a, float* __restrict__ terms) {
+    constexpr int RPG = rows_per_group(KIND);
+    constexpr int SPT = scales_per_tile(KIND);
+    constexpr int ROWS = 32 * RPG;
+    __shared__ __align__(16) float xs[FA_WARPS * 128];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int panel = blockIdx.x, r = blockIdx.y, tok = blockIdx.z;
+    const int nb = a.nb;
+    const float* xr = a.x + (size_t)tok * a.n_cols;
+    const bool vec_ok = ((a.n_cols & 3) == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
+    {
+        const int c = r * FA_WARPS * 128 + tid * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c + 3 < nb * 128) {
+            if (vec_ok) v = *reinterpret_cast<const float4*>(xr + c);
+            else v = make_float4(xr[c], xr[c + 1], xr[c + 2], xr[c + 3]);
+        }
+        *reinterpret_cast<float4*>(&xs[tid * 4]) = v;
+    }
+    __syncthreads();
+    const int blk = r * FA_WARPS + warp;
+    if (blk >= nb) return;
+    const size_t tile = (size_t)panel * nb + blk;
+    uint32_t w[32];
+#pragma unroll
+    for (int p = 0; p < 8; p++) {
+        const uint4 v = __ldg(a.bits + (tile * 8 + p) * 32 + lane);
+        w[4 * p] = v.x; w[4 * p + 1] = v.y; w[4 * p + 2] = v.z; w[4 * p + 3] = v.w;
+    }
+    float tree[RPG];
+    Node<KIND, 1, 0>::eval(w, &xs[warp * 128], tree);
+    uint32_t sc[SPT / 2];
+    if (KIND == KIND_Q1) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.scales) + tile * 32 + lane);
+        sc[0] = v.x; sc[1] = v.y; sc[2] = v.z; sc[3] = v.w;
+    } else {
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(a.scales) + tile * 32 + lane);
+        sc[0] = v.x; sc[1] = v.y;
+    }
+    float* dst = terms + (((size_t)tok * a.n_panels + panel) * nb + blk) * ROWS + lane * RPG;
+#pragma unroll
+    for (int rr = 0; rr < RPG; rr++) dst[rr] = __fmul_rn(tree[rr], shader_h2f((sc[rr >> 1] >> (16 * (rr & 1))) & 0xffffu));
+}
+
+// One thread per (token, row): the terms of its row in block order.
+template <int KIND>
+__global__ void __launch_bounds__(256) f32act_sum_kernel(const __grid_constant__ FaArgs a, const float* __restrict__ terms) {
+    constexpr int ROWS = 32 * rows_per_group(KIND);
+    const int grow = blockIdx.x * 256 + threadIdx.x, tok = blockIdx.y;
+    if (grow >= a.n_rows) return;
+    const int panel = grow / ROWS, row = grow % ROWS;
+    const float* t = terms + ((size_t)tok * a.n_panels + panel) * a.nb * ROWS + row;
+    float acc = 0.0f;
+    for (int b = 0; b < a.nb; b++) acc = __fadd_rn(acc, t[(size_t)b * ROWS]);
+    float* o = a.out + (size_t)tok * a.ld_out + grow;
+    *o = a.accumulate ? __fadd_rn(*o, acc) : acc;
+}
+
 }  // namespace
+
+size_t f32act_terms_bytes(int kind, int nb, int n_panels, int seq_len) {
+    return (size_t)seq_len * n_panels * nb * 32 * rows_per_group(kind) * sizeof(float);
+}
+
+int launch_f32act_two_phase(int kind, const uint4* bits, const void* scales, int n_rows, int n_cols, int nb, int n_panels,
+                            const float* x, int seq_len, float* out, int ld_out, bool accumulate, float* terms, cudaStream_t st) {
+    if (n_rows <= 0 || seq_len <= 0) return 0;
+    FaArgs a;
+    a.bits = bits; a.scales = scales; a.x = x; a.out = out;
+    a.n_rows = n_rows; a.n_cols = n_cols; a.nb = nb; a.n_panels = n_panels; a.seq_len = seq_len; a.ld_out = ld_out;
+    a.accumulate = accumulate ? 1 : 0;
+    const int rounds = (nb + FA_WARPS - 1) / FA_WARPS;
+    if (rounds > 0) {
+        const dim3 g1(n_panels, rounds, seq_len);
+        if (kind == KIND_Q1) f32act_terms_kernel<KIND_Q1><<<g1, FA_THREADS, 0, st>>>(a, terms);
+        else if (kind == KIND_Q2) f32act_terms_kernel<KIND_Q2><<<g1, FA_THREADS, 0, st>>>(a, terms);
+        else { set_error("f32-activation matmul: kind %d has no shader counterpart", kind); return -7; }
+        HB_CUDA(cudaGetLastError());
+    }
+    const dim3 g2((n_rows + 255) / 256, seq_len);
+    if (kind == KIND_Q1) f32act_sum_kernel<KIND_Q1><<<g2, 256, 0, st>>>(a, terms);
+    else f32act_sum_kernel<KIND_Q2><<<g2, 256, 0, st>>>(a, terms);
+    HB_CUDA(cudaGetLastError());
+    return 0;
+}
 
 int launch_f32act(int kind, const uint4* bits, const void* scales, int n_rows, int n_cols, int nb, int n_panels, const float* x,
                   int seq_len, float* out, int ld_out, bool accumulate, cudaStream_t st) {
