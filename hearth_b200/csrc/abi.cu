@@ -955,7 +955,7 @@ extern "C" int hb200_matmul_f32_dev(hb200_weight_t w, hb200_act_t a, size_t seq_
     cudaStream_t st = (cudaStream_t)stream;
     if (w->kind == KIND_Q4K || w->kind == KIND_Q6K)
         return launch_kquant_gemv(w->kind, w->kq, w->d16, (int)w->n_rows, (int)w->n_cols, w->nb, w->n_panels, a->x, (int)seq_len,
-                                  out_dev, (int)ld_out, g_ctx.sm_count, st);
+                                  out_dev, (int)ld_out, g_ctx.sm_count, st, g_ctx.d_status);
     rc = launch_quantize_q8_0(a->x, (int)seq_len, (int)a->n_cols, a->q, a->d, a->sums, a->ld_q, a->ld_b, nullptr, 0, st);
     if (rc) return rc;
     return dot_rows_launch(w, a, seq_len, out_dev, ld_out, st);
@@ -1245,7 +1245,7 @@ extern "C" int hb200_matmul_f32_fused(const hb200_weight_t* ws, size_t n_weights
         float* out_dev = reinterpret_cast<float*>(g_ctx.d_out) + off;
         if (w->kind == KIND_Q4K || w->kind == KIND_Q6K) {
             if ((rc = launch_kquant_gemv(w->kind, w->kq, w->d16, (int)w->n_rows, (int)w->n_cols, w->nb, w->n_panels, a->x, (int)seq_len,
-                                         out_dev, (int)total, g_ctx.sm_count, st))) return rc;
+                                         out_dev, (int)total, g_ctx.sm_count, st, g_ctx.d_status))) return rc;
         } else {
             if (!quantized) {
                 if ((rc = launch_quantize_q8_0(a->x, (int)seq_len, (int)n_cols, a->q, a->d, a->sums, a->ld_q, a->ld_b, nullptr, 0, st))) return rc;
@@ -1647,7 +1647,7 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
         if ((rc = (g.rows ? launch_gemm_tcr_list : launch_gemm_tc_list)(g.kind, g.mats_dev, g.chunks_dev, g.n_tiles, g.grid, g_ctx.d_status, st)))
             return rc;
     for (const hb200_batch::KqGroup& g : b->kq_groups)
-        if ((rc = launch_kquant_gemv_list(g.kind, g.mt, g.mats_dev, g.chunks_dev, g.n_items, g.grid, st))) return rc;
+        if ((rc = launch_kquant_gemv_list(g.kind, g.mt, g.mats_dev, g.chunks_dev, g.n_items, g.grid, st, g_ctx.d_status))) return rc;
     return HB200_OK;
     HB_GUARD_END
 }

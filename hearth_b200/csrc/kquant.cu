@@ -36,6 +36,9 @@ namespace hb200 {
 namespace {
 
 constexpr int KQ_THREADS = 256;
+#ifndef KQ_M8_TOKEN_OUTER
+#define KQ_M8_TOKEN_OUTER 1
+#endif
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -45,10 +48,14 @@ __device__ __forceinline__ void cp_async_commit_wait_all() {
     asm volatile("cp.async.commit_group;\n cp.async.wait_group 0;" ::: "memory");
 }
 __device__ __forceinline__ float h2f_bits(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)h)); }
-__device__ __forceinline__ float reduce8(const float* l) {
-    const float q0 = __fadd_rn(l[0], l[4]), q1 = __fadd_rn(l[1], l[5]);
-    const float q2 = __fadd_rn(l[2], l[6]), q3 = __fadd_rn(l[3], l[7]);
-    return __fadd_rn(__fadd_rn(q0, q2), __fadd_rn(q1, q3));
+// Reduction of the eight accumulation lanes in the order ((l0+l4)+(l2+l6))+((l1+l5)+(l3+l7)), lanes held as the pairs
+// (l0,l1) (l2,l3) (l4,l5) (l6,l7): three packed adds (add.rn.f32x2, two independently rounded fp32 sums per instruction
+// on sm_100) and one scalar add.
+__device__ __forceinline__ float reduce8(const float2* l) {
+    const float2 q01 = __fadd2_rn(l[0], l[2]);  // (l0+l4, l1+l5)
+    const float2 q23 = __fadd2_rn(l[1], l[3]);  // (l2+l6, l3+l7)
+    const float2 h = __fadd2_rn(q01, q23);      // (q0+q2, q1+q3)
+    return __fadd_rn(h.x, h.y);
 }
 
 template <int KIND, int MT = 1>
@@ -87,6 +94,7 @@ struct KqLaunch {
     const int* chunks;
     int n_items;
     uint32_t magic;  // 0x4B000000 (2^23 as a float), kept a run-time value: as a literal it was re-materialised before every byte permute
+    int* status;     // device word for an expired bounded wait (may be null)
     KqMat single;
 };
 using KqArgs = KqMat;
@@ -301,8 +309,11 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
             pn = piece_ptr(nxt);
             if (KIND == KIND_Q6K) dnext = q6_d(nxt);
         }
-        uint4 wn[KIND == KIND_Q4K ? 9 : 1];
-        if (KIND == KIND_Q4K) {  // fetched up front into a second set of registers (see the note at w[])
+        // Q4_K with eight tokens per pass: a round is long (every piece serves eight tokens), so each piece is refilled in
+        // place as soon as its sub-block has been expanded and the second register set goes to the token chains instead.
+        constexpr bool Q4_REFILL = (KIND == KIND_Q4K) && (MT >= 8);
+        uint4 wn[(KIND == KIND_Q4K && !Q4_REFILL) ? 9 : 1];
+        if (KIND == KIND_Q4K && !Q4_REFILL) {  // fetched up front into a second set of registers (see the note at w[])
 #pragma unroll
             for (int i = 0; i < 9; i++) wn[i] = __ldg(pn + i * 32);
         }
@@ -318,6 +329,7 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
                 const float d = h2f_bits(w[0].x & 0xffffu), dmin = h2f_bits(w[0].x >> 16);
                 const uint32_t sw[3] = {w[0].y, w[0].z, w[0].w};  // the 12 scale bytes
                 const uint32_t magic = L.magic;
+                if (Q4_REFILL) w[0] = __ldg(pn);
                 // FAST: nibble -> float without a shift, a mask and a convert per weight: a byte permute drops the nibble
                 // into the mantissa of 2^23 (0x4B0000nn = 8388608 + n), and fma(2^23 + n, scf, -(2^23 * scf)) is the
                 // correctly rounded n * scf, i.e. the same bits as the separate multiply (2^23 * scf is exact).  That
@@ -337,53 +349,63 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
                         const float scf = __fmul_rn((float)sc, d), mnf = __fmul_rn((float)mn, dmin);
                         const float c0 = __fmul_rn(-8388608.0f, scf);
                         const uint32_t qw[4] = {w[1 + sb].x, w[1 + sb].y, w[1 + sb].z, w[1 + sb].w};
-                        auto expand8 = [&](int tt, float (&v)[8]) {  // elements 8tt..8tt+7 of the sub-block live in word tt
+                        // Every multiply-add, subtract and add below works on two neighbouring elements at once
+                        // (fma.rn.f32x2 / add.rn.f32x2: each half rounded as the scalar instruction rounds it), which halves
+                        // the issue slots of the arithmetic; a - b is computed as a + (-b), the same value and rounding.
+                        const float2 scf2 = make_float2(scf, scf), c02 = make_float2(c0, c0), nmn2 = make_float2(-mnf, -mnf);
+                        auto expand8 = [&](int tt, float2 (&v)[4]) {  // elements 8tt..8tt+7 of the sub-block live in word tt
                             if (FAST) {
                                 const uint32_t ev = qw[tt] & 0x0F0F0F0Fu, od = (qw[tt] >> 4) & 0x0F0F0F0Fu;  // elements 0,2,4,6 / 1,3,5,7
 #pragma unroll
-                                for (int j = 0; j < 8; j++) {
-                                    const float nf = __uint_as_float(__byte_perm((j & 1) ? od : ev, magic, 0x7540u + (j >> 1)));
-                                    v[j] = __fsub_rn(fmaf(nf, scf, c0), mnf);
+                                for (int p = 0; p < 4; p++) {
+                                    const float2 nf = make_float2(__uint_as_float(__byte_perm(ev, magic, 0x7540u + p)),
+                                                                  __uint_as_float(__byte_perm(od, magic, 0x7540u + p)));
+                                    v[p] = __fadd2_rn(__ffma2_rn(nf, scf2, c02), nmn2);
                                 }
                             } else {
 #pragma unroll
-                                for (int j = 0; j < 8; j++) v[j] = __fsub_rn(__fmul_rn((float)((qw[tt] >> (4 * j)) & 0xF), scf), mnf);
+                                for (int p = 0; p < 4; p++)
+                                    v[p] = make_float2(__fsub_rn(__fmul_rn((float)((qw[tt] >> (8 * p)) & 0xF), scf), mnf),
+                                                       __fsub_rn(__fmul_rn((float)((qw[tt] >> (8 * p + 4)) & 0xF), scf), mnf));
                             }
                         };
-                        if (MT >= 8) {
+                        const float2 zero2 = make_float2(0.0f, 0.0f);
+                        if (MT >= 8 && KQ_M8_TOKEN_OUTER) {
                             // Eight tokens: the 32 values of the sub-block are expanded once into registers, then every token
                             // runs its eight fused-multiply-add chains over them (one set of chains alive at a time).
-                            float vv[4][8];
+                            float2 vv[4][4];
 #pragma unroll
                             for (int tt = 0; tt < 4; tt++) expand8(tt, vv[tt]);
+                            if (Q4_REFILL) w[1 + sb] = __ldg(pn + (1 + sb) * 32);
 #pragma unroll
                             for (int m = 0; m < MT; m++) {
-                                float lanes1[8];
+                                float2 lanes1[4];
 #pragma unroll
                                 for (int tt = 0; tt < 4; tt++) {
                                     const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][warp * 256 + sb * 32 + tt * 8]);
                                     const float4 x0 = xp[0], x1 = xp[1];
-                                    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                                    const float2 xs[4] = {make_float2(x0.x, x0.y), make_float2(x0.z, x0.w), make_float2(x1.x, x1.y), make_float2(x1.z, x1.w)};
 #pragma unroll
-                                    for (int j = 0; j < 8; j++) lanes1[j] = fmaf(vv[tt][j], xs[j], tt == 0 ? 0.0f : lanes1[j]);
+                                    for (int p = 0; p < 4; p++) lanes1[p] = __ffma2_rn(vv[tt][p], xs[p], tt == 0 ? zero2 : lanes1[p]);
                                 }
                                 reinterpret_cast<float*>(&sm.term[tbuf][warp * 2 + (sb >> 2)][m][lane])[sb & 3] = reduce8(lanes1);
                             }
                         } else {
-                        float lanes[MT][8];
+                        float2 lanes[MT][4];
 #pragma unroll
                         for (int tt = 0; tt < 4; tt++) {
-                            float v[8];
+                            float2 v[4];
                             expand8(tt, v);
 #pragma unroll
                             for (int m = 0; m < MT; m++) {
                                 const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][warp * 256 + sb * 32 + tt * 8]);
                                 const float4 x0 = xp[0], x1 = xp[1];
-                                const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                                const float2 xs[4] = {make_float2(x0.x, x0.y), make_float2(x0.z, x0.w), make_float2(x1.x, x1.y), make_float2(x1.z, x1.w)};
 #pragma unroll
-                                for (int j = 0; j < 8; j++) lanes[m][j] = fmaf(v[j], xs[j], tt == 0 ? 0.0f : lanes[m][j]);
+                                for (int p = 0; p < 4; p++) lanes[m][p] = __ffma2_rn(v[p], xs[p], tt == 0 ? zero2 : lanes[m][p]);
                             }
                         }
+                        if (Q4_REFILL) w[1 + sb] = __ldg(pn + (1 + sb) * 32);
 #pragma unroll
                         for (int m = 0; m < MT; m++)  // scalar stores into the float4 slots: no registers held across sub-blocks
                             reinterpret_cast<float*>(&sm.term[tbuf][warp * 2 + (sb >> 2)][m][lane])[sb & 3] = reduce8(lanes[m]);
@@ -392,6 +414,9 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
                 };
                 if (fabsf(d) <= 65504.0f) block_body(std::true_type{});
                 else block_body(std::false_type{});
+            } else if (Q4_REFILL) {
+#pragma unroll
+                for (int i = 0; i < 9; i++) w[i] = __ldg(pn + i * 32);
             }
         } else {
             const int blk = r * G::BLK_PER_ROUND + (uq0 >> 2);
@@ -421,13 +446,22 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
                         const uint32_t A = word(12 * h + 3 * g), B = word(12 * h + 3 * g + 1), C = word(12 * h + 3 * g + 2);
                         // windows of three fields each, at stream bits 0, 18, 36, 54, 72 and (one field) 90
                         const uint32_t win[6] = {A, __funnelshift_r(A, B, 18), B >> 4, __funnelshift_r(B, C, 22), C >> 8, C >> 26};
-                        float qf[16];
+                        // Two neighbouring elements per instruction (add / mul / fma .rn.f32x2, each half rounded as the scalar
+                        // instruction rounds it).  Element i sits 6 (i % 3) bits up in its window, so the pair (2p, 2p+1) has the
+                        // shifts (0,6), (12,0), (6,12) for p % 3 = 0, 1, 2.
+                        const float2 mul2[3] = {make_float2(mul[0], mul[1]), make_float2(mul[2], mul[0]), make_float2(mul[1], mul[2])};
+                        const float2 off2[3] = {make_float2(-(8388608.0f + 32.0f), -(8388608.0f + 2048.0f)),
+                                                make_float2(-(8388608.0f + 131072.0f), -(8388608.0f + 32.0f)),
+                                                make_float2(-(8388608.0f + 2048.0f), -(8388608.0f + 131072.0f))};
+                        float2 qf[8];
 #pragma unroll
-                        for (int i = 0; i < 16; i++) {
-                            const int s6 = 6 * (i % 3);
-                            const float f = __uint_as_float((win[i / 3] & (0x3Fu << s6)) | magic);
-                            qf[i] = __fmul_rn(__fadd_rn(f, -(8388608.0f + (float)(32 << s6))), mul[i % 3]);
+                        for (int p = 0; p < 8; p++) {
+                            const int i0 = 2 * p, i1 = 2 * p + 1;
+                            const float2 f = make_float2(__uint_as_float((win[i0 / 3] & (0x3Fu << (6 * (i0 % 3)))) | magic),
+                                                         __uint_as_float((win[i1 / 3] & (0x3Fu << (6 * (i1 % 3)))) | magic));
+                            qf[p] = __fmul2_rn(__fadd2_rn(f, off2[p % 3]), mul2[p % 3]);
                         }
+                        const float2 zero2 = make_float2(0.0f, 0.0f);
 #pragma unroll
                         for (int hh = 0; hh < 2; hh++) {
                             const int u = 2 * g + hh;  // the quarter's u-th run of eight elements
@@ -435,11 +469,11 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
                             for (int m = 0; m < MT; m++) {
                                 const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][(uq0 + h) * 64 + u * 8]);
                                 const float4 x0 = xp[0], x1 = xp[1];
-                                float lanes[8];
-                                lanes[0] = fmaf(qf[8 * hh + 0], x0.x, 0.0f); lanes[1] = fmaf(qf[8 * hh + 1], x0.y, 0.0f);
-                                lanes[2] = fmaf(qf[8 * hh + 2], x0.z, 0.0f); lanes[3] = fmaf(qf[8 * hh + 3], x0.w, 0.0f);
-                                lanes[4] = fmaf(qf[8 * hh + 4], x1.x, 0.0f); lanes[5] = fmaf(qf[8 * hh + 5], x1.y, 0.0f);
-                                lanes[6] = fmaf(qf[8 * hh + 6], x1.z, 0.0f); lanes[7] = fmaf(qf[8 * hh + 7], x1.w, 0.0f);
+                                float2 lanes[4];
+                                lanes[0] = __ffma2_rn(qf[4 * hh + 0], make_float2(x0.x, x0.y), zero2);
+                                lanes[1] = __ffma2_rn(qf[4 * hh + 1], make_float2(x0.z, x0.w), zero2);
+                                lanes[2] = __ffma2_rn(qf[4 * hh + 2], make_float2(x1.x, x1.y), zero2);
+                                lanes[3] = __ffma2_rn(qf[4 * hh + 3], make_float2(x1.z, x1.w), zero2);
                                 tq[m][u & 3] = reduce8(lanes);
                                 if ((u & 3) == 3) sm.term[tbuf][(uq0 + h) * 2 + (u >> 2)][m][lane] = make_float4(tq[m][0], tq[m][1], tq[m][2], tq[m][3]);
                             }
@@ -454,7 +488,7 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
             }
             dcur = dnext;
         }
-        if (KIND == KIND_Q4K) {
+        if (KIND == KIND_Q4K && !Q4_REFILL) {
 #pragma unroll
             for (int i = 0; i < 9; i++) w[i] = wn[i];
         }
@@ -470,6 +504,280 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
     }
 }
 
+// ---- Q4_K, eight tokens per pass ---------------------------------------------------------------------------------
+//
+// With eight tokens per expanded weight the general kernel above is bound by shared memory, not by arithmetic: lane =
+// row makes every read of x a broadcast, a broadcast 16-byte read costs two wavefronts of the one-per-cycle shared
+// memory pipe, and it feeds only four multiply-adds per lane (measured: 56 % of that pipe, 35 % of the FMA pipe); the
+// 64 KB of x per round went through 16 cp.async instructions per thread, which cost a fifth of the time.  Here
+//   * a lane owns TWO rows of the panel (li and li + 16), and the two halves of a warp work on different blocks of the
+//     round (half 0: one of blocks 0..3, half 1: one of blocks 4..7; a warp takes sub-blocks 0..3 or 4..7 of both), so
+//     one 16-byte read per lane - two addresses per warp - feeds eight multiply-adds per lane;
+//   * x sits in shared memory as two half rows per token (columns 0..1023 and 1024..2047 of the round), the second
+//     one 16 bytes further than a multiple of 128, so that the two halves of a warp hit different banks;
+//   * every half row is one bulk copy (cp.async.bulk, completion on an mbarrier) issued by one thread; an x that is
+//     not 16-byte aligned goes through ordinary loads instead.
+// Each sub-block of a row is still expanded once per eight tokens, every multiply-add, add and reduction is the same
+// operation on the same operands as above, and the ordered replay is unchanged: same bits.  Weight pieces are
+// refilled in place with the next round's as soon as they have been expanded.  The wait for a bulk copy is bounded:
+// on expiry the CTA records status code 40 and stops.
+template <int MT>
+struct Kq4WideSmem {
+    static constexpr int HALF = 1024 + 4;  // floats per half row
+    alignas(16) float x[2][MT][2][HALF];
+    alignas(16) float4 term[16][MT][32];  // four consecutive ordered terms of a row side by side, 64 per row and round
+    alignas(8) unsigned long long bar[2];
+};
+
+__device__ __forceinline__ uint32_t kq_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool kq_mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool kq_mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 22); i++)
+        if (kq_mbar_try(bar, parity)) return true;
+    return false;
+}
+
+template <int MT>
+__global__ void __launch_bounds__(KQ_THREADS, 1) kq4_wide_kernel(const __grid_constant__ KqLaunch L) {
+    using G = KqGeom<KIND_Q4K, MT>;
+    using S = Kq4WideSmem<MT>;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    S& sm = *reinterpret_cast<S*>(smem_raw);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int half = lane >> 4, li = lane & 15;  // rows li and li + 16
+    const int sset = warp & 1;                   // sub-blocks 4 sset + u, u = 0..3 ...
+    const int rb = half * 4 + (warp >> 1);       // ... of block rb of the round
+
+    int it0, it1;
+    if (L.chunks) {
+        it0 = L.chunks[blockIdx.x];
+        it1 = L.chunks[blockIdx.x + 1];
+    } else {
+        it0 = (int)(((long long)L.n_items * blockIdx.x) / gridDim.x);
+        it1 = (int)(((long long)L.n_items * (blockIdx.x + 1)) / gridDim.x);
+    }
+    if (it0 >= it1) return;
+
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(kq_smem_u32(&sm.bar[0])), "r"(1) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(kq_smem_u32(&sm.bar[1])), "r"(1) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    int mi = 0;
+    auto first_step = [&](int gitem) {
+        KqStep st;
+        st.m = &L.single;
+        if (L.mats) {
+            while (gitem >= L.mats[mi].item_end) mi++;
+            st.m = &L.mats[mi];
+        }
+        const int item = gitem - st.m->item_begin, tiles = kq_tiles<MT>(*st.m);
+        st.panel = item / tiles;
+        st.tok0 = (item - st.panel * tiles) * MT;
+        st.nblk = st.m->nblk;
+        st.r = 0;
+        st.rounds = max(1, (st.nblk + G::BLK_PER_ROUND - 1) / G::BLK_PER_ROUND);
+        return st;
+    };
+    auto next_step = [&](const KqStep& st, int& gitem) {
+        KqStep n = st;
+        if (++n.r == st.rounds) {
+            gitem++;
+            if (gitem < it1) n = first_step(gitem);
+        }
+        return n;
+    };
+
+    // x of round st.r into buffer buf.  Returns true when the data comes by bulk copy (completion on bar[buf]).
+    auto stage = [&](const KqStep& st, int buf) -> bool {
+        const KqMat& a = *st.m;
+        const int tok0 = st.tok0;
+        const int col0 = st.r * G::CH;
+        const bool bulk_ok = ((a.n_cols & 3) == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
+        if (bulk_ok) {
+            if (tid == 0) {
+                const int ntok = min(MT, a.seq_len - tok0);
+                const int c0 = min(1024, a.n_cols - col0), c1 = max(0, min(1024, a.n_cols - col0 - 1024));  // valid columns per half
+                const uint32_t bar = kq_smem_u32(&sm.bar[buf]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(ntok * (c0 + c1) * 4)) : "memory");
+                for (int m = 0; m < ntok; m++) {
+                    const float* src = a.x + (size_t)(tok0 + m) * a.n_cols + col0;
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                     kq_smem_u32(&sm.x[buf][m][0][0])),
+                                 "l"(src), "r"((uint32_t)(c0 * 4)), "r"(bar)
+                                 : "memory");
+                    if (c1 > 0)
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                         kq_smem_u32(&sm.x[buf][m][1][0])),
+                                     "l"(src + 1024), "r"((uint32_t)(c1 * 4)), "r"(bar)
+                                     : "memory");
+                }
+            }
+            return true;
+        }
+        for (int idx = tid; idx < MT * G::CH; idx += KQ_THREADS) {
+            const int m = idx / G::CH, c = idx % G::CH;
+            const int col = col0 + c;
+            sm.x[buf][m][c >> 10][c & 1023] = (tok0 + m < a.seq_len && col < a.n_cols) ? a.x[(size_t)(tok0 + m) * a.n_cols + col] : 0.0f;
+        }
+        return false;
+    };
+
+    // This lane's pieces of its block in a step: header and sub-block pieces of rows li and li + 16.  A step
+    // without that block (the ragged last round, or no next step) points at the matrix's first block: never used.
+    auto block_ptr = [&](const KqStep& st) -> const uint4* {
+        const int blk = st.r * 8 + rb;
+        const size_t base = blk < st.nblk ? ((size_t)st.panel * st.nblk + blk) : 0;
+        return st.m->kq + base * 9 * 32 + li;
+    };
+    uint4 hd[2], pc[4][2];
+    auto load_all = [&](const uint4* p) {
+#pragma unroll
+        for (int rr = 0; rr < 2; rr++) {
+            hd[rr] = __ldg(p + rr * 16);
+#pragma unroll
+            for (int u = 0; u < 4; u++) pc[u][rr] = __ldg(p + (1 + 4 * sset + u) * 32 + rr * 16);
+        }
+    };
+
+    float run = 0.0f;  // thread tid owns the chain of (token tid / 32, row tid % 32)
+    auto replay = [&](const KqStep& st) {
+        if (tid < MT * 32) {
+            const KqMat& a = *st.m;
+            const int m = tid >> 5, row = tid & 31;
+            const int nvalid = min(G::TERMS, G::TERMS_PER_BLK * (st.nblk - st.r * G::BLK_PER_ROUND));
+            float acc = run;
+            for (int k = 0; k < nvalid / 4; k++) {
+                const float4 t = sm.term[k][m][row];
+                acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, t.x), t.y), t.z), t.w);
+            }
+            if (st.r == st.rounds - 1) {
+                const int grow = st.panel * 32 + row;
+                const int tok = st.tok0 + m;
+                if (grow < a.n_rows && tok < a.seq_len) a.out[(size_t)tok * a.ld_out + grow] = acc;
+                acc = 0.0f;
+            }
+            run = acc;
+        }
+    };
+
+    int gitem = it0;
+    KqStep cur = first_step(gitem), prev = cur;
+    uint32_t bulk = 0;   // bit b: buffer b is being filled by a bulk copy whose completion has not been waited for yet
+    uint32_t phase = 0;  // bit b: parity of the next completion of bar[b]
+    bulk = stage(cur, 0) ? 1u : 0u;
+    load_all(block_ptr(cur));
+    const uint32_t magic = L.magic;
+    const float2 zero2 = make_float2(0.0f, 0.0f);
+    for (int t = 0; gitem < it1; t++) {
+        const int buf = t & 1;
+        if ((bulk >> buf) & 1u) {
+            if (!kq_mbar_wait(kq_smem_u32(&sm.bar[buf]), (phase >> buf) & 1u)) {
+                if (L.status) atomicCAS(L.status, 0, 40);
+                return;  // the copy engine did not deliver within the bound: nothing sensible can follow
+            }
+            phase ^= 1u << buf;
+        }
+        __syncthreads();
+        const uint4* pn;
+        {
+            int gnext = gitem;
+            const KqStep nxt = next_step(cur, gnext);
+            const bool nb_bulk = (gnext < it1) ? stage(nxt, buf ^ 1) : false;
+            bulk = (bulk & ~(1u << (buf ^ 1))) | ((nb_bulk ? 1u : 0u) << (buf ^ 1));
+            pn = block_ptr(nxt);
+        }
+        if (cur.r * 8 + rb < cur.nblk) {
+            float d[2], dmin[2];
+            uint32_t sw_lo[2], sw_hi[2];  // the six scale bytes of this warp's four sub-blocks (q4_k.rs:51-96)
+#pragma unroll
+            for (int rr = 0; rr < 2; rr++) {
+                d[rr] = h2f_bits(hd[rr].x & 0xffffu);
+                dmin[rr] = h2f_bits(hd[rr].x >> 16);
+                sw_lo[rr] = sset ? __funnelshift_r(hd[rr].z, hd[rr].w, 16) : hd[rr].y;
+                sw_hi[rr] = sset ? (hd[rr].w >> 16) : hd[rr].z;
+                hd[rr] = __ldg(pn + rr * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                float2 vv[2][4][4];
+#pragma unroll
+                for (int rr = 0; rr < 2; rr++) {
+                    const int i3 = (u >> 1) * 3;  // first of the three scale bytes of the sub-block pair, inside the window
+                    auto wbyte = [&](int i) { return ((i < 4 ? sw_lo[rr] >> (8 * i) : sw_hi[rr] >> (8 * (i - 4)))) & 0xffu; };
+                    const uint32_t s0 = wbyte(i3), s1 = wbyte(i3 + 1), s2 = wbyte(i3 + 2);
+                    const uint32_t sc = (u & 1) ? ((s1 >> 4) | ((s2 & 0x03) << 4)) : (s0 & 0x3F);
+                    const uint32_t mn = (u & 1) ? ((s2 >> 2) & 0x3F) : ((s0 >> 6) | ((s1 & 0x0F) << 2));
+                    const float scf = __fmul_rn((float)sc, d[rr]), mnf = __fmul_rn((float)mn, dmin[rr]);
+                    const uint32_t qw[4] = {pc[u][rr].x, pc[u][rr].y, pc[u][rr].z, pc[u][rr].w};
+                    if (fabsf(d[rr]) <= 65504.0f) {
+                        // nibble -> float by a byte permute into the mantissa of 2^23, then fma(2^23 + n, scf, -(2^23 scf)):
+                        // the correctly rounded n * scf (see the general kernel), two elements per instruction
+                        const float c0 = __fmul_rn(-8388608.0f, scf);
+                        const float2 scf2 = make_float2(scf, scf), c02 = make_float2(c0, c0), nmn2 = make_float2(-mnf, -mnf);
+#pragma unroll
+                        for (int tt = 0; tt < 4; tt++) {
+                            const uint32_t ev = qw[tt] & 0x0F0F0F0Fu, od = (qw[tt] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+                            for (int p = 0; p < 4; p++) {
+                                const float2 nf = make_float2(__uint_as_float(__byte_perm(ev, magic, 0x7540u + p)),
+                                                              __uint_as_float(__byte_perm(od, magic, 0x7540u + p)));
+                                vv[rr][tt][p] = __fadd2_rn(__ffma2_rn(nf, scf2, c02), nmn2);
+                            }
+                        }
+                    } else {  // an infinite or NaN d: the literal multiply and subtract, so that inf and NaN come out as in the reference
+#pragma unroll
+                        for (int tt = 0; tt < 4; tt++)
+#pragma unroll
+                            for (int p = 0; p < 4; p++)
+                                vv[rr][tt][p] = make_float2(__fsub_rn(__fmul_rn((float)((qw[tt] >> (8 * p)) & 0xF), scf), mnf),
+                                                            __fsub_rn(__fmul_rn((float)((qw[tt] >> (8 * p + 4)) & 0xF), scf), mnf));
+                    }
+                    pc[u][rr] = __ldg(pn + (1 + 4 * sset + u) * 32 + rr * 16);
+                }
+                const float* xsub = &sm.x[buf][0][half][(warp >> 1) * 256 + (4 * sset + u) * 32];
+                float* tdst = reinterpret_cast<float*>(&sm.term[rb * 2 + sset][0][0]) + u;
+#pragma unroll
+                for (int m = 0; m < MT; m++) {
+                    float2 l0[4], l1[4];
+#pragma unroll
+                    for (int tt = 0; tt < 4; tt++) {
+                        const float4* xp = reinterpret_cast<const float4*>(xsub + m * (2 * S::HALF) + tt * 8);
+                        const float4 x0 = xp[0], x1 = xp[1];
+                        const float2 xs[4] = {make_float2(x0.x, x0.y), make_float2(x0.z, x0.w), make_float2(x1.x, x1.y), make_float2(x1.z, x1.w)};
+#pragma unroll
+                        for (int p = 0; p < 4; p++) {
+                            l0[p] = __ffma2_rn(vv[0][tt][p], xs[p], tt == 0 ? zero2 : l0[p]);
+                            l1[p] = __ffma2_rn(vv[1][tt][p], xs[p], tt == 0 ? zero2 : l1[p]);
+                        }
+                    }
+                    tdst[(m * 32 + li) * 4] = reduce8(l0);
+                    tdst[(m * 32 + li + 16) * 4] = reduce8(l1);
+                }
+            }
+        } else {
+            load_all(pn);
+        }
+        prev = cur;
+        cur = next_step(cur, gitem);
+        __syncthreads();  // the round's terms are complete; the next round's barrier protects them again
+        replay(prev);
+    }
+}
+
 // Resident CTAs per SM of each instantiation, measured by the occupancy API at prepare time: the grid of the
 // persistent kernel is sized to exactly one wave.
 int g_kq_ctas[2][9] = {};
@@ -477,7 +785,8 @@ int g_kq_ctas[2][9] = {};
 template <int KIND, int MT>
 int launch_mt(const KqLaunch& L, int grid, cudaStream_t st) {
     if (L.n_items <= 0 || grid <= 0) return 0;
-    kq_gemv_kernel<KIND, MT><<<grid, KQ_THREADS, sizeof(KqSmem<KIND, MT>), st>>>(L);
+    if constexpr (KIND == KIND_Q4K && MT >= 8) kq4_wide_kernel<MT><<<grid, KQ_THREADS, sizeof(Kq4WideSmem<MT>), st>>>(L);
+    else kq_gemv_kernel<KIND, MT><<<grid, KQ_THREADS, sizeof(KqSmem<KIND, MT>), st>>>(L);
     HB_CUDA(cudaGetLastError());
     return 0;
 }
@@ -492,9 +801,14 @@ int launch_kind(const KqLaunch& L, int mt, int grid, cudaStream_t st) {
 
 template <int KIND, int MT>
 int prepare_one() {
-    HB_CUDA(cudaFuncSetAttribute(kq_gemv_kernel<KIND, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(KqSmem<KIND, MT>)));
     int n = 0;
-    HB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kq_gemv_kernel<KIND, MT>, KQ_THREADS, sizeof(KqSmem<KIND, MT>)));
+    if constexpr (KIND == KIND_Q4K && MT >= 8) {
+        HB_CUDA(cudaFuncSetAttribute(kq4_wide_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Kq4WideSmem<MT>)));
+        HB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kq4_wide_kernel<MT>, KQ_THREADS, sizeof(Kq4WideSmem<MT>)));
+    } else {
+        HB_CUDA(cudaFuncSetAttribute(kq_gemv_kernel<KIND, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(KqSmem<KIND, MT>)));
+        HB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kq_gemv_kernel<KIND, MT>, KQ_THREADS, sizeof(KqSmem<KIND, MT>)));
+    }
     g_kq_ctas[KIND == KIND_Q4K ? 0 : 1][MT] = n > 0 ? n : 1;
     return 0;
 }
@@ -549,10 +863,10 @@ int kquant_grid(int kind, int mt, int sm_count, int n_items) {
 }
 
 int launch_kquant_gemv(int kind, const uint4* kq, const unsigned short* d16, int n_rows, int n_cols, int nblk, int n_panels,
-                       const float* x, int seq_len, float* out, int ld_out, int sm_count, cudaStream_t st) {
+                       const float* x, int seq_len, float* out, int ld_out, int sm_count, cudaStream_t st, int* status) {
     if (n_rows <= 0 || seq_len <= 0) return 0;
     KqLaunch L;
-    L.mats = nullptr; L.chunks = nullptr; L.magic = 0x4B000000u;
+    L.mats = nullptr; L.chunks = nullptr; L.magic = 0x4B000000u; L.status = status;
     KqMat& a = L.single;
     a.kq = kq; a.d16 = d16; a.x = x; a.out = out;
     a.n_rows = n_rows; a.n_cols = n_cols; a.nblk = nblk; a.n_panels = n_panels; a.seq_len = seq_len; a.ld_out = ld_out;
@@ -566,9 +880,10 @@ int launch_kquant_gemv(int kind, const uint4* kq, const unsigned short* d16, int
     return -7;
 }
 
-int launch_kquant_gemv_list(int kind, int mt, const KqMat* mats_dev, const int* chunks_dev, int n_items, int grid, cudaStream_t st) {
+int launch_kquant_gemv_list(int kind, int mt, const KqMat* mats_dev, const int* chunks_dev, int n_items, int grid, cudaStream_t st,
+                            int* status) {
     KqLaunch L;
-    L.mats = mats_dev; L.chunks = chunks_dev; L.n_items = n_items; L.magic = 0x4B000000u;
+    L.mats = mats_dev; L.chunks = chunks_dev; L.n_items = n_items; L.magic = 0x4B000000u; L.status = status;
     L.single = KqMat{};
     if (kind == KIND_Q4K) return launch_kind<KIND_Q4K>(L, mt, grid, st);
     if (kind == KIND_Q6K) return launch_kind<KIND_Q6K>(L, mt, grid, st);
