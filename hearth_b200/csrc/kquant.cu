@@ -504,29 +504,55 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
     }
 }
 
-// ---- Q4_K, eight tokens per pass ---------------------------------------------------------------------------------
+// ---- eight tokens per pass -----------------------------------------------------------------------------------------
 //
 // With eight tokens per expanded weight the general kernel above is bound by shared memory, not by arithmetic: lane =
 // row makes every read of x a broadcast, a broadcast 16-byte read costs two wavefronts of the one-per-cycle shared
-// memory pipe, and it feeds only four multiply-adds per lane (measured: 56 % of that pipe, 35 % of the FMA pipe); the
-// 64 KB of x per round went through 16 cp.async instructions per thread, which cost a fifth of the time.  Here
+// memory pipe, and it feeds only four multiply-adds per lane (measured on Q4_K: 56 % of that pipe, 35 % of the FMA
+// pipe); the x of a round went through 16 cp.async instructions per thread, which cost a fifth of the time.  Here
 //   * a lane owns TWO rows of the panel (li and li + 16), and the two halves of a warp work on different blocks of the
-//     round (half 0: one of blocks 0..3, half 1: one of blocks 4..7; a warp takes sub-blocks 0..3 or 4..7 of both), so
-//     one 16-byte read per lane - two addresses per warp - feeds eight multiply-adds per lane;
-//   * x sits in shared memory as two half rows per token (columns 0..1023 and 1024..2047 of the round), the second
-//     one 16 bytes further than a multiple of 128, so that the two halves of a warp hit different banks;
+//     round (half 0 on the first half of the round's blocks, half 1 on the second), so one 16-byte read per lane - two
+//     addresses per warp - feeds eight multiply-adds per lane;
+//   * x sits in shared memory as two half rows per token (the columns of the first and of the second half of the
+//     round's blocks), the second one 16 bytes further than a multiple of 128, so that the two halves of a warp hit
+//     different banks;
 //   * every half row is one bulk copy (cp.async.bulk, completion on an mbarrier) issued by one thread; an x that is
 //     not 16-byte aligned goes through ordinary loads instead.
-// Each sub-block of a row is still expanded once per eight tokens, every multiply-add, add and reduction is the same
-// operation on the same operands as above, and the ordered replay is unchanged: same bits.  Weight pieces are
+// A round is eight blocks of Q4_K (a warp: sub-blocks 0..3 or 4..7 of one block per half, 64 ordered terms per row) or
+// four blocks of Q6_K (a warp: one 64-element quarter of one block per half, 128 ordered terms per row).  Each weight
+// of a row is still expanded once per eight tokens, every multiply-add, add and reduction is the same operation on
+// the same operands as in the general kernel, and the ordered replay is unchanged: same bits.  Weight pieces are
 // refilled in place with the next round's as soon as they have been expanded.  The wait for a bulk copy is bounded:
 // on expiry the CTA records status code 40 and stops.
-template <int MT>
-struct Kq4WideSmem {
-    static constexpr int HALF = 1024 + 4;  // floats per half row
-    alignas(16) float x[2][MT][2][HALF];
-    alignas(16) float4 term[16][MT][32];  // four consecutive ordered terms of a row side by side, 64 per row and round
+template <int KIND>
+struct KqWideGeom {
+    static constexpr int BLK_PER_ROUND = (KIND == KIND_Q4K) ? 8 : 4;
+    static constexpr int CH = BLK_PER_ROUND * 256;                   // columns of x per round
+    static constexpr int HALF_COLS = CH / 2;
+    static constexpr int HALF = HALF_COLS + 4;                       // floats per half row in shared memory
+    static constexpr int TERMS_PER_BLK = (KIND == KIND_Q4K) ? 8 : 32;
+    static constexpr int TERMS = BLK_PER_ROUND * TERMS_PER_BLK;      // ordered terms per row and round
+    static constexpr int NP = (KIND == KIND_Q4K) ? 9 : 13;
+};
+
+template <int KIND, int MT>
+struct KqWideSmem {
+    using W = KqWideGeom<KIND>;
+    alignas(16) float x[2][MT][2][W::HALF];
+    // Ordered terms of a round, in groups of four consecutive terms (group k4, member c) per (token, row):
+    //   Q4_K  term[half][k4 % (K4/2)][m][c][row] as floats, the second half's terms (written by lanes 16..31 of every warp)
+    //         64 bytes further than a multiple of 128, so that one 4-byte store per lane has no bank conflict;
+    //   Q6_K  term[k4][m][c / 2][row][c % 2]: an 8-byte store per lane, rows next to each other.
+    static constexpr int K4 = W::TERMS / 4;
+    static constexpr int TERM_HALF = (K4 / 2) * MT * 4 * 32 + (KIND == KIND_Q4K ? 16 : 0);  // floats per half
+    alignas(16) float term[2 * TERM_HALF];
     alignas(8) unsigned long long bar[2];
+    // float index of term (k4, m, c) of row `row`
+    __device__ __forceinline__ static int term_at(int k4, int m, int c, int row) {
+        const int hh = k4 >= K4 / 2 ? 1 : 0, kk = k4 - hh * (K4 / 2);
+        if (KIND == KIND_Q4K) return hh * TERM_HALF + ((kk * MT + m) * 4 + c) * 32 + row;
+        return hh * TERM_HALF + (((kk * MT + m) * 2 + (c >> 1)) * 32 + row) * 2 + (c & 1);
+    }
 };
 
 __device__ __forceinline__ uint32_t kq_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -547,16 +573,18 @@ __device__ __forceinline__ bool kq_mbar_wait(uint32_t bar, uint32_t parity) {
     return false;
 }
 
-template <int MT>
-__global__ void __launch_bounds__(KQ_THREADS, 1) kq4_wide_kernel(const __grid_constant__ KqLaunch L) {
-    using G = KqGeom<KIND_Q4K, MT>;
-    using S = Kq4WideSmem<MT>;
+template <int KIND, int MT>
+__global__ void __launch_bounds__(KQ_THREADS, 1) kq_wide_kernel(const __grid_constant__ KqLaunch L) {
+    using W = KqWideGeom<KIND>;
+    using S = KqWideSmem<KIND, MT>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     S& sm = *reinterpret_cast<S*>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int half = lane >> 4, li = lane & 15;  // rows li and li + 16
-    const int sset = warp & 1;                   // sub-blocks 4 sset + u, u = 0..3 ...
-    const int rb = half * 4 + (warp >> 1);       // ... of block rb of the round
+    // Q4_K: sub-blocks 4 part + u (u = 0..3) of block rb of the round.  Q6_K: quarter `part` of block rb.
+    const int part = (KIND == KIND_Q4K) ? (warp & 1) : (warp & 3);
+    const int bih = (KIND == KIND_Q4K) ? (warp >> 1) : (warp >> 2);  // block inside this half of the round
+    const int rb = half * (W::BLK_PER_ROUND / 2) + bih;
 
     int it0, it1;
     if (L.chunks) {
@@ -588,7 +616,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq4_wide_kernel(const __grid_co
         st.tok0 = (item - st.panel * tiles) * MT;
         st.nblk = st.m->nblk;
         st.r = 0;
-        st.rounds = max(1, (st.nblk + G::BLK_PER_ROUND - 1) / G::BLK_PER_ROUND);
+        st.rounds = max(1, (st.nblk + W::BLK_PER_ROUND - 1) / W::BLK_PER_ROUND);
         return st;
     };
     auto next_step = [&](const KqStep& st, int& gitem) {
@@ -604,12 +632,13 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq4_wide_kernel(const __grid_co
     auto stage = [&](const KqStep& st, int buf) -> bool {
         const KqMat& a = *st.m;
         const int tok0 = st.tok0;
-        const int col0 = st.r * G::CH;
+        const int col0 = st.r * W::CH;
         const bool bulk_ok = ((a.n_cols & 3) == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
         if (bulk_ok) {
             if (tid == 0) {
                 const int ntok = min(MT, a.seq_len - tok0);
-                const int c0 = min(1024, a.n_cols - col0), c1 = max(0, min(1024, a.n_cols - col0 - 1024));  // valid columns per half
+                // valid columns of each half (multiples of 256)
+                const int c0 = min(W::HALF_COLS, a.n_cols - col0), c1 = max(0, min(W::HALF_COLS, a.n_cols - col0 - W::HALF_COLS));
                 const uint32_t bar = kq_smem_u32(&sm.bar[buf]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(ntok * (c0 + c1) * 4)) : "memory");
@@ -622,55 +651,87 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq4_wide_kernel(const __grid_co
                     if (c1 > 0)
                         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                                          kq_smem_u32(&sm.x[buf][m][1][0])),
-                                     "l"(src + 1024), "r"((uint32_t)(c1 * 4)), "r"(bar)
+                                     "l"(src + W::HALF_COLS), "r"((uint32_t)(c1 * 4)), "r"(bar)
                                      : "memory");
                 }
             }
             return true;
         }
-        for (int idx = tid; idx < MT * G::CH; idx += KQ_THREADS) {
-            const int m = idx / G::CH, c = idx % G::CH;
+        for (int idx = tid; idx < MT * W::CH; idx += KQ_THREADS) {
+            const int m = idx / W::CH, c = idx % W::CH;
             const int col = col0 + c;
-            sm.x[buf][m][c >> 10][c & 1023] = (tok0 + m < a.seq_len && col < a.n_cols) ? a.x[(size_t)(tok0 + m) * a.n_cols + col] : 0.0f;
+            sm.x[buf][m][c / W::HALF_COLS][c % W::HALF_COLS] =
+                (tok0 + m < a.seq_len && col < a.n_cols) ? a.x[(size_t)(tok0 + m) * a.n_cols + col] : 0.0f;
         }
         return false;
     };
 
-    // This lane's pieces of its block in a step: header and sub-block pieces of rows li and li + 16.  A step
-    // without that block (the ragged last round, or no next step) points at the matrix's first block: never used.
-    auto block_ptr = [&](const KqStep& st) -> const uint4* {
-        const int blk = st.r * 8 + rb;
-        const size_t base = blk < st.nblk ? ((size_t)st.panel * st.nblk + blk) : 0;
-        return st.m->kq + base * 9 * 32 + li;
+    // Index of this lane's block in a step (panel * nblk + blk); a step without that block (the ragged last round, or
+    // no next step) gives the matrix's first block: what is fetched from it is never used.
+    auto block_index = [&](const KqStep& st) -> size_t {
+        const int blk = st.r * W::BLK_PER_ROUND + rb;
+        return blk < st.nblk ? ((size_t)st.panel * st.nblk + blk) : 0;
     };
+    // Q4_K: headers hd[row] and the four sub-block pieces pc[u][row].  Q6_K: the quarter's three stream pieces pc[i][row],
+    // its four int8 scales sq[row] and the block's d dq[row].
     uint4 hd[2], pc[4][2];
-    auto load_all = [&](const uint4* p) {
+    uint32_t sq[2], dq[2];
+    auto piece0 = [&](const KqStep& st) -> const uint4* {
+        return st.m->kq + (block_index(st) * W::NP + (KIND == KIND_Q4K ? 0 : 3 * part)) * 32 + li;
+    };
+    auto q6_scale_word = [&](const KqStep& st, int rr) -> uint32_t {
+        return __ldg(reinterpret_cast<const uint32_t*>(st.m->kq + (block_index(st) * 13 + 12) * 32 + li + rr * 16) + part);
+    };
+    auto q6_d = [&](const KqStep& st, int rr) -> uint32_t { return __ldg(st.m->d16 + block_index(st) * 32 + li + rr * 16); };
+    auto load_all = [&](const KqStep& st) {
+        const uint4* p = piece0(st);
 #pragma unroll
         for (int rr = 0; rr < 2; rr++) {
-            hd[rr] = __ldg(p + rr * 16);
+            if (KIND == KIND_Q4K) {
+                hd[rr] = __ldg(p + rr * 16);
 #pragma unroll
-            for (int u = 0; u < 4; u++) pc[u][rr] = __ldg(p + (1 + 4 * sset + u) * 32 + rr * 16);
+                for (int u = 0; u < 4; u++) pc[u][rr] = __ldg(p + (1 + 4 * part + u) * 32 + rr * 16);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 3; i++) pc[i][rr] = __ldg(p + i * 32 + rr * 16);
+                sq[rr] = q6_scale_word(st, rr);
+                dq[rr] = q6_d(st, rr);
+            }
         }
     };
 
-    float run = 0.0f;  // thread tid owns the chain of (token tid / 32, row tid % 32)
+    float run[(MT * 32 + KQ_THREADS - 1) / KQ_THREADS];  // thread tid owns the chain of (token tid / 32, row tid % 32)
+#pragma unroll
+    for (int c = 0; c < (MT * 32 + KQ_THREADS - 1) / KQ_THREADS; c++) run[c] = 0.0f;
     auto replay = [&](const KqStep& st) {
-        if (tid < MT * 32) {
-            const KqMat& a = *st.m;
-            const int m = tid >> 5, row = tid & 31;
-            const int nvalid = min(G::TERMS, G::TERMS_PER_BLK * (st.nblk - st.r * G::BLK_PER_ROUND));
-            float acc = run;
-            for (int k = 0; k < nvalid / 4; k++) {
-                const float4 t = sm.term[k][m][row];
-                acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, t.x), t.y), t.z), t.w);
+        const KqMat& a = *st.m;
+        const int nvalid = min(W::TERMS, W::TERMS_PER_BLK * (st.nblk - st.r * W::BLK_PER_ROUND));
+#pragma unroll
+        for (int c = 0; c < (MT * 32 + KQ_THREADS - 1) / KQ_THREADS; c++) {
+            const int chain = tid + c * KQ_THREADS;
+            if (chain < MT * 32) {
+                const int m = chain >> 5, row = chain & 31;
+                float acc = run[c];
+                for (int k = 0; k < nvalid / 4; k++) {
+                    float t0, t1, t2, t3;
+                    if (KIND == KIND_Q4K) {
+                        const float* tp = &sm.term[S::term_at(k, m, 0, row)];
+                        t0 = tp[0]; t1 = tp[32]; t2 = tp[64]; t3 = tp[96];
+                    } else {
+                        const float2 ta = *reinterpret_cast<const float2*>(&sm.term[S::term_at(k, m, 0, row)]);
+                        const float2 tb = *reinterpret_cast<const float2*>(&sm.term[S::term_at(k, m, 2, row)]);
+                        t0 = ta.x; t1 = ta.y; t2 = tb.x; t3 = tb.y;
+                    }
+                    acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, t0), t1), t2), t3);
+                }
+                if (st.r == st.rounds - 1) {
+                    const int grow = st.panel * 32 + row;
+                    const int tok = st.tok0 + m;
+                    if (grow < a.n_rows && tok < a.seq_len) a.out[(size_t)tok * a.ld_out + grow] = acc;
+                    acc = 0.0f;
+                }
+                run[c] = acc;
             }
-            if (st.r == st.rounds - 1) {
-                const int grow = st.panel * 32 + row;
-                const int tok = st.tok0 + m;
-                if (grow < a.n_rows && tok < a.seq_len) a.out[(size_t)tok * a.ld_out + grow] = acc;
-                acc = 0.0f;
-            }
-            run = acc;
         }
     };
 
@@ -679,7 +740,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq4_wide_kernel(const __grid_co
     uint32_t bulk = 0;   // bit b: buffer b is being filled by a bulk copy whose completion has not been waited for yet
     uint32_t phase = 0;  // bit b: parity of the next completion of bar[b]
     bulk = stage(cur, 0) ? 1u : 0u;
-    load_all(block_ptr(cur));
+    load_all(cur);
     const uint32_t magic = L.magic;
     const float2 zero2 = make_float2(0.0f, 0.0f);
     for (int t = 0; gitem < it1; t++) {
@@ -692,87 +753,162 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq4_wide_kernel(const __grid_co
             phase ^= 1u << buf;
         }
         __syncthreads();
-        const uint4* pn;
+        int gnext = gitem;
+        const KqStep nxt = next_step(cur, gnext);
         {
-            int gnext = gitem;
-            const KqStep nxt = next_step(cur, gnext);
             const bool nb_bulk = (gnext < it1) ? stage(nxt, buf ^ 1) : false;
             bulk = (bulk & ~(1u << (buf ^ 1))) | ((nb_bulk ? 1u : 0u) << (buf ^ 1));
-            pn = block_ptr(nxt);
         }
-        if (cur.r * 8 + rb < cur.nblk) {
-            float d[2], dmin[2];
-            uint32_t sw_lo[2], sw_hi[2];  // the six scale bytes of this warp's four sub-blocks (q4_k.rs:51-96)
-#pragma unroll
-            for (int rr = 0; rr < 2; rr++) {
-                d[rr] = h2f_bits(hd[rr].x & 0xffffu);
-                dmin[rr] = h2f_bits(hd[rr].x >> 16);
-                sw_lo[rr] = sset ? __funnelshift_r(hd[rr].z, hd[rr].w, 16) : hd[rr].y;
-                sw_hi[rr] = sset ? (hd[rr].w >> 16) : hd[rr].z;
-                hd[rr] = __ldg(pn + rr * 16);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                float2 vv[2][4][4];
+        const uint4* pn = piece0(nxt);
+        if (cur.r * W::BLK_PER_ROUND + rb < cur.nblk) {
+            if constexpr (KIND == KIND_Q4K) {
+                float d[2], dmin[2];
+                uint32_t sw_lo[2], sw_hi[2];  // the six scale bytes of this warp's four sub-blocks (q4_k.rs:51-96)
 #pragma unroll
                 for (int rr = 0; rr < 2; rr++) {
-                    const int i3 = (u >> 1) * 3;  // first of the three scale bytes of the sub-block pair, inside the window
-                    auto wbyte = [&](int i) { return ((i < 4 ? sw_lo[rr] >> (8 * i) : sw_hi[rr] >> (8 * (i - 4)))) & 0xffu; };
-                    const uint32_t s0 = wbyte(i3), s1 = wbyte(i3 + 1), s2 = wbyte(i3 + 2);
-                    const uint32_t sc = (u & 1) ? ((s1 >> 4) | ((s2 & 0x03) << 4)) : (s0 & 0x3F);
-                    const uint32_t mn = (u & 1) ? ((s2 >> 2) & 0x3F) : ((s0 >> 6) | ((s1 & 0x0F) << 2));
-                    const float scf = __fmul_rn((float)sc, d[rr]), mnf = __fmul_rn((float)mn, dmin[rr]);
-                    const uint32_t qw[4] = {pc[u][rr].x, pc[u][rr].y, pc[u][rr].z, pc[u][rr].w};
-                    if (fabsf(d[rr]) <= 65504.0f) {
-                        // nibble -> float by a byte permute into the mantissa of 2^23, then fma(2^23 + n, scf, -(2^23 scf)):
-                        // the correctly rounded n * scf (see the general kernel), two elements per instruction
-                        const float c0 = __fmul_rn(-8388608.0f, scf);
-                        const float2 scf2 = make_float2(scf, scf), c02 = make_float2(c0, c0), nmn2 = make_float2(-mnf, -mnf);
+                    d[rr] = h2f_bits(hd[rr].x & 0xffffu);
+                    dmin[rr] = h2f_bits(hd[rr].x >> 16);
+                    sw_lo[rr] = part ? __funnelshift_r(hd[rr].z, hd[rr].w, 16) : hd[rr].y;
+                    sw_hi[rr] = part ? (hd[rr].w >> 16) : hd[rr].z;
+                    hd[rr] = __ldg(pn + rr * 16);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    float2 vv[2][4][4];
+#pragma unroll
+                    for (int rr = 0; rr < 2; rr++) {
+                        const int i3 = (u >> 1) * 3;  // first of the three scale bytes of the sub-block pair, inside the window
+                        auto wbyte = [&](int i) { return ((i < 4 ? sw_lo[rr] >> (8 * i) : sw_hi[rr] >> (8 * (i - 4)))) & 0xffu; };
+                        const uint32_t s0 = wbyte(i3), s1 = wbyte(i3 + 1), s2 = wbyte(i3 + 2);
+                        const uint32_t sc = (u & 1) ? ((s1 >> 4) | ((s2 & 0x03) << 4)) : (s0 & 0x3F);
+                        const uint32_t mn = (u & 1) ? ((s2 >> 2) & 0x3F) : ((s0 >> 6) | ((s1 & 0x0F) << 2));
+                        const float scf = __fmul_rn((float)sc, d[rr]), mnf = __fmul_rn((float)mn, dmin[rr]);
+                        const uint32_t qw[4] = {pc[u][rr].x, pc[u][rr].y, pc[u][rr].z, pc[u][rr].w};
+                        if (fabsf(d[rr]) <= 65504.0f) {
+                            // nibble -> float by a byte permute into the mantissa of 2^23, then fma(2^23 + n, scf, -(2^23 scf)):
+                            // the correctly rounded n * scf (see the general kernel), two elements per instruction
+                            const float c0 = __fmul_rn(-8388608.0f, scf);
+                            const float2 scf2 = make_float2(scf, scf), c02 = make_float2(c0, c0), nmn2 = make_float2(-mnf, -mnf);
+#pragma unroll
+                            for (int tt = 0; tt < 4; tt++) {
+                                const uint32_t ev = qw[tt] & 0x0F0F0F0Fu, od = (qw[tt] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+                                for (int p = 0; p < 4; p++) {
+                                    const float2 nf = make_float2(__uint_as_float(__byte_perm(ev, magic, 0x7540u + p)),
+                                                                  __uint_as_float(__byte_perm(od, magic, 0x7540u + p)));
+                                    vv[rr][tt][p] = __fadd2_rn(__ffma2_rn(nf, scf2, c02), nmn2);
+                                }
+                            }
+                        } else {  // an infinite or NaN d: the literal multiply and subtract, so that inf and NaN come out as in the reference
+#pragma unroll
+                            for (int tt = 0; tt < 4; tt++)
+#pragma unroll
+                                for (int p = 0; p < 4; p++)
+                                    vv[rr][tt][p] = make_float2(__fsub_rn(__fmul_rn((float)((qw[tt] >> (8 * p)) & 0xF), scf), mnf),
+                                                                __fsub_rn(__fmul_rn((float)((qw[tt] >> (8 * p + 4)) & 0xF), scf), mnf));
+                        }
+                        pc[u][rr] = __ldg(pn + (1 + 4 * part + u) * 32 + rr * 16);
+                    }
+                    const float* xsub = &sm.x[buf][0][half][bih * 256 + (4 * part + u) * 32];
+                    float* tdst = &sm.term[S::term_at(rb * 2 + part, 0, u, li)];  // token m, row li + 16 rr: + m * 128 + rr * 16
+                    // The terms of all tokens are kept in registers and stored after the loop: with a store between two
+                    // tokens the compiler cannot move the next token's reads of x (same shared memory) ahead of it, and
+                    // every token would wait out its own load, multiply-add and reduction latencies alone.
+                    float tv[MT][2];
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        float2 l0[4], l1[4];
 #pragma unroll
                         for (int tt = 0; tt < 4; tt++) {
-                            const uint32_t ev = qw[tt] & 0x0F0F0F0Fu, od = (qw[tt] >> 4) & 0x0F0F0F0Fu;
+                            const float4* xp = reinterpret_cast<const float4*>(xsub + m * (2 * W::HALF) + tt * 8);
+                            const float4 x0 = xp[0], x1 = xp[1];
+                            const float2 xs[4] = {make_float2(x0.x, x0.y), make_float2(x0.z, x0.w), make_float2(x1.x, x1.y), make_float2(x1.z, x1.w)};
 #pragma unroll
                             for (int p = 0; p < 4; p++) {
-                                const float2 nf = make_float2(__uint_as_float(__byte_perm(ev, magic, 0x7540u + p)),
-                                                              __uint_as_float(__byte_perm(od, magic, 0x7540u + p)));
-                                vv[rr][tt][p] = __fadd2_rn(__ffma2_rn(nf, scf2, c02), nmn2);
+                                l0[p] = __ffma2_rn(vv[0][tt][p], xs[p], tt == 0 ? zero2 : l0[p]);
+                                l1[p] = __ffma2_rn(vv[1][tt][p], xs[p], tt == 0 ? zero2 : l1[p]);
                             }
                         }
-                    } else {  // an infinite or NaN d: the literal multiply and subtract, so that inf and NaN come out as in the reference
-#pragma unroll
-                        for (int tt = 0; tt < 4; tt++)
-#pragma unroll
-                            for (int p = 0; p < 4; p++)
-                                vv[rr][tt][p] = make_float2(__fsub_rn(__fmul_rn((float)((qw[tt] >> (8 * p)) & 0xF), scf), mnf),
-                                                            __fsub_rn(__fmul_rn((float)((qw[tt] >> (8 * p + 4)) & 0xF), scf), mnf));
+                        tv[m][0] = reduce8(l0);
+                        tv[m][1] = reduce8(l1);
                     }
-                    pc[u][rr] = __ldg(pn + (1 + 4 * sset + u) * 32 + rr * 16);
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        tdst[m * 128] = tv[m][0];
+                        tdst[m * 128 + 16] = tv[m][1];
+                    }
                 }
-                const float* xsub = &sm.x[buf][0][half][(warp >> 1) * 256 + (4 * sset + u) * 32];
-                float* tdst = reinterpret_cast<float*>(&sm.term[rb * 2 + sset][0][0]) + u;
+            } else {
+                float d[2];
+                uint32_t scw[2];
 #pragma unroll
-                for (int m = 0; m < MT; m++) {
-                    float2 l0[4], l1[4];
+                for (int rr = 0; rr < 2; rr++) {
+                    d[rr] = h2f_bits(dq[rr]);
+                    scw[rr] = sq[rr];
+                    sq[rr] = q6_scale_word(nxt, rr);
+                    dq[rr] = q6_d(nxt, rr);
+                }
 #pragma unroll
-                    for (int tt = 0; tt < 4; tt++) {
-                        const float4* xp = reinterpret_cast<const float4*>(xsub + m * (2 * S::HALF) + tt * 8);
-                        const float4 x0 = xp[0], x1 = xp[1];
-                        const float2 xs[4] = {make_float2(x0.x, x0.y), make_float2(x0.z, x0.w), make_float2(x1.x, x1.y), make_float2(x1.z, x1.w)};
+                for (int g = 0; g < 4; g++) {  // 16 elements = 96 stream bits = words 3g..3g+2 of the quarter, one int8 scale
+                    float2 qf[2][8];
 #pragma unroll
-                        for (int p = 0; p < 4; p++) {
-                            l0[p] = __ffma2_rn(vv[0][tt][p], xs[p], tt == 0 ? zero2 : l0[p]);
-                            l1[p] = __ffma2_rn(vv[1][tt][p], xs[p], tt == 0 ? zero2 : l1[p]);
+                    for (int rr = 0; rr < 2; rr++) {
+                        const int sci = (int)(int8_t)((scw[rr] >> (8 * g)) & 0xff);
+                        const float sd = __fmul_rn((float)sci, d[rr]);
+                        // (word & 0x3F << s) | 2^23 is the float 2^23 + quant * 2^s, minus (2^23 + 32 * 2^s) is
+                        // (quant - 32) * 2^s exactly, and times sd / 2^s rounds as (quant - 32) * sd does (see the general kernel)
+                        const float mul[3] = {sd, __fmul_rn(sd, 0.015625f), __fmul_rn(sd, 0.000244140625f)};
+                        auto word = [&](int i) { const uint4& v = pc[i >> 2][rr]; return (i & 3) == 0 ? v.x : ((i & 3) == 1 ? v.y : ((i & 3) == 2 ? v.z : v.w)); };
+                        const uint32_t A = word(3 * g), B = word(3 * g + 1), C = word(3 * g + 2);
+                        const uint32_t win[6] = {A, __funnelshift_r(A, B, 18), B >> 4, __funnelshift_r(B, C, 22), C >> 8, C >> 26};
+                        const float2 mul2[3] = {make_float2(mul[0], mul[1]), make_float2(mul[2], mul[0]), make_float2(mul[1], mul[2])};
+                        const float2 off2[3] = {make_float2(-(8388608.0f + 32.0f), -(8388608.0f + 2048.0f)),
+                                                make_float2(-(8388608.0f + 131072.0f), -(8388608.0f + 32.0f)),
+                                                make_float2(-(8388608.0f + 2048.0f), -(8388608.0f + 131072.0f))};
+#pragma unroll
+                        for (int p = 0; p < 8; p++) {
+                            const int i0 = 2 * p, i1 = 2 * p + 1;
+                            const float2 f = make_float2(__uint_as_float((win[i0 / 3] & (0x3Fu << (6 * (i0 % 3)))) | magic),
+                                                         __uint_as_float((win[i1 / 3] & (0x3Fu << (6 * (i1 % 3)))) | magic));
+                            qf[rr][p] = __fmul2_rn(__fadd2_rn(f, off2[p % 3]), mul2[p % 3]);
+                        }
+                        if (g >= 1) pc[g - 1][rr] = __ldg(pn + (g - 1) * 32 + rr * 16);  // group g ends in the quarter's piece g - 1
+                    }
+                    const float* xsub = &sm.x[buf][0][half][bih * 256 + part * 64 + g * 16];
+                    // the two terms of the group are components 2 (g & 1), 2 (g & 1) + 1 of the row's float4 number (g >> 1) of the quarter
+                    float* tdst = &sm.term[S::term_at((rb * 4 + part) * 2 + (g >> 1), 0, 2 * (g & 1), li)];  // token m, row li + 16 rr: + m * 128 + rr * 32
+                    float2 tv[MT][2];  // stored after the loop, see the Q4_K branch
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        const float4* xp = reinterpret_cast<const float4*>(xsub + m * (2 * W::HALF));
+                        const float4 xa = xp[0], xb = xp[1], xc = xp[2], xd = xp[3];
+                        const float2 xs[8] = {make_float2(xa.x, xa.y), make_float2(xa.z, xa.w), make_float2(xb.x, xb.y), make_float2(xb.z, xb.w),
+                                              make_float2(xc.x, xc.y), make_float2(xc.z, xc.w), make_float2(xd.x, xd.y), make_float2(xd.z, xd.w)};
+#pragma unroll
+                        for (int rr = 0; rr < 2; rr++) {
+                            float2 la[4], lb[4];
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                la[k] = __ffma2_rn(qf[rr][k], xs[k], zero2);
+                                lb[k] = __ffma2_rn(qf[rr][4 + k], xs[4 + k], zero2);
+                            }
+                            tv[m][rr] = make_float2(reduce8(la), reduce8(lb));
                         }
                     }
-                    tdst[(m * 32 + li) * 4] = reduce8(l0);
-                    tdst[(m * 32 + li + 16) * 4] = reduce8(l1);
+#pragma unroll
+                    for (int m = 0; m < MT; m++)
+#pragma unroll
+                        for (int rr = 0; rr < 2; rr++) *reinterpret_cast<float2*>(tdst + m * 128 + rr * 32) = tv[m][rr];
                 }
+                pc[2][0] = __ldg(pn + 2 * 32);
+                pc[2][1] = __ldg(pn + 2 * 32 + 16);
             }
         } else {
-            load_all(pn);
+            load_all(nxt);
         }
         prev = cur;
-        cur = next_step(cur, gitem);
+        cur = nxt;
+        gitem = gnext;
         __syncthreads();  // the round's terms are complete; the next round's barrier protects them again
         replay(prev);
     }
@@ -785,7 +921,7 @@ int g_kq_ctas[2][9] = {};
 template <int KIND, int MT>
 int launch_mt(const KqLaunch& L, int grid, cudaStream_t st) {
     if (L.n_items <= 0 || grid <= 0) return 0;
-    if constexpr (KIND == KIND_Q4K && MT >= 8) kq4_wide_kernel<MT><<<grid, KQ_THREADS, sizeof(Kq4WideSmem<MT>), st>>>(L);
+    if constexpr (MT >= 8) kq_wide_kernel<KIND, MT><<<grid, KQ_THREADS, sizeof(KqWideSmem<KIND, MT>), st>>>(L);
     else kq_gemv_kernel<KIND, MT><<<grid, KQ_THREADS, sizeof(KqSmem<KIND, MT>), st>>>(L);
     HB_CUDA(cudaGetLastError());
     return 0;
@@ -802,9 +938,9 @@ int launch_kind(const KqLaunch& L, int mt, int grid, cudaStream_t st) {
 template <int KIND, int MT>
 int prepare_one() {
     int n = 0;
-    if constexpr (KIND == KIND_Q4K && MT >= 8) {
-        HB_CUDA(cudaFuncSetAttribute(kq4_wide_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(Kq4WideSmem<MT>)));
-        HB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kq4_wide_kernel<MT>, KQ_THREADS, sizeof(Kq4WideSmem<MT>)));
+    if constexpr (MT >= 8) {
+        HB_CUDA(cudaFuncSetAttribute(kq_wide_kernel<KIND, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(KqWideSmem<KIND, MT>)));
+        HB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kq_wide_kernel<KIND, MT>, KQ_THREADS, sizeof(KqWideSmem<KIND, MT>)));
     } else {
         HB_CUDA(cudaFuncSetAttribute(kq_gemv_kernel<KIND, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(KqSmem<KIND, MT>)));
         HB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kq_gemv_kernel<KIND, MT>, KQ_THREADS, sizeof(KqSmem<KIND, MT>)));
