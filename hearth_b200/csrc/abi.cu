@@ -10,6 +10,8 @@
 // wrapped in a catch-all and returns a status code.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -73,11 +75,14 @@ struct BatchEntry {
 };
 struct BatchGroup {  // one launch
     int kind, m;
-    DotOp* ops_dev = nullptr;
-    DotItem* items_dev = nullptr;
-    int* chunks_dev = nullptr;  // grid + 1 item boundaries, balanced by blocks per panel
+    FlatRec* recs_dev = nullptr;   // per CTA a run of segments (whole panels, or a part of a panel cut between two CTAs), each with its op
+    int* seg_begin_dev = nullptr;  // grid + 1
+    float* carry_dev = nullptr;    // running sums handed from the CTA before a cut to the CTA after it
+    int* cflags_dev = nullptr;     // per carry slot: arrivals of writer warps so far (eight per launch)
+    int epoch = 0;                 // launches of this group so far
     int grid = 0;
-    int n_items = 0;
+    int n_items = 0;  // panels
+    int n_segs = 0;   // segments of the plan
 };
 struct hb200_batch {
     std::vector<BatchEntry> entries;
@@ -282,7 +287,7 @@ int dot_rows_launch(const hb200_weight* w, const hb200_act* a, size_t seq_len, f
         fill_op(op, w, a, tok0, out, ld_out, nullptr);
         int grid = g_ctx.sm_count * gemv_dp4a_ctas_per_sm(m);
         if (grid > w->n_panels) grid = w->n_panels;
-        const int rc = launch_gemv_dp4a(w->kind, m, false, nullptr, nullptr, nullptr, grid, w->n_panels, &op, st);
+        const int rc = launch_gemv_dp4a(w->kind, m, false, nullptr, grid, w->n_panels, &op, st);
         if (rc) return rc;
     }
     return 0;
@@ -294,7 +299,9 @@ int check_device_status() {
     HB_CUDA(cudaMemcpy(&h, g_ctx.d_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (h != 0) {
         cudaMemset(g_ctx.d_status, 0, sizeof(int));
-        set_error("a bounded wait inside a tensor-core kernel expired (code %d); results of that call are invalid", h);
+        // 1..9: mbarrier waits of the tensor-core kernels; 40: bulk copy of x in the eight-token K-quant kernel; 50: carry
+        // of a panel cut between two CTAs (decode matvec); 100 + r: peer rank r's flag
+        set_error("a bounded wait inside a kernel expired (code %d); results of that call are invalid", h);
         return HB200_ERR_TIMEOUT;
     }
     return 0;
@@ -1282,7 +1289,7 @@ extern "C" int hb200_block_dots_i32(hb200_weight_t w, const uint8_t* a_q8, size_
         fill_op(op, w, g_ctx.act, s, nullptr, w->n_rows, (int32_t*)g_ctx.d_out + s * per_tok);
         int grid = g_ctx.sm_count * gemv_dp4a_ctas_per_sm(1);
         if (grid > w->n_panels) grid = w->n_panels;
-        if ((rc = launch_gemv_dp4a(w->kind, 1, true, nullptr, nullptr, nullptr, grid, w->n_panels, &op, g_ctx.stream))) return rc;
+        if ((rc = launch_gemv_dp4a(w->kind, 1, true, nullptr, grid, w->n_panels, &op, g_ctx.stream))) return rc;
     }
     HB_CUDA(cudaMemcpyAsync(out, g_ctx.d_out, out_bytes, cudaMemcpyDeviceToHost, g_ctx.stream));
     HB_CUDA(cudaStreamSynchronize(g_ctx.stream));
@@ -1445,6 +1452,82 @@ static std::vector<int> balanced_chunks(const std::vector<int>& cost, int grid) 
     return chunks;
 }
 
+// Work plan of a list launch of the decode matvec.  Item i is panel panel[i] of op op[i] and takes rounds[i] rounds.
+// With enough work (at least two of the longest items per CTA) the list of ALL rounds is cut into `grid` equal shares,
+// and a cut inside an item splits it between two neighbouring CTAs (the earlier one hands its running sums over in
+// carry slot c, c = index of the later CTA); otherwise the cuts fall between items (balanced_chunks).  Per CTA the
+// segments come in the order [first rounds of the item cut at its end] [whole items, consecutive panels of one op
+// merged] [last rounds of the item cut at its start], so that a CTA produces the carry its neighbour needs before
+// anything else and consumes the carry it needs after everything else.
+static void plan_flat(const int* op, const int* panel, const int* rounds, int n, int grid, std::vector<FlatSeg>& segs,
+                      std::vector<int>& seg_begin) {
+    segs.clear();
+    seg_begin.assign(grid + 1, 0);
+    if (n <= 0 || grid <= 0) return;
+    std::vector<long long> pre(n + 1, 0);
+    int maxr = 1;
+    for (int i = 0; i < n; i++) {
+        pre[i + 1] = pre[i] + rounds[i];
+        if (rounds[i] > maxr) maxr = rounds[i];
+    }
+    const long long R = pre[n];
+    std::vector<long long> cut(grid + 1, R);
+    cut[0] = 0;
+    if (R >= 2LL * grid * maxr) {
+        for (int c = 1; c < grid; c++) cut[c] = (R * c) / grid;
+    } else {
+        std::vector<int> cost(rounds, rounds + n);
+        for (int& v : cost) v = v * 8 + 1;  // a small fixed share per panel, as measured for the item-granular plan
+        const std::vector<int> chunks = balanced_chunks(cost, grid);
+        for (int c = 1; c < grid; c++) cut[c] = pre[chunks[c]];
+    }
+    int i = 0;
+    for (int c = 0; c < grid; c++) {
+        seg_begin[c] = (int)segs.size();
+        const long long lo = cut[c], hi = cut[c + 1];
+        if (lo >= hi) continue;
+        while (pre[i + 1] <= lo) i++;
+        std::vector<FlatSeg> whole;
+        FlatSeg head{}, tail{};
+        bool has_head = false, has_tail = false;
+        for (int j = i; j < n && pre[j] < hi; j++) {
+            const int a = (int)(std::max(lo, pre[j]) - pre[j]), b = (int)(std::min(hi, pre[j + 1]) - pre[j]);
+            FlatSeg sg{};
+            sg.op = op[j]; sg.p0 = panel[j]; sg.cnt = 1; sg.r0 = a; sg.r1 = b;
+            sg.flags = (a > 0 ? 1 : 0) | (b < rounds[j] ? 2 : 0);
+            sg.carry_in = a > 0 ? c : 0;
+            sg.carry_out = b < rounds[j] ? c + 1 : 0;
+            if (sg.flags & 2) { head = sg; has_head = true; }       // the item cut at this CTA's end (may also start from a carry)
+            else if (sg.flags & 1) { tail = sg; has_tail = true; }  // the item cut at this CTA's start
+            else if (!whole.empty() && whole.back().op == sg.op && whole.back().p0 + whole.back().cnt == sg.p0 && whole.back().r1 == sg.r1) whole.back().cnt++;
+            else whole.push_back(sg);
+        }
+        if (has_head) segs.push_back(head);
+        for (const FlatSeg& w : whole) segs.push_back(w);
+        if (has_tail) segs.push_back(tail);
+    }
+    seg_begin[grid] = (int)segs.size();
+}
+
+extern "C" int hb200_plan_rounds(const int* op, const int* panel, const int* rounds, size_t n_items, int grid, int* seg_begin,
+                                 int* segs, size_t seg_cap, size_t* n_segs) {
+    HB_GUARD_BEGIN
+    if ((n_items && (!op || !panel || !rounds)) || !seg_begin || !n_segs || (seg_cap && !segs)) { set_error("null buffer"); return HB200_ERR_NULL; }
+    if (grid <= 0) { set_error("grid must be positive"); return HB200_ERR_BAD_SHAPE; }
+    for (size_t i = 0; i < n_items; i++)
+        if (rounds[i] <= 0) { set_error("an item takes at least one round"); return HB200_ERR_BAD_SHAPE; }
+    std::vector<FlatSeg> out;
+    std::vector<int> begin;
+    plan_flat(op, panel, rounds, (int)n_items, grid, out, begin);
+    *n_segs = out.size();
+    if (out.size() > seg_cap) { set_error("%zu segments do not fit the %zu given", out.size(), seg_cap); return HB200_ERR_TOO_LARGE; }
+    for (int c = 0; c <= grid; c++) seg_begin[c] = begin[c];
+    static_assert(sizeof(FlatSeg) == 8 * sizeof(int), "a segment is eight ints");
+    if (!out.empty()) memcpy(segs, out.data(), out.size() * sizeof(FlatSeg));
+    return HB200_OK;
+    HB_GUARD_END
+}
+
 extern "C" int hb200_plan_chunks(const int* cost, size_t n_items, int grid, int* chunks) {
     HB_GUARD_BEGIN
     if ((!cost && n_items) || !chunks) { set_error("null buffer"); return HB200_ERR_NULL; }
@@ -1488,9 +1571,7 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
             slot.first.push_back(op);
             for (int p = 0; p < e.w->n_panels; p++) {
                 slot.second.push_back(make_int2(idx, p));
-                // rounds of the panel; its fixed share (output stores, the last replay) measured as negligible: a share of one
-                // round made the 8B Q1_0 decode set 15 % slower than none, an eighth of a round is the same as none
-                slot.cost.push_back(((e.w->nb + 7) / 8) * 8 + 1);
+                slot.cost.push_back(e.w->nb > 8 ? (e.w->nb + 7) / 8 : 1);  // rounds of the panel
             }
         }
     }
@@ -1500,16 +1581,37 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
         g.m = kv.first.second;
         g.n_items = (int)kv.second.second.size();
         if (g.n_items == 0) continue;
-        HB_CUDA(cudaMalloc(&g.ops_dev, kv.second.first.size() * sizeof(DotOp)));
-        HB_CUDA(cudaMalloc(&g.items_dev, kv.second.second.size() * sizeof(DotItem)));
-        HB_CUDA(cudaMemcpy(g.ops_dev, kv.second.first.data(), kv.second.first.size() * sizeof(DotOp), cudaMemcpyHostToDevice));
-        HB_CUDA(cudaMemcpy(g.items_dev, kv.second.second.data(), kv.second.second.size() * sizeof(DotItem), cudaMemcpyHostToDevice));
-        // Contiguous, cost-balanced runs of items per CTA.
+        // One wave of CTAs; each gets an equal share of the launch's rounds (see plan_flat).
         g.grid = g_ctx.sm_count * gemv_dp4a_ctas_per_sm(g.m);
-        if (g.grid > g.n_items) g.grid = g.n_items;
-        const std::vector<int> chunks = balanced_chunks(kv.second.cost, g.grid);
-        HB_CUDA(cudaMalloc(&g.chunks_dev, chunks.size() * sizeof(int)));
-        HB_CUDA(cudaMemcpy(g.chunks_dev, chunks.data(), chunks.size() * sizeof(int), cudaMemcpyHostToDevice));
+        {
+            std::vector<int> iop(g.n_items), ipanel(g.n_items);
+            long long total_rounds = 0;
+            for (int i = 0; i < g.n_items; i++) {
+                iop[i] = kv.second.second[i].x;
+                ipanel[i] = kv.second.second[i].y;
+                total_rounds += kv.second.cost[i];
+            }
+            int max_rounds = 1;
+            for (int c : kv.second.cost) max_rounds = c > max_rounds ? c : max_rounds;
+            // too little work to cut panels (plan_flat's rule): whole panels, and no more CTAs than panels
+            if (total_rounds < 2LL * g.grid * max_rounds && g.grid > g.n_items) g.grid = g.n_items;
+            std::vector<FlatSeg> segs;
+            std::vector<int> seg_begin;
+            plan_flat(iop.data(), ipanel.data(), kv.second.cost.data(), g.n_items, g.grid, segs, seg_begin);
+            g.n_segs = (int)segs.size();
+            std::vector<FlatRec> recs(segs.size());
+            for (size_t i = 0; i < segs.size(); i++) {
+                recs[i].seg = segs[i];
+                recs[i].op = kv.second.first[segs[i].op];
+            }
+            HB_CUDA(cudaMalloc(&g.recs_dev, recs.size() * sizeof(FlatRec)));
+            HB_CUDA(cudaMemcpy(g.recs_dev, recs.data(), recs.size() * sizeof(FlatRec), cudaMemcpyHostToDevice));
+            HB_CUDA(cudaMalloc(&g.seg_begin_dev, seg_begin.size() * sizeof(int)));
+            HB_CUDA(cudaMemcpy(g.seg_begin_dev, seg_begin.data(), seg_begin.size() * sizeof(int), cudaMemcpyHostToDevice));
+            HB_CUDA(cudaMalloc(&g.carry_dev, (size_t)(g.grid + 1) * FLAT_CARRY_FLOATS * sizeof(float)));
+            HB_CUDA(cudaMalloc(&g.cflags_dev, (size_t)(g.grid + 1) * sizeof(int)));
+            HB_CUDA(cudaMemset(g.cflags_dev, 0, (size_t)(g.grid + 1) * sizeof(int)));
+        }
         b->groups.push_back(g);
     }
     // Tensor-core ops: per weight kind one list of matrices whose 128 x 64 tiles are numbered consecutively, and
@@ -1636,11 +1738,13 @@ extern "C" int hb200_batch_launch(hb200_batch_t b, void* stream) {
         pt.area_off = b->peer_area_floats ? (long long)((pt.epoch - 1) & 1) * (long long)b->peer_area_floats : 0;
     }
     for (size_t gi = 0; gi < b->groups.size(); gi++) {
-        const BatchGroup& g = b->groups[gi];
+        BatchGroup& g = b->groups[gi];
         pt.publish = (gi + 1 == b->groups.size()) ? 1 : 0;
-        if ((rc = launch_gemv_dp4a(g.kind, g.m, false, g.ops_dev, g.items_dev, g.chunks_dev, g.grid, g.n_items, nullptr, st,
-                                   pt.n > 1 ? &pt : nullptr)))
-            return rc;
+        FlatLaunch fl;
+        fl.recs = g.recs_dev; fl.seg_begin = g.seg_begin_dev; fl.carry = g.carry_dev; fl.cflags = g.cflags_dev;
+        fl.epoch = ++g.epoch;
+        fl.status = g_ctx.d_status;
+        if ((rc = launch_gemv_dp4a(g.kind, g.m, false, &fl, g.grid, g.n_segs, nullptr, st, pt.n > 1 ? &pt : nullptr))) return rc;
     }
     if (pt.n > 1 && b->groups.empty() && (rc = launch_peer_publish(pt, st))) return rc;
     for (const hb200_batch::TcGroup& g : b->tc_groups)
@@ -1735,9 +1839,10 @@ extern "C" int hb200_batch_free(hb200_batch_t b) {
     HB_USE(b);
     if (!b) return HB200_OK;
     for (BatchGroup& g : b->groups) {
-        if (g.ops_dev) cudaFree(g.ops_dev);
-        if (g.items_dev) cudaFree(g.items_dev);
-        if (g.chunks_dev) cudaFree(g.chunks_dev);
+        if (g.recs_dev) cudaFree(g.recs_dev);
+        if (g.seg_begin_dev) cudaFree(g.seg_begin_dev);
+        if (g.carry_dev) cudaFree(g.carry_dev);
+        if (g.cflags_dev) cudaFree(g.cflags_dev);
     }
     for (hb200_batch::TcGroup& g : b->tc_groups) {
         if (g.mats_dev) cudaFree(g.mats_dev);

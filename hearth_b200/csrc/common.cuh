@@ -140,9 +140,32 @@ constexpr int GEMV_MAX_M = 4;  // tokens one dp4a launch handles per op
 // cost-balanced run of items; items of one op must be consecutive panels), or, with ops_dev == nullptr, the one op
 // `single` (host memory, passed by value to the grid) whose n_items panels are split evenly over `grid` CTAs.
 // `peers` (may be null) turns the output stores into stores to every rank's buffer plus the closing flag exchange.
-int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const DotItem* items_dev, const int* chunks_dev,
-                     int grid, int n_items, const DotOp* single, cudaStream_t st, const PeerTable* peers = nullptr);
+
 int gemv_dp4a_ctas_per_sm(int m);  // resident CTAs per SM the kernel for m tokens is built for
+// List launches of the decode matvec: per CTA a run of segments (consecutive whole panels of one op, or rounds
+// [r0, r1) of ONE panel).  A panel cut between two CTAs is summed in order across them: the first part's CTA writes
+// its running sums to carry slot `carry_out`, the second part's CTA starts from slot `carry_in` (flags bit 0: starts
+// from a carry, bit 1: ends in a carry).  For whole panels r0 = 0 and r1 = rounds of the op.
+struct FlatSeg {
+    int op, p0, cnt, r0, r1, flags, carry_in, carry_out;
+};
+constexpr int FLAT_CARRY_FLOATS = GEMV_MAX_M * 256;  // one slot: running sums of a panel (up to 256 rows) for up to 4 tokens
+struct FlatRec {  // what a CTA needs to start a segment, in one 112-byte record (copied ahead into shared memory)
+    FlatSeg seg;
+    DotOp op;
+};
+struct FlatLaunch {
+    const FlatRec* recs;   // null: not a list launch
+    const int* seg_begin;  // [grid + 1]
+    float* carry;          // [slots][FLAT_CARRY_FLOATS]
+    int* cflags;           // [slots]: warps that have written the slot so far (eight per launch)
+    int epoch;
+    int* status;           // device word for an expired wait (may be null)
+};
+// `list` (a planned work list, n_items = its number of segments) or, when list is null, the one op `single` whose
+// n_items panels are split evenly over the grid.
+int launch_gemv_dp4a(int kind, int m, bool int_out, const FlatLaunch* list, int grid, int n_items, const DotOp* single,
+                     cudaStream_t st, const PeerTable* peers = nullptr);
 // The flag exchange alone (one thread): closes a peer launch of a rank whose shard is empty, so that every rank
 // publishes every epoch.
 int launch_peer_publish(const PeerTable& peers, cudaStream_t st);

@@ -33,6 +33,8 @@
 //          adds them in block order, one round behind the producers.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace hb200 {
 
 namespace {
@@ -102,10 +104,110 @@ __device__ __forceinline__ void peer_flag_exchange(const PeerTable& peers) {
     }
 }
 
+// The arithmetic of one round for one warp: block `blk` of `panel` (weight pieces w, scales ws) against the staged
+// activation columns in buffer `buf`; leaves the per-block terms in shared memory (or, INT_OUT, stores the int32
+// sub-block dots).
+template <int KIND, int M, bool INT_OUT>
+__device__ __forceinline__ void round_terms(Smem<KIND, M>& sm, const uint4 (&w)[8], const uint4& ws, int buf, int warp, int lane, int blk,
+                                            int panel, const DotOp* op) {  // op: read for INT_OUT only
+    using S = Smem<KIND, M>;
+    constexpr int RPG = S::RPG;
+    constexpr int RP = S::RP;
+    (void)RP; (void)blk; (void)panel;
+        float bacc[M][RPG];
+#pragma unroll
+        for (int m = 0; m < M; m++)
+#pragma unroll
+            for (int g = 0; g < RPG; g++) bacc[m][g] = 0.0f;
+
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            int acc[M][RPG];
+#pragma unroll
+            for (int m = 0; m < M; m++)
+#pragma unroll
+                for (int g = 0; g < RPG; g++) acc[m][g] = INT_OUT ? 0 : MAGIC_I;
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                int4 a4[M];
+#pragma unroll
+                for (int m = 0; m < M; m++)
+                    a4[m] = *reinterpret_cast<const int4*>(&sm.aq[buf][m][warp * 128 + s * 32 + h * 16]);
+#pragma unroll
+                for (int jj = 0; jj < 4; jj++) {
+                    const int j = 4 * h + jj;                      // word of the sub-block: columns 4j..4j+3
+                    const int q = (j >> 1) * 8 + s * 2 + (j & 1);  // its position in the tile
+                    const uint32_t word = comp(w[q >> 2], q & 3);
+#pragma unroll
+                    for (int g = 0; g < RPG; g++) {
+                        uint32_t msk;
+                        if (KIND == KIND_Q1) msk = word & (0x01010101u << g);
+                        else if (KIND == KIND_Q2) msk = word & (0x03030303u << (2 * g));
+                        else msk = word;
+#pragma unroll
+                        for (int m = 0; m < M; m++) {
+                            if (KIND == KIND_Q8) acc[m][g] = dp4a_s8s8(msk, compi(a4[m], jj), acc[m][g]);
+                            else acc[m][g] = dp4a_u8s8(msk, compi(a4[m], jj), acc[m][g]);
+                        }
+                    }
+                }
+            }
+            // Widen the sub-block sums.
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                const float a_d = sm.ad[buf][m][warp * 4 + s];
+                const float a_sum = sm.asum[buf][m][warp * 4 + s];
+#pragma unroll
+                for (int g = 0; g < RPG; g++) {
+                    if (INT_OUT) {
+                        int iv;
+                        if (KIND == KIND_Q1) iv = ((acc[m][g] << 1) >> g) - (int)a_sum;       // 2*S1 - sum(a)
+                        else if (KIND == KIND_Q2) iv = (acc[m][g] >> (2 * g)) - (int)a_sum;  // S_code - sum(a)
+                        else iv = acc[m][g];
+                        const int row = panel * RP + lane * RPG + g;
+                        if (row < op->n_rows && blk * 4 + s < op->n_sub)
+                            op->iout[((size_t)m * op->n_rows + row) * op->n_sub + blk * 4 + s] = iv;
+                    } else {
+                        const float accf = __fadd_rn(__int_as_float(acc[m][g]), -MAGIC_F);  // exact (float)sum
+                        if (KIND == KIND_Q8) {
+                            const float wd = __half2float(__ushort_as_half(
+                                (unsigned short)((s < 2 ? ws.x : ws.y) >> (16 * (s & 1)))));
+                            // ((float)sumi * d_w) * d_a, each product rounded (q8_0.rs:169)
+                            sm.term[buf][warp][m][s * 32 + lane] = __fmul_rn(__fmul_rn(accf, wd), a_d);
+                        } else {
+                            // exact integer I as fp32, then block_acc += I * a_scale (exact product, one rounding)
+                            const float c = (KIND == KIND_Q1) ? (2.0f / (float)(1 << g)) : (1.0f / (float)(1 << (2 * g)));
+                            const float i_f = fmaf(accf, c, -a_sum);
+                            bacc[m][g] = fmaf(i_f, a_d, bacc[m][g]);
+                        }
+                    }
+                }
+            }
+        }
+        if (!INT_OUT && KIND != KIND_Q8) {
+            float wd[RPG];
+#pragma unroll
+            for (int g = 0; g < RPG; g++) {
+                const uint32_t pair = (g < 2) ? ws.x : (g < 4 ? ws.y : (g < 6 ? ws.z : ws.w));
+                wd[g] = __half2float(__ushort_as_half((unsigned short)(pair >> (16 * (g & 1)))));
+            }
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                float4* tp = reinterpret_cast<float4*>(&sm.term[buf][warp][m][lane * RPG]);
+#pragma unroll
+                for (int g4 = 0; g4 < RPG / 4; g4++)
+                    tp[g4] = make_float4(__fmul_rn(bacc[m][4 * g4], wd[4 * g4]), __fmul_rn(bacc[m][4 * g4 + 1], wd[4 * g4 + 1]),
+                                         __fmul_rn(bacc[m][4 * g4 + 2], wd[4 * g4 + 2]), __fmul_rn(bacc[m][4 * g4 + 3], wd[4 * g4 + 3]));
+            }
+        }
+}
+
 template <int KIND, int M, bool INT_OUT>
 __global__ void __launch_bounds__(THREADS, (M <= 2 ? 2 : 1))
-gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ items, const int* __restrict__ chunks,
-                 int n_items, const __grid_constant__ DotOp single, const __grid_constant__ PeerTable peers) {
+gemv_dp4a_kernel(const __grid_constant__ FlatLaunch A, int n_items, const __grid_constant__ DotOp single,
+                 const __grid_constant__ PeerTable peers) {
+    const FlatRec* __restrict__ recs = A.recs;  // null: the one op `single`, its panels split evenly over the CTAs
+    __shared__ __align__(16) FlatRec srec[2];   // this segment's record and, copied in while it runs, the next one's
     using S = Smem<KIND, M>;
     constexpr int RPG = S::RPG;
     constexpr int RP = S::RP;
@@ -115,57 +217,108 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    // This CTA's contiguous run of work items.  A list launch reads cost-balanced boundaries; a single-op launch
-    // splits the panels of `single` evenly.
-    int it = ops ? chunks[blockIdx.x] : (int)(((long long)n_items * blockIdx.x) / gridDim.x);
-    const int it_end = ops ? chunks[blockIdx.x + 1] : (int)(((long long)n_items * (blockIdx.x + 1)) / gridDim.x);
+    // This CTA's work.  A list launch reads its run of segments from the plan (FlatSeg: consecutive whole panels of one
+    // op, or rounds [r0, r1) of ONE panel that the plan cut between two neighbouring CTAs); a single-op launch splits the
+    // panels of `single` evenly.  Of a cut panel, the CTA before the cut computes the first rounds and hands the running
+    // sums of the panel's rows over in a carry slot in global memory; the CTA after the cut starts its ordered sum from
+    // them: the same additions in the same order, the same bits.  The plan puts the part a CTA hands over first in its
+    // run and the part it receives a carry for last, so the carry was written long before it is read; the wait for it
+    // is bounded all the same (status code 50).  A slot's flag counts the warps that have written it, eight per launch.
+    int it = recs ? A.seg_begin[blockIdx.x] : (int)(((long long)n_items * blockIdx.x) / gridDim.x);
+    const int it_end = recs ? A.seg_begin[blockIdx.x + 1] : (int)(((long long)n_items * (blockIdx.x + 1)) / gridDim.x);
+    constexpr int REC_PIECES = (int)(sizeof(FlatRec) / 16);
+    static_assert(sizeof(FlatRec) % 16 == 0, "a record is copied in 16-byte pieces");
+    // The record of segment i into slot i & 1, asynchronously: it lands under the rounds of the segment before it (every
+    // round waits for the thread's outstanding copies), so a change of segment costs no dependent global reads.
+    auto fetch_rec = [&](int i) {
+        if (tid < REC_PIECES)
+            cp_async16(reinterpret_cast<char*>(&srec[i & 1]) + tid * 16, reinterpret_cast<const char*>(recs + i) + tid * 16);
+    };
+    if (recs && it < it_end) {
+        fetch_rec(it);
+        cp_async_commit_wait_all();
+    }
+
+    uint4 wn[8];   // weight pieces of the next round
+    uint4 wsn;     // its scales (Q1_0: 8 f16; Q2_0 / Q8_0: 4 f16 in .x .y)
+    int b0 = 0;        // shared-memory buffer of the segment's first round (rounds alternate from there)
+    bool pre = false;  // the segment's first round was fetched under the last round of the segment before it
 
     while (it < it_end) {
-        // One segment: consecutive panels [p0, p0 + cnt) of one op.  Rounds run back to back across the panels,
-        // so the weight prefetch never drains inside a segment.
-        const DotOp op = ops ? ops[items[it].x] : single;
-        const int p0 = ops ? items[it].y : it;
-        const int op_panels = (op.n_rows + RP - 1) / RP;
-        const int cnt = min(it_end - it, op_panels - p0);
-        it += cnt;
+        // One segment.  Rounds run back to back across its panels, so the weight prefetch never drains inside it; the
+        // first round of the NEXT segment of a list is fetched under this segment's last round.
+        FlatSeg sg;
+        DotOp op;
+        if (recs) {
+            __syncthreads();  // the record is in place (copied during the previous segment, or just now)
+            sg = srec[it & 1].seg;
+            op = srec[it & 1].op;
+            it++;
+            if (it < it_end) fetch_rec(it);  // overwrites the slot of the segment before this one: nobody reads it any more
+        } else {
+            sg.op = 0; sg.p0 = it; sg.cnt = it_end - it; sg.r0 = 0; sg.r1 = 0; sg.flags = 0; sg.carry_in = 0; sg.carry_out = 0;
+            it = it_end;
+            op = single;
+        }
+        const int p0 = sg.p0;
         const int nb = op.nb;
         const int rounds = max(1, (nb + WARPS - 1) / WARPS);
-        const int total = cnt * rounds;
+        const int r_begin = sg.flags ? sg.r0 : 0;
+        const int total = sg.flags ? (sg.r1 - sg.r0) : sg.cnt * rounds;
+        const bool carry_in = sg.flags & 1, carry_out = sg.flags & 2;
 
         // Stage the activation columns of round r into buffer `buf` (cp.async, 16 B each).
-        auto stage = [&](int r, int buf) {
+        auto stage_of = [&](const DotOp& o, int r, int buf) {
             for (int idx = tid; idx < 80 * M; idx += THREADS) {
                 const int m = idx / 80, p = idx % 80;
                 if (p < 64)
-                    cp_async16(&sm.aq[buf][m][p * 16], op.aq + (size_t)m * op.ld_q + (size_t)r * 1024 + p * 16);
+                    cp_async16(&sm.aq[buf][m][p * 16], o.aq + (size_t)m * o.ld_q + (size_t)r * 1024 + p * 16);
                 else if (p < 72)
-                    cp_async16(&sm.ad[buf][m][(p - 64) * 4], op.ad + (size_t)m * op.ld_b + r * 32 + (p - 64) * 4);
+                    cp_async16(&sm.ad[buf][m][(p - 64) * 4], o.ad + (size_t)m * o.ld_b + r * 32 + (p - 64) * 4);
                 else
-                    cp_async16(&sm.asum[buf][m][(p - 72) * 4], op.asum + (size_t)m * op.ld_b + r * 32 + (p - 72) * 4);
+                    cp_async16(&sm.asum[buf][m][(p - 72) * 4], o.asum + (size_t)m * o.ld_b + r * 32 + (p - 72) * 4);
             }
         };
+        auto stage = [&](int r, int buf) { stage_of(op, r, buf); };
 
-        uint4 wn[8];   // weight pieces of the next round
-        uint4 wsn;     // its scales (Q1_0: 8 f16; Q2_0 / Q8_0: 4 f16 in .x .y)
-        auto load_w = [&](int panel, int r) {
+        auto load_w_of = [&](const DotOp& o, int panel, int r) {
             const int blk = r * WARPS + warp;
-            if (blk < nb) {
-                const size_t tile = (size_t)panel * nb + blk;
-                const uint4* p = op.bits + tile * 256 + lane;
+            if (blk < o.nb) {
+                const size_t tile = (size_t)panel * o.nb + blk;
+                const uint4* p = o.bits + tile * 256 + lane;
 #pragma unroll
                 for (int i = 0; i < 8; i++) wn[i] = __ldg(p + i * 32);
                 if (KIND == KIND_Q1) {
-                    wsn = __ldg(reinterpret_cast<const uint4*>(op.scales) + tile * 32 + lane);
+                    wsn = __ldg(reinterpret_cast<const uint4*>(o.scales) + tile * 32 + lane);
                 } else {
-                    const uint2 s2 = __ldg(reinterpret_cast<const uint2*>(op.scales) + tile * 32 + lane);
+                    const uint2 s2 = __ldg(reinterpret_cast<const uint2*>(o.scales) + tile * 32 + lane);
                     wsn = make_uint4(s2.x, s2.y, 0u, 0u);
                 }
             }
         };
+        auto load_w = [&](int panel, int r) { load_w_of(op, panel, r); };
 
         float run[NRUN];
 #pragma unroll
         for (int k = 0; k < NRUN; k++) run[k] = 0.0f;
+        if (carry_in) {  // every thread polls for itself (no CTA barrier); normally the flag has long been raised
+            volatile int* f = A.cflags + sg.carry_in;
+            const int target = A.epoch * WARPS;
+            unsigned spins = 0;
+            while (*f - target < 0) {
+                if (++spins > (1u << 20)) {
+                    if (A.status) atomicCAS(A.status, 0, 50);
+                    break;
+                }
+                __nanosleep(64);
+            }
+            __threadfence();
+#pragma unroll
+            for (int k = 0; k < NRUN; k++) {
+                const int idx = tid + k * THREADS;
+                if (idx < M * RP) run[k] = __ldcg(A.carry + (size_t)sg.carry_in * FLAT_CARRY_FLOATS + idx);
+            }
+        }
 
         // Adds the terms of round r of `panel` (buffer `buf`) to the running sums, in block order; after the last
         // round of a panel the sums are the outputs of that panel.
@@ -206,12 +359,16 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
             }
         };
 
-        __syncthreads();  // the previous segment's shared memory is no longer read
-        stage(0, 0);
-        load_w(p0, 0);
+        if (!pre) {
+            __syncthreads();  // the previous segment's shared memory is no longer read
+            stage(r_begin, b0);
+            load_w(p0, r_begin);
+        }
+        pre = false;
+        const bool more_segs = recs && it < it_end;  // `it` is the next segment by now, its record is in srec[it & 1] after this segment's first barrier
 
-        int panel = p0, r = 0;            // position of round t
-        int ppanel = p0, pr = 0;          // position of round t - 1
+        int panel = p0, r = r_begin;            // position of round t
+        int ppanel = p0, pr = r_begin;          // position of round t - 1
         for (int t = 0; t < total; t++) {
             cp_async_commit_wait_all();
             __syncthreads();  // activations of round t landed; terms of round t-1 visible
@@ -222,108 +379,38 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
             int npanel = panel, nr = r + 1;
             if (nr == rounds) { nr = 0; npanel = panel + 1; }
             if (t + 1 < total) {
-                stage(nr, (t + 1) & 1);
+                stage(nr, (t + 1 + b0) & 1);
                 load_w(npanel, nr);
+            } else if (more_segs) {  // the last round: fetch the first round of the next segment
+                const FlatRec& nx = srec[it & 1];
+                const int nr0 = nx.seg.flags ? nx.seg.r0 : 0;
+                stage_of(nx.op, nr0, (t + 1 + b0) & 1);
+                load_w_of(nx.op, nx.seg.p0, nr0);
+                pre = true;
             }
-            if (!INT_OUT && t > 0) replay(ppanel, pr, (t - 1) & 1);
+            if (!INT_OUT && t > 0) replay(ppanel, pr, (t - 1 + b0) & 1);
 
-            const int buf = t & 1;
+            const int buf = (t + b0) & 1;
             const int blk = r * WARPS + warp;
-            if (blk < nb) {
-                float bacc[M][RPG];
-#pragma unroll
-                for (int m = 0; m < M; m++)
-#pragma unroll
-                    for (int g = 0; g < RPG; g++) bacc[m][g] = 0.0f;
-
-#pragma unroll
-                for (int s = 0; s < 4; s++) {
-                    int acc[M][RPG];
-#pragma unroll
-                    for (int m = 0; m < M; m++)
-#pragma unroll
-                        for (int g = 0; g < RPG; g++) acc[m][g] = INT_OUT ? 0 : MAGIC_I;
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        int4 a4[M];
-#pragma unroll
-                        for (int m = 0; m < M; m++)
-                            a4[m] = *reinterpret_cast<const int4*>(&sm.aq[buf][m][warp * 128 + s * 32 + h * 16]);
-#pragma unroll
-                        for (int jj = 0; jj < 4; jj++) {
-                            const int j = 4 * h + jj;                      // word of the sub-block: columns 4j..4j+3
-                            const int q = (j >> 1) * 8 + s * 2 + (j & 1);  // its position in the tile
-                            const uint32_t word = comp(w[q >> 2], q & 3);
-#pragma unroll
-                            for (int g = 0; g < RPG; g++) {
-                                uint32_t msk;
-                                if (KIND == KIND_Q1) msk = word & (0x01010101u << g);
-                                else if (KIND == KIND_Q2) msk = word & (0x03030303u << (2 * g));
-                                else msk = word;
-#pragma unroll
-                                for (int m = 0; m < M; m++) {
-                                    if (KIND == KIND_Q8) acc[m][g] = dp4a_s8s8(msk, compi(a4[m], jj), acc[m][g]);
-                                    else acc[m][g] = dp4a_u8s8(msk, compi(a4[m], jj), acc[m][g]);
-                                }
-                            }
-                        }
-                    }
-                    // Widen the sub-block sums.
-#pragma unroll
-                    for (int m = 0; m < M; m++) {
-                        const float a_d = sm.ad[buf][m][warp * 4 + s];
-                        const float a_sum = sm.asum[buf][m][warp * 4 + s];
-#pragma unroll
-                        for (int g = 0; g < RPG; g++) {
-                            if (INT_OUT) {
-                                int iv;
-                                if (KIND == KIND_Q1) iv = ((acc[m][g] << 1) >> g) - (int)a_sum;       // 2*S1 - sum(a)
-                                else if (KIND == KIND_Q2) iv = (acc[m][g] >> (2 * g)) - (int)a_sum;  // S_code - sum(a)
-                                else iv = acc[m][g];
-                                const int row = panel * RP + lane * RPG + g;
-                                if (row < op.n_rows && blk * 4 + s < op.n_sub)
-                                    op.iout[((size_t)m * op.n_rows + row) * op.n_sub + blk * 4 + s] = iv;
-                            } else {
-                                const float accf = __fadd_rn(__int_as_float(acc[m][g]), -MAGIC_F);  // exact (float)sum
-                                if (KIND == KIND_Q8) {
-                                    const float wd = __half2float(__ushort_as_half(
-                                        (unsigned short)((s < 2 ? ws.x : ws.y) >> (16 * (s & 1)))));
-                                    // ((float)sumi * d_w) * d_a, each product rounded (q8_0.rs:169)
-                                    sm.term[buf][warp][m][s * 32 + lane] = __fmul_rn(__fmul_rn(accf, wd), a_d);
-                                } else {
-                                    // exact integer I as fp32, then block_acc += I * a_scale (exact product, one rounding)
-                                    const float c = (KIND == KIND_Q1) ? (2.0f / (float)(1 << g)) : (1.0f / (float)(1 << (2 * g)));
-                                    const float i_f = fmaf(accf, c, -a_sum);
-                                    bacc[m][g] = fmaf(i_f, a_d, bacc[m][g]);
-                                }
-                            }
-                        }
-                    }
-                }
-                if (!INT_OUT && KIND != KIND_Q8) {
-                    float wd[RPG];
-#pragma unroll
-                    for (int g = 0; g < RPG; g++) {
-                        const uint32_t pair = (g < 2) ? ws.x : (g < 4 ? ws.y : (g < 6 ? ws.z : ws.w));
-                        wd[g] = __half2float(__ushort_as_half((unsigned short)(pair >> (16 * (g & 1)))));
-                    }
-#pragma unroll
-                    for (int m = 0; m < M; m++) {
-                        float4* tp = reinterpret_cast<float4*>(&sm.term[buf][warp][m][lane * RPG]);
-#pragma unroll
-                        for (int g4 = 0; g4 < RPG / 4; g4++)
-                            tp[g4] = make_float4(__fmul_rn(bacc[m][4 * g4], wd[4 * g4]), __fmul_rn(bacc[m][4 * g4 + 1], wd[4 * g4 + 1]),
-                                                 __fmul_rn(bacc[m][4 * g4 + 2], wd[4 * g4 + 2]), __fmul_rn(bacc[m][4 * g4 + 3], wd[4 * g4 + 3]));
-                    }
-                }
-            }
+            if (blk < nb) round_terms<KIND, M, INT_OUT>(sm, w, ws, buf, warp, lane, blk, panel, &op);
             ppanel = panel; pr = r;
             panel = npanel; r = nr;
         }
         if (!INT_OUT) {
             __syncthreads();
-            replay(ppanel, pr, (total - 1) & 1);
+            replay(ppanel, pr, (total - 1 + b0) & 1);
+            if (carry_out) {  // the part ended before the panel's last round: the sums go to the CTA that continues it
+#pragma unroll
+                for (int k = 0; k < NRUN; k++) {
+                    const int idx = tid + k * THREADS;
+                    if (idx < M * RP) __stcg(A.carry + (size_t)sg.carry_out * FLAT_CARRY_FLOATS + idx, run[k]);
+                }
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicAdd(A.cflags + sg.carry_out, 1);
+            }
         }
+        b0 = (b0 + total) & 1;
     }
 
     if (!INT_OUT && peers.n > 1) {
@@ -345,11 +432,10 @@ gemv_dp4a_kernel(const DotOp* __restrict__ ops, const DotItem* __restrict__ item
 __global__ void peer_publish_kernel(const __grid_constant__ PeerTable peers) { peer_flag_exchange(peers); }
 
 template <int KIND, int M, bool INT_OUT>
-int launch_one(const DotOp* ops, const DotItem* items, const int* chunks, int grid, int n_items, const DotOp& single,
-               const PeerTable& peers, cudaStream_t st) {
+int launch_one(const FlatLaunch& A, int grid, int n_items, const DotOp& single, const PeerTable& peers, cudaStream_t st) {
     using S = Smem<KIND, M>;
     if (grid <= 0 || n_items <= 0) return 0;
-    gemv_dp4a_kernel<KIND, M, INT_OUT><<<grid, THREADS, sizeof(S), st>>>(ops, items, chunks, n_items, single, peers);
+    gemv_dp4a_kernel<KIND, M, INT_OUT><<<grid, THREADS, sizeof(S), st>>>(A, n_items, single, peers);
     HB_CUDA(cudaGetLastError());
     return 0;
 }
@@ -363,17 +449,17 @@ int prepare_one() {
 }
 
 template <int KIND>
-int launch_kind(int m, bool int_out, const DotOp* ops, const DotItem* items, const int* chunks, int grid, int n_items,
-                const DotOp& single, const PeerTable& peers, cudaStream_t st) {
+int launch_kind(int m, bool int_out, const FlatLaunch& A, int grid, int n_items, const DotOp& single, const PeerTable& peers,
+                cudaStream_t st) {
     if (int_out) {
         if (m != 1) { set_error("integer block-dot output runs one token per launch"); return -4; }
-        return launch_one<KIND, 1, true>(ops, items, chunks, grid, n_items, single, peers, st);
+        return launch_one<KIND, 1, true>(A, grid, n_items, single, peers, st);
     }
     switch (m) {
-        case 1: return launch_one<KIND, 1, false>(ops, items, chunks, grid, n_items, single, peers, st);
-        case 2: return launch_one<KIND, 2, false>(ops, items, chunks, grid, n_items, single, peers, st);
-        case 3: return launch_one<KIND, 3, false>(ops, items, chunks, grid, n_items, single, peers, st);
-        case 4: return launch_one<KIND, 4, false>(ops, items, chunks, grid, n_items, single, peers, st);
+        case 1: return launch_one<KIND, 1, false>(A, grid, n_items, single, peers, st);
+        case 2: return launch_one<KIND, 2, false>(A, grid, n_items, single, peers, st);
+        case 3: return launch_one<KIND, 3, false>(A, grid, n_items, single, peers, st);
+        case 4: return launch_one<KIND, 4, false>(A, grid, n_items, single, peers, st);
         default: set_error("gemv_dp4a: m=%d outside 1..%d", m, GEMV_MAX_M); return -4;
     }
 }
@@ -408,18 +494,20 @@ int launch_peer_publish(const PeerTable& peers, cudaStream_t st) {
     return 0;
 }
 
-int launch_gemv_dp4a(int kind, int m, bool int_out, const DotOp* ops_dev, const DotItem* items_dev, const int* chunks_dev,
-                     int grid, int n_items, const DotOp* single, cudaStream_t st, const PeerTable* peers) {
+int launch_gemv_dp4a(int kind, int m, bool int_out, const FlatLaunch* list, int grid, int n_items, const DotOp* single,
+                     cudaStream_t st, const PeerTable* peers) {
     static const DotOp none = {};
     static const PeerTable no_peers = {};
+    static const FlatLaunch no_list = {};
     const DotOp& one = single ? *single : none;
     const PeerTable& pt = peers ? *peers : no_peers;
-    if (!ops_dev && !single) { set_error("gemv_dp4a: neither an op list nor a single op"); return -5; }
-    if (ops_dev && !chunks_dev) { set_error("gemv_dp4a: a list launch needs chunk boundaries"); return -5; }
+    const FlatLaunch& A = list ? *list : no_list;
+    if (!list && !single) { set_error("gemv_dp4a: neither a work list nor a single op"); return -5; }
+    if (list && (!list->recs || !list->seg_begin)) { set_error("gemv_dp4a: a list launch needs segment records and their boundaries"); return -5; }
     switch (kind) {
-        case KIND_Q1: return launch_kind<KIND_Q1>(m, int_out, ops_dev, items_dev, chunks_dev, grid, n_items, one, pt, st);
-        case KIND_Q2: return launch_kind<KIND_Q2>(m, int_out, ops_dev, items_dev, chunks_dev, grid, n_items, one, pt, st);
-        case KIND_Q8: return launch_kind<KIND_Q8>(m, int_out, ops_dev, items_dev, chunks_dev, grid, n_items, one, pt, st);
+        case KIND_Q1: return launch_kind<KIND_Q1>(m, int_out, A, grid, n_items, one, pt, st);
+        case KIND_Q2: return launch_kind<KIND_Q2>(m, int_out, A, grid, n_items, one, pt, st);
+        case KIND_Q8: return launch_kind<KIND_Q8>(m, int_out, A, grid, n_items, one, pt, st);
         default: set_error("gemv_dp4a: kind %d has no Q8_0 dot", kind); return -7;
     }
 }

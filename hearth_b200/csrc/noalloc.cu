@@ -123,7 +123,7 @@ extern "C" int hb200_matmul_f32_noalloc(hb200_weight_t w, const float* x_dev, si
         op.ld_b = view.ld_b;
         int grid = sms * gemv_dp4a_ctas_per_sm((int)seq_len);
         if (grid > w->n_panels) grid = w->n_panels;
-        return launch_gemv_dp4a(w->kind, (int)seq_len, false, nullptr, nullptr, nullptr, grid, w->n_panels, &op, st);
+        return launch_gemv_dp4a(w->kind, (int)seq_len, false, nullptr, grid, w->n_panels, &op, st);
     } catch (...) {
         set_error("unexpected C++ exception");
         return HB200_ERR_CUDA;

@@ -39,6 +39,8 @@ SIGNATURES = {
     "hb200_block_bytes": (_sz, [_int]),
     "hb200_measure_i8_peak": (_int, [C.POINTER(C.c_double)]),
     "hb200_plan_chunks": (_int, [C.POINTER(C.c_int), C.c_size_t, _int, C.POINTER(C.c_int)]),
+    "hb200_plan_rounds": (_int, [C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_size_t, _int, C.POINTER(C.c_int),
+                                 C.POINTER(C.c_int), C.c_size_t, C.POINTER(C.c_size_t)]),
     "hb200_byte_size": (_sz, [_int, _sz]),
     "hb200_selected_kernel": (C.c_char_p, [_int, _sz]),
     "hb200_dispatch_report": (_int, [C.POINTER(_int), _sz, C.c_char_p, _sz, C.POINTER(_sz)]),

@@ -117,6 +117,25 @@ HB200_API int hb200_measure_i8_peak(double *tops);
  * an item is a whole panel of rows whose cost depends on its matrix. */
 HB200_API int hb200_plan_chunks(const int *cost, size_t n_items, int grid, int *chunks);
 
+/* The work plan of a list launch of the decode matvec, exported for tests.
+ * Item i is panel panel[i] of op op[i] and takes rounds[i] rounds (one round =
+ * eight 128-column blocks).  With at least two of the longest items per CTA
+ * the list of all rounds is cut into `grid` equal shares, and an item that a
+ * cut falls into is split between the two neighbouring CTAs: the earlier one
+ * computes its first rounds and hands the running fp32 sums over, the later
+ * one continues the same ordered sum (same bits as an unsplit panel).  With
+ * less work the cuts fall between items.  seg_begin gets grid + 1 entries;
+ * CTA c owns segments seg_begin[c] .. seg_begin[c+1]-1.  A segment is eight
+ * ints {op, first panel, panel count, r0, r1, flags, carry_in, carry_out}:
+ * rounds [r0, r1) of `count` consecutive panels (r0 = 0 and r1 = rounds for
+ * whole panels; count = 1 for a part); flags bit 0: starts from the carry
+ * slot carry_in, bit 1: ends by writing carry slot carry_out.  *n_segs
+ * receives the number of segments; HB200_ERR_TOO_LARGE if seg_cap (segments
+ * that fit in segs) is too small.  Needs no device.  Reference: rows are split
+ * evenly over threads (hearth-llm/src/pool.rs:321-323). */
+HB200_API int hb200_plan_rounds(const int *op, const int *panel, const int *rounds, size_t n_items, int grid,
+                                int *seg_begin, int *segs, size_t seg_cap, size_t *n_segs);
+
 /* ---- block geometry ----------------------------------------------------- */
 
 /* GgmlDType::block_size / block_bytes / byte_size

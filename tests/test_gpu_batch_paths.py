@@ -192,3 +192,48 @@ def test_kquant_configured_shapes_in_one_batch(hb, oracle, seq_len):
             a.free()
         for W in Ws:
             W.free()
+
+
+@pytest.mark.parametrize("dtype,seq_len", [(Q1_0, 1), (Q1_0, 2), (Q2_0, 1), (PQ2_0, 4), (Q1_0, 7), (8, 2)])
+def test_decode_list_launch_with_cut_panels(hb, oracle, dtype, seq_len):
+    """A recorded batch of decode matvecs large enough that the launch's rounds are cut into equal shares per CTA and
+    panels are split between neighbouring CTAs (the ordered sum of such a panel continues from a carry in global
+    memory).  Matrices with one, two and three rounds per panel (the last one ragged), a ragged last panel, and a
+    change of matrix in mid-pipeline in every CTA.  Every row of every matrix is compared with the oracle, twice (the
+    second launch reuses the carry slots with a new epoch)."""
+    import torch
+    dev = torch.device("cuda:0")
+    rpp = {Q1_0: 256, Q2_0: 128, PQ2_0: 128, 8: 32}[dtype]  # rows per panel
+    scale = 1 if dtype != 8 else 2  # Q8_0 panels are small: more of them
+    specs = ([(25 * rpp - 37, 2048)] * (20 * scale) + [(16 * rpp, 2304)] * (16 * scale) + [(8 * rpp, 1024)] * (8 * scale)
+             + [(3 * rpp + 1, 128)] * 4)
+    ks = sorted({k for _, k in specs})
+    acts = {k: hb.Act(seq_len, k) for k in ks}
+    xs = {k: synth.activations(seq_len, k, seed=seq_len * 13 + k) for k in ks}
+    ws = [synth.weights(dtype, n, k, seed=500 + i, allow_code3=True) for i, (n, k) in enumerate(specs)]
+    Ws = [hb.Weight.upload(dtype, n, k, w) for (n, k), w in zip(specs, ws)]
+    total = sum(n for n, _ in specs)
+    out_dev = torch.full((seq_len, total), float("nan"), dtype=torch.float32, device=dev)
+    batch = hb.Batch()
+    off = 0
+    for (n, k), W in zip(specs, Ws):
+        batch.add(W, acts[k], seq_len, out_dev[:, off:], ld_out=total)
+        off += n
+    batch.seal()
+    try:
+        for k, a in acts.items():
+            a.quantize(seq_len, x_dev=torch.from_numpy(xs[k]).to(dev))
+        q8 = {k: oracle.quantize_q8_0(xs[k]) for k in ks}
+        want = np.concatenate([oracle.dot_rows_batched(dtype, w, q8[k], n, k) for (n, k), w in zip(specs, ws)], axis=1)
+        for rep in range(2):
+            out_dev.fill_(float("nan"))
+            batch.launch()
+            torch.cuda.synchronize()
+            hb.check_status()
+            assert_bits_equal(out_dev.cpu().numpy(), want, f"dtype {dtype}, {seq_len} tokens, launch {rep}")
+    finally:
+        batch.free()
+        for a in acts.values():
+            a.free()
+        for W in Ws:
+            W.free()
