@@ -1453,7 +1453,8 @@ static std::vector<int> balanced_chunks(const std::vector<int>& cost, int grid) 
 }
 
 // Work plan of a list launch of the decode matvec.  Item i is panel panel[i] of op op[i] and takes rounds[i] rounds.
-// With enough work (at least two of the longest items per CTA) the list of ALL rounds is cut into `grid` equal shares,
+// With enough work (at least two of the longest items per CTA) and a balance that cuts between items cannot reach
+// (largest share more than 3 % above the mean), the list of ALL rounds is cut into `grid` equal shares,
 // and a cut inside an item splits it between two neighbouring CTAs (the earlier one hands its running sums over in
 // carry slot c, c = index of the later CTA); otherwise the cuts fall between items (balanced_chunks).  Per CTA the
 // segments come in the order [first rounds of the item cut at its end] [whole items, consecutive panels of one op
@@ -1473,12 +1474,17 @@ static void plan_flat(const int* op, const int* panel, const int* rounds, int n,
     const long long R = pre[n];
     std::vector<long long> cut(grid + 1, R);
     cut[0] = 0;
-    if (R >= 2LL * grid * maxr) {
+    // Cuts between items first; panels are cut only where that leaves the largest share more than 3 % above the mean (a
+    // big model on one GPU balances to within 0.5 % without, and every cut panel costs its two CTAs a segment more).
+    std::vector<int> cost(rounds, rounds + n);
+    for (int& v : cost) v = v * 8 + 1;  // a small fixed share per panel, as measured for the item-granular plan
+    const std::vector<int> chunks = balanced_chunks(cost, grid);
+    long long largest = 0;
+    for (int c = 0; c < grid; c++) largest = std::max(largest, pre[chunks[c + 1]] - pre[chunks[c]]);
+    const bool cut_panels = R >= 2LL * grid * maxr && largest * grid * 100 > R * 103;
+    if (cut_panels) {
         for (int c = 1; c < grid; c++) cut[c] = (R * c) / grid;
     } else {
-        std::vector<int> cost(rounds, rounds + n);
-        for (int& v : cost) v = v * 8 + 1;  // a small fixed share per panel, as measured for the item-granular plan
-        const std::vector<int> chunks = balanced_chunks(cost, grid);
         for (int c = 1; c < grid; c++) cut[c] = pre[chunks[c]];
     }
     int i = 0;

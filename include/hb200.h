@@ -119,8 +119,9 @@ HB200_API int hb200_plan_chunks(const int *cost, size_t n_items, int grid, int *
 
 /* The work plan of a list launch of the decode matvec, exported for tests.
  * Item i is panel panel[i] of op op[i] and takes rounds[i] rounds (one round =
- * eight 128-column blocks).  With at least two of the longest items per CTA
- * the list of all rounds is cut into `grid` equal shares, and an item that a
+ * eight 128-column blocks).  With at least two of the longest items per CTA,
+ * and when cuts between items would leave the largest share more than 3 %
+ * above the mean, the list of all rounds is cut into `grid` equal shares, and an item that a
  * cut falls into is split between the two neighbouring CTAs: the earlier one
  * computes its first rounds and hands the running fp32 sums over, the later
  * one continues the same ordered sum (same bits as an unsplit panel).  With
