@@ -365,6 +365,59 @@ def time_secondary(hb, torch, dist, name, rank, world, dev, stream, steps):
     return entry
 
 
+def time_producers(hb, torch, dev, stream, steps=5):
+    """Device-timed activation producers, one launch each over an input larger than the L2 (the shapes of an 8B model,
+    4096 or 12288 tokens): the Q8_0 quantizer (hearth-quant/src/q8_0.rs:20-51) alone and fused behind the RMS norm, the
+    gated activation and the Hadamard rotation (hearth-llm/src/ops.rs:489, :273; model/qwen35.rs:924-943).  Algorithmic
+    bytes per element: the f32 inputs read, one int8 and 2 x 4 / 32 bytes of block values written."""
+    peak, _ = measured_peaks()
+    out = []
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    def entry(name, kernel, ms, n_elem, in_bytes_per_elem, shape):
+        alg = n_elem * (in_bytes_per_elem + 1.25)
+        gbs = alg / (ms * 1e-3) / 1e9
+        return {"producer": name, "kernel": kernel, "shape": shape, "launches_per_step": 1, "ms_per_step": ms,
+                "algorithmic_bytes_per_step": alg,
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak}}
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(77)
+    M, K = 4096, 12288  # 201 MB of f32 per input
+    x = torch.randn((M, K), generator=gen, device=dev, dtype=torch.float32)
+    up = torch.randn((M, K), generator=gen, device=dev, dtype=torch.float32)
+    act = hb.Act(M, K)
+    ms = timed(lambda: act.quantize(M, x_dev=x, stream=stream))
+    out.append(entry("quantize_q8_0", "quantize_q8_0_kernel", ms, M * K, 4, f"[{M}][{K}]"))
+    ms = timed(lambda: act.silu_mul_q8(x, up, M, stream=stream))
+    out.append(entry("silu_mul_q8", "silu_mul_q8_kernel", ms, M * K, 8, f"2 x [{M}][{K}]"))
+    act.free()
+    del x, up
+    M, K = 12288, 4096
+    x = torch.randn((M, K), generator=gen, device=dev, dtype=torch.float32)
+    act = hb.Act(M, K)
+    wt = torch.rand((K,), generator=gen, device=dev, dtype=torch.float32) + 0.5
+    ms = timed(lambda: act.rms_norm_q8(x, wt, 1e-6, M, stream=stream))
+    out.append(entry("rms_norm_q8", "rms_norm_q8_kernel", ms, M * K, 4, f"[{M}][{K}]"))
+    signs = torch.where(torch.rand((K,), generator=gen, device=dev) < 0.5, -1.0, 1.0).to(torch.float32)
+    ms = timed(lambda: act.hadamard_quantize(M, 256, x_dev=x, signs_dev=signs, stream=stream))
+    out.append(entry("hadamard_quantize_q8_0", "hadamard_quantize_kernel", ms, M * K, 4, f"[{M}][{K}], blocks of 256"))
+    act.free()
+    hb.check_status()
+    return out
+
+
 def shared_pinned(torch, name, n_floats, rank, world, dist):
     """One float32 host buffer shared by all ranks of the node (a file in /dev/shm mapped by every process) and
     page-locked in each of them, so that each rank's readback lands in its own part of ONE host buffer.
@@ -659,6 +712,13 @@ def run_ours(args, cfg, rank, world, local_rank):
             except Exception as e:  # noqa: BLE001 - one failed extra workload must not lose the headline line
                 secondary.append({"workload": name, "error": f"{type(e).__name__}: {e}"})
 
+    producers = None
+    if world == 1 and not args.quick and not args.no_secondary and args.workload == DEFAULT_WORKLOAD:
+        try:
+            producers = time_producers(hb, torch, dev, stream)
+        except Exception as e:  # noqa: BLE001
+            producers = [{"error": f"{type(e).__name__}: {e}"}]
+
     if rank == 0:
         ab = algorithmic_bytes(cfg)
         metric, unit, value, roof = roofline_of(hb, cfg, ms_per_step, world)
@@ -693,6 +753,8 @@ def run_ours(args, cfg, rank, world, local_rank):
                                               "value": ab["weights"] / (ms_nccl / args.steps * 1e-3) / 1e9, "unit": UNIT}
         if secondary:
             line["secondary"] = secondary
+        if producers:
+            line["producers"] = producers
         if world == 1 and not args.no_cpu and not args.quick:
             arm = CpuArm(cfg, 0, 1)
             t0 = time.perf_counter()
@@ -733,7 +795,18 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="skip the extra workloads reported under 'secondary'")
     ap.add_argument("--quick", action="store_true",
                     help="kernel timing only: no clock-sampling burst, no end-to-end leg, no CPU leg (for profiler runs)")
+    ap.add_argument("--producers-only", action="store_true",
+                    help="time only the activation producers (quantizer, fused norm / activation / rotation) on one GPU")
     args = ap.parse_args()
+    if args.producers_only:
+        import torch
+        from hearth_b200 import api as hb
+        hb.init(0)
+        dev = torch.device("cuda:0")
+        torch.cuda.set_device(dev)
+        stream = torch.cuda.current_stream()
+        print(json.dumps({"producers": time_producers(hb, torch, dev, stream, steps=max(1, min(args.steps, 5)))}), flush=True)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
