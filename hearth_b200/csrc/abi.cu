@@ -1656,18 +1656,18 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
     // K-quant ops: per (kind, tokens per pass) one list of matrices whose items (32-row panel x token tile) are numbered
     // consecutively, and contiguous runs of items per CTA balanced by rounds.
     for (int kind : {KIND_Q4K, KIND_Q6K})
-        for (int mt : {1, 2, 4, 8}) {
+        for (int mt : {1, 2, 4, 8, 16}) {
             std::vector<KqMat> mats;
             std::vector<int> cost;
             int n_items = 0;
             for (const BatchEntry& e : b->kquant) {
-                if (e.w->kind != kind || kquant_tokens_per_pass((int)e.seq_len) != mt) continue;
+                if (e.w->kind != kind || kquant_tokens_per_pass(kind, (int)e.seq_len) != mt) continue;
                 KqMat m;
                 m.kq = e.w->kq; m.d16 = e.w->d16; m.x = e.a->x; m.out = e.out;
                 m.n_rows = (int)e.w->n_rows; m.n_cols = (int)e.w->n_cols; m.nblk = e.w->nb; m.n_panels = e.w->n_panels;
                 m.seq_len = (int)e.seq_len; m.ld_out = (int)e.ld_out;
                 m.item_begin = n_items;
-                m.item_end = n_items + kquant_items(m.n_panels, m.seq_len);
+                m.item_end = n_items + kquant_items(kind, m.n_panels, m.seq_len);
                 for (int t = m.item_begin; t < m.item_end; t++) cost.push_back(kquant_rounds(kind, m.nblk));
                 n_items = m.item_end;
                 mats.push_back(m);

@@ -267,10 +267,10 @@ struct KqMat {
 };
 int launch_kquant_gemv(int kind, const uint4* kq, const unsigned short* d16, int n_rows, int n_cols, int nblk, int n_panels,
                        const float* x, int seq_len, float* out, int ld_out, int sm_count, cudaStream_t st, int* status = nullptr);
-// Many matrices of one kind and one tokens-per-pass class (1, 2, 4 or 8) in one launch.  `status`: device word that the
+// Many matrices of one kind and one tokens-per-pass class (1, 2, 4, 8; Q4_K also 16) in one launch.  `status`: device word that the
 // eight-token Q4_K kernel sets (code 40) if its bounded wait for a bulk copy of x expires; may be null.
-int kquant_tokens_per_pass(int seq_len);
-int kquant_items(int n_panels, int seq_len);
+int kquant_tokens_per_pass(int kind, int seq_len);
+int kquant_items(int kind, int n_panels, int seq_len);
 int kquant_rounds(int kind, int nblk);
 int kquant_grid(int kind, int mt, int sm_count, int n_items);
 int launch_kquant_gemv_list(int kind, int mt, const KqMat* mats_dev, const int* chunks_dev, int n_items, int grid, cudaStream_t st,

@@ -524,20 +524,25 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
 // the same operands as in the general kernel, and the ordered replay is unchanged: same bits.  Weight pieces are
 // refilled in place with the next round's as soon as they have been expanded.  The wait for a bulk copy is bounded:
 // on expiry the CTA records status code 40 and stops.
-template <int KIND>
+template <int KIND, int MT>
 struct KqWideGeom {
-    static constexpr int BLK_PER_ROUND = (KIND == KIND_Q4K) ? 8 : 4;
+    // Q4_K: a (warp, half) unit takes SPU = 32 / MT sub-blocks of a block, so that its expanded weights serve MT tokens
+    // and the x of a round (2 SPU blocks) and its terms fill the same shared memory for 8 and 16 (or 32) tokens per pass.
+    static constexpr int SPU = (KIND == KIND_Q4K) ? 32 / MT : 0;
+    static constexpr int BLK_PER_ROUND = (KIND == KIND_Q4K) ? 2 * SPU : 4;
     static constexpr int CH = BLK_PER_ROUND * 256;                   // columns of x per round
     static constexpr int HALF_COLS = CH / 2;
     static constexpr int HALF = HALF_COLS + 4;                       // floats per half row in shared memory
     static constexpr int TERMS_PER_BLK = (KIND == KIND_Q4K) ? 8 : 32;
     static constexpr int TERMS = BLK_PER_ROUND * TERMS_PER_BLK;      // ordered terms per row and round
     static constexpr int NP = (KIND == KIND_Q4K) ? 9 : 13;
+    static_assert(KIND != KIND_Q4K || MT == 8 || MT == 16 || MT == 32, "Q4_K: 8, 16 or 32 tokens per pass");
+    static_assert(KIND != KIND_Q6K || MT == 8, "Q6_K: 8 tokens per pass");
 };
 
 template <int KIND, int MT>
 struct KqWideSmem {
-    using W = KqWideGeom<KIND>;
+    using W = KqWideGeom<KIND, MT>;
     alignas(16) float x[2][MT][2][W::HALF];
     // Ordered terms of a round, in groups of four consecutive terms (group k4, member c) per (token, row):
     //   Q4_K  term[half][k4 % (K4/2)][m][c][row] as floats, the second half's terms (written by lanes 16..31 of every warp)
@@ -575,15 +580,17 @@ __device__ __forceinline__ bool kq_mbar_wait(uint32_t bar, uint32_t parity) {
 
 template <int KIND, int MT>
 __global__ void __launch_bounds__(KQ_THREADS, 1) kq_wide_kernel(const __grid_constant__ KqLaunch L) {
-    using W = KqWideGeom<KIND>;
+    using W = KqWideGeom<KIND, MT>;
     using S = KqWideSmem<KIND, MT>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     S& sm = *reinterpret_cast<S*>(smem_raw);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int half = lane >> 4, li = lane & 15;  // rows li and li + 16
-    // Q4_K: sub-blocks 4 part + u (u = 0..3) of block rb of the round.  Q6_K: quarter `part` of block rb.
-    const int part = (KIND == KIND_Q4K) ? (warp & 1) : (warp & 3);
-    const int bih = (KIND == KIND_Q4K) ? (warp >> 1) : (warp >> 2);  // block inside this half of the round
+    // Q4_K: sub-blocks SPU part + u (u = 0..SPU-1) of block rb of the round.  Q6_K: quarter `part` of block rb.
+    constexpr int SPU = (KIND == KIND_Q4K) ? W::SPU : 1;
+    constexpr int UPB = (KIND == KIND_Q4K) ? 8 / SPU : 4;  // units (warps) per block
+    const int part = warp % UPB;
+    const int bih = warp / UPB;  // block inside this half of the round
     const int rb = half * (W::BLK_PER_ROUND / 2) + bih;
 
     int it0, it1;
@@ -635,24 +642,25 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq_wide_kernel(const __grid_con
         const int col0 = st.r * W::CH;
         const bool bulk_ok = ((a.n_cols & 3) == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
         if (bulk_ok) {
-            if (tid == 0) {
+            if (warp == 0) {  // one copy per lane and turn: issued by one thread they would make its warp the round's straggler
                 const int ntok = min(MT, a.seq_len - tok0);
                 // valid columns of each half (multiples of 256)
                 const int c0 = min(W::HALF_COLS, a.n_cols - col0), c1 = max(0, min(W::HALF_COLS, a.n_cols - col0 - W::HALF_COLS));
                 const uint32_t bar = kq_smem_u32(&sm.bar[buf]);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(ntok * (c0 + c1) * 4)) : "memory");
-                for (int m = 0; m < ntok; m++) {
-                    const float* src = a.x + (size_t)(tok0 + m) * a.n_cols + col0;
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                     kq_smem_u32(&sm.x[buf][m][0][0])),
-                                 "l"(src), "r"((uint32_t)(c0 * 4)), "r"(bar)
-                                 : "memory");
-                    if (c1 > 0)
+                if (lane == 0)
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(ntok * (c0 + c1) * 4)) : "memory");
+                __syncwarp();
+                for (int c = lane; c < 2 * ntok; c += 32) {
+                    const int m = c >> 1, hh = c & 1;
+                    const int cols = hh ? c1 : c0;
+                    if (cols > 0) {
+                        const float* src = a.x + (size_t)(tok0 + m) * a.n_cols + col0 + hh * W::HALF_COLS;
                         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                                         kq_smem_u32(&sm.x[buf][m][1][0])),
-                                     "l"(src + W::HALF_COLS), "r"((uint32_t)(c1 * 4)), "r"(bar)
+                                         kq_smem_u32(&sm.x[buf][m][hh][0])),
+                                     "l"(src), "r"((uint32_t)(cols * 4)), "r"(bar)
                                      : "memory");
+                    }
                 }
             }
             return true;
@@ -690,7 +698,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq_wide_kernel(const __grid_con
             if (KIND == KIND_Q4K) {
                 hd[rr] = __ldg(p + rr * 16);
 #pragma unroll
-                for (int u = 0; u < 4; u++) pc[u][rr] = __ldg(p + (1 + 4 * part + u) * 32 + rr * 16);
+                for (int u = 0; u < SPU; u++) pc[u][rr] = __ldg(p + (1 + SPU * part + u) * 32 + rr * 16);
             } else {
 #pragma unroll
                 for (int i = 0; i < 3; i++) pc[i][rr] = __ldg(p + i * 32 + rr * 16);
@@ -763,25 +771,29 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq_wide_kernel(const __grid_con
         if (cur.r * W::BLK_PER_ROUND + rb < cur.nblk) {
             if constexpr (KIND == KIND_Q4K) {
                 float d[2], dmin[2];
-                uint32_t sw_lo[2], sw_hi[2];  // the six scale bytes of this warp's four sub-blocks (q4_k.rs:51-96)
+                uint32_t sw[2][3];  // the 12 scale bytes of the block (q4_k.rs:51-96)
 #pragma unroll
                 for (int rr = 0; rr < 2; rr++) {
                     d[rr] = h2f_bits(hd[rr].x & 0xffffu);
                     dmin[rr] = h2f_bits(hd[rr].x >> 16);
-                    sw_lo[rr] = part ? __funnelshift_r(hd[rr].z, hd[rr].w, 16) : hd[rr].y;
-                    sw_hi[rr] = part ? (hd[rr].w >> 16) : hd[rr].z;
+                    sw[rr][0] = hd[rr].y; sw[rr][1] = hd[rr].z; sw[rr][2] = hd[rr].w;
                     hd[rr] = __ldg(pn + rr * 16);
                 }
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int u = 0; u < SPU; u++) {
+                    const int sb = SPU * part + u;  // sub-block of the block; its pair sb >> 1 owns scale bytes 3 (sb >> 1) .. + 2
                     float2 vv[2][4][4];
 #pragma unroll
                     for (int rr = 0; rr < 2; rr++) {
-                        const int i3 = (u >> 1) * 3;  // first of the three scale bytes of the sub-block pair, inside the window
-                        auto wbyte = [&](int i) { return ((i < 4 ? sw_lo[rr] >> (8 * i) : sw_hi[rr] >> (8 * (i - 4)))) & 0xffu; };
-                        const uint32_t s0 = wbyte(i3), s1 = wbyte(i3 + 1), s2 = wbyte(i3 + 2);
-                        const uint32_t sc = (u & 1) ? ((s1 >> 4) | ((s2 & 0x03) << 4)) : (s0 & 0x3F);
-                        const uint32_t mn = (u & 1) ? ((s2 >> 2) & 0x3F) : ((s0 >> 6) | ((s1 & 0x0F) << 2));
+                        // the pair's three bytes as one window: bytes o .. o + 2 of the 12, o = 3 (sb >> 1)
+                        const int o = 3 * (sb >> 1), wi = o >> 2;
+                        const uint32_t lo = wi == 0 ? sw[rr][0] : (wi == 1 ? sw[rr][1] : sw[rr][2]);
+                        const uint32_t hi = wi == 0 ? sw[rr][1] : (wi == 1 ? sw[rr][2] : 0u);
+                        const uint32_t win = __funnelshift_r(lo, hi, 8 * (o & 3));
+                        const uint32_t s0 = win & 0xffu, s1 = (win >> 8) & 0xffu, s2 = (win >> 16) & 0xffu;
+                        const bool odd = sb & 1;
+                        const uint32_t sc = odd ? ((s1 >> 4) | ((s2 & 0x03) << 4)) : (s0 & 0x3F);
+                        const uint32_t mn = odd ? ((s2 >> 2) & 0x3F) : ((s0 >> 6) | ((s1 & 0x0F) << 2));
                         const float scf = __fmul_rn((float)sc, d[rr]), mnf = __fmul_rn((float)mn, dmin[rr]);
                         const uint32_t qw[4] = {pc[u][rr].x, pc[u][rr].y, pc[u][rr].z, pc[u][rr].w};
                         if (fabsf(d[rr]) <= 65504.0f) {
@@ -807,35 +819,39 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq_wide_kernel(const __grid_con
                                     vv[rr][tt][p] = make_float2(__fsub_rn(__fmul_rn((float)((qw[tt] >> (8 * p)) & 0xF), scf), mnf),
                                                                 __fsub_rn(__fmul_rn((float)((qw[tt] >> (8 * p + 4)) & 0xF), scf), mnf));
                         }
-                        pc[u][rr] = __ldg(pn + (1 + 4 * part + u) * 32 + rr * 16);
+                        pc[u][rr] = __ldg(pn + (1 + SPU * part + u) * 32 + rr * 16);
                     }
-                    const float* xsub = &sm.x[buf][0][half][bih * 256 + (4 * part + u) * 32];
-                    float* tdst = &sm.term[S::term_at(rb * 2 + part, 0, u, li)];  // token m, row li + 16 rr: + m * 128 + rr * 16
-                    // The terms of all tokens are kept in registers and stored after the loop: with a store between two
-                    // tokens the compiler cannot move the next token's reads of x (same shared memory) ahead of it, and
-                    // every token would wait out its own load, multiply-add and reduction latencies alone.
-                    float tv[MT][2];
+                    const float* xsub = &sm.x[buf][0][half][bih * 256 + sb * 32];
+                    float* tdst = &sm.term[S::term_at(rb * 2 + (sb >> 2), 0, sb & 3, li)];  // token m, row li + 16 rr: + m * 128 + rr * 16
+                    // The terms of eight tokens at a time are kept in registers and stored after their loop: with a store
+                    // between two tokens the compiler cannot move the next token's reads of x (same shared memory) ahead of
+                    // it, and every token would wait out its own load, multiply-add and reduction latencies alone.
 #pragma unroll
-                    for (int m = 0; m < MT; m++) {
-                        float2 l0[4], l1[4];
+                    for (int m0 = 0; m0 < MT; m0 += 8) {
+                        float tv[8][2];
 #pragma unroll
-                        for (int tt = 0; tt < 4; tt++) {
-                            const float4* xp = reinterpret_cast<const float4*>(xsub + m * (2 * W::HALF) + tt * 8);
-                            const float4 x0 = xp[0], x1 = xp[1];
-                            const float2 xs[4] = {make_float2(x0.x, x0.y), make_float2(x0.z, x0.w), make_float2(x1.x, x1.y), make_float2(x1.z, x1.w)};
+                        for (int mm = 0; mm < 8; mm++) {
+                            const int m = m0 + mm;
+                            float2 l0[4], l1[4];
 #pragma unroll
-                            for (int p = 0; p < 4; p++) {
-                                l0[p] = __ffma2_rn(vv[0][tt][p], xs[p], tt == 0 ? zero2 : l0[p]);
-                                l1[p] = __ffma2_rn(vv[1][tt][p], xs[p], tt == 0 ? zero2 : l1[p]);
+                            for (int tt = 0; tt < 4; tt++) {
+                                const float4* xp = reinterpret_cast<const float4*>(xsub + m * (2 * W::HALF) + tt * 8);
+                                const float4 x0 = xp[0], x1 = xp[1];
+                                const float2 xs[4] = {make_float2(x0.x, x0.y), make_float2(x0.z, x0.w), make_float2(x1.x, x1.y), make_float2(x1.z, x1.w)};
+#pragma unroll
+                                for (int p = 0; p < 4; p++) {
+                                    l0[p] = __ffma2_rn(vv[0][tt][p], xs[p], tt == 0 ? zero2 : l0[p]);
+                                    l1[p] = __ffma2_rn(vv[1][tt][p], xs[p], tt == 0 ? zero2 : l1[p]);
+                                }
                             }
+                            tv[mm][0] = reduce8(l0);
+                            tv[mm][1] = reduce8(l1);
                         }
-                        tv[m][0] = reduce8(l0);
-                        tv[m][1] = reduce8(l1);
-                    }
 #pragma unroll
-                    for (int m = 0; m < MT; m++) {
-                        tdst[m * 128] = tv[m][0];
-                        tdst[m * 128 + 16] = tv[m][1];
+                        for (int mm = 0; mm < 8; mm++) {
+                            tdst[(m0 + mm) * 128] = tv[mm][0];
+                            tdst[(m0 + mm) * 128 + 16] = tv[mm][1];
+                        }
                     }
                 }
             } else {
@@ -916,7 +932,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq_wide_kernel(const __grid_con
 
 // Resident CTAs per SM of each instantiation, measured by the occupancy API at prepare time: the grid of the
 // persistent kernel is sized to exactly one wave.
-int g_kq_ctas[2][9] = {};
+int g_kq_ctas[2][17] = {};
 
 template <int KIND, int MT>
 int launch_mt(const KqLaunch& L, int grid, cudaStream_t st) {
@@ -932,6 +948,9 @@ int launch_kind(const KqLaunch& L, int mt, int grid, cudaStream_t st) {
     if (mt == 1) return launch_mt<KIND, 1>(L, grid, st);
     if (mt == 2) return launch_mt<KIND, 2>(L, grid, st);
     if (mt == 8) return launch_mt<KIND, 8>(L, grid, st);
+    if constexpr (KIND == KIND_Q4K) {
+        if (mt == 16) return launch_mt<KIND, 16>(L, grid, st);
+    }
     return launch_mt<KIND, 4>(L, grid, st);
 }
 
@@ -957,6 +976,7 @@ int kquant_prepare() {
     if ((rc = prepare_one<KIND_Q4K, 2>())) return rc;
     if ((rc = prepare_one<KIND_Q4K, 4>())) return rc;
     if ((rc = prepare_one<KIND_Q4K, 8>())) return rc;
+    if ((rc = prepare_one<KIND_Q4K, 16>())) return rc;
     if ((rc = prepare_one<KIND_Q6K, 1>())) return rc;
     if ((rc = prepare_one<KIND_Q6K, 2>())) return rc;
     if ((rc = prepare_one<KIND_Q6K, 4>())) return rc;
@@ -979,10 +999,19 @@ int launch_kquant_repack(int kind, const uint8_t* raw, size_t row_bytes, int n_r
 }
 
 // One pass over the weights serves 1, 2, 4 or 8 tokens: from eight tokens on the weights are expanded once per eight.
-int kquant_tokens_per_pass(int seq_len) { return seq_len == 1 ? 1 : (seq_len == 2 ? 2 : (seq_len < 8 ? 4 : 8)); }
+// One pass over the weights serves 1, 2, 4 or 8 tokens, Q4_K also 16.  From eight tokens on, the cheaper tiling: a pass
+// costs its tokens (padding included) plus a fixed share worth 1.7 tokens (measured on the 14336 x 4096 set: 0.615 ms for
+// a pass of eight, 1.123 ms for a pass of sixteen).  Thirty-two tokens per pass (rounds of two blocks) measured slower
+// than two passes of sixteen: 2.49 against 2.25 ms, the fixed cost of four times as many rounds outweighs the expansion saved.
+int kquant_tokens_per_pass(int kind, int seq_len) {
+    if (seq_len < 8) return seq_len == 1 ? 1 : (seq_len == 2 ? 2 : 4);
+    if (kind != KIND_Q4K) return 8;
+    const double c8 = (double)((seq_len + 7) / 8) * (8 + 1.7), c16 = (double)((seq_len + 15) / 16) * (16 + 1.7);
+    return c16 < c8 ? 16 : 8;
+}
 
-int kquant_items(int n_panels, int seq_len) {
-    const int mt = kquant_tokens_per_pass(seq_len);
+int kquant_items(int kind, int n_panels, int seq_len) {
+    const int mt = kquant_tokens_per_pass(kind, seq_len);
     return ((seq_len + mt - 1) / mt) * n_panels;
 }
 
@@ -1006,9 +1035,9 @@ int launch_kquant_gemv(int kind, const uint4* kq, const unsigned short* d16, int
     KqMat& a = L.single;
     a.kq = kq; a.d16 = d16; a.x = x; a.out = out;
     a.n_rows = n_rows; a.n_cols = n_cols; a.nblk = nblk; a.n_panels = n_panels; a.seq_len = seq_len; a.ld_out = ld_out;
-    const int mt = kquant_tokens_per_pass(seq_len);
+    const int mt = kquant_tokens_per_pass(kind, seq_len);
     a.item_begin = 0;
-    a.item_end = L.n_items = kquant_items(n_panels, seq_len);
+    a.item_end = L.n_items = kquant_items(kind, n_panels, seq_len);
     const int grid = kquant_grid(kind, mt, sm_count, L.n_items);
     if (kind == KIND_Q4K) return launch_kind<KIND_Q4K>(L, mt, grid, st);
     if (kind == KIND_Q6K) return launch_kind<KIND_Q6K>(L, mt, grid, st);

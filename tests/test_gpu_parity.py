@@ -195,7 +195,11 @@ def test_row_range_upload_is_the_pool_row_split(hb, oracle):
 
 @pytest.mark.parametrize("dtype", [Q4_K, Q6_K])
 @pytest.mark.parametrize("n_rows,n_cols,seq_len", [(64, 4096, 1), (37, 512, 3), (5, 14336, 2), (1, 256, 1),
-                                                    (33, 1280, 9), (40, 768, 5), (70, 2304, 1), (3, 1792, 2)])
+                                                    (33, 1280, 9), (40, 768, 5), (70, 2304, 1), (3, 1792, 2),
+                                                    # eight and more tokens: the two-rows-per-lane kernel, Q4_K with 8, 16 or
+                                                    # 32 tokens per pass; ragged last rounds (5, 9, 3, 1 blocks), ragged token tiles
+                                                    (1, 256, 8), (33, 1280, 12), (70, 2304, 16), (37, 512, 17), (64, 4096, 32),
+                                                    (40, 768, 33), (5, 14336, 40), (96, 2048, 64)])
 def test_kquant_f32_matvec(hb, oracle, dtype, n_rows, n_cols, seq_len):
     """Tolerance-level parity (the 8-lane reduce order is an assumption shared with the oracle)."""
     w = synth.weights(dtype, n_rows, n_cols, seed=dtype + n_rows)
@@ -211,7 +215,7 @@ def test_kquant_f32_matvec(hb, oracle, dtype, n_rows, n_cols, seq_len):
 
 
 @pytest.mark.parametrize("dtype", [Q4_K, Q6_K])
-@pytest.mark.parametrize("seq_len", [1, 3])
+@pytest.mark.parametrize("seq_len", [1, 3, 8, 16, 32])
 def test_kquant_non_finite_block_scales(hb, oracle, dtype, seq_len):
     """Blocks whose f16 d (or dmin) is inf or NaN leave the fast nibble-to-float path: inf and NaN must come out in the
     rows the reference puts them in, and every other row keeps its bits."""
