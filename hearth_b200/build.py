@@ -46,6 +46,47 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+# The bounds-checked debug build: the translation units whose kernels carry index checks (and the host layer, which
+# reports them) are compiled again with -DHB200_BOUNDS; the others are shared with the normal build.
+BOUNDS_LIB = os.path.join(HERE, "libhearth_b200_bounds.so")
+BOUNDS_SOURCES = ["abi.cu", "quantize.cu", "producers.cu", "gemv_dp4a.cu", "kquant.cu", "noalloc.cu"]
+
+
+def build_bounds(force: bool = False) -> str:
+    """libhearth_b200_bounds.so: the same library with -DHB200_BOUNDS (load it with HB200_LIB=<path>)."""
+    build(force=force)
+    obj_b = os.path.join(HERE, "build_bounds")
+    os.makedirs(obj_b, exist_ok=True)
+    nvcc = _nvcc()
+    headers = _headers()
+    jobs = []
+    for src in BOUNDS_SOURCES:
+        s = os.path.join(CSRC, src)
+        o = os.path.join(obj_b, src.replace(".cu", ".o"))
+        if force or _stale(o, [s] + headers):
+            jobs.append((src, [nvcc] + NVCC_FLAGS + ["-DHB200_BOUNDS", "-c", s, "-o", o]))
+
+    def run(job):
+        src, cmd = job
+        p = subprocess.run(cmd, capture_output=True, text=True)
+        return src, p.returncode, p.stdout + p.stderr
+
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as ex:
+            for src, rc, out in ex.map(run, jobs):
+                if rc:
+                    sys.stderr.write(f"--- {src} (bounds)\n{out}\n")
+                    raise RuntimeError(f"nvcc failed on {src} (bounds-checked build)")
+    objs = [os.path.join(obj_b if s in BOUNDS_SOURCES else OBJ, s.replace(".cu", ".o")) for s in SOURCES]
+    if force or jobs or _stale(BOUNDS_LIB, objs):
+        cmd = [nvcc, "-shared", "-o", BOUNDS_LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
+        p = subprocess.run(cmd, capture_output=True, text=True)
+        if p.returncode:
+            sys.stderr.write(p.stdout + p.stderr)
+            raise RuntimeError("link failed (bounds-checked build)")
+    return BOUNDS_LIB
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     """HB200_NVCC_EXTRA in the environment adds nvcc flags (a -D switch for a measurement build, -Xptxas options); a
     build with extra flags always recompiles everything."""
@@ -85,4 +126,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--bounds" in sys.argv:
+        print(build_bounds(force="--force" in sys.argv))
+    else:
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -304,8 +304,23 @@ int check_device_status() {
         set_error("a bounded wait inside a kernel expired (code %d); results of that call are invalid", h);
         return HB200_ERR_TIMEOUT;
     }
+#ifdef HB200_BOUNDS
+    // the bounds-checked build: indices outside their buffers were counted (and skipped) by the kernels
+    int (*const fetch[])(int*, int*) = {bounds_fetch_dp4a, bounds_fetch_kquant, bounds_fetch_quantize, bounds_fetch_producers};
+    const char* const unit[] = {"gemv_dp4a.cu", "kquant.cu", "quantize.cu", "producers.cu"};
+    for (int i = 0; i < 4; i++) {
+        int site = 0, count = 0;
+        const int rc = fetch[i](&site, &count);
+        if (rc) return rc;
+        if (count) {
+            set_error("bounds-checked build: %d accesses of %s fell outside their buffers and were skipped, the first at site %d", count, unit[i], site);
+            return HB200_ERR_CUDA;
+        }
+    }
+#endif
     return 0;
 }
+
 
 // The activation the host-buffer calls stage their input in: one per width, kept for the life of the context (a
 // model alternates between a handful of widths - d_model, the FFN width - so nothing is allocated or freed after the
@@ -1531,6 +1546,46 @@ extern "C" int hb200_plan_rounds(const int* op, const int* panel, const int* rou
     static_assert(sizeof(FlatSeg) == 8 * sizeof(int), "a segment is eight ints");
     if (!out.empty()) memcpy(segs, out.data(), out.size() * sizeof(FlatSeg));
     return HB200_OK;
+    HB_GUARD_END
+}
+
+extern "C" int hb200_bounds_checked(void) {
+#ifdef HB200_BOUNDS
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+extern "C" int hb200_bounds_selftest(void) {
+    HB_GUARD_BEGIN
+#ifdef HB200_BOUNDS
+    int rc = need_ctx();
+    if (rc) return rc;
+    // The quantizer on one token of 2048 columns with a block-value pitch that is too small on purpose (32 instead of
+    // 64; the buffers themselves are large enough): the 32 stores of block values beyond the pitch must be counted and
+    // skipped, and reported by the status check as site 23.
+    float* x = nullptr; int8_t* q = nullptr; float* d = nullptr; float* sums = nullptr;
+    HB_CUDA(cudaMalloc(&x, 2048 * sizeof(float)));
+    HB_CUDA(cudaMalloc(&q, 2048));
+    HB_CUDA(cudaMalloc(&d, 64 * sizeof(float)));
+    HB_CUDA(cudaMalloc(&sums, 64 * sizeof(float)));
+    HB_CUDA(cudaMemset(x, 0, 2048 * sizeof(float)));
+    rc = launch_quantize_q8_0(x, 1, 2048, q, d, sums, 2048, 32, nullptr, 0, g_ctx.stream);
+    if (!rc) { HB_CUDA(cudaStreamSynchronize(g_ctx.stream)); }
+    cudaFree(x); cudaFree(q); cudaFree(d); cudaFree(sums);
+    if (rc) return rc;
+    int site = 0, count = 0;
+    if ((rc = bounds_fetch_quantize(&site, &count))) return rc;
+    if (site != 23 || count != 32) {
+        set_error("bounds self-test: expected 32 skipped accesses at site 23, found %d at site %d", count, site);
+        return HB200_ERR_CUDA;
+    }
+    return HB200_OK;
+#else
+    set_error("not the bounds-checked build");
+    return HB200_ERR_UNSUPPORTED;
+#endif
     HB_GUARD_END
 }
 

@@ -94,6 +94,46 @@ int use_slot_of(int slot);
         }                                                                                    \
     } while (0)
 
+// ---- bounds-checked debug build (-DHB200_BOUNDS: libhearth_b200_bounds.so) ------------------------------------------
+// In that build every global-memory index the streaming kernels compute (decode matvec, K-quant matvec, quantizer
+// core and the producers built on it) is compared with the extent its buffer has by the op's own dimensions before
+// the access is made.  A violation is counted, the first one's site number kept, and the access skipped, so nothing
+// faults; hb200_check_status then returns an error naming the site.  The tensor-core kernels read global memory through
+// TMA tensor maps, which the hardware bounds-checks.  In the normal build HB_IDX is the constant true.
+#ifdef HB200_BOUNDS
+struct BoundsWord { int site, count; };
+static __device__ BoundsWord t_bounds_word;  // one per translation unit
+__device__ __forceinline__ bool hb_idx_ok(bool ok, int site) {
+    if (!ok) {
+        atomicCAS(&t_bounds_word.site, 0, site);
+        atomicAdd(&t_bounds_word.count, 1);
+    }
+    return ok;
+}
+#define HB_IDX(idx, extent, site) hb200::hb_idx_ok((unsigned long long)(idx) < (unsigned long long)(extent), (site))
+// Host side of a translation unit: fetch and clear its word.
+#define HB_BOUNDS_FETCH(fn)                                                                        \
+    int fn(int* site, int* count) {                                                                \
+        BoundsWord h = {0, 0};                                                                     \
+        HB_CUDA(cudaMemcpyFromSymbol(&h, t_bounds_word, sizeof(h)));                                \
+        if (h.count) {                                                                             \
+            const BoundsWord z = {0, 0};                                                           \
+            HB_CUDA(cudaMemcpyToSymbol(t_bounds_word, &z, sizeof(z)));                              \
+        }                                                                                          \
+        *site = h.site;                                                                            \
+        *count = h.count;                                                                          \
+        return 0;                                                                                  \
+    }
+#else
+#define HB_IDX(idx, extent, site) (true)
+#define HB_BOUNDS_FETCH(fn) \
+    int fn(int* site, int* count) { *site = 0; *count = 0; return 0; }
+#endif
+int bounds_fetch_dp4a(int* site, int* count);      // sites 1..9
+int bounds_fetch_kquant(int* site, int* count);    // sites 11..19
+int bounds_fetch_quantize(int* site, int* count);  // sites 21..24 (quantize.cu)
+int bounds_fetch_producers(int* site, int* count); // sites 21..24 (producers.cu)
+
 // ---- launchers implemented in the kernel translation units ----------------
 
 // One activation of a list quantization: f32 rows at x -> the Q8_0 planes q / d / sums.

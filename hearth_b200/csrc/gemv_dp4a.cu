@@ -165,7 +165,8 @@ __device__ __forceinline__ void round_terms(Smem<KIND, M>& sm, const uint4 (&w)[
                         else if (KIND == KIND_Q2) iv = (acc[m][g] >> (2 * g)) - (int)a_sum;  // S_code - sum(a)
                         else iv = acc[m][g];
                         const int row = panel * RP + lane * RPG + g;
-                        if (row < op->n_rows && blk * 4 + s < op->n_sub)
+                        if (row < op->n_rows && blk * 4 + s < op->n_sub &&
+                            HB_IDX(((size_t)m * op->n_rows + row) * op->n_sub + blk * 4 + s, (size_t)M * op->n_rows * op->n_sub, 6))
                             op->iout[((size_t)m * op->n_rows + row) * op->n_sub + blk * 4 + s] = iv;
                     } else {
                         const float accf = __fadd_rn(__int_as_float(acc[m][g]), -MAGIC_F);  // exact (float)sum
@@ -231,7 +232,7 @@ gemv_dp4a_kernel(const __grid_constant__ FlatLaunch A, int n_items, const __grid
     // The record of segment i into slot i & 1, asynchronously: it lands under the rounds of the segment before it (every
     // round waits for the thread's outstanding copies), so a change of segment costs no dependent global reads.
     auto fetch_rec = [&](int i) {
-        if (tid < REC_PIECES)
+        if (tid < REC_PIECES && HB_IDX(i, n_items, 8))
             cp_async16(reinterpret_cast<char*>(&srec[i & 1]) + tid * 16, reinterpret_cast<const char*>(recs + i) + tid * 16);
     };
     if (recs && it < it_end) {
@@ -271,19 +272,23 @@ gemv_dp4a_kernel(const __grid_constant__ FlatLaunch A, int n_items, const __grid
         auto stage_of = [&](const DotOp& o, int r, int buf) {
             for (int idx = tid; idx < 80 * M; idx += THREADS) {
                 const int m = idx / 80, p = idx % 80;
-                if (p < 64)
-                    cp_async16(&sm.aq[buf][m][p * 16], o.aq + (size_t)m * o.ld_q + (size_t)r * 1024 + p * 16);
-                else if (p < 72)
-                    cp_async16(&sm.ad[buf][m][(p - 64) * 4], o.ad + (size_t)m * o.ld_b + r * 32 + (p - 64) * 4);
-                else
-                    cp_async16(&sm.asum[buf][m][(p - 72) * 4], o.asum + (size_t)m * o.ld_b + r * 32 + (p - 72) * 4);
+                if (p < 64) {
+                    if (HB_IDX((size_t)r * 1024 + p * 16 + 15, o.ld_q, 3))
+                        cp_async16(&sm.aq[buf][m][p * 16], o.aq + (size_t)m * o.ld_q + (size_t)r * 1024 + p * 16);
+                } else if (p < 72) {
+                    if (HB_IDX(r * 32 + (p - 64) * 4 + 3, o.ld_b, 4))
+                        cp_async16(&sm.ad[buf][m][(p - 64) * 4], o.ad + (size_t)m * o.ld_b + r * 32 + (p - 64) * 4);
+                } else {
+                    if (HB_IDX(r * 32 + (p - 72) * 4 + 3, o.ld_b, 4))
+                        cp_async16(&sm.asum[buf][m][(p - 72) * 4], o.asum + (size_t)m * o.ld_b + r * 32 + (p - 72) * 4);
+                }
             }
         };
         auto stage = [&](int r, int buf) { stage_of(op, r, buf); };
 
         auto load_w_of = [&](const DotOp& o, int panel, int r) {
             const int blk = r * WARPS + warp;
-            if (blk < o.nb) {
+            if (blk < o.nb && HB_IDX((size_t)panel * o.nb + blk, (size_t)((o.n_rows + RP - 1) / RP) * o.nb, 1)) {
                 const size_t tile = (size_t)panel * o.nb + blk;
                 const uint4* p = o.bits + tile * 256 + lane;
 #pragma unroll
@@ -316,7 +321,8 @@ gemv_dp4a_kernel(const __grid_constant__ FlatLaunch A, int n_items, const __grid
 #pragma unroll
             for (int k = 0; k < NRUN; k++) {
                 const int idx = tid + k * THREADS;
-                if (idx < M * RP) run[k] = __ldcg(A.carry + (size_t)sg.carry_in * FLAT_CARRY_FLOATS + idx);
+                if (idx < M * RP && HB_IDX(sg.carry_in, gridDim.x + 1, 7) && HB_IDX(idx, FLAT_CARRY_FLOATS, 7))
+                    run[k] = __ldcg(A.carry + (size_t)sg.carry_in * FLAT_CARRY_FLOATS + idx);
             }
         }
 
@@ -340,7 +346,7 @@ gemv_dp4a_kernel(const __grid_constant__ FlatLaunch A, int n_items, const __grid
                     }
                     if (last) {
                         const int grow = panel * RP + row;
-                        if (grow < op.n_rows) {
+                        if (grow < op.n_rows && HB_IDX((size_t)m * op.ld_out + grow, (size_t)(M - 1) * op.ld_out + op.n_rows, 5)) {
                             float* dst = op.out + (size_t)m * op.ld_out + grow;
                             if (peers.n > 1) {
                                 // the same offset inside every rank's output area: one local and n-1 peer stores
@@ -403,7 +409,8 @@ gemv_dp4a_kernel(const __grid_constant__ FlatLaunch A, int n_items, const __grid
 #pragma unroll
                 for (int k = 0; k < NRUN; k++) {
                     const int idx = tid + k * THREADS;
-                    if (idx < M * RP) __stcg(A.carry + (size_t)sg.carry_out * FLAT_CARRY_FLOATS + idx, run[k]);
+                    if (idx < M * RP && HB_IDX(sg.carry_out, gridDim.x + 1, 7) && HB_IDX(idx, FLAT_CARRY_FLOATS, 7))
+                        __stcg(A.carry + (size_t)sg.carry_out * FLAT_CARRY_FLOATS + idx, run[k]);
                 }
                 __threadfence();
                 __syncwarp();
@@ -486,6 +493,8 @@ int gemv_dp4a_prepare() {
 }
 
 int gemv_dp4a_ctas_per_sm(int m) { return m <= 2 ? 2 : 1; }
+
+HB_BOUNDS_FETCH(bounds_fetch_dp4a)
 
 int launch_peer_publish(const PeerTable& peers, cudaStream_t st) {
     if (peers.n <= 1) return 0;

@@ -226,7 +226,8 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
             const int col = st.r * G::CH + p * 4;
             float* dst = &sm.x[buf][m][p * 4];
             if (tok0 + m < a.seq_len && col + 3 < a.n_cols && vec_ok) {
-                cp_async16(dst, a.x + (size_t)(tok0 + m) * a.n_cols + col);
+                if (HB_IDX((size_t)(tok0 + m) * a.n_cols + col + 3, (size_t)a.seq_len * a.n_cols, 13))
+                    cp_async16(dst, a.x + (size_t)(tok0 + m) * a.n_cols + col);
             } else {
 #pragma unroll
                 for (int k = 0; k < 4; k++)
@@ -248,14 +249,16 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
     auto block_of = [&](const KqStep& st) { return (KIND == KIND_Q4K) ? (st.r * 8 + warp) : (st.r * G::BLK_PER_ROUND + (uq0 >> 2)); };
     auto piece_ptr = [&](const KqStep& st) -> const uint4* {
         const int blk = block_of(st);
-        const size_t base = blk < st.nblk ? ((size_t)st.panel * st.nblk + blk) : 0;
+        size_t base = blk < st.nblk ? ((size_t)st.panel * st.nblk + blk) : 0;
+        if (!HB_IDX(base, (size_t)st.m->n_panels * st.nblk, 11)) base = 0;
         return st.m->kq + (base * G::NP + (KIND == KIND_Q4K ? 0 : 3 * (uq0 & 3))) * 32 + lane;
     };
     // Q6_K: the scale piece is number 12 of the block (the pointer stands at piece 3q), d sits in its own array.
     auto q6_scales = [&](const uint4* p) { return __ldg(p + (12 - 3 * (uq0 & 3)) * 32); };
     auto q6_d = [&](const KqStep& st) -> uint32_t {
         const int blk = block_of(st);
-        const size_t base = blk < st.nblk ? ((size_t)st.panel * st.nblk + blk) : 0;
+        size_t base = blk < st.nblk ? ((size_t)st.panel * st.nblk + blk) : 0;
+        if (!HB_IDX(base, (size_t)st.m->n_panels * st.nblk, 12)) base = 0;
         return __ldg(st.m->d16 + base * 32 + lane);
     };
     auto load_all = [&](const uint4* p, const KqStep& st) {
@@ -284,7 +287,8 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
             if (st.r == st.rounds - 1) {
                 const int grow = st.panel * 32 + row;
                 const int tok = st.tok0 + m;
-                if (grow < a.n_rows && tok < a.seq_len) a.out[(size_t)tok * a.ld_out + grow] = acc;
+                if (grow < a.n_rows && tok < a.seq_len && HB_IDX((size_t)tok * a.ld_out + grow, (size_t)(a.seq_len - 1) * a.ld_out + a.n_rows, 14))
+                    a.out[(size_t)tok * a.ld_out + grow] = acc;
                 acc = 0.0f;
             }
             run = acc;
@@ -654,7 +658,7 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq_wide_kernel(const __grid_con
                 for (int c = lane; c < 2 * ntok; c += 32) {
                     const int m = c >> 1, hh = c & 1;
                     const int cols = hh ? c1 : c0;
-                    if (cols > 0) {
+                    if (cols > 0 && HB_IDX((size_t)(tok0 + m) * a.n_cols + col0 + hh * W::HALF_COLS + cols - 1, (size_t)a.seq_len * a.n_cols, 17)) {
                         const float* src = a.x + (size_t)(tok0 + m) * a.n_cols + col0 + hh * W::HALF_COLS;
                         asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                                          kq_smem_u32(&sm.x[buf][m][hh][0])),
@@ -678,7 +682,8 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq_wide_kernel(const __grid_con
     // no next step) gives the matrix's first block: what is fetched from it is never used.
     auto block_index = [&](const KqStep& st) -> size_t {
         const int blk = st.r * W::BLK_PER_ROUND + rb;
-        return blk < st.nblk ? ((size_t)st.panel * st.nblk + blk) : 0;
+        const size_t base = blk < st.nblk ? ((size_t)st.panel * st.nblk + blk) : 0;
+        return HB_IDX(base, (size_t)st.m->n_panels * st.nblk, 16) ? base : 0;
     };
     // Q4_K: headers hd[row] and the four sub-block pieces pc[u][row].  Q6_K: the quarter's three stream pieces pc[i][row],
     // its four int8 scales sq[row] and the block's d dq[row].
@@ -735,7 +740,8 @@ __global__ void __launch_bounds__(KQ_THREADS, 1) kq_wide_kernel(const __grid_con
                 if (st.r == st.rounds - 1) {
                     const int grow = st.panel * 32 + row;
                     const int tok = st.tok0 + m;
-                    if (grow < a.n_rows && tok < a.seq_len) a.out[(size_t)tok * a.ld_out + grow] = acc;
+                    if (grow < a.n_rows && tok < a.seq_len && HB_IDX((size_t)tok * a.ld_out + grow, (size_t)(a.seq_len - 1) * a.ld_out + a.n_rows, 18))
+                        a.out[(size_t)tok * a.ld_out + grow] = acc;
                     acc = 0.0f;
                 }
                 run[c] = acc;
@@ -985,6 +991,8 @@ int kquant_prepare() {
 }
 
 size_t kquant_pieces_per_block(int kind) { return kind == KIND_Q4K ? 9 : 13; }
+
+HB_BOUNDS_FETCH(bounds_fetch_kquant)
 
 int launch_kquant_repack(int kind, const uint8_t* raw, size_t row_bytes, int n_rows, int nblk, int n_panels, uint4* kq,
                          unsigned short* d16, cudaStream_t st) {

@@ -235,4 +235,6 @@ int launch_hadamard_quantize(const float* x, const float* signs, int block_size,
     return 0;
 }
 
+HB_BOUNDS_FETCH(bounds_fetch_producers)
+
 }  // namespace hb200

@@ -127,4 +127,6 @@ int launch_store_q8_0(const int8_t* q, const float* d, int ld_q, int ld_b, int s
     return 0;
 }
 
+HB_BOUNDS_FETCH(bounds_fetch_quantize)
+
 }  // namespace hb200

@@ -88,12 +88,12 @@ __device__ __forceinline__ void quantize_vals(const float v[4], int n_cols, int 
 
     const int blk = c0 >> 5;
     const bool live = (blk * 32) < n_cols;  // block holds at least one real column
-    *reinterpret_cast<uint32_t*>(q + (size_t)m * ld_q + c0) = live ? word : 0u;
-    if ((threadIdx.x & 7) == 0) {
+    if (HB_IDX(c0 + 3, ld_q, 22)) *reinterpret_cast<uint32_t*>(q + (size_t)m * ld_q + c0) = live ? word : 0u;
+    if ((threadIdx.x & 7) == 0 && HB_IDX(blk, ld_b, 23)) {
         d[(size_t)m * ld_b + blk] = live ? __half2float(h) : 0.0f;
         sums[(size_t)m * ld_b + blk] = live ? (float)s : 0.0f;
     }
-    if (RAW_OUT && live) {
+    if (RAW_OUT && live && HB_IDX((size_t)blk * 34 + 33, raw_stride, 24)) {
         uint8_t* rb = raw + (size_t)m * raw_stride + (size_t)blk * 34;
         if ((threadIdx.x & 7) == 0) {
             const unsigned short hb = __half_as_ushort(h);

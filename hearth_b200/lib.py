@@ -9,7 +9,9 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libhearth_b200.so")
+# HB200_LIB in the environment selects another build of the same library (the bounds-checked debug build,
+# libhearth_b200_bounds.so); there is no fallback either way.
+LIB_PATH = os.environ.get("HB200_LIB") or os.path.join(HERE, "libhearth_b200.so")
 
 # GGML type ids on this path (hearth-gguf/src/ggml.rs:49-101 of the reference).
 Q8_0, Q4_K, Q6_K, Q1_0_G128_LEGACY, Q1_0, Q2_0, Q1_0_G128, PQ2_0, PTQ1_0 = 8, 12, 14, 39, 41, 42, 43, 142, 143
@@ -38,6 +40,8 @@ SIGNATURES = {
     "hb200_block_size": (_sz, [_int]),
     "hb200_block_bytes": (_sz, [_int]),
     "hb200_measure_i8_peak": (_int, [C.POINTER(C.c_double)]),
+    "hb200_bounds_checked": (_int, []),
+    "hb200_bounds_selftest": (_int, []),
     "hb200_plan_chunks": (_int, [C.POINTER(C.c_int), C.c_size_t, _int, C.POINTER(C.c_int)]),
     "hb200_plan_rounds": (_int, [C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int), C.c_size_t, _int, C.POINTER(C.c_int),
                                  C.POINTER(C.c_int), C.c_size_t, C.POINTER(C.c_size_t)]),

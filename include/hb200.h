@@ -108,6 +108,20 @@ HB200_API int hb200_sm_count(void);
  * TOP/s: the denominator for the prefill kernel's roofline fraction.  No
  * reference counterpart; takes about ten milliseconds. */
 HB200_API int hb200_measure_i8_peak(double *tops);
+/* 1 if this library is the bounds-checked debug build (compiled with
+ * -DHB200_BOUNDS as libhearth_b200_bounds.so), 0 otherwise.  In that build the
+ * streaming kernels compare every global-memory index they compute with the
+ * extent the op's own dimensions give its buffer, skip an access that falls
+ * outside and count it; hb200_check_status then returns HB200_ERR_CUDA with
+ * the number of such accesses and the site of the first.  It stands in for
+ * compute-sanitizer's memcheck where that tool is not available. */
+HB200_API int hb200_bounds_checked(void);
+/* Bounds-checked build only (HB200_ERR_UNSUPPORTED otherwise): runs the
+ * quantizer with a block-value pitch that is too small on purpose, over buffers
+ * that are large enough, and returns HB200_OK if exactly the stores beyond the
+ * pitch were counted and skipped.  Nothing faults. */
+HB200_API int hb200_bounds_selftest(void);
+
 /* The split of a work list over persistent CTAs that hb200_batch_seal uses:
  * n_items items with the given costs, in order, become `grid` contiguous
  * runs whose largest total cost is as small as contiguity allows;

@@ -32,4 +32,7 @@ def hb():
     """The CUDA library, bound to device 0.  GPU tests only."""
     from hearth_b200 import api
     api.init(0)
-    return api
+    yield api
+    # whatever the kernels recorded on the device and no test asked for: an expired bounded wait, or - in the
+    # bounds-checked build - an index outside its buffer
+    api.check_status()
