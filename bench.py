@@ -418,6 +418,43 @@ def time_producers(hb, torch, dev, stream, steps=5):
     return out
 
 
+def time_f32act(hb, torch, dev, stream, steps=5):
+    """The f32-activation matvec (the arithmetic of the reference's GPU shader, hearth-compute/src/shaders/q1_0_matmul.wgsl:38-97,
+    dispatched by GpuCompute::dequant_matmul_cached, hearth-compute/src/lib.rs:104-251) at the 8B gate shape, one token:
+    40 distinct 12288 x 4096 Q1_0 weights (283 MB, more than twice the L2), one launch each per step."""
+    peak, _ = measured_peaks()
+    n_rows, n_cols, n = 12288, 4096, 40
+    ws = [hb.Weight.upload_dev(41, n_rows, n_cols, synth.weights_torch(41, n_rows, n_cols, 900 + i, dev)) for i in range(n)]
+    x = torch.randn((1, n_cols), device=dev, dtype=torch.float32)
+    out = torch.zeros((1, n_rows), device=dev, dtype=torch.float32)
+
+    def step():
+        for w in ws:
+            hb.dequant_matmul_f32act_dev(w, x, 1, out, stream=stream)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    wbytes = n * n_rows * (n_cols // 128) * 18
+    for w in ws:
+        w.free()
+    hb.check_status()
+    gbs = wbytes / (ms * 1e-3) / 1e9
+    return {"workload": "f32act_q1_12288x4096_m1_x40", "format": "Q1_0", "tokens": 1, "metric": METRIC, "value": gbs, "unit": UNIT,
+            "ms_per_step": ms, "us_per_matrix": ms * 1e3 / n, "steps": steps, "gpu_launches_per_step": n, "weight_bytes": wbytes,
+            "kernel": "f32act_q1_0",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak},
+            "l2": "per-GPU inputs exceed the 126 MB L2",
+            "note": "f32 activations, the shader's 128-leaf reduction tree per block; one launch per matrix"}
+
+
 def shared_pinned(torch, name, n_floats, rank, world, dist):
     """One float32 host buffer shared by all ranks of the node (a file in /dev/shm mapped by every process) and
     page-locked in each of them, so that each rank's readback lands in its own part of ONE host buffer.
@@ -711,6 +748,11 @@ def run_ours(args, cfg, rank, world, local_rank):
                 secondary.append(time_secondary(hb, torch, dist, name, rank, world, dev, stream, k))
             except Exception as e:  # noqa: BLE001 - one failed extra workload must not lose the headline line
                 secondary.append({"workload": name, "error": f"{type(e).__name__}: {e}"})
+        if world == 1:
+            try:
+                secondary.append(time_f32act(hb, torch, dev, stream))
+            except Exception as e:  # noqa: BLE001
+                secondary.append({"workload": "f32act_q1_12288x4096_m1_x40", "error": f"{type(e).__name__}: {e}"})
 
     producers = None
     if world == 1 and not args.quick and not args.no_secondary and args.workload == DEFAULT_WORKLOAD:
@@ -805,7 +847,9 @@ def main():
         dev = torch.device("cuda:0")
         torch.cuda.set_device(dev)
         stream = torch.cuda.current_stream()
-        print(json.dumps({"producers": time_producers(hb, torch, dev, stream, steps=max(1, min(args.steps, 5)))}), flush=True)
+        k = max(1, min(args.steps, 5))
+        print(json.dumps({"producers": time_producers(hb, torch, dev, stream, steps=k),
+                          "f32act": time_f32act(hb, torch, dev, stream, steps=k)}), flush=True)
         return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
