@@ -785,7 +785,7 @@ def run_ours(args, cfg, rank, world, local_rank):
             "roofline": roof,
             "e2e": ({"value": (total_ops(cfg) / (e2e_ms * 1e-3) / 1e12) if is_prefill(cfg) else ab["weights"] / (e2e_ms * 1e-3) / 1e9, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                      "ms_per_step": e2e_ms, "bytes_counted": "summed over ranks",
-                     "call": "hb200_batch_run_host on every rank: the step's inputs up, list quantize, recorded batch, the rank's own outputs back; pinned host buffers; single-token steps run as eight pipelined runs (upload, compute and readback streams)"
+                     "call": "hb200_batch_run_host on every rank: the step's inputs up, list quantize, recorded batch, the rank's own outputs back; pinned host buffers; single-token steps run as six pipelined runs with short first and last ones (upload, compute and readback streams)"
                              + ("; " + e2e_note if e2e_note else "")} if e2e_ms else None),
         }
         if multi_check:

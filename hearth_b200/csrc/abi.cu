@@ -1360,22 +1360,30 @@ static int build_segments(hb200_batch* b) {
     auto entry_of = [&](size_t i) -> const BatchEntry& { return b->order[i].first ? b->kquant[b->order[i].second] : b->entries[b->order[i].second]; };
     for (size_t i = 0; i < n_ops; i++)
         if (entry_of(i).seq_len != 1) return 0;
-    const int n_seg = 8;  // measured on the 27B step: 4, 6 and 8 runs within 1.5 % of each other, 2, 12 and 16 slower by 5 %
+    // Shares of the runs, in 1/32 of the weight bytes: a short first run lets the kernels start after a thirtieth of the
+    // inputs has arrived, a short last one leaves a thirtieth of the outputs to read back after the last kernel.  Measured
+    // on the 27B step (device time 0.96 ms on that GPU): eight equal runs 1.03 ms end to end, 1-7-8-8-7-1 0.988,
+    // 1-6-9-9-6-1 0.977, 1-3-12-12-3-1 0.980, 1-10-10-10-1 1.013, 1-15-15-1 1.051; more than eight runs cost more than
+    // their shorter ends save.
+    std::vector<int> cum;
+    int den = 0;
+    for (int v : {1, 6, 9, 9, 6, 1}) { den += v; cum.push_back(den); }
     std::vector<size_t> bytes(n_ops);
     size_t total = 0;
     for (size_t i = 0; i < n_ops; i++) { bytes[i] = entry_of(i).w->resident_bytes; total += bytes[i]; }
-    std::vector<size_t> cut(n_seg + 1, n_ops);
+    const int n_runs = (int)cum.size();
+    std::vector<size_t> cut(n_runs + 1, n_ops);
     cut[0] = 0;
     size_t run = 0;
     int next = 1;
-    for (size_t i = 0; i < n_ops && next < n_seg; i++) {
+    for (size_t i = 0; i < n_ops && next < n_runs; i++) {
         run += bytes[i];
-        while (next < n_seg && run * n_seg >= total * next) cut[next++] = i + 1;
+        while (next < n_runs && run * den >= total * (size_t)cum[next - 1]) cut[next++] = i + 1;
     }
     std::vector<hb200_batch::Segment> segs;
     size_t act_seen = 0;  // activations are listed in order of first use, so each run's new ones are a contiguous range
     const float* prev_hi = nullptr;
-    for (int k = 0; k < n_seg; k++) {
+    for (int k = 0; k < n_runs; k++) {
         if (cut[k] >= cut[k + 1]) continue;
         hb200_batch::Segment sg;
         sg.ops = new hb200_batch();
