@@ -494,6 +494,13 @@ class Batch:
         assert x_host.dtype == np.float32 and x_host.size >= self.input_floats and out_host.dtype == np.float32
         check(_l.load().hb200_batch_run_host(self._h, _np_ptr(x_host), C.c_void_p(out_dev.data_ptr()), out_host.size, _np_ptr(out_host)))
 
+    def run_dev(self, x_dev, out_dev, out_host: np.ndarray, x_stream=None) -> None:
+        """The same step with its inputs already on the device (float32 tensor of input_floats values in run_host's
+        layout, written on x_stream): a device copy, the list quantizer, the recorded batch, the outputs back."""
+        assert out_host.dtype == np.float32 and x_dev.numel() >= self.input_floats
+        check(_l.load().hb200_batch_run_dev(self._h, C.c_void_p(x_dev.data_ptr()), _stream_ptr(x_stream),
+                                            C.c_void_p(out_dev.data_ptr()), out_host.size, _np_ptr(out_host)))
+
     @property
     def launch_count(self) -> int:
         return int(_l.load().hb200_batch_launch_count(self._h))

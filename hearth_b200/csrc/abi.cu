@@ -138,6 +138,7 @@ struct Context {
     hb200_act_t act = nullptr;                // the one in use, an entry of `acts`
     std::map<size_t, hb200_act_t> acts;       // by width
     int* d_status = nullptr;  // device word set by kernels whose bounded waits expire
+    cudaEvent_t ev_inputs = nullptr;  // orders a step's compute behind the stream that produced its device-resident inputs
     void* d_argmax = nullptr;  // ticket + partial results of the argmax kernel, then one result word
     uint8_t* d_terms = nullptr;  // per-block terms of the two-phase f32-activation matvec
     size_t d_terms_bytes = 0;
@@ -464,6 +465,7 @@ extern "C" int hb200_shutdown(void) {
         if (c.d_in) cudaFree(c.d_in);
         if (c.d_out) cudaFree(c.d_out);
         if (c.d_status) cudaFree(c.d_status);
+        if (c.ev_inputs) cudaEventDestroy(c.ev_inputs);
         if (c.d_argmax) cudaFree(c.d_argmax);
         if (c.d_terms) cudaFree(c.d_terms);
         if (c.stream) cudaStreamDestroy(c.stream);
@@ -1838,16 +1840,24 @@ extern "C" int hb200_multi_batch_launch(hb200_batch_t const* batches, int n, voi
 
 extern "C" size_t hb200_batch_input_floats(hb200_batch_t b) { return (b && b->sealed) ? b->input_floats : 0; }
 
-extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const float* out_dev_base, size_t out_floats,
-                                    float* out_host) {
-    HB_GUARD_BEGIN
-    HB_USE(b);
+// One recorded step: inputs from host memory (x_host) or, x_dev given, from a device buffer of the same layout that was
+// filled on x_stream; outputs read back to out_host.
+static int batch_run(hb200_batch_t b, const float* x_host, const float* x_dev, cudaStream_t x_stream, const float* out_dev_base,
+                     size_t out_floats, float* out_host) {
     int rc = need_ctx();
     if (rc) return rc;
     if (!b) { set_error("null batch"); return HB200_ERR_NULL; }
     if (!b->sealed) { set_error("batch is not sealed"); return HB200_ERR_BAD_SHAPE; }
-    if ((b->input_floats && !x_host) || (out_floats && (!out_dev_base || !out_host))) { set_error("null buffer"); return HB200_ERR_NULL; }
+    if ((b->input_floats && !x_host && !x_dev) || (out_floats && (!out_dev_base || !out_host))) { set_error("null buffer"); return HB200_ERR_NULL; }
     cudaStream_t st = g_ctx.stream;
+    if (x_dev) {
+        // the inputs are on the device already: one device copy into the staging area the quantizer reads (8 MB take a few
+        // microseconds), ordered behind the stream that produced them
+        if (!g_ctx.ev_inputs) HB_CUDA(cudaEventCreateWithFlags(&g_ctx.ev_inputs, cudaEventDisableTiming));
+        HB_CUDA(cudaEventRecord(g_ctx.ev_inputs, x_stream));
+        HB_CUDA(cudaStreamWaitEvent(st, g_ctx.ev_inputs, 0));
+        if (b->input_floats) HB_CUDA(cudaMemcpyAsync(b->x_stage, x_dev, b->input_floats * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    }
     if (!b->segments.empty() && out_floats) {
         // Pipelined: uploads on one stream, quantize + matvec on the compute stream, readbacks on a third; run k's
         // compute overlaps run k+1's upload and run k-1's readback.  Every stream is drained before returning.
@@ -1857,13 +1867,15 @@ extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const 
         if (spans_ok) {
             for (size_t k = 0; k < b->segments.size(); k++) {
                 const auto& sg = b->segments[k];
-                if (sg.act_hi > sg.act_lo) {
-                    const size_t f_lo = b->act_offset[sg.act_lo];
-                    const size_t f_hi = sg.act_hi < b->acts.size() ? b->act_offset[sg.act_hi] : b->input_floats;
-                    HB_CUDA(cudaMemcpyAsync(b->x_stage + f_lo, x_host + f_lo, (f_hi - f_lo) * sizeof(float), cudaMemcpyHostToDevice, g_ctx.copy_in));
+                if (!x_dev) {
+                    if (sg.act_hi > sg.act_lo) {
+                        const size_t f_lo = b->act_offset[sg.act_lo];
+                        const size_t f_hi = sg.act_hi < b->acts.size() ? b->act_offset[sg.act_hi] : b->input_floats;
+                        HB_CUDA(cudaMemcpyAsync(b->x_stage + f_lo, x_host + f_lo, (f_hi - f_lo) * sizeof(float), cudaMemcpyHostToDevice, g_ctx.copy_in));
+                    }
+                    HB_CUDA(cudaEventRecord(b->seg_in[k], g_ctx.copy_in));
+                    HB_CUDA(cudaStreamWaitEvent(st, b->seg_in[k], 0));
                 }
-                HB_CUDA(cudaEventRecord(b->seg_in[k], g_ctx.copy_in));
-                HB_CUDA(cudaStreamWaitEvent(st, b->seg_in[k], 0));
                 if (b->has_kquant_inputs)
                     for (size_t i = sg.act_lo; i < sg.act_hi; i++)
                         HB_CUDA(cudaMemcpyAsync(b->acts[i]->x, b->x_stage + b->act_offset[i], b->act_seq[i] * b->acts[i]->n_cols * sizeof(float),
@@ -1881,7 +1893,7 @@ extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const 
             return HB200_OK;
         }
     }
-    if (b->input_floats) HB_CUDA(cudaMemcpyAsync(b->x_stage, x_host, b->input_floats * sizeof(float), cudaMemcpyHostToDevice, st));
+    if (b->input_floats && !x_dev) HB_CUDA(cudaMemcpyAsync(b->x_stage, x_host, b->input_floats * sizeof(float), cudaMemcpyHostToDevice, st));
     if (b->has_kquant_inputs)
         for (size_t i = 0; i < b->acts.size(); i++)
             HB_CUDA(cudaMemcpyAsync(b->acts[i]->x, b->x_stage + b->act_offset[i], b->act_seq[i] * b->acts[i]->n_cols * sizeof(float),
@@ -1893,6 +1905,22 @@ extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const 
     HB_CUDA(cudaStreamSynchronize(st));
     if (!b->tensor.empty() || !b->tensor_rows.empty()) return check_device_status();
     return HB200_OK;
+}
+
+extern "C" int hb200_batch_run_host(hb200_batch_t b, const float* x_host, const float* out_dev_base, size_t out_floats,
+                                    float* out_host) {
+    HB_GUARD_BEGIN
+    HB_USE(b);
+    return batch_run(b, x_host, nullptr, nullptr, out_dev_base, out_floats, out_host);
+    HB_GUARD_END
+}
+
+extern "C" int hb200_batch_run_dev(hb200_batch_t b, const float* x_dev, void* x_stream, const float* out_dev_base, size_t out_floats,
+                                   float* out_host) {
+    HB_GUARD_BEGIN
+    HB_USE(b);
+    if (b && b->input_floats && !x_dev) { set_error("null input buffer"); return HB200_ERR_NULL; }
+    return batch_run(b, nullptr, x_dev, (cudaStream_t)x_stream, out_dev_base, out_floats, out_host);
     HB_GUARD_END
 }
 

@@ -102,6 +102,7 @@ SIGNATURES = {
     "hb200_multi_batch_launch": (_int, [C.POINTER(_vp), _int, C.POINTER(_vp)]),
     "hb200_batch_launch_count": (_int, [_vp]),
     "hb200_batch_run_host": (_int, [_vp, _vp, _vp, _sz, _vp]),
+    "hb200_batch_run_dev": (_int, [_vp, _vp, _vp, _vp, _sz, _vp]),
     "hb200_batch_input_floats": (_sz, [_vp]),
     "hb200_peer_alloc": (_int, [_sz, C.POINTER(_vp), _vp]),
     "hb200_peer_free": (_int, [_vp]),

@@ -389,6 +389,14 @@ HB200_API int hb200_batch_launch_count(hb200_batch_t b);
 HB200_API int hb200_batch_run_host(hb200_batch_t b, const float *x_host, const float *out_dev_base, size_t out_floats,
                                    float *out_host);
 HB200_API size_t hb200_batch_input_floats(hb200_batch_t b);
+/* The same step with the inputs already on the device: x_dev holds what x_host
+ * would (same layout, hb200_batch_input_floats() floats), written on x_stream
+ * (the step is ordered behind what that stream holds at the time of the call):
+ * the step of a caller whose activations are produced on the device (the
+ * reference's GPU path keeps them resident between ops,
+ * hearth-compute/src/lib.rs:104-251).  The outputs are read back as above. */
+HB200_API int hb200_batch_run_dev(hb200_batch_t b, const float *x_dev, void *x_stream, const float *out_dev_base,
+                                  size_t out_floats, float *out_host);
 
 /* ---- row-sharded multi-GPU outputs --------------------------------------- */
 

@@ -237,3 +237,48 @@ def test_decode_list_launch_with_cut_panels(hb, oracle, dtype, seq_len):
             a.free()
         for W in Ws:
             W.free()
+
+
+def test_step_from_device_inputs_equals_step_from_host_inputs(hb):
+    """hb200_batch_run_dev (inputs already on the device, written on another stream) gives the bits of
+    hb200_batch_run_host, through the pipelined runs of a single-token step (64 ops) and through the one-shot path."""
+    import torch
+    dev = torch.device("cuda:0")
+    for n_ops, seq_len in ((64, 1), (6, 3)):
+        specs = [((Q1_0, Q2_0, PQ2_0, 8)[i % 4], 256 + 32 * (i % 5), (1024, 2048, 1152)[i % 3]) for i in range(n_ops)]
+        ks = sorted({k for _, _, k in specs})
+        acts = {k: hb.Act(seq_len, k) for k in ks}
+        Ws = [hb.Weight.upload(dt, n, k, synth.weights(dt, n, k, seed=700 + i)) for i, (dt, n, k) in enumerate(specs)]
+        total = sum(n for _, n, _ in specs)
+        out_dev = torch.zeros((seq_len, total), dtype=torch.float32, device=dev)
+        batch = hb.Batch()
+        off = 0
+        for (dt, n, k), W in zip(specs, Ws):
+            batch.add(W, acts[k], seq_len, out_dev[:, off:], ld_out=total)
+            off += n
+        batch.seal()
+        try:
+            # the batch lists its activations in order of first use
+            order = []
+            for _, _, k in specs:
+                if k not in order:
+                    order.append(k)
+            x_host = np.concatenate([synth.activations(seq_len, k, seed=70 + k).reshape(-1) for k in order])
+            assert batch.input_floats == x_host.size
+            a = np.zeros((seq_len, total), dtype=np.float32)
+            b = np.full((seq_len, total), np.nan, dtype=np.float32)
+            batch.run_host(x_host, out_dev, a)
+            out_dev.fill_(float("nan"))
+            side = torch.cuda.Stream(device=dev)
+            with torch.cuda.stream(side):
+                x_dev = torch.from_numpy(x_host).to(dev, non_blocking=False)
+                x_dev = x_dev * 1.0  # produced by a kernel on the side stream
+            batch.run_dev(x_dev, out_dev, b, x_stream=side)
+            hb.check_status()
+            assert_bits_equal(b, a, f"{n_ops} ops, {seq_len} tokens")
+        finally:
+            batch.free()
+            for x in acts.values():
+                x.free()
+            for W in Ws:
+                W.free()
