@@ -700,11 +700,29 @@ def run_ours(args, cfg, rank, world, local_rank):
             e2e_note = ("every rank reads back its own row slices into its part of one shared page-locked host buffer"
                         if registered else "shared host buffer could not be page-locked; pageable copies")
 
-        # Inputs are replicated: every rank uploads all of them, pipelined under its compute.  (Uploading 1/G per rank and
-        # assembling the rest with one NCCL all-gather before hb200_batch_run_dev measured slower at four ranks, 0.49 against
-        # 0.41 ms: the upload, the collective and the compute then run one after the other.)
-        def e2e_step():
-            batch.run_host(xh, out_local, oh)
+        # Inputs are replicated on the ranks.  Up to four ranks every rank uploads all of them, pipelined under its compute.
+        # At eight ranks that upload (8.4 MB per rank, eight at a time through one host) takes twice as long as a rank's
+        # share of the compute - measured: 0.422 ms end to end at four ranks, 0.440 at eight - so there every rank uploads
+        # 1/G of the inputs and one NCCL all-gather assembles them on the devices before hb200_batch_run_dev: the host
+        # links carry every input once per step.  (At four ranks that form measured slower, 0.49 ms: upload, collective
+        # and compute run one after the other.)
+        shard_inputs = world >= 8
+        if shard_inputs:
+            nfl = batch.input_floats
+            per = -(-nfl // world)
+            xg = torch.zeros(per * world, dtype=torch.float32, device=dev)
+            lo, hi = rank * per, min((rank + 1) * per, nfl)
+
+            def e2e_step():
+                with torch.cuda.stream(stream):
+                    if hi > lo:
+                        xg[lo:hi].copy_(x_pinned[lo:hi], non_blocking=True)
+                    dist.all_gather_into_tensor(xg, xg[rank * per:(rank + 1) * per])
+                batch.run_dev(xg, out_local, oh, x_stream=stream)
+            e2e_note = (e2e_note or "") + "; every rank uploads 1/G of the inputs, one NCCL all-gather assembles them on the devices (hb200_batch_run_dev)"
+        else:
+            def e2e_step():
+                batch.run_host(xh, out_local, oh)
         e2e_steps = max(1, min(args.steps, 20 if M <= 4 else 3))
         for _ in range(2):
             e2e_step()
@@ -719,7 +737,8 @@ def run_ours(args, cfg, rank, world, local_rank):
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e2e_ms = float(tt.item()) / e2e_steps * 1e3
         # bytes summed over the ranks: every rank uploads every input (activations are replicated), each output once
-        counts = torch.tensor([float(batch.input_floats * 4), float(M * slice_rows * 4)], dtype=torch.float64, device=dev)
+        counts = torch.tensor([float(max(hi - lo, 0) * 4 if shard_inputs else batch.input_floats * 4), float(M * slice_rows * 4)],
+                              dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(counts, op=dist.ReduceOp.SUM)
         h2d, d2h = int(counts[0].item()), int(counts[1].item())
