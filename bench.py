@@ -312,16 +312,32 @@ def roofline_of(hb, cfg, ms_per_step, world):
 
 
 def time_secondary(hb, torch, dist, name, rank, world, dev, stream, steps):
-    """Device-timed steps of one more workload (weights generated, timed, freed).  N > 1: row shards + NCCL gather."""
+    """Device-timed steps of one more workload (weights generated, timed, freed).  N > 1: row shards + NCCL gather; the
+    layer set then runs as eight recorded batches of consecutive layers, and the all-gather of each batch's output
+    slices runs on a second stream under the kernels of the next one (at 32 tokens the outputs are 428 MB per step: gathered
+    in one piece behind the last kernel they cost as much as a rank's share of the compute at eight ranks)."""
     cfg = synth.CONFIGS[name]
-    wl = Workload(hb, torch, cfg, rank, world, dev)
-    out_all = torch.zeros((world * wl.M, wl.slice_rows), dtype=torch.float32, device=dev) if world > 1 else None
+    n_parts = 8 if (world > 1 and cfg["layers"] >= 8) else 1
+    parts = []
+    for k in range(n_parts):
+        c = dict(cfg)
+        c["layers"] = cfg["layers"] * (k + 1) // n_parts - cfg["layers"] * k // n_parts
+        parts.append(Workload(hb, torch, c, rank, world, dev))
+    wl = parts[0]
+    outs_all = [torch.zeros((world * p.M, p.slice_rows), dtype=torch.float32, device=dev) for p in parts] if world > 1 else None
+    comm = torch.cuda.Stream(device=dev) if world > 1 else None
+    done = [torch.cuda.Event() for _ in parts]
 
     def step():
-        wl.batch.launch(stream)
+        for k, p in enumerate(parts):
+            p.batch.launch(stream)
+            if world > 1:
+                done[k].record(stream)
+                comm.wait_event(done[k])
+                with torch.cuda.stream(comm):
+                    dist.all_gather_into_tensor(outs_all[k], p.out_local)
         if world > 1:
-            with torch.cuda.stream(stream):
-                dist.all_gather_into_tensor(out_all, wl.out_local)
+            stream.wait_stream(comm)
 
     def barrier():
         torch.cuda.synchronize()
@@ -343,8 +359,9 @@ def time_secondary(hb, torch, dist, name, rank, world, dev, stream, steps):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item()) / steps
-    launches = wl.batch.launch_count
-    wl.free()
+    launches = sum(p.batch.launch_count for p in parts)
+    for p in parts:
+        p.free()
     metric, unit, value, roof = roofline_of(hb, cfg, ms, world)
     ab = algorithmic_bytes(cfg)
     entry = {"workload": name, "format": FORMAT_NAME.get(cfg["dtype"], str(cfg["dtype"])), "tokens": cfg["seq_len"],
@@ -355,7 +372,7 @@ def time_secondary(hb, torch, dist, name, rank, world, dev, stream, steps):
     if "frac_of_nominal_8tbs" in roof:
         entry["roofline"]["frac_of_nominal_8tbs"] = roof["frac_of_nominal_8tbs"]
     if world > 1:
-        entry["gather"] = "NCCL all-gather of output slices"
+        entry["gather"] = f"NCCL all-gather of output slices, {n_parts} pieces, each under the kernels of the next piece"
     if name.startswith("c0_q1_single_x"):
         n = cfg["layers"]
         entry["note"] = (f"the single 6144 x 2048 Q1_0 matvec (1.77 MB, shorter than a launch and L2-resident when repeated) is "

@@ -79,7 +79,7 @@ struct BatchGroup {  // one launch
     int* seg_begin_dev = nullptr;  // grid + 1
     float* carry_dev = nullptr;    // running sums handed from the CTA before a cut to the CTA after it
     int* cflags_dev = nullptr;     // per carry slot: arrivals of writer warps so far (eight per launch)
-    int epoch = 0;                 // launches of this group so far
+    unsigned epoch = 0;            // launches of this group so far (wraps; the kernels compare differences)
     int grid = 0;
     int n_items = 0;  // panels
     int n_segs = 0;   // segments of the plan

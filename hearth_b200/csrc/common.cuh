@@ -199,7 +199,7 @@ struct FlatLaunch {
     const int* seg_begin;  // [grid + 1]
     float* carry;          // [slots][FLAT_CARRY_FLOATS]
     int* cflags;           // [slots]: warps that have written the slot so far (eight per launch)
-    int epoch;
+    unsigned epoch;        // launches of this work list so far, this one included
     int* status;           // device word for an expired wait (may be null)
 };
 // `list` (a planned work list, n_items = its number of segments) or, when list is null, the one op `single` whose

@@ -308,9 +308,9 @@ gemv_dp4a_kernel(const __grid_constant__ FlatLaunch A, int n_items, const __grid
         for (int k = 0; k < NRUN; k++) run[k] = 0.0f;
         if (carry_in) {  // every thread polls for itself (no CTA barrier); normally the flag has long been raised
             volatile int* f = A.cflags + sg.carry_in;
-            const int target = A.epoch * WARPS;
+            const unsigned target = A.epoch * (unsigned)WARPS;  // counts wrap around together: only their difference is looked at
             unsigned spins = 0;
-            while (*f - target < 0) {
+            while ((int)((unsigned)*f - target) < 0) {
                 if (++spins > (1u << 20)) {
                     if (A.status) atomicCAS(A.status, 0, 50);
                     break;
