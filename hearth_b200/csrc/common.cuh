@@ -76,6 +76,14 @@ struct PeerTable {
     int* status;             // device word for an expired wait
 };
 
+// A 16-byte read of weight data that a launch uses once: no line is kept in L1 for it (measured on the decode matvec:
+// 1.5 to 3 % faster than the allocating read-only load).
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
+    uint4 v;
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
 // One work item of a batched launch: panel `y` of op `x`.
 typedef int2 DotItem;
 

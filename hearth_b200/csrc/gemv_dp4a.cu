@@ -292,7 +292,7 @@ gemv_dp4a_kernel(const __grid_constant__ FlatLaunch A, int n_items, const __grid
                 const size_t tile = (size_t)panel * o.nb + blk;
                 const uint4* p = o.bits + tile * 256 + lane;
 #pragma unroll
-                for (int i = 0; i < 8; i++) wn[i] = __ldg(p + i * 32);
+                for (int i = 0; i < 8; i++) wn[i] = ldg_stream(p + i * 32);
                 if (KIND == KIND_Q1) {
                     wsn = __ldg(reinterpret_cast<const uint4*>(o.scales) + tile * 32 + lane);
                 } else {
