@@ -210,7 +210,6 @@ gemv_dp4a_kernel(const __grid_constant__ FlatLaunch A, int n_items, const __grid
     const FlatRec* __restrict__ recs = A.recs;  // null: the one op `single`, its panels split evenly over the CTAs
     __shared__ __align__(16) FlatRec srec[2];   // this segment's record and, copied in while it runs, the next one's
     using S = Smem<KIND, M>;
-    constexpr int RPG = S::RPG;
     constexpr int RP = S::RP;
     constexpr int NRUN = (M * RP + THREADS - 1) / THREADS;  // running sums per thread
     extern __shared__ __align__(16) unsigned char smem_raw[];
