@@ -114,93 +114,93 @@ __device__ __forceinline__ void round_terms(Smem<KIND, M>& sm, const uint4 (&w)[
     constexpr int RPG = S::RPG;
     constexpr int RP = S::RP;
     (void)RP; (void)blk; (void)panel;
-        float bacc[M][RPG];
+    float bacc[M][RPG];
+#pragma unroll
+    for (int m = 0; m < M; m++)
+#pragma unroll
+        for (int g = 0; g < RPG; g++) bacc[m][g] = 0.0f;
+
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+        int acc[M][RPG];
 #pragma unroll
         for (int m = 0; m < M; m++)
 #pragma unroll
-            for (int g = 0; g < RPG; g++) bacc[m][g] = 0.0f;
-
+            for (int g = 0; g < RPG; g++) acc[m][g] = INT_OUT ? 0 : MAGIC_I;
 #pragma unroll
-        for (int s = 0; s < 4; s++) {
-            int acc[M][RPG];
+        for (int h = 0; h < 2; h++) {
+            int4 a4[M];
 #pragma unroll
             for (int m = 0; m < M; m++)
+                a4[m] = *reinterpret_cast<const int4*>(&sm.aq[buf][m][warp * 128 + s * 32 + h * 16]);
 #pragma unroll
-                for (int g = 0; g < RPG; g++) acc[m][g] = INT_OUT ? 0 : MAGIC_I;
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                int4 a4[M];
-#pragma unroll
-                for (int m = 0; m < M; m++)
-                    a4[m] = *reinterpret_cast<const int4*>(&sm.aq[buf][m][warp * 128 + s * 32 + h * 16]);
-#pragma unroll
-                for (int jj = 0; jj < 4; jj++) {
-                    const int j = 4 * h + jj;                      // word of the sub-block: columns 4j..4j+3
-                    const int q = (j >> 1) * 8 + s * 2 + (j & 1);  // its position in the tile
-                    const uint32_t word = comp(w[q >> 2], q & 3);
-#pragma unroll
-                    for (int g = 0; g < RPG; g++) {
-                        uint32_t msk;
-                        if (KIND == KIND_Q1) msk = word & (0x01010101u << g);
-                        else if (KIND == KIND_Q2) msk = word & (0x03030303u << (2 * g));
-                        else msk = word;
-#pragma unroll
-                        for (int m = 0; m < M; m++) {
-                            if (KIND == KIND_Q8) acc[m][g] = dp4a_s8s8(msk, compi(a4[m], jj), acc[m][g]);
-                            else acc[m][g] = dp4a_u8s8(msk, compi(a4[m], jj), acc[m][g]);
-                        }
-                    }
-                }
-            }
-            // Widen the sub-block sums.
-#pragma unroll
-            for (int m = 0; m < M; m++) {
-                const float a_d = sm.ad[buf][m][warp * 4 + s];
-                const float a_sum = sm.asum[buf][m][warp * 4 + s];
+            for (int jj = 0; jj < 4; jj++) {
+                const int j = 4 * h + jj;                      // word of the sub-block: columns 4j..4j+3
+                const int q = (j >> 1) * 8 + s * 2 + (j & 1);  // its position in the tile
+                const uint32_t word = comp(w[q >> 2], q & 3);
 #pragma unroll
                 for (int g = 0; g < RPG; g++) {
-                    if (INT_OUT) {
-                        int iv;
-                        if (KIND == KIND_Q1) iv = ((acc[m][g] << 1) >> g) - (int)a_sum;       // 2*S1 - sum(a)
-                        else if (KIND == KIND_Q2) iv = (acc[m][g] >> (2 * g)) - (int)a_sum;  // S_code - sum(a)
-                        else iv = acc[m][g];
-                        const int row = panel * RP + lane * RPG + g;
-                        if (row < op->n_rows && blk * 4 + s < op->n_sub &&
-                            HB_IDX(((size_t)m * op->n_rows + row) * op->n_sub + blk * 4 + s, (size_t)M * op->n_rows * op->n_sub, 6))
-                            op->iout[((size_t)m * op->n_rows + row) * op->n_sub + blk * 4 + s] = iv;
-                    } else {
-                        const float accf = __fadd_rn(__int_as_float(acc[m][g]), -MAGIC_F);  // exact (float)sum
-                        if (KIND == KIND_Q8) {
-                            const float wd = __half2float(__ushort_as_half(
-                                (unsigned short)((s < 2 ? ws.x : ws.y) >> (16 * (s & 1)))));
-                            // ((float)sumi * d_w) * d_a, each product rounded (q8_0.rs:169)
-                            sm.term[buf][warp][m][s * 32 + lane] = __fmul_rn(__fmul_rn(accf, wd), a_d);
-                        } else {
-                            // exact integer I as fp32, then block_acc += I * a_scale (exact product, one rounding)
-                            const float c = (KIND == KIND_Q1) ? (2.0f / (float)(1 << g)) : (1.0f / (float)(1 << (2 * g)));
-                            const float i_f = fmaf(accf, c, -a_sum);
-                            bacc[m][g] = fmaf(i_f, a_d, bacc[m][g]);
-                        }
+                    uint32_t msk;
+                    if (KIND == KIND_Q1) msk = word & (0x01010101u << g);
+                    else if (KIND == KIND_Q2) msk = word & (0x03030303u << (2 * g));
+                    else msk = word;
+#pragma unroll
+                    for (int m = 0; m < M; m++) {
+                        if (KIND == KIND_Q8) acc[m][g] = dp4a_s8s8(msk, compi(a4[m], jj), acc[m][g]);
+                        else acc[m][g] = dp4a_u8s8(msk, compi(a4[m], jj), acc[m][g]);
                     }
                 }
             }
         }
-        if (!INT_OUT && KIND != KIND_Q8) {
-            float wd[RPG];
+        // Widen the sub-block sums.
+#pragma unroll
+        for (int m = 0; m < M; m++) {
+            const float a_d = sm.ad[buf][m][warp * 4 + s];
+            const float a_sum = sm.asum[buf][m][warp * 4 + s];
 #pragma unroll
             for (int g = 0; g < RPG; g++) {
-                const uint32_t pair = (g < 2) ? ws.x : (g < 4 ? ws.y : (g < 6 ? ws.z : ws.w));
-                wd[g] = __half2float(__ushort_as_half((unsigned short)(pair >> (16 * (g & 1)))));
-            }
-#pragma unroll
-            for (int m = 0; m < M; m++) {
-                float4* tp = reinterpret_cast<float4*>(&sm.term[buf][warp][m][lane * RPG]);
-#pragma unroll
-                for (int g4 = 0; g4 < RPG / 4; g4++)
-                    tp[g4] = make_float4(__fmul_rn(bacc[m][4 * g4], wd[4 * g4]), __fmul_rn(bacc[m][4 * g4 + 1], wd[4 * g4 + 1]),
-                                         __fmul_rn(bacc[m][4 * g4 + 2], wd[4 * g4 + 2]), __fmul_rn(bacc[m][4 * g4 + 3], wd[4 * g4 + 3]));
+                if (INT_OUT) {
+                    int iv;
+                    if (KIND == KIND_Q1) iv = ((acc[m][g] << 1) >> g) - (int)a_sum;       // 2*S1 - sum(a)
+                    else if (KIND == KIND_Q2) iv = (acc[m][g] >> (2 * g)) - (int)a_sum;  // S_code - sum(a)
+                    else iv = acc[m][g];
+                    const int row = panel * RP + lane * RPG + g;
+                    if (row < op->n_rows && blk * 4 + s < op->n_sub &&
+                        HB_IDX(((size_t)m * op->n_rows + row) * op->n_sub + blk * 4 + s, (size_t)M * op->n_rows * op->n_sub, 6))
+                        op->iout[((size_t)m * op->n_rows + row) * op->n_sub + blk * 4 + s] = iv;
+                } else {
+                    const float accf = __fadd_rn(__int_as_float(acc[m][g]), -MAGIC_F);  // exact (float)sum
+                    if (KIND == KIND_Q8) {
+                        const float wd = __half2float(__ushort_as_half(
+                            (unsigned short)((s < 2 ? ws.x : ws.y) >> (16 * (s & 1)))));
+                        // ((float)sumi * d_w) * d_a, each product rounded (q8_0.rs:169)
+                        sm.term[buf][warp][m][s * 32 + lane] = __fmul_rn(__fmul_rn(accf, wd), a_d);
+                    } else {
+                        // exact integer I as fp32, then block_acc += I * a_scale (exact product, one rounding)
+                        const float c = (KIND == KIND_Q1) ? (2.0f / (float)(1 << g)) : (1.0f / (float)(1 << (2 * g)));
+                        const float i_f = fmaf(accf, c, -a_sum);
+                        bacc[m][g] = fmaf(i_f, a_d, bacc[m][g]);
+                    }
+                }
             }
         }
+    }
+    if (!INT_OUT && KIND != KIND_Q8) {
+        float wd[RPG];
+#pragma unroll
+        for (int g = 0; g < RPG; g++) {
+            const uint32_t pair = (g < 2) ? ws.x : (g < 4 ? ws.y : (g < 6 ? ws.z : ws.w));
+            wd[g] = __half2float(__ushort_as_half((unsigned short)(pair >> (16 * (g & 1)))));
+        }
+#pragma unroll
+        for (int m = 0; m < M; m++) {
+            float4* tp = reinterpret_cast<float4*>(&sm.term[buf][warp][m][lane * RPG]);
+#pragma unroll
+            for (int g4 = 0; g4 < RPG / 4; g4++)
+                tp[g4] = make_float4(__fmul_rn(bacc[m][4 * g4], wd[4 * g4]), __fmul_rn(bacc[m][4 * g4 + 1], wd[4 * g4 + 1]),
+                                     __fmul_rn(bacc[m][4 * g4 + 2], wd[4 * g4 + 2]), __fmul_rn(bacc[m][4 * g4 + 3], wd[4 * g4 + 3]));
+        }
+    }
 }
 
 template <int KIND, int M, bool INT_OUT>
