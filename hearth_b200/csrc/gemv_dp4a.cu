@@ -16,7 +16,11 @@
 //     `* w_scale` and the running sum use __fmul_rn / __fadd_rn.
 //
 // Work decomposition (HBM-bound streaming; grid = resident CTAs x SM count).
-//   item  = one panel (32 row groups) of one op; CTAs walk the item list.
+//   item  = one panel (32 row groups) of one op.  A list launch follows a plan made on the host (FlatRec records): per
+//           CTA a run of segments, each consecutive whole panels of one op or the first / last rounds of one panel that
+//           the plan cut between two neighbouring CTAs - the earlier CTA hands the panel's running sums over in global
+//           memory and the later one continues the same ordered sum.  The next segment's record and its first round are
+//           fetched while the current segment runs.
 //   lane  = one row group of the panel; all lanes of a warp read the same
 //           128-column block, so activation reads from shared memory are broadcasts.
 //   warp  = one block per round; 8 warps cover 8 consecutive blocks (1024
@@ -32,8 +36,6 @@
 //   order: per-block terms go to shared memory; one thread per (token, row)
 //          adds them in block order, one round behind the producers.
 #include "common.cuh"
-
-#include <type_traits>
 
 namespace hb200 {
 
