@@ -26,7 +26,10 @@
 // Kernel: lane = row, so all lanes of a warp use the same columns and x comes from shared memory as
 // broadcasts; a warp takes one block (Q4_K) or a quarter block (Q6_K) per round, eight warps make 64 ordered
 // terms per row and round; next round's pieces are loaded into the registers of the pieces just used up; one thread per (token, row)
-// adds the terms in order, one round behind.  Up to four tokens share one pass over the weights.
+// adds the terms in order, one round behind.  Up to four tokens share one pass over the weights in this kernel; from
+// eight tokens on kq_wide_kernel (further down: two rows per lane, x by bulk copy, 8 or 16 tokens per expansion) runs.
+// All multiply-adds, adds and multiplies are issued two elements at a time (fma / add / mul .rn.f32x2, each half rounded
+// as the scalar instruction rounds it).
 #include "common.cuh"
 
 #include <type_traits>
@@ -36,9 +39,6 @@ namespace hb200 {
 namespace {
 
 constexpr int KQ_THREADS = 256;
-#ifndef KQ_M8_TOKEN_OUTER
-#define KQ_M8_TOKEN_OUTER 1
-#endif
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -72,17 +72,12 @@ struct KqGeom {
     static constexpr int TERMS = BLK_PER_ROUND * TERMS_PER_BLK;       // ordered terms per row and round
 };
 
-// Term buffers: two, so that the ordered replay of a round runs under the arithmetic of the next one - except for the
-// eight-token pass, whose round is long (eight tokens of arithmetic per expanded weight) and whose replay keeps all
-// 256 threads busy (one chain per (token, row)): there the replay follows its round directly and one buffer is enough,
-// which is what lets eight tokens of x and of terms fit in shared memory at all.
-template <int MT>
-constexpr int kq_term_bufs() { return MT >= 8 ? 1 : 2; }
-
+// Two term buffers, so that the ordered replay of a round runs under the arithmetic of the next one.
 template <int KIND, int MT>
 struct KqSmem {
+    static_assert(MT <= 4, "eight and more tokens per pass run kq_wide_kernel");
     alignas(16) float x[2][MT][KqGeom<KIND, MT>::CH];
-    alignas(16) float4 term[kq_term_bufs<MT>()][KqGeom<KIND, MT>::TERMS / 4][MT][32];  // four consecutive ordered terms of a row side by side
+    alignas(16) float4 term[2][KqGeom<KIND, MT>::TERMS / 4][MT][32];  // four consecutive ordered terms of a row side by side
 };
 
 // What one launch works through: `mats` (device memory) or, when mats is null, the one matrix `single`.  Items are
@@ -169,7 +164,7 @@ struct KqStep {
 // Resident CTAs per SM the register allocation of the Q6_K kernels is held to (0: none given).  The Q4_K kernels are
 // left to the allocator: told any number it schedules more aggressively and spills.
 template <int KIND, int MT>
-constexpr int kq_min_ctas() { return KIND == KIND_Q6K ? (MT == 1 ? 3 : (MT >= 8 ? 0 : 2)) : 0; }
+constexpr int kq_min_ctas() { return KIND == KIND_Q6K ? (MT == 1 ? 3 : 2) : 0; }
 
 template <int KIND, int MT>
 __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_kernel(const __grid_constant__ KqLaunch L) {
@@ -313,19 +308,15 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
             pn = piece_ptr(nxt);
             if (KIND == KIND_Q6K) dnext = q6_d(nxt);
         }
-        // Q4_K with eight tokens per pass: a round is long (every piece serves eight tokens), so each piece is refilled in
-        // place as soon as its sub-block has been expanded and the second register set goes to the token chains instead.
-        constexpr bool Q4_REFILL = (KIND == KIND_Q4K) && (MT >= 8);
-        uint4 wn[(KIND == KIND_Q4K && !Q4_REFILL) ? 9 : 1];
-        if (KIND == KIND_Q4K && !Q4_REFILL) {  // fetched up front into a second set of registers (see the note at w[])
+        uint4 wn[KIND == KIND_Q4K ? 9 : 1];
+        if (KIND == KIND_Q4K) {  // fetched up front into a second set of registers (see the note at w[])
 #pragma unroll
             for (int i = 0; i < 9; i++) wn[i] = __ldg(pn + i * 32);
         }
-        constexpr bool LATE_REPLAY = kq_term_bufs<MT>() == 2;  // replay one round behind, from the other term buffer
-        if (LATE_REPLAY && t > 0) replay(prev, (t - 1) & 1);
+        if (t > 0) replay(prev, (t - 1) & 1);  // one round behind, from the other term buffer
 
         const int buf = t & 1;
-        const int tbuf = LATE_REPLAY ? buf : 0;
+        const int tbuf = buf;
         const int nblk = cur.nblk, r = cur.r;
         if (KIND == KIND_Q4K) {
             const int blk = r * 8 + warp;
@@ -333,7 +324,6 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
                 const float d = h2f_bits(w[0].x & 0xffffu), dmin = h2f_bits(w[0].x >> 16);
                 const uint32_t sw[3] = {w[0].y, w[0].z, w[0].w};  // the 12 scale bytes
                 const uint32_t magic = L.magic;
-                if (Q4_REFILL) w[0] = __ldg(pn);
                 // FAST: nibble -> float without a shift, a mask and a convert per weight: a byte permute drops the nibble
                 // into the mantissa of 2^23 (0x4B0000nn = 8388608 + n), and fma(2^23 + n, scf, -(2^23 * scf)) is the
                 // correctly rounded n * scf, i.e. the same bits as the separate multiply (2^23 * scf is exact).  That
@@ -374,27 +364,6 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
                             }
                         };
                         const float2 zero2 = make_float2(0.0f, 0.0f);
-                        if (MT >= 8 && KQ_M8_TOKEN_OUTER) {
-                            // Eight tokens: the 32 values of the sub-block are expanded once into registers, then every token
-                            // runs its eight fused-multiply-add chains over them (one set of chains alive at a time).
-                            float2 vv[4][4];
-#pragma unroll
-                            for (int tt = 0; tt < 4; tt++) expand8(tt, vv[tt]);
-                            if (Q4_REFILL) w[1 + sb] = __ldg(pn + (1 + sb) * 32);
-#pragma unroll
-                            for (int m = 0; m < MT; m++) {
-                                float2 lanes1[4];
-#pragma unroll
-                                for (int tt = 0; tt < 4; tt++) {
-                                    const float4* xp = reinterpret_cast<const float4*>(&sm.x[buf][m][warp * 256 + sb * 32 + tt * 8]);
-                                    const float4 x0 = xp[0], x1 = xp[1];
-                                    const float2 xs[4] = {make_float2(x0.x, x0.y), make_float2(x0.z, x0.w), make_float2(x1.x, x1.y), make_float2(x1.z, x1.w)};
-#pragma unroll
-                                    for (int p = 0; p < 4; p++) lanes1[p] = __ffma2_rn(vv[tt][p], xs[p], tt == 0 ? zero2 : lanes1[p]);
-                                }
-                                reinterpret_cast<float*>(&sm.term[tbuf][warp * 2 + (sb >> 2)][m][lane])[sb & 3] = reduce8(lanes1);
-                            }
-                        } else {
                         float2 lanes[MT][4];
 #pragma unroll
                         for (int tt = 0; tt < 4; tt++) {
@@ -409,18 +378,13 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
                                 for (int p = 0; p < 4; p++) lanes[m][p] = __ffma2_rn(v[p], xs[p], tt == 0 ? zero2 : lanes[m][p]);
                             }
                         }
-                        if (Q4_REFILL) w[1 + sb] = __ldg(pn + (1 + sb) * 32);
 #pragma unroll
                         for (int m = 0; m < MT; m++)  // scalar stores into the float4 slots: no registers held across sub-blocks
                             reinterpret_cast<float*>(&sm.term[tbuf][warp * 2 + (sb >> 2)][m][lane])[sb & 3] = reduce8(lanes[m]);
-                        }
                     }
                 };
                 if (fabsf(d) <= 65504.0f) block_body(std::true_type{});
                 else block_body(std::false_type{});
-            } else if (Q4_REFILL) {
-#pragma unroll
-                for (int i = 0; i < 9; i++) w[i] = __ldg(pn + i * 32);
             }
         } else {
             const int blk = r * G::BLK_PER_ROUND + (uq0 >> 2);
@@ -492,16 +456,13 @@ __global__ void __launch_bounds__(KQ_THREADS, kq_min_ctas<KIND, MT>()) kq_gemv_k
             }
             dcur = dnext;
         }
-        if (KIND == KIND_Q4K && !Q4_REFILL) {
+        if (KIND == KIND_Q4K) {
 #pragma unroll
             for (int i = 0; i < 9; i++) w[i] = wn[i];
         }
         prev = cur;
         cur = next_step(cur, gitem);
-        if (!LATE_REPLAY) {  // the round's terms are complete after this barrier; the next round's barrier protects them again
-            __syncthreads();
-            replay(prev, 0);
-        } else if (gitem >= it1) {
+        if (gitem >= it1) {  // the last round's terms
             __syncthreads();
             replay(prev, t & 1);
         }
