@@ -116,6 +116,12 @@ __device__ __forceinline__ void round_terms(Smem<KIND, M>& sm, const uint4 (&w)[
     constexpr int RPG = S::RPG;
     constexpr int RP = S::RP;
     (void)RP; (void)blk; (void)panel;
+    // Q2_0, one token: the last row of a lane's group needs no mask.  The dot of the whole word is sum_g 4^g S_g, so
+    // that row's accumulator takes the unmasked word and the other three accumulators are subtracted from it once per
+    // sub-block: three subtractions instead of eight LOP3, on the pipe the unpack saturates.  Started at
+    // RPG * MAGIC_I (mod 2^32) it ends, like the others, at MAGIC_I + its own sum.  (The masks are shared by all
+    // tokens, the subtractions are not; for Q1_0 the chain of seven subtractions measured slower than the eight LOP3.)
+    constexpr bool TOTAL = (KIND == KIND_Q2 && M == 1);
     float bacc[M][RPG];
 #pragma unroll
     for (int m = 0; m < M; m++)
@@ -128,7 +134,8 @@ __device__ __forceinline__ void round_terms(Smem<KIND, M>& sm, const uint4 (&w)[
 #pragma unroll
         for (int m = 0; m < M; m++)
 #pragma unroll
-            for (int g = 0; g < RPG; g++) acc[m][g] = INT_OUT ? 0 : MAGIC_I;
+            for (int g = 0; g < RPG; g++)
+                acc[m][g] = INT_OUT ? 0 : ((TOTAL && g == RPG - 1) ? (int)((unsigned)MAGIC_I * (unsigned)RPG) : MAGIC_I);
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             int4 a4[M];
@@ -143,7 +150,8 @@ __device__ __forceinline__ void round_terms(Smem<KIND, M>& sm, const uint4 (&w)[
 #pragma unroll
                 for (int g = 0; g < RPG; g++) {
                     uint32_t msk;
-                    if (KIND == KIND_Q1) msk = word & (0x01010101u << g);
+                    if (TOTAL && g == RPG - 1) msk = word;
+                    else if (KIND == KIND_Q1) msk = word & (0x01010101u << g);
                     else if (KIND == KIND_Q2) msk = word & (0x03030303u << (2 * g));
                     else msk = word;
 #pragma unroll
@@ -152,6 +160,15 @@ __device__ __forceinline__ void round_terms(Smem<KIND, M>& sm, const uint4 (&w)[
                         else acc[m][g] = dp4a_u8s8(msk, compi(a4[m], jj), acc[m][g]);
                     }
                 }
+            }
+        }
+        if (TOTAL) {
+#pragma unroll
+            for (int m = 0; m < M; m++) {
+                unsigned t = (unsigned)acc[m][RPG - 1];
+#pragma unroll
+                for (int g = 0; g < RPG - 1; g++) t -= (unsigned)acc[m][g];
+                acc[m][RPG - 1] = (int)t;
             }
         }
         // Widen the sub-block sums.
