@@ -120,7 +120,8 @@ __device__ __forceinline__ void round_terms(Smem<KIND, M>& sm, const uint4 (&w)[
     // that row's accumulator takes the unmasked word and the other three accumulators are subtracted from it once per
     // sub-block: three subtractions instead of eight LOP3, on the pipe the unpack saturates.  Started at
     // RPG * MAGIC_I (mod 2^32) it ends, like the others, at MAGIC_I + its own sum.  (The masks are shared by all
-    // tokens, the subtractions are not; for Q1_0 the chain of seven subtractions measured slower than the eight LOP3.)
+    // tokens, the subtractions are not: at two and three tokens it measured 1.5 and 0.7 % slower; for Q1_0 the chain of
+    // seven subtractions measured slower than the eight LOP3.)
     constexpr bool TOTAL = (KIND == KIND_Q2 && M == 1);
     float bacc[M][RPG];
 #pragma unroll
