@@ -259,7 +259,7 @@ int check_pair(const hb200_weight* w, const hb200_act* a, size_t seq_len, size_t
 
 namespace {
 
-// Which kernel a Q8_0-activation op runs on: the streaming dp4a kernel (passes of four tokens), the few-token
+// Which kernel a Q8_0-activation op runs on: the streaming dp4a kernel (even passes of at most four tokens), the few-token
 // tensor-core kernel (rows on the MMA's M side) or the prefill tensor-core kernel (tokens on the M side).
 enum DotPath { PATH_DP4A = 0, PATH_TC_ROWS = 1, PATH_TC = 2 };
 DotPath dot_path(const hb200_weight* w, const hb200_act* a, size_t seq_len) {
@@ -267,6 +267,14 @@ DotPath dot_path(const hb200_weight* w, const hb200_act* a, size_t seq_len) {
     if (gemm_tcr_wanted(w->kind, seq_len)) return PATH_TC_ROWS;
     if (gemm_tc_wanted(w->kind, seq_len)) return PATH_TC;
     return PATH_DP4A;
+}
+
+// Tokens of the next streaming-kernel pass when `left` remain: the fewest passes of at most GEMV_MAX_M tokens, as even
+// as possible (5 = 3 + 2, 9 = 3 + 3 + 3): a pass costs a fixed part plus a part per token, and the fixed part of a
+// one-token pass is the dearest.  Every token's result is independent of how the passes are cut.
+size_t dp4a_pass_tokens(size_t left) {
+    const size_t passes = (left + GEMV_MAX_M - 1) / GEMV_MAX_M;
+    return (left + passes - 1) / passes;
 }
 
 int dot_rows_launch(const hb200_weight* w, const hb200_act* a, size_t seq_len, float* out, size_t ld_out, cudaStream_t st) {
@@ -282,13 +290,13 @@ int dot_rows_launch(const hb200_weight* w, const hb200_act* a, size_t seq_len, f
     if (path == PATH_TC)
         return launch_gemm_tc(w->kind, a->qmap_dev, w->bits, w->scales, a->d, a->ld_b, (int)w->n_rows, w->nb, (int)seq_len, out,
                               (int)ld_out, g_ctx.sm_count, g_ctx.d_status, st);
-    for (size_t tok0 = 0; tok0 < seq_len; tok0 += GEMV_MAX_M) {
-        const int m = (int)((seq_len - tok0) < (size_t)GEMV_MAX_M ? (seq_len - tok0) : GEMV_MAX_M);
+    for (size_t tok0 = 0, m = 0; tok0 < seq_len; tok0 += m) {
+        m = dp4a_pass_tokens(seq_len - tok0);
         DotOp op;
         fill_op(op, w, a, tok0, out, ld_out, nullptr);
-        int grid = g_ctx.sm_count * gemv_dp4a_ctas_per_sm(m);
+        int grid = g_ctx.sm_count * gemv_dp4a_ctas_per_sm(w->kind, (int)m);
         if (grid > w->n_panels) grid = w->n_panels;
-        const int rc = launch_gemv_dp4a(w->kind, m, false, nullptr, grid, w->n_panels, &op, st);
+        const int rc = launch_gemv_dp4a(w->kind, (int)m, false, nullptr, grid, w->n_panels, &op, st);
         if (rc) return rc;
     }
     return 0;
@@ -1304,7 +1312,7 @@ extern "C" int hb200_block_dots_i32(hb200_weight_t w, const uint8_t* a_q8, size_
     for (size_t s = 0; s < seq_len; s++) {
         DotOp op;
         fill_op(op, w, g_ctx.act, s, nullptr, w->n_rows, (int32_t*)g_ctx.d_out + s * per_tok);
-        int grid = g_ctx.sm_count * gemv_dp4a_ctas_per_sm(1);
+        int grid = g_ctx.sm_count * gemv_dp4a_ctas_per_sm(w->kind, 1);
         if (grid > w->n_panels) grid = w->n_panels;
         if ((rc = launch_gemv_dp4a(w->kind, 1, true, nullptr, grid, w->n_panels, &op, g_ctx.stream))) return rc;
     }
@@ -1633,9 +1641,9 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
         const DotPath path = b->peers.n > 1 ? PATH_DP4A : dot_path(e.w, e.a, e.seq_len);
         if (path == PATH_TC) { b->tensor.push_back(e); continue; }
         if (path == PATH_TC_ROWS) { b->tensor_rows.push_back(e); continue; }
-        for (size_t tok0 = 0; tok0 < e.seq_len; tok0 += GEMV_MAX_M) {
-            const int m = (int)((e.seq_len - tok0) < (size_t)GEMV_MAX_M ? (e.seq_len - tok0) : GEMV_MAX_M);
-            auto& slot = acc[{e.w->kind, m}];
+        for (size_t tok0 = 0, m = 0; tok0 < e.seq_len; tok0 += m) {
+            m = dp4a_pass_tokens(e.seq_len - tok0);
+            auto& slot = acc[{e.w->kind, (int)m}];
             DotOp op;
             fill_op(op, e.w, e.a, tok0, e.out, e.ld_out, nullptr);
             const int idx = (int)slot.first.size();
@@ -1653,7 +1661,7 @@ extern "C" int hb200_batch_seal(hb200_batch_t b) {
         g.n_items = (int)kv.second.second.size();
         if (g.n_items == 0) continue;
         // One wave of CTAs; each gets an equal share of the launch's rounds (see plan_flat).
-        g.grid = g_ctx.sm_count * gemv_dp4a_ctas_per_sm(g.m);
+        g.grid = g_ctx.sm_count * gemv_dp4a_ctas_per_sm(g.kind, g.m);
         {
             std::vector<int> iop(g.n_items), ipanel(g.n_items);
             long long total_rounds = 0;

@@ -189,7 +189,7 @@ constexpr int GEMV_MAX_M = 4;  // tokens one dp4a launch handles per op
 // `single` (host memory, passed by value to the grid) whose n_items panels are split evenly over `grid` CTAs.
 // `peers` (may be null) turns the output stores into stores to every rank's buffer plus the closing flag exchange.
 
-int gemv_dp4a_ctas_per_sm(int m);  // resident CTAs per SM the kernel for m tokens is built for
+int gemv_dp4a_ctas_per_sm(int kind, int m);  // resident CTAs per SM the kernel of this kind for m tokens is built for
 // List launches of the decode matvec: per CTA a run of segments (consecutive whole panels of one op, or rounds
 // [r0, r1) of ONE panel).  A panel cut between two CTAs is summed in order across them: the first part's CTA writes
 // its running sums to carry slot `carry_out`, the second part's CTA starts from slot `carry_in` (flags bit 0: starts

@@ -64,6 +64,12 @@ __device__ __forceinline__ void cp_async_commit_wait_all() {
 __device__ __forceinline__ uint32_t comp(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 __device__ __forceinline__ int compi(const int4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
+// Resident CTAs per SM the kernel of (kind, tokens) is compiled for: two wherever its registers fit in 128 without
+// spilling (Q2_0 up to four tokens, Q8_0 up to three, Q1_0 - eight rows per lane - up to two).
+__host__ __device__ constexpr int dp4a_ctas_per_sm(int kind, int m) {
+    return (m <= 2 || (kind == KIND_Q2 && m <= 4) || (kind == KIND_Q8 && m <= 3)) ? 2 : 1;
+}
+
 template <int KIND, int M>
 struct Smem {
     static constexpr int RPG = rows_per_group(KIND);
@@ -224,7 +230,7 @@ __device__ __forceinline__ void round_terms(Smem<KIND, M>& sm, const uint4 (&w)[
 }
 
 template <int KIND, int M, bool INT_OUT>
-__global__ void __launch_bounds__(THREADS, (M <= 2 ? 2 : 1))
+__global__ void __launch_bounds__(THREADS, dp4a_ctas_per_sm(KIND, M))
 gemv_dp4a_kernel(const __grid_constant__ FlatLaunch A, int n_items, const __grid_constant__ DotOp single,
                  const __grid_constant__ PeerTable peers) {
     const FlatRec* __restrict__ recs = A.recs;  // null: the one op `single`, its panels split evenly over the CTAs
@@ -511,7 +517,7 @@ int gemv_dp4a_prepare() {
     return 0;
 }
 
-int gemv_dp4a_ctas_per_sm(int m) { return m <= 2 ? 2 : 1; }
+int gemv_dp4a_ctas_per_sm(int kind, int m) { return dp4a_ctas_per_sm(kind, m); }
 
 HB_BOUNDS_FETCH(bounds_fetch_dp4a)
 

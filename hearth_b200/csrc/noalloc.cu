@@ -121,7 +121,7 @@ extern "C" int hb200_matmul_f32_noalloc(hb200_weight_t w, const float* x_dev, si
         op.ld_out = (int)ld_out;
         op.ld_q = view.ld_q;
         op.ld_b = view.ld_b;
-        int grid = sms * gemv_dp4a_ctas_per_sm((int)seq_len);
+        int grid = sms * gemv_dp4a_ctas_per_sm(w->kind, (int)seq_len);
         if (grid > w->n_panels) grid = w->n_panels;
         return launch_gemv_dp4a(w->kind, (int)seq_len, false, nullptr, grid, w->n_panels, &op, st);
     } catch (...) {

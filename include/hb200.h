@@ -161,7 +161,7 @@ HB200_API size_t hb200_byte_size(int dtype, size_t n_cols);
 
 /* hearth_quant::selected_kernel (hearth-quant/src/lib.rs:411-418): name of the
  * CUDA kernel variant that serves (dtype, seq_len); "none" if unsupported.
- * Q1_0 / Q2_0 family: "gemv_dp4a_*" (streaming, passes of four tokens) up to 10 /
+ * Q1_0 / Q2_0 family: "gemv_dp4a_*" (streaming, even passes of at most four tokens) up to 10 /
  * 11 tokens, "gemm_tcgen05_i8_rows_*" (weight rows on the MMA's M side) up to
  * 64 tokens, "gemm_tcgen05_i8_*" (tokens on the M side) above. */
 HB200_API const char *hb200_selected_kernel(int dtype, size_t seq_len);
