@@ -64,11 +64,11 @@ __device__ __forceinline__ void cp_async_commit_wait_all() {
 __device__ __forceinline__ uint32_t comp(const uint4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 __device__ __forceinline__ int compi(const int4& v, int i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
-// Resident CTAs per SM the kernel of (kind, tokens) is compiled for: two wherever its registers fit in 128 without
-// spilling (Q2_0 up to four tokens, Q8_0 up to three, Q1_0 - eight rows per lane - up to two).
-__host__ __device__ constexpr int dp4a_ctas_per_sm(int kind, int m) {
-    return (m <= 2 || (kind == KIND_Q2 && m <= 4) || (kind == KIND_Q8 && m <= 3)) ? 2 : 1;
-}
+// Resident CTAs per SM the kernel of (kind, tokens) is compiled for: two, i.e. at most 128 registers, except Q8_0 at
+// four tokens.  Q2_0 fits without spilling up to four tokens (three and four tokens: 12 % faster than one CTA per SM),
+// Q8_0 up to three; Q1_0 - eight rows per lane - spills 58 bytes at three tokens and 218 at four and is still 2.5 and
+// 5 % faster with two CTAs.
+__host__ __device__ constexpr int dp4a_ctas_per_sm(int kind, int m) { return (kind == KIND_Q8 && m > 3) ? 1 : 2; }
 
 template <int KIND, int M>
 struct Smem {
